@@ -1,0 +1,182 @@
+// Kernel selection and launch for pointwise apply (built-in operators and
+// NVRTC-compiled expressions share this path).
+#include "thb_internal.h"
+#include "../kernels/math_policy.cuh"
+#include "../kernels/apply_kernels.cuh"
+
+#include <cstring>
+
+namespace thb {
+
+// Constants of the exact division by d used by thb_fastdiv.
+static void fastdiv_constants(uint32_t d, uint32_t* magic, uint32_t* shift) {
+  uint32_t l = 0;
+  while (l < 32 && (uint64_t(1) << l) < d) ++l;  // ceil(log2 d)
+  uint64_t m = ((uint64_t(1) << 32) * ((uint64_t(1) << l) - d)) / d + 1;
+  *magic = (uint32_t)m;
+  uint32_t sh1 = l < 1 ? l : 1, sh2 = l > 0 ? l - 1 : 0;
+  *shift = sh1 | (sh2 << 8);
+}
+
+static void fill_layout(ThbLayout* L, float* data, const Collapsed& c) {
+  memset(L, 0, sizeof *L);
+  L->data = data;
+  L->dims = c.dims;
+  for (int d = 0; d < c.dims; ++d) {
+    L->size[d] = (uint32_t)c.size[d];
+    L->stride[d] = (uint32_t)c.stride[d];
+    fastdiv_constants((uint32_t)c.size[d], &L->magic[d], &L->shift[d]);
+  }
+}
+
+static int misalign_elems(const float* p) {  // elements before the next 16-byte boundary
+  return (int)(((16 - ((uintptr_t)p & 15)) & 15) >> 2);
+}
+
+int launch_apply(const ApplyKernels& k, cudaStream_t st, int nt, const thb200_tensor* t, float val1,
+                 float val2, const float* p1, const float* p2, bool dry_run, int* plan_out) {
+  if (plan_out) *plan_out = PLAN_NONE;
+  if (nt < 1 || nt > 3) return fail("apply: %d tensors (1..3 supported)", nt);
+  if (k.nt != nt) return fail("apply: operator %s takes %d tensors, got %d", k.name ? k.name : "?", k.nt, nt);
+  for (int i = 0; i < nt; ++i)
+    if (t[i].ndim > THB200_MAX_DIMS) return fail("Apply: too many dimensions in tensor %d", i + 1);
+  const int64_t n = num_elements(t[0]);
+  for (int i = 1; i < nt; ++i)
+    if (num_elements(t[i]) != n) return fail("element size mismatch between tensors 1 and %d", i + 1);
+  if (n == 0) return 0;
+  for (int i = 0; i < nt; ++i)
+    if (!t[i].data) return fail("apply: tensor %d has no device memory", i + 1);
+
+  Collapsed c[3];
+  bool all_contig = true;
+  for (int i = 0; i < nt; ++i) {
+    if (!collapse(t[i].ndim, t[i].size, t[i].stride, -1, &c[i])) return fail("apply: bad layout in tensor %d", i + 1);
+    all_contig = all_contig && c[i].contiguous();
+  }
+  ThbScalars s{val1, val2, p1, p2};
+  const int sms = sm_count();
+
+  if (all_contig) {
+    int head = misalign_elems(t[0].data);
+    bool same_phase = ((uintptr_t)t[0].data & 3) == 0;
+    for (int i = 1; i < nt; ++i) same_phase = same_phase && misalign_elems(t[i].data) == head;
+    if (same_phase) {
+      if (plan_out) *plan_out = PLAN_CONTIG;
+      if (dry_run) return 0;
+      if (head > n) head = (int)n;
+      float* a = t[0].data;
+      const float* b = nt >= 2 ? t[1].data : nullptr;
+      const float* cc = nt >= 3 ? t[2].data : nullptr;
+      int64_t nn = n;
+      int64_t nvec = (n - head) >> 2;
+      int64_t blocks = (nvec + THB_CONTIG_THREADS * THB_CONTIG_UNROLL - 1) / (THB_CONTIG_THREADS * THB_CONTIG_UNROLL);
+      int64_t cap = (int64_t)sms * 32;
+      if (blocks > cap) blocks = cap;
+      if (blocks < 1) blocks = 1;
+      void* args[] = {&a, &b, &cc, &nn, &head, &s};
+      THB_CUDA(cudaLaunchKernel(k.contig, dim3((unsigned)blocks), dim3(THB_CONTIG_THREADS), args, 0, st));
+      return 0;
+    }
+  }
+
+  for (int i = 0; i < nt; ++i)
+    if (!can_use_32bit(t[i].ndim, t[i].size, t[i].stride))
+      return fail("apply: tensor %d needs 64-bit index math on a non-contiguous layout: not implemented", i + 1);
+
+  // 2-D tile path: at least one operand is column-major-like and all agree on R x C.
+  {
+    int64_t R = 0, C = 0;
+    bool ok = true, any_col = false;
+    for (int i = 0; i < nt && ok; ++i)
+      if (c[i].dims == 2) {
+        if (R == 0) { R = c[i].size[0]; C = c[i].size[1]; }
+        else if (R != c[i].size[0] || C != c[i].size[1]) ok = false;
+      } else if (c[i].dims != 1) ok = false;
+    if (ok && R > 0 && R * C == n && k.tile2d) {
+      ThbTile2d P;
+      memset(&P, 0, sizeof P);
+      for (int i = 0; i < nt && ok; ++i) {
+        P.data[i] = t[i].data;
+        if (c[i].dims == 1) {
+          if (c[i].stride[0] != 1) ok = false;
+          P.sr[i] = C; P.sc[i] = 1;
+        } else {
+          P.sr[i] = c[i].stride[0]; P.sc[i] = c[i].stride[1];
+          if (P.sc[i] == 1) {}
+          else if (P.sr[i] == 1) { P.colmajor |= 1 << i; any_col = true; }
+          else ok = false;
+        }
+      }
+      if (ok && any_col) {
+        if (plan_out) *plan_out = PLAN_TILE2D;
+        if (dry_run) return 0;
+        P.R = (uint32_t)R; P.C = (uint32_t)C;
+        P.tilesC = (uint32_t)((C + THB_TILE - 1) / THB_TILE);
+        uint64_t ntiles = (uint64_t)((R + THB_TILE - 1) / THB_TILE) * P.tilesC;
+        P.ntiles = (uint32_t)ntiles;
+        uint64_t blocks = ntiles;
+        uint64_t cap = (uint64_t)sms * 64;
+        if (blocks > cap) blocks = cap;
+        void* args[] = {&P, &s};
+        THB_CUDA(cudaLaunchKernel(k.tile2d, dim3((unsigned)blocks), dim3(THB_TILE, THB_TILE_ROWS), args, 0, st));
+        return 0;
+      }
+    }
+  }
+
+  if (plan_out) *plan_out = PLAN_STRIDED;
+  if (dry_run) return 0;
+  ThbLayout L[3];
+  memset(L, 0, sizeof L);
+  for (int i = 0; i < nt; ++i) fill_layout(&L[i], t[i].data, c[i]);
+  uint64_t nn = (uint64_t)n;
+  uint64_t per_block = THB_STRIDED_THREADS * THB_STRIDED_UNROLL;
+  uint64_t blocks = (nn + per_block - 1) / per_block;
+  uint64_t cap = (uint64_t)sms * 32;
+  if (blocks > cap) blocks = cap;
+  void* args[] = {&L[0], &L[1], &L[2], &nn, &s};
+  THB_CUDA(cudaLaunchKernel(k.strided, dim3((unsigned)blocks), dim3(THB_STRIDED_THREADS), args, 0, st));
+  return 0;
+}
+
+}  // namespace thb
+
+extern "C" {
+
+int thb200_op_code(const char* name) {
+  if (!name) return -1;
+  for (int i = 0; i < thb::builtin_op_count(); ++i)
+    if (strcmp(thb::builtin_op(i)->name, name) == 0) return i;
+  return -1;
+}
+
+int thb200_op_arity(int op) {
+  const thb::ApplyKernels* k = thb::builtin_op(op);
+  return k ? k->nt : -1;
+}
+
+int thb200_apply_plan(int ntensors, const thb200_tensor* t) {
+  thb::ApplyKernels k;
+  k.nt = ntensors;
+  k.tile2d = (const void*)1;  // eligibility only; nothing is launched
+  int plan = 0;
+  if (thb::launch_apply(k, nullptr, ntensors, t, 0, 0, nullptr, nullptr, true, &plan)) return -1;
+  return plan;
+}
+
+int thb200_apply_op(void* stream, int op, int ntensors, const thb200_tensor* t, float val1, float val2,
+                    const float* point1, const float* point2) {
+  const thb::ApplyKernels* k = thb::builtin_op(op);
+  if (!k) return thb::fail("apply: unknown operator code %d", op);
+  return thb::launch_apply(*k, (cudaStream_t)stream, ntensors, t, val1, val2, point1, point2, false, nullptr);
+}
+
+int thb200_apply_expr(void* stream, const char* body, int ntensors, const thb200_tensor* t, float val1,
+                      float val2, const float* point1, const float* point2) {
+  if (!body) return thb::fail("apply: null expression");
+  const thb::ApplyKernels* k = nullptr;
+  if (int rc = thb::expr_kernels(ntensors, body, &k)) return rc;
+  return thb::launch_apply(*k, (cudaStream_t)stream, ntensors, t, val1, val2, point1, point2, false, nullptr);
+}
+
+}  // extern "C"

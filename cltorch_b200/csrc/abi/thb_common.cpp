@@ -1,0 +1,136 @@
+// Error reporting and the host-side index helpers of include/thb200.h.
+#include "thb_internal.h"
+
+#include <algorithm>
+#include <climits>
+#include <cstdarg>
+#include <cstdio>
+#include <mutex>
+
+namespace thb {
+
+static thread_local std::string g_last_error;
+
+int fail(const char* fmt, ...) {
+  char buf[1024];
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(buf, sizeof buf, fmt, ap);
+  va_end(ap);
+  g_last_error = buf;
+  return 1;
+}
+
+int fail_cuda(cudaError_t e, const char* what) {
+  return fail("CUDA error %d (%s) in %s", (int)e, cudaGetErrorString(e), what);
+}
+
+int64_t num_elements(const thb200_tensor& t) {
+  if (t.ndim == 0) return 0;
+  int64_t n = 1;
+  for (int i = 0; i < t.ndim; ++i) n *= t.size[i];
+  return n;
+}
+
+// Dimension collapsing, following TensorInfo<IndexType>::TensorInfo
+// (reference src/lib/THClReduceApplyUtils.h:68-170): walk from the innermost
+// dimension outwards, skip size-1 dims (the reduce dim counts as size 1), and
+// fold an outer dim into the current run when its stride continues the run.
+bool collapse(int ndim, const int64_t* size, const int64_t* stride, int reduce_dim, Collapsed* out) {
+  if (ndim < 0 || ndim > THB200_MAX_DIMS || reduce_dim >= ndim) return false;
+  int64_t rs[THB200_MAX_DIMS], rst[THB200_MAX_DIMS];  // runs, innermost first
+  int nruns = 0;
+  for (int i = ndim - 1; i >= 0; --i) {
+    int64_t sz = (i == reduce_dim) ? 1 : size[i];
+    if (sz == 1) continue;
+    if (nruns > 0 && stride[i] == rs[nruns - 1] * rst[nruns - 1]) {
+      rs[nruns - 1] *= sz;
+    } else {
+      rs[nruns] = sz;
+      rst[nruns] = stride[i];
+      ++nruns;
+    }
+  }
+  if (nruns == 0) {  // every dim has size 1: a single point
+    out->dims = 1;
+    out->size[0] = 1;
+    out->stride[0] = 1;
+    return true;
+  }
+  out->dims = nruns;
+  for (int i = 0; i < nruns; ++i) {
+    out->size[i] = rs[nruns - 1 - i];
+    out->stride[i] = rst[nruns - 1 - i];
+  }
+  return true;
+}
+
+// Largest reachable offset and the element count both below UINT_MAX
+// (reference src/lib/THClReduceApplyUtils.cpp:9-30).
+bool can_use_32bit(int ndim, const int64_t* size, const int64_t* stride) {
+  int64_t n = 1;
+  for (int i = 0; i < ndim; ++i) n *= size[i];
+  if (ndim == 0) n = 0;
+  if (n >= (int64_t)UINT_MAX) return false;
+  int64_t offset = 0;
+  for (int i = ndim - 1; i >= 0; --i) {
+    if (size[i] > 0) offset += (size[i] - 1) * stride[i];
+  }
+  return offset < (int64_t)UINT_MAX;
+}
+
+int sm_count() {
+  static std::mutex mu;
+  static int cached[64];
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 148;
+  std::lock_guard<std::mutex> lock(mu);
+  if (cached[dev] == 0) {
+    int n = 0;
+    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
+    cached[dev] = n;
+  }
+  return cached[dev];
+}
+
+}  // namespace thb
+
+extern "C" {
+
+const char* thb200_last_error(void) { return thb::g_last_error.c_str(); }
+
+int thb200_collapse_dims(int ndim, const int64_t* size, const int64_t* stride, int reduce_dim,
+                         int64_t* out_size, int64_t* out_stride) {
+  thb::Collapsed c;
+  if (!thb::collapse(ndim, size, stride, reduce_dim, &c)) {
+    thb::fail("collapse: bad arguments (ndim=%d, reduce_dim=%d)", ndim, reduce_dim);
+    return -1;
+  }
+  for (int i = 0; i < c.dims; ++i) {
+    out_size[i] = c.size[i];
+    out_stride[i] = c.stride[i];
+  }
+  return c.dims;
+}
+
+int thb200_can_use_32bit_index(int ndim, const int64_t* size, const int64_t* stride) {
+  return thb::can_use_32bit(ndim, size, stride) ? 1 : 0;
+}
+
+int thb200_overlapping_indices(int ndim, const int64_t* size, const int64_t* stride) {
+  // Dims of size > 1 sorted by ascending stride; the view overlaps itself when
+  // the smallest stride is < 1 or when a dim does not clear the extent of the
+  // next smaller one (reference src/lib/THClReduceApplyUtils.cpp:69-121).
+  std::pair<int64_t, int64_t> d[THB200_MAX_DIMS];  // (stride, size)
+  int k = 0;
+  for (int i = 0; i < ndim && i < THB200_MAX_DIMS; ++i)
+    if (size[i] > 1) d[k++] = std::make_pair(stride[i], size[i]);
+  if (k == 0) return 0;
+  std::sort(d, d + k);
+  if (d[0].first < 1) return 1;
+  for (int i = 1; i < k; ++i)
+    if (d[i].first < d[i - 1].first * d[i - 1].second) return 1;
+  return 0;
+}
+
+}  // extern "C"

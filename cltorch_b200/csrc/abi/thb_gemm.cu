@@ -1,0 +1,142 @@
+// Host side of thb200_gemm: operand split, TMA descriptors, launch.
+#include "thb_internal.h"
+#include "../kernels/gemm_kernels.cuh"
+
+#include <cudaTypedefs.h>
+#include <mutex>
+
+namespace thb {
+
+static int64_t round_up(int64_t x, int64_t m) { return (x + m - 1) / m * m; }
+
+// cuTensorMapEncodeTiled through the runtime, so that the library does not link libcuda.
+static PFN_cuTensorMapEncodeTiled_v12000 tensor_map_encoder() {
+  static PFN_cuTensorMapEncodeTiled_v12000 fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPointByVersion("cuTensorMapEncodeTiled", &p, 12000, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = (PFN_cuTensorMapEncodeTiled_v12000)p;
+  });
+  return fn;
+}
+
+// [parts = 2 * batch][rows][Kp] fp32, box 32 x box_rows x 1, 128-byte swizzle.
+static int make_operand_map(CUtensorMap* map, const float* base, int64_t rows, int64_t Kp, int64_t parts, int box_rows) {
+  auto enc = tensor_map_encoder();
+  if (!enc) return fail("gemm: cuTensorMapEncodeTiled is not available from this driver");
+  cuuint64_t dims[3] = {(cuuint64_t)Kp, (cuuint64_t)rows, (cuuint64_t)parts};
+  cuuint64_t strides[2] = {(cuuint64_t)Kp * 4, (cuuint64_t)Kp * 4 * (cuuint64_t)rows};
+  cuuint32_t box[3] = {THB_GEMM_BK, (cuuint32_t)box_rows, 1};
+  cuuint32_t estr[3] = {1, 1, 1};
+  CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, (void*)base, dims, strides, box, estr,
+                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return fail("gemm: cuTensorMapEncodeTiled failed with %d", (int)r);
+  return 0;
+}
+
+struct Workspace {
+  float* a;  // [batch][2][m][Kp]
+  float* b;  // [batch][2][n][Kp]
+  int* status;
+  size_t bytes;
+};
+
+static Workspace carve(void* ws, int64_t m, int64_t n, int64_t k, int64_t batch) {
+  const int64_t Kp = round_up(k, THB_GEMM_BK);
+  Workspace w;
+  size_t a_bytes = (size_t)round_up(batch * 2 * m * Kp * 4, 1024);
+  size_t b_bytes = (size_t)round_up(batch * 2 * n * Kp * 4, 1024);
+  w.a = (float*)ws;
+  w.b = (float*)((char*)ws + a_bytes);
+  w.status = (int*)((char*)ws + a_bytes + b_bytes);
+  w.bytes = a_bytes + b_bytes + 1024;
+  return w;
+}
+
+}  // namespace thb
+
+using namespace thb;
+
+extern "C" {
+
+size_t thb200_gemm_workspace_bytes(int64_t m, int64_t n, int64_t k, int64_t batch) {
+  if (m <= 0 || n <= 0 || k <= 0 || batch <= 0) return 1024;
+  return carve(nullptr, m, n, k, batch).bytes;
+}
+
+int thb200_gemm(void* stream, char transa, char transb, int64_t m, int64_t n, int64_t k, float alpha, const float* a,
+                int64_t lda, const float* b, int64_t ldb, float beta, float* c, int64_t ldc, int64_t batch,
+                int64_t stride_a, int64_t stride_b, int64_t stride_c, void* workspace, size_t workspace_bytes) {
+  cudaStream_t st = (cudaStream_t)stream;
+  const bool ta = (transa == 't' || transa == 'T'), tb = (transb == 't' || transb == 'T');
+  if (!ta && transa != 'n' && transa != 'N') return fail("gemm: transa must be 'n' or 't'");
+  if (!tb && transb != 'n' && transb != 'N') return fail("gemm: transb must be 'n' or 't'");
+  if (m < 0 || n < 0 || k < 0 || batch < 0) return fail("gemm: negative extent");
+  if (m == 0 || n == 0 || batch == 0) return 0;
+  if (m > INT32_MAX || n > INT32_MAX || k > INT32_MAX || batch > 65535) return fail("gemm: extent too large");
+  if (!a || !b || !c) return fail("gemm: null operand");
+  if (lda < (ta ? k : m) || ldb < (tb ? n : k) || ldc < m)
+    return fail("gemm: leading dimension too small (lda=%lld ldb=%lld ldc=%lld)", (long long)lda, (long long)ldb, (long long)ldc);
+  if (((uintptr_t)workspace & 1023) != 0) return fail("gemm: workspace must be 1024-byte aligned");
+  Workspace w = carve(workspace, m, n, k > 0 ? k : 1, batch);
+  if (!workspace || workspace_bytes < w.bytes)
+    return fail("gemm: workspace too small (%zu bytes, need %zu)", workspace_bytes, w.bytes);
+
+  const int64_t Kp = round_up(k > 0 ? k : 1, THB_GEMM_BK);
+  // op(A)(i, kk): column-major A, 'n': a[i + kk*lda] (unit stride along i), 't': a[kk + i*lda]
+  {
+    dim3 grid((unsigned)(Kp / 32), (unsigned)((m + 31) / 32), (unsigned)batch);
+    if (!ta) thb_gemm_split<true><<<grid, 256, 0, st>>>(a, 1, lda, stride_a, w.a, (int)m, (int)k, (int)Kp);
+    else thb_gemm_split<false><<<grid, 256, 0, st>>>(a, lda, 1, stride_a, w.a, (int)m, (int)k, (int)Kp);
+    THB_CUDA(cudaGetLastError());
+  }
+  // B' row j, column kk = op(B)(kk, j): 'n': b[kk + j*ldb] (unit stride along kk), 't': b[j + kk*ldb]
+  {
+    dim3 grid((unsigned)(Kp / 32), (unsigned)((n + 31) / 32), (unsigned)batch);
+    if (!tb) thb_gemm_split<false><<<grid, 256, 0, st>>>(b, ldb, 1, stride_b, w.b, (int)n, (int)k, (int)Kp);
+    else thb_gemm_split<true><<<grid, 256, 0, st>>>(b, 1, ldb, stride_b, w.b, (int)n, (int)k, (int)Kp);
+    THB_CUDA(cudaGetLastError());
+  }
+  THB_CUDA(cudaMemsetAsync(w.status, 0, sizeof(int), st));
+
+  CUtensorMap map_a, map_b;
+  if (int rc = make_operand_map(&map_a, w.a, m, Kp, 2 * batch, THB_GEMM_BM)) return rc;
+  if (int rc = make_operand_map(&map_b, w.b, n, Kp, 2 * batch, THB_GEMM_BN)) return rc;
+
+  THB_CUDA(cudaFuncSetAttribute(thb_gemm_3xtf32, cudaFuncAttributeMaxDynamicSharedMemorySize, THB_GEMM_SMEM_BYTES));
+
+  ThbGemmParams p;
+  p.c = c;
+  p.ldc = ldc;
+  p.batch_stride_c = stride_c;
+  p.m = (int)m;
+  p.n = (int)n;
+  p.kblocks = k > 0 ? (int)(Kp / THB_GEMM_BK) : 0;
+  p.alpha = alpha;
+  p.beta = beta;
+  p.tiles_m = (int)((m + THB_GEMM_BM - 1) / THB_GEMM_BM);
+  p.tiles_n = (int)((n + THB_GEMM_BN - 1) / THB_GEMM_BN);
+  p.status = w.status;
+  if (p.kblocks == 0) { p.kblocks = 1; }  // k == 0: the split wrote zeros, so C = beta * C
+  dim3 grid((unsigned)(p.tiles_m * p.tiles_n), 1, (unsigned)batch);
+  thb_gemm_3xtf32<<<grid, THB_GEMM_THREADS, THB_GEMM_SMEM_BYTES, st>>>(map_a, map_b, p);
+  THB_CUDA(cudaGetLastError());
+  return 0;
+}
+
+/* Status word of the last thb200_gemm on this workspace: 0 = completed,
+ * 1/2/3 = a bounded wait of the producer / MMA issuer / epilogue gave up.
+ * Synchronises the stream. */
+int thb200_gemm_status(void* stream, int64_t m, int64_t n, int64_t k, int64_t batch, void* workspace) {
+  Workspace w = carve(workspace, m, n, k > 0 ? k : 1, batch);
+  int h = -1;
+  THB_CUDA(cudaMemcpyAsync(&h, w.status, sizeof(int), cudaMemcpyDeviceToHost, (cudaStream_t)stream));
+  THB_CUDA(cudaStreamSynchronize((cudaStream_t)stream));
+  return h;
+}
+
+}  // extern "C"

@@ -1,0 +1,57 @@
+// Host-side declarations shared by the sources behind include/thb200.h.
+#pragma once
+#include <cuda_runtime.h>
+#include <stdint.h>
+#include <string>
+#include <vector>
+#include "thb200.h"
+
+namespace thb {
+
+// Records the message for thb200_last_error() and returns a non-zero status.
+int fail(const char* fmt, ...) __attribute__((format(printf, 1, 2)));
+int fail_cuda(cudaError_t e, const char* what);
+
+#define THB_CUDA(expr)                                         \
+  do {                                                         \
+    cudaError_t thb_e_ = (expr);                               \
+    if (thb_e_ != cudaSuccess) return ::thb::fail_cuda(thb_e_, #expr); \
+  } while (0)
+
+struct Collapsed {
+  int dims = 0;
+  int64_t size[THB200_MAX_DIMS];
+  int64_t stride[THB200_MAX_DIMS];
+  bool contiguous() const { return dims == 1 && stride[0] == 1; }
+};
+
+int64_t num_elements(const thb200_tensor& t);  // 0 for ndim == 0, as THClTensor_nElement
+bool collapse(int ndim, const int64_t* size, const int64_t* stride, int reduce_dim, Collapsed* out);
+bool can_use_32bit(int ndim, const int64_t* size, const int64_t* stride);
+int sm_count();  // of the current device, cached per device
+
+// Kernel handles of one pointwise operator: device function pointers usable
+// with cudaLaunchKernel (nvcc-compiled symbols or cudaKernel_t from NVRTC).
+struct ApplyKernels {
+  const void* contig = nullptr;
+  const void* strided = nullptr;
+  const void* tile2d = nullptr;
+  int nt = 0;
+  bool reads_out = true;
+  const char* name = nullptr;
+  const char* body = nullptr;
+};
+
+enum ApplyPlan { PLAN_NONE = 0, PLAN_CONTIG = 1, PLAN_STRIDED = 2, PLAN_TILE2D = 3 };
+
+// Chooses the kernel for these operands and launches it.
+int launch_apply(const ApplyKernels& k, cudaStream_t st, int nt, const thb200_tensor* t, float val1,
+                 float val2, const float* p1, const float* p2, bool dry_run, int* plan_out);
+
+const ApplyKernels* builtin_op(int code);
+int builtin_op_count();
+
+// NVRTC: kernels for a user expression body, compiled on first use.
+int expr_kernels(int nt, const std::string& body, const ApplyKernels** out);
+
+}  // namespace thb

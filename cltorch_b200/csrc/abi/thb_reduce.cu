@@ -1,0 +1,334 @@
+// Host side of the reductions in include/thb200.h: kernel selection, grid
+// sizing and scratch layout.
+#include "thb_internal.h"
+#include "../kernels/math_policy.cuh"
+#include "../kernels/reduce_kernels.cuh"
+
+#include <cstring>
+
+namespace thb {
+
+void fastdiv_constants_pub(uint32_t d, uint32_t* magic, uint32_t* shift) {
+  uint32_t l = 0;
+  while (l < 32 && (uint64_t(1) << l) < d) ++l;
+  uint64_t m = ((uint64_t(1) << 32) * ((uint64_t(1) << l) - d)) / d + 1;
+  *magic = (uint32_t)m;
+  uint32_t sh1 = l < 1 ? l : 1, sh2 = l > 0 ? l - 1 : 0;
+  *shift = sh1 | (sh2 << 8);
+}
+
+static void fill_layout(ThbLayout* L, float* data, const Collapsed& c) {
+  memset(L, 0, sizeof *L);
+  L->data = data;
+  L->dims = c.dims;
+  for (int d = 0; d < c.dims; ++d) {
+    L->size[d] = (uint32_t)c.size[d];
+    L->stride[d] = (uint32_t)c.stride[d];
+    fastdiv_constants_pub((uint32_t)c.size[d], &L->magic[d], &L->shift[d]);
+  }
+}
+
+static int64_t reduce_all_blocks(int64_t n) {
+  int64_t per_block = (int64_t)THB_RA_THREADS * THB_RA_UNROLL * 4;
+  int64_t blocks = (n + per_block - 1) / per_block;
+  if (blocks > THB_RA_MAX_BLOCKS) blocks = THB_RA_MAX_BLOCKS;
+  if (blocks < 1) blocks = 1;
+  return blocks;
+}
+
+// Calls f.template operator()<Mod, Red>() for the pair the reference's
+// front-ends use; false for a pair nobody asks for.
+template <class F>
+static bool dispatch_pair(int modify, int reduce, F&& f) {
+  switch (modify) {
+    case THB200_MOD_COPY:
+      switch (reduce) {
+        case THB200_RED_ADD: f.template operator()<ModCopy, RedAdd>(); return true;
+        case THB200_RED_MUL: f.template operator()<ModCopy, RedMul>(); return true;
+        case THB200_RED_MIN: f.template operator()<ModCopy, RedMin>(); return true;
+        case THB200_RED_MAX: f.template operator()<ModCopy, RedMax>(); return true;
+        case THB200_RED_AND: f.template operator()<ModCopy, RedAnd>(); return true;
+        case THB200_RED_OR: f.template operator()<ModCopy, RedOr>(); return true;
+      }
+      return false;
+    case THB200_MOD_ABSPOW:
+      if (reduce == THB200_RED_ADD) { f.template operator()<ModAbsPow, RedAdd>(); return true; }
+      return false;
+    case THB200_MOD_NEZERO:
+      if (reduce == THB200_RED_ADD) { f.template operator()<ModNeZero, RedAdd>(); return true; }
+      return false;
+    case THB200_MOD_SQDEV:
+      if (reduce == THB200_RED_ADD) { f.template operator()<ModSqDev, RedAdd>(); return true; }
+      return false;
+  }
+  return false;
+}
+
+template <class F>
+static bool dispatch_red(int reduce, F&& f) {
+  switch (reduce) {
+    case THB200_RED_ADD: f.template operator()<RedAdd>(); return true;
+    case THB200_RED_MUL: f.template operator()<RedMul>(); return true;
+    case THB200_RED_MIN: f.template operator()<RedMin>(); return true;
+    case THB200_RED_MAX: f.template operator()<RedMax>(); return true;
+    case THB200_RED_AND: f.template operator()<RedAnd>(); return true;
+    case THB200_RED_OR: f.template operator()<RedOr>(); return true;
+  }
+  return false;
+}
+
+struct ReduceAllArgs {
+  cudaStream_t st;
+  const thb200_tensor* in;
+  int64_t n;
+  float init, mparam;
+  const float* mpoint;
+  int fin;
+  float fparam;
+  float* d_out;
+  float* scratch;
+  bool contig;
+  int head;
+  Collapsed c;
+  cudaError_t err = cudaSuccess;
+
+  template <class Mod, class Red>
+  void operator()() {
+    const int blocks = (int)reduce_all_blocks(n);
+    if (contig) {
+      thb_reduce_all_pass1_contig<Mod, Red><<<blocks, THB_RA_THREADS, 0, st>>>(in->data, n, head, init, mparam,
+                                                                              mpoint, scratch);
+    } else {
+      ThbLayout L;
+      fill_layout(&L, in->data, c);
+      thb_reduce_all_pass1_strided<Mod, Red><<<blocks, THB_RA_THREADS, 0, st>>>(L, (thb_u64)n, init, mparam,
+                                                                               mpoint, scratch);
+    }
+    err = cudaGetLastError();
+    if (err != cudaSuccess) return;
+    thb_reduce_all_pass2<Red><<<1, 1024, 0, st>>>(scratch, blocks, init, fin, fparam, d_out);
+    err = cudaGetLastError();
+  }
+};
+
+// How many chunks the reduced dimension is cut into so that a reduction with few
+// slices still fills the GPU.
+static uint32_t pick_chunks(int64_t nslices, int64_t rsize) {
+  const int64_t want_threads = (int64_t)sm_count() * 1024;
+  if (nslices >= want_threads || rsize < 256) return 1;
+  int64_t chunks = (want_threads + nslices - 1) / nslices;
+  int64_t max_chunks = rsize / 64;
+  if (chunks > max_chunks) chunks = max_chunks;
+  if (chunks > 1024) chunks = 1024;
+  if (chunks < 1) chunks = 1;
+  return (uint32_t)chunks;
+}
+
+struct ReduceDimArgs {
+  cudaStream_t st;
+  ThbLayout out, in;
+  uint32_t rsize, rstride, nslices;
+  float init, mparam;
+  float* scratch;
+  uint32_t nchunks, chunk_len;
+  cudaError_t err = cudaSuccess;
+
+  template <class Mod, class Red>
+  void operator()() {
+    const int sms = sm_count();
+    if (rstride == 1) {
+      if (rsize >= 1024) {
+        unsigned blocks = nslices < (unsigned)sms * 64u ? nslices : (unsigned)sms * 64u;
+        thb_reduce_dim_contig_block<Mod, Red><<<blocks, THB_RD_THREADS, 0, st>>>(out, in, rsize, nslices, init, mparam);
+      } else {
+        uint64_t blocks = ((uint64_t)nslices + 7) / 8;
+        if (blocks > (uint64_t)sms * 64) blocks = (uint64_t)sms * 64;
+        thb_reduce_dim_contig_warp<Mod, Red><<<(unsigned)blocks, THB_RD_THREADS, 0, st>>>(out, in, rsize, nslices, init, mparam);
+      }
+      err = cudaGetLastError();
+      return;
+    }
+    uint64_t bx = ((uint64_t)nslices + THB_RD_THREADS - 1) / THB_RD_THREADS;
+    if (bx > 65535u * 16u) bx = 65535u * 16u;
+    dim3 grid((unsigned)bx, nchunks);
+    thb_reduce_dim_noncontig<Mod, Red><<<grid, THB_RD_THREADS, 0, st>>>(out, in, rsize, rstride, nslices, chunk_len,
+                                                                       nchunks, init, mparam, scratch);
+    err = cudaGetLastError();
+    if (err != cudaSuccess || nchunks == 1) return;
+    thb_reduce_dim_fold_chunks<Red><<<(unsigned)bx, THB_RD_THREADS, 0, st>>>(out, scratch, nslices, nchunks, init);
+    err = cudaGetLastError();
+  }
+};
+
+struct FoldArgs {
+  cudaStream_t st;
+  const float* partials;
+  int count;
+  float init;
+  float* d_out;
+  cudaError_t err = cudaSuccess;
+  template <class Red>
+  void operator()() {
+    thb_reduce_all_pass2<Red><<<1, 1024, 0, st>>>(partials, count, init, THB_FIN_NONE, 1.f, d_out);
+    err = cudaGetLastError();
+  }
+};
+
+static float identity_of(int reduce) {
+  switch (reduce) {
+    case THB200_RED_ADD: return 0.f;
+    case THB200_RED_MUL: return 1.f;
+    case THB200_RED_MIN: return __builtin_inff();
+    case THB200_RED_MAX: return -__builtin_inff();
+    case THB200_RED_AND: return 1.f;
+    case THB200_RED_OR: return 0.f;
+  }
+  return 0.f;
+}
+
+template <bool IS_MAX>
+static int argreduce(cudaStream_t st, float* values, float* indices, const float* src, int64_t outer, int64_t n,
+                     int64_t inner, float* scratch, size_t scratch_bytes) {
+  const int sms = sm_count();
+  if (inner == 1) {
+    if (n < 1024) {
+      int64_t blocks = (outer + 7) / 8;
+      if (blocks > (int64_t)sms * 64) blocks = (int64_t)sms * 64;
+      thb_argreduce_rows<IS_MAX, true><<<(unsigned)blocks, THB_RD_THREADS, 0, st>>>(values, indices, src, outer, (thb_u32)n);
+    } else {
+      int64_t blocks = outer < (int64_t)sms * 64 ? outer : (int64_t)sms * 64;
+      thb_argreduce_rows<IS_MAX, false><<<(unsigned)blocks, THB_RD_THREADS, 0, st>>>(values, indices, src, outer, (thb_u32)n);
+    }
+    THB_CUDA(cudaGetLastError());
+    return 0;
+  }
+  const int64_t nslices = outer * inner;
+  const uint32_t nchunks = pick_chunks(nslices, n);
+  const uint32_t chunk_len = (uint32_t)((n + nchunks - 1) / nchunks);
+  float* pval = scratch;
+  int* pidx = reinterpret_cast<int*>(scratch + (size_t)nchunks * nslices);
+  if (nchunks > 1 && (!scratch || scratch_bytes < (size_t)nchunks * nslices * 8))
+    return fail("max/min: scratch too small (%zu bytes, need %zu)", scratch_bytes, (size_t)nchunks * nslices * 8);
+  int64_t bx = (nslices + THB_RD_THREADS - 1) / THB_RD_THREADS;
+  if (bx > 65535 * 16) bx = 65535 * 16;
+  dim3 grid((unsigned)bx, nchunks);
+  thb_argreduce_cols<IS_MAX><<<grid, THB_RD_THREADS, 0, st>>>(values, indices, src, outer, (thb_u32)n, inner, chunk_len,
+                                                             nchunks, pval, pidx);
+  THB_CUDA(cudaGetLastError());
+  if (nchunks > 1) {
+    thb_argreduce_fold_chunks<IS_MAX><<<(unsigned)bx, THB_RD_THREADS, 0, st>>>(values, indices, pval, pidx, nslices, nchunks);
+    THB_CUDA(cudaGetLastError());
+  }
+  return 0;
+}
+
+}  // namespace thb
+
+using namespace thb;
+
+extern "C" {
+
+size_t thb200_reduce_all_scratch_bytes(int64_t n) { return (size_t)reduce_all_blocks(n) * sizeof(float); }
+
+int thb200_reduce_all(void* stream, int modify, int reduce, const thb200_tensor* in, float init, float mod_param,
+                      const float* mod_point, int fin, float fin_param, float* d_out, float* scratch,
+                      size_t scratch_bytes) {
+  if (!in || !d_out) return fail("reduceAll: null argument");
+  if (in->ndim > THB200_MAX_DIMS) return fail("reduceAll: too many dimensions");
+  ReduceAllArgs a;
+  a.st = (cudaStream_t)stream;
+  a.in = in;
+  a.n = num_elements(*in);
+  a.init = init; a.mparam = mod_param; a.mpoint = mod_point;
+  a.fin = fin; a.fparam = fin_param;
+  a.d_out = d_out; a.scratch = scratch;
+  if (a.n > 0 && !in->data) return fail("reduceAll: input has no device memory");
+  if (!scratch || scratch_bytes < thb200_reduce_all_scratch_bytes(a.n))
+    return fail("reduceAll: scratch too small (%zu bytes, need %zu)", scratch_bytes, thb200_reduce_all_scratch_bytes(a.n));
+  if (!collapse(in->ndim, in->size, in->stride, -1, &a.c)) return fail("reduceAll: bad layout");
+  a.contig = a.n == 0 || (a.c.contiguous() && ((uintptr_t)in->data & 3) == 0);
+  a.head = a.contig && a.n > 0 ? (int)(((16 - ((uintptr_t)in->data & 15)) & 15) >> 2) : 0;
+  if (a.head > a.n) a.head = (int)a.n;
+  if (!a.contig && !can_use_32bit(in->ndim, in->size, in->stride))
+    return fail("reduceAll: non-contiguous tensor needs 64-bit index math: not implemented");
+  if (!dispatch_pair(modify, reduce, a)) return fail("reduceAll: unsupported modify/reduce pair (%d, %d)", modify, reduce);
+  if (a.err != cudaSuccess) return fail_cuda(a.err, "reduceAll launch");
+  return 0;
+}
+
+int thb200_fold_partials(void* stream, int reduce, const float* d_partials, int count, float* d_out) {
+  if (!d_partials || !d_out || count < 1 || count > 1024) return fail("fold_partials: bad arguments");
+  FoldArgs a;
+  a.st = (cudaStream_t)stream;
+  a.partials = d_partials; a.count = count; a.init = identity_of(reduce); a.d_out = d_out;
+  if (!dispatch_red(reduce, a)) return fail("fold_partials: unknown reduce op %d", reduce);
+  if (a.err != cudaSuccess) return fail_cuda(a.err, "fold_partials launch");
+  return 0;
+}
+
+static int reduce_dim_geometry(const thb200_tensor* in, int dim, int64_t* nslices, int64_t* rsize, int64_t* rstride) {
+  if (!in || in->ndim < 1 || in->ndim > THB200_MAX_DIMS) return fail("reduceDim: bad input tensor");
+  if (dim < 0 || dim >= in->ndim) return fail("reduceDim: dimension %d out of range", dim);
+  *rsize = in->size[dim];
+  *rstride = in->stride[dim];
+  int64_t n = num_elements(*in);
+  *nslices = *rsize > 0 ? n / *rsize : 0;
+  return 0;
+}
+
+size_t thb200_reduce_dim_scratch_bytes(const thb200_tensor* in, int dim) {
+  int64_t nslices, rsize, rstride;
+  if (reduce_dim_geometry(in, dim, &nslices, &rsize, &rstride)) return 0;
+  if (rstride == 1 || nslices == 0) return 0;
+  uint32_t chunks = pick_chunks(nslices, rsize);
+  return chunks > 1 ? (size_t)chunks * nslices * sizeof(float) : 0;
+}
+
+int thb200_reduce_dim(void* stream, int modify, int reduce, const thb200_tensor* out, const thb200_tensor* in, int dim,
+                      float init, float mod_param, float* scratch, size_t scratch_bytes) {
+  int64_t nslices, rsize, rstride;
+  if (int rc = reduce_dim_geometry(in, dim, &nslices, &rsize, &rstride)) return rc;
+  if (!out) return fail("reduceDim: null output");
+  if (nslices == 0) return 0;
+  if (num_elements(*out) != nslices) return fail("reduceDim: output has %lld elements, expected %lld",
+                                                 (long long)num_elements(*out), (long long)nslices);
+  if (!in->data || !out->data) return fail("reduceDim: tensor has no device memory");
+  if (!can_use_32bit(in->ndim, in->size, in->stride) || !can_use_32bit(out->ndim, out->size, out->stride))
+    return fail("reduceDim: tensor needs 64-bit index math: not implemented");
+  Collapsed co, ci;
+  if (!collapse(out->ndim, out->size, out->stride, -1, &co) || !collapse(in->ndim, in->size, in->stride, dim, &ci))
+    return fail("reduceDim: bad layout");
+  ReduceDimArgs a;
+  a.st = (cudaStream_t)stream;
+  fill_layout(&a.out, out->data, co);
+  fill_layout(&a.in, in->data, ci);
+  a.rsize = (uint32_t)rsize; a.rstride = (uint32_t)rstride; a.nslices = (uint32_t)nslices;
+  a.init = init; a.mparam = mod_param; a.scratch = scratch;
+  a.nchunks = rstride == 1 ? 1 : pick_chunks(nslices, rsize);
+  a.chunk_len = (uint32_t)((rsize + a.nchunks - 1) / a.nchunks);
+  if (a.nchunks > 1 && (!scratch || scratch_bytes < (size_t)a.nchunks * nslices * sizeof(float)))
+    return fail("reduceDim: scratch too small (%zu bytes, need %zu)", scratch_bytes,
+                (size_t)a.nchunks * nslices * sizeof(float));
+  if (!dispatch_pair(modify, reduce, a)) return fail("reduceDim: unsupported modify/reduce pair (%d, %d)", modify, reduce);
+  if (a.err != cudaSuccess) return fail_cuda(a.err, "reduceDim launch");
+  return 0;
+}
+
+size_t thb200_reduce_dim_index_scratch_bytes(int64_t outer, int64_t n, int64_t inner) {
+  if (inner <= 1 || outer * inner == 0) return 0;
+  uint32_t chunks = pick_chunks(outer * inner, n);
+  return chunks > 1 ? (size_t)chunks * outer * inner * (sizeof(float) + sizeof(int)) : 0;
+}
+
+int thb200_reduce_dim_index(void* stream, int is_max, float* values, float* indices, const float* src, int64_t outer,
+                            int64_t n, int64_t inner, float* scratch, size_t scratch_bytes) {
+  if (outer < 0 || n < 0 || inner < 0) return fail("max/min: negative extent");
+  if (outer * inner == 0 || n == 0) return 0;
+  if (!values || !indices || !src) return fail("max/min: null pointer");
+  if (n >= (int64_t(1) << 24)) return fail("max/min: reduced dimension of %lld does not fit an fp32 index", (long long)n);
+  if (n >= (int64_t(1) << 31)) return fail("max/min: dimension too large");
+  return is_max ? argreduce<true>((cudaStream_t)stream, values, indices, src, outer, n, inner, scratch, scratch_bytes)
+                : argreduce<false>((cudaStream_t)stream, values, indices, src, outer, n, inner, scratch, scratch_bytes);
+}
+
+}  // extern "C"

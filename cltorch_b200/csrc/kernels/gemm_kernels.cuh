@@ -1,0 +1,331 @@
+// fp32 GEMM on the 5th-generation tensor cores (tcgen05, sm_100a) with fp32
+// accuracy from three TF32 products.
+//
+//   C(m x n, column-major) = alpha * A' * B'^T + beta * C
+//
+// Each fp32 operand x is split as x = hi + lo with hi = tf32(x) (round to
+// nearest, low 13 mantissa bits zero) and lo = x - hi (exact in fp32). The
+// product is accumulated in fp32 in tensor memory as
+//   lo_a*hi_b + hi_a*lo_b + hi_a*hi_b
+// per 8-deep k step; lo_a*lo_b (relative size 2^-22) is dropped.
+//
+// Two kernels:
+//  thb_gemm_split   reads op(A) (or op(B)) once and writes hi and lo as
+//                   row-major [rows][Kp] matrices ("K-major"), Kp = K rounded
+//                   up to 32 and zero-filled, so that the GEMM kernel needs a
+//                   single operand layout whatever transa/transb were.
+//  thb_gemm_3xtf32  one 128 x 256 output tile per CTA. Warp 0 lane 0 issues TMA
+//                   loads (cp.async.bulk.tensor, 128-byte swizzle, no
+//                   multicast) of the four operand tiles of a k block into a
+//                   2-stage shared-memory ring; warp 1 lane 0 issues
+//                   tcgen05.mma.kind::tf32 (M=128, N=256, K=8), three per k
+//                   step, into a 128-lane x 256-column TMEM accumulator and
+//                   commits to mbarriers; warps 2-5 read the accumulator with
+//                   tcgen05.ld and write C with coalesced stores.
+//
+// Every wait is bounded: after THB_GEMM_WAIT_LIMIT_NS a waiter records a
+// code in *status, raises the CTA's abort flag and everybody falls through to
+// the common exit, where tensor memory is released.
+#pragma once
+
+#include <cuda.h>
+#include <stdint.h>
+
+#define THB_GEMM_BM 128
+#define THB_GEMM_BN 256
+#define THB_GEMM_BK 32
+#define THB_GEMM_STAGES 2
+#define THB_GEMM_THREADS 192
+#define THB_GEMM_TILE_A_BYTES (THB_GEMM_BM * THB_GEMM_BK * 4)
+#define THB_GEMM_TILE_B_BYTES (THB_GEMM_BN * THB_GEMM_BK * 4)
+#define THB_GEMM_STAGE_BYTES (2 * THB_GEMM_TILE_A_BYTES + 2 * THB_GEMM_TILE_B_BYTES)
+#define THB_GEMM_SMEM_BYTES (THB_GEMM_STAGES * THB_GEMM_STAGE_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/)
+#define THB_GEMM_TMEM_COLS 256
+#define THB_GEMM_WAIT_LIMIT_NS 2000000000ull  // 2 s
+#define THB_GEMM_GROUP_M 16
+
+// ---- operand split ----------------------------------------------------------
+// src element (r, k) is at src[r * sr + k * sk]; TRANS selects which of the two
+// is the unit-stride direction (false: sk == 1, true: sr == 1).
+__device__ __forceinline__ float thb_round_tf32(float x) {
+  uint32_t h;
+  asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(h) : "f"(x));
+  return __uint_as_float(h);
+}
+
+template <bool TRANS>
+__global__ void __launch_bounds__(256)
+thb_gemm_split(const float* __restrict__ src, long long sr, long long sk, long long batch_stride_src,
+               float* __restrict__ dst, int rows, int K, int Kp) {
+  // dst: [batch][2][rows][Kp], part 0 = hi, part 1 = lo
+  __shared__ float tile[32][33];
+  const int b = blockIdx.z;
+  const float* s = src + (long long)b * batch_stride_src;
+  float* hi = dst + ((long long)b * 2 + 0) * rows * (long long)Kp;
+  float* lo = dst + ((long long)b * 2 + 1) * rows * (long long)Kp;
+  const int k0 = blockIdx.x * 32, r0 = blockIdx.y * 32;
+  const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;  // 32 x 8
+  if (TRANS) {
+    // unit stride along r: read (r0 + tx, k0 + ty + 8j), transpose through smem
+#pragma unroll
+    for (int j = 0; j < 32; j += 8) {
+      int r = r0 + tx, k = k0 + ty + j;
+      tile[ty + j][tx] = (r < rows && k < K) ? s[(long long)r * sr + (long long)k * sk] : 0.f;
+    }
+    __syncthreads();
+#pragma unroll
+    for (int j = 0; j < 32; j += 8) {
+      int r = r0 + ty + j, k = k0 + tx;
+      if (r < rows && k < Kp) {
+        float x = tile[tx][ty + j];
+        const float h = thb_round_tf32(x);
+        hi[(long long)r * Kp + k] = h;
+        lo[(long long)r * Kp + k] = x - h;
+      }
+    }
+  } else {
+#pragma unroll
+    for (int j = 0; j < 32; j += 8) {
+      int r = r0 + ty + j, k = k0 + tx;
+      if (r < rows && k < Kp) {
+        float x = (k < K) ? s[(long long)r * sr + (long long)k * sk] : 0.f;
+        const float h = thb_round_tf32(x);
+        hi[(long long)r * Kp + k] = h;
+        lo[(long long)r * Kp + k] = x - h;
+      }
+    }
+  }
+}
+
+// ---- PTX helpers ------------------------------------------------------------
+__device__ __forceinline__ uint32_t thb_smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void thb_mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void thb_mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool thb_mbar_try_wait(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+// Bounded wait; false when the limit ran out or another thread already gave up.
+__device__ __forceinline__ unsigned long long thb_globaltimer_ns() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+  return t;
+}
+__device__ __forceinline__ bool thb_mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+  if (thb_mbar_try_wait(bar, parity)) return true;
+  const unsigned long long t0 = thb_globaltimer_ns();
+  for (uint32_t i = 1;; ++i) {
+    if (thb_mbar_try_wait(bar, parity)) return true;
+    if ((i & 63u) == 0) {
+      if (*abort_flag) return false;
+      if (thb_globaltimer_ns() - t0 > THB_GEMM_WAIT_LIMIT_NS) return false;
+    }
+  }
+}
+__device__ __forceinline__ void thb_tma_load_3d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int x, int y, int z) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
+      ::"r"(dst), "l"(map), "r"(bar), "r"(x), "r"(y), "r"(z)
+      : "memory");
+}
+// Shared-memory matrix descriptor: K-major tile, rows of 128 bytes, 128-byte
+// swizzle, 8-row groups 1024 bytes apart.
+__device__ __forceinline__ uint64_t thb_umma_desc_sw128(uint32_t smem_addr) {
+  uint64_t d = 0;
+  d |= (uint64_t)((smem_addr & 0x3FFFFu) >> 4);  // start address, bits [0,14)
+  d |= (uint64_t)1 << 16;                        // leading byte offset (unused for swizzled K-major)
+  d |= (uint64_t)(1024 >> 4) << 32;              // stride byte offset, bits [32,46)
+  d |= (uint64_t)1 << 46;                        // descriptor version of sm_100
+  d |= (uint64_t)2 << 61;                        // layout: 128-byte swizzle
+  return d;
+}
+// Instruction descriptor of tcgen05.mma.kind::tf32: fp32 accumulate, TF32 A and
+// B, both K-major, N at bits [17,23) in units of 8, M at bits [24,29) in units of 16.
+__device__ __forceinline__ uint32_t thb_umma_idesc_tf32(int M, int N) {
+  return (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)(N >> 3) << 17) | ((uint32_t)(M >> 4) << 24);
+}
+__device__ __forceinline__ void thb_umma_tf32(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc,
+                                              uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::tf32 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+__device__ __forceinline__ void thb_umma_commit(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+
+struct ThbGemmParams {
+  float* c;
+  long long ldc, batch_stride_c;
+  int m, n, kblocks;
+  float alpha, beta;
+  int tiles_m, tiles_n;
+  int* status;  // 0 = fine; otherwise the code of the first wait that gave up
+};
+
+__global__ void __launch_bounds__(THB_GEMM_THREADS, 1)
+thb_gemm_3xtf32(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                ThbGemmParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  // tiles need 1024-byte alignment for the 128-byte swizzle
+  uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  uint64_t* bars = (uint64_t*)(smem + THB_GEMM_STAGES * THB_GEMM_STAGE_BYTES);
+  // bars[0..S): full, bars[S..2S): empty, bars[2S]: accumulator ready
+  uint32_t* tmem_slot = (uint32_t*)(bars + 2 * THB_GEMM_STAGES + 1);
+  volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
+  volatile int* never_set = abort_flag + 1;  // stays 0: for the waits of the exit path
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+  // grouped tile order: THB_GEMM_GROUP_M row tiles share their B tiles in L2
+  const int tile = blockIdx.x;
+  const int group_sz = THB_GEMM_GROUP_M * p.tiles_n;
+  const int group = tile / group_sz;
+  const int first_m = group * THB_GEMM_GROUP_M;
+  const int gm = min(THB_GEMM_GROUP_M, p.tiles_m - first_m);
+  const int tile_m = first_m + (tile % group_sz) % gm;
+  const int tile_n = (tile % group_sz) / gm;
+  const int batch = blockIdx.z;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < THB_GEMM_STAGES; ++s) {
+      thb_mbar_init(thb_smem_u32(&bars[s]), 1);
+      thb_mbar_init(thb_smem_u32(&bars[THB_GEMM_STAGES + s]), 1);
+    }
+    thb_mbar_init(thb_smem_u32(&bars[2 * THB_GEMM_STAGES]), 1);
+    abort_flag[0] = 0;
+    abort_flag[1] = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(thb_smem_u32(tmem_slot)),
+                 "r"(THB_GEMM_TMEM_COLS) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      // ---- TMA producer ----
+      int issued = 0;
+      for (int kb = 0; kb < p.kblocks; ++kb) {
+        const int s = kb % THB_GEMM_STAGES;
+        const uint32_t round = kb / THB_GEMM_STAGES;
+        if (kb >= THB_GEMM_STAGES &&
+            !thb_mbar_wait(thb_smem_u32(&bars[THB_GEMM_STAGES + s]), (round - 1) & 1, abort_flag)) {
+          if (!*abort_flag) { *abort_flag = 1; atomicCAS(p.status, 0, 1); }
+          break;
+        }
+        const uint32_t full = thb_smem_u32(&bars[s]);
+        uint8_t* st = smem + s * THB_GEMM_STAGE_BYTES;
+        thb_mbar_expect_tx(full, THB_GEMM_STAGE_BYTES);
+        const int k0 = kb * THB_GEMM_BK;
+        thb_tma_load_3d(thb_smem_u32(st), &map_a, full, k0, tile_m * THB_GEMM_BM, batch * 2 + 0);
+        thb_tma_load_3d(thb_smem_u32(st + THB_GEMM_TILE_A_BYTES), &map_a, full, k0, tile_m * THB_GEMM_BM, batch * 2 + 1);
+        thb_tma_load_3d(thb_smem_u32(st + 2 * THB_GEMM_TILE_A_BYTES), &map_b, full, k0, tile_n * THB_GEMM_BN, batch * 2 + 0);
+        thb_tma_load_3d(thb_smem_u32(st + 2 * THB_GEMM_TILE_A_BYTES + THB_GEMM_TILE_B_BYTES), &map_b, full, k0,
+                        tile_n * THB_GEMM_BN, batch * 2 + 1);
+        issued = kb + 1;
+      }
+      if (*abort_flag) {
+        // do not leave while copies into this CTA's shared memory are in flight
+        for (int kb = max(0, issued - THB_GEMM_STAGES); kb < issued; ++kb)
+          thb_mbar_wait(thb_smem_u32(&bars[kb % THB_GEMM_STAGES]), (kb / THB_GEMM_STAGES) & 1, never_set);
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      // ---- MMA issuer ----
+      const uint32_t idesc = thb_umma_idesc_tf32(THB_GEMM_BM, THB_GEMM_BN);
+      bool ok = true;
+      for (int kb = 0; kb < p.kblocks && ok; ++kb) {
+        const int s = kb % THB_GEMM_STAGES;
+        const uint32_t round = kb / THB_GEMM_STAGES;
+        if (!thb_mbar_wait(thb_smem_u32(&bars[s]), round & 1, abort_flag)) {
+          if (!*abort_flag) { *abort_flag = 1; atomicCAS(p.status, 0, 2); }
+          ok = false;
+          break;
+        }
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        const uint32_t st = thb_smem_u32(smem + s * THB_GEMM_STAGE_BYTES);
+        const uint64_t a_hi = thb_umma_desc_sw128(st);
+        const uint64_t a_lo = thb_umma_desc_sw128(st + THB_GEMM_TILE_A_BYTES);
+        const uint64_t b_hi = thb_umma_desc_sw128(st + 2 * THB_GEMM_TILE_A_BYTES);
+        const uint64_t b_lo = thb_umma_desc_sw128(st + 2 * THB_GEMM_TILE_A_BYTES + THB_GEMM_TILE_B_BYTES);
+#pragma unroll
+        for (int kk = 0; kk < THB_GEMM_BK / 8; ++kk) {
+          const uint64_t adv = (uint64_t)((kk * 32) >> 4);  // 8 tf32 = 32 bytes further along K
+          thb_umma_tf32(tmem_base, a_lo + adv, b_hi + adv, idesc, (kb | kk) != 0);
+          thb_umma_tf32(tmem_base, a_hi + adv, b_lo + adv, idesc, 1);
+          thb_umma_tf32(tmem_base, a_hi + adv, b_hi + adv, idesc, 1);
+        }
+        thb_umma_commit(thb_smem_u32(&bars[THB_GEMM_STAGES + s]));  // stage may be refilled
+      }
+      thb_umma_commit(thb_smem_u32(&bars[2 * THB_GEMM_STAGES]));  // accumulator complete
+      // after giving up: let the MMAs already issued drain before tensor memory is released
+      if (!ok) thb_mbar_wait(thb_smem_u32(&bars[2 * THB_GEMM_STAGES]), 0, never_set);
+    }
+  } else {
+    // ---- epilogue: warps 2..5 own TMEM lanes 32*(warp%4) .. +31 ----
+    const int lane_group = warp & 3;
+    bool ok = thb_mbar_wait(thb_smem_u32(&bars[2 * THB_GEMM_STAGES]), 0, abort_flag);
+    if (!ok && !*abort_flag) { *abort_flag = 1; atomicCAS(p.status, 0, 3); }
+    ok = __all_sync(0xffffffffu, ok);
+    if (ok) {
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      const int row = tile_m * THB_GEMM_BM + lane_group * 32 + lane;
+      float* cb = p.c + (long long)batch * p.batch_stride_c;
+#pragma unroll 1
+      for (int c0 = 0; c0 < THB_GEMM_BN; c0 += 32) {
+        uint32_t r[32];
+        const uint32_t taddr = tmem_base + ((uint32_t)(lane_group * 32) << 16) + (uint32_t)c0;
+        asm volatile(
+            "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+            "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+            "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+            : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+              "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+              "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+              "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+            : "r"(taddr));
+        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+        if (row < p.m) {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) {
+            const int col = tile_n * THB_GEMM_BN + c0 + j;
+            if (col < p.n) {
+              float* dst = cb + row + (long long)col * p.ldc;
+              float v = p.alpha * __uint_as_float(r[j]);
+              if (p.beta != 0.f) v += p.beta * *dst;
+              *dst = v;
+            }
+          }
+        }
+      }
+    }
+  }
+
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  if (warp == 1) {
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(THB_GEMM_TMEM_COLS) : "memory");
+  }
+}

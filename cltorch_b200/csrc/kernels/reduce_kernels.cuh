@@ -1,0 +1,415 @@
+// Reduction kernels for sm_100a: whole-tensor reductions (two passes, fixed
+// order, no atomics), reductions along one dimension, and max/min along one
+// dimension with the position of the extreme value.
+//
+// They replace the OpenCL kernels THClTensor_reduceAll / Pass1 / Pass2
+// (reference src/lib/THClReduceAll.cl:24-100), THClTensor_reduceContigDim /
+// reduceNoncontigDim (src/lib/THClReduce.cl:30-111), reduceBlock
+// (src/lib/THClReduceApplyUtils.cl:76-124) and
+// THClTensor_kernel_transformReduce{Outer,Innermost}DimIndex
+// (src/lib/THClTensorMathTransformReduce.cl:17-102).
+#pragma once
+#include "apply_kernels.cuh"
+
+// ---- modify / reduce operators ---------------------------------------------
+// modifyOp strings of the reference: CopyOp "*out = *in1"; NormFunctor
+// "pow(fabs(*in1), p)"; PartialNotEqualFunctor "*in1 != 0"
+// (src/lib/THClTensorMath2.cpp:336-356); the squared deviation is the
+// square_functor of the commented varall (src/lib/THClTensorMath2.cpp:197-207).
+struct ModCopy { static __device__ __forceinline__ float apply(float x, float, float) { return x; } };
+struct ModAbsPow { static __device__ __forceinline__ float apply(float x, float p, float) { return thb_pow(fabsf(x), p); } };
+struct ModNeZero { static __device__ __forceinline__ float apply(float x, float, float) { return x != 0.0f; } };
+struct ModSqDev { static __device__ __forceinline__ float apply(float x, float, float m) { return (x - m) * (x - m); } };
+// reduceOp strings: TensorAddOp, TensorMulOp, MinOp (fmin), MaxOp (fmax)
+// (src/lib/THClTensorMathPointwise.h:62-140), logicalall/any functors
+// "(int)*in1 && (int)*in2" (src/lib/THClTensorMath.cpp:444-460).
+struct RedAdd { static __device__ __forceinline__ float apply(float a, float b) { return a + b; } };
+struct RedMul { static __device__ __forceinline__ float apply(float a, float b) { return a * b; } };
+struct RedMin { static __device__ __forceinline__ float apply(float a, float b) { return fminf(a, b); } };
+struct RedMax { static __device__ __forceinline__ float apply(float a, float b) { return fmaxf(a, b); } };
+struct RedAnd { static __device__ __forceinline__ float apply(float a, float b) { return (float)((int)a && (int)b); } };
+struct RedOr { static __device__ __forceinline__ float apply(float a, float b) { return (float)((int)a || (int)b); } };
+
+#define THB_FULL_MASK 0xffffffffu
+
+// Folds the values of the calling block's threads in a fixed order; the result
+// is valid in thread 0. `smem` holds one float per warp.
+template <class Red>
+__device__ __forceinline__ float thb_block_fold(float v, float init, float* smem) {
+#pragma unroll
+  for (int off = 16; off > 0; off >>= 1) v = Red::apply(v, __shfl_down_sync(THB_FULL_MASK, v, off));
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int nwarps = (blockDim.x + 31) >> 5;
+  if (lane == 0) smem[warp] = v;
+  __syncthreads();
+  if (warp == 0) {
+    v = lane < nwarps ? smem[lane] : init;
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) v = Red::apply(v, __shfl_down_sync(THB_FULL_MASK, v, off));
+  }
+  return v;
+}
+
+// ---- reduceAll --------------------------------------------------------------
+#define THB_RA_THREADS 256
+#define THB_RA_UNROLL 4
+#define THB_RA_MAX_BLOCKS 1184  // fixed, so that the summation order does not depend on the device
+
+// Pass 1 over one contiguous run. `head` as in thb_apply_contig.
+template <class Mod, class Red>
+__global__ void __launch_bounds__(THB_RA_THREADS)
+thb_reduce_all_pass1_contig(const float* in, thb_i64 n, int head, float init, float mparam,
+                            const float* mpoint, float* partials) {
+  __shared__ float smem[32];
+  const float mp = mpoint ? *mpoint : 0.f;
+  const thb_i64 nvec = (n - head) >> 2;
+  const float4* in4 = reinterpret_cast<const float4*>(in + head);
+  float acc[4] = {init, init, init, init};
+
+  const thb_i64 step = (thb_i64)gridDim.x * (THB_RA_THREADS * THB_RA_UNROLL);
+  for (thb_i64 base = (thb_i64)blockIdx.x * (THB_RA_THREADS * THB_RA_UNROLL) + threadIdx.x; base < nvec;
+       base += step) {
+    float4 v[THB_RA_UNROLL];
+#pragma unroll
+    for (int u = 0; u < THB_RA_UNROLL; ++u) {
+      thb_i64 i = base + u * THB_RA_THREADS;
+      if (i < nvec) v[u] = in4[i];
+    }
+#pragma unroll
+    for (int u = 0; u < THB_RA_UNROLL; ++u) {
+      thb_i64 i = base + u * THB_RA_THREADS;
+      if (i < nvec) {
+        acc[0] = Red::apply(acc[0], Mod::apply(v[u].x, mparam, mp));
+        acc[1] = Red::apply(acc[1], Mod::apply(v[u].y, mparam, mp));
+        acc[2] = Red::apply(acc[2], Mod::apply(v[u].z, mparam, mp));
+        acc[3] = Red::apply(acc[3], Mod::apply(v[u].w, mparam, mp));
+      }
+    }
+  }
+  if (blockIdx.x == 0) {
+    const thb_i64 tail0 = head + (nvec << 2);
+    const int ntail = (int)(n - tail0);
+    const int t = threadIdx.x;
+    if (t < head) acc[0] = Red::apply(acc[0], Mod::apply(in[t], mparam, mp));
+    else if (t - head < ntail) acc[0] = Red::apply(acc[0], Mod::apply(in[tail0 + (t - head)], mparam, mp));
+  }
+  float r = Red::apply(Red::apply(acc[0], acc[1]), Red::apply(acc[2], acc[3]));
+  r = thb_block_fold<Red>(r, init, smem);
+  if (threadIdx.x == 0) partials[blockIdx.x] = r;
+}
+
+// Pass 1 over any strided layout (32-bit index math).
+template <class Mod, class Red>
+__global__ void __launch_bounds__(THB_RA_THREADS)
+thb_reduce_all_pass1_strided(ThbLayout L, thb_u64 n, float init, float mparam, const float* mpoint,
+                             float* partials) {
+  __shared__ float smem[32];
+  const float mp = mpoint ? *mpoint : 0.f;
+  float acc = init;
+  const thb_u64 step = (thb_u64)gridDim.x * (THB_RA_THREADS * THB_RA_UNROLL);
+  for (thb_u64 base = (thb_u64)blockIdx.x * (THB_RA_THREADS * THB_RA_UNROLL) + threadIdx.x; base < n;
+       base += step) {
+    float v[THB_RA_UNROLL];
+#pragma unroll
+    for (int u = 0; u < THB_RA_UNROLL; ++u) {
+      thb_u64 i = base + (thb_u64)u * THB_RA_THREADS;
+      if (i < n) v[u] = L.data[thb_offset(L, (thb_u32)i)];
+    }
+#pragma unroll
+    for (int u = 0; u < THB_RA_UNROLL; ++u) {
+      thb_u64 i = base + (thb_u64)u * THB_RA_THREADS;
+      if (i < n) acc = Red::apply(acc, Mod::apply(v[u], mparam, mp));
+    }
+  }
+  acc = thb_block_fold<Red>(acc, init, smem);
+  if (threadIdx.x == 0) partials[blockIdx.x] = acc;
+}
+
+#define THB_FIN_NONE 0
+#define THB_FIN_DIV 1
+#define THB_FIN_DIV_SQRT 2
+
+// Pass 2: one block folds the pass-1 partials and writes the finished scalar.
+template <class Red>
+__global__ void __launch_bounds__(1024)
+thb_reduce_all_pass2(const float* partials, int count, float init, int fin, float fparam, float* out) {
+  __shared__ float smem[32];
+  float r = init;
+  for (int i = threadIdx.x; i < count; i += blockDim.x) r = Red::apply(r, partials[i]);
+  r = thb_block_fold<Red>(r, init, smem);
+  if (threadIdx.x == 0) {
+    if (fin == THB_FIN_DIV) r = r / fparam;
+    else if (fin == THB_FIN_DIV_SQRT) r = sqrtf(r / fparam);
+    out[0] = r;
+  }
+}
+
+// ---- reduce along one dimension --------------------------------------------
+// Slice s of the input starts at in.data[thb_offset(in, s)] (the layout has the
+// reduced dimension forced to size 1) and has `rsize` elements `rstride` apart;
+// its result goes to out.data[thb_offset(out, s)].
+
+// rstride == 1, one block per slice (long slices).
+#define THB_RD_THREADS 256
+template <class Mod, class Red>
+__global__ void __launch_bounds__(THB_RD_THREADS)
+thb_reduce_dim_contig_block(ThbLayout out, ThbLayout in, thb_u32 rsize, thb_u32 nslices, float init,
+                            float mparam) {
+  __shared__ float smem[32];
+  for (thb_u32 s = blockIdx.x; s < nslices; s += gridDim.x) {
+    const float* p = in.data + thb_offset(in, s);
+    float acc[4] = {init, init, init, init};
+    if ((((thb_u64)p) & 15) == 0 && (rsize & 3) == 0) {
+      const float4* p4 = reinterpret_cast<const float4*>(p);
+      const thb_u32 nvec = rsize >> 2;
+      for (thb_u32 i = threadIdx.x; i < nvec; i += THB_RD_THREADS * 4) {
+        float4 v[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u)
+          if (i + u * THB_RD_THREADS < nvec) v[u] = p4[i + u * THB_RD_THREADS];
+#pragma unroll
+        for (int u = 0; u < 4; ++u)
+          if (i + u * THB_RD_THREADS < nvec) {
+            acc[0] = Red::apply(acc[0], Mod::apply(v[u].x, mparam, 0.f));
+            acc[1] = Red::apply(acc[1], Mod::apply(v[u].y, mparam, 0.f));
+            acc[2] = Red::apply(acc[2], Mod::apply(v[u].z, mparam, 0.f));
+            acc[3] = Red::apply(acc[3], Mod::apply(v[u].w, mparam, 0.f));
+          }
+      }
+    } else {
+      for (thb_u32 i = threadIdx.x; i < rsize; i += THB_RD_THREADS)
+        acc[0] = Red::apply(acc[0], Mod::apply(p[i], mparam, 0.f));
+    }
+    float r = Red::apply(Red::apply(acc[0], acc[1]), Red::apply(acc[2], acc[3]));
+    r = thb_block_fold<Red>(r, init, smem);
+    if (threadIdx.x == 0) out.data[thb_offset(out, s)] = r;
+    __syncthreads();
+  }
+}
+
+// rstride == 1, one warp per slice (short slices).
+template <class Mod, class Red>
+__global__ void __launch_bounds__(THB_RD_THREADS)
+thb_reduce_dim_contig_warp(ThbLayout out, ThbLayout in, thb_u32 rsize, thb_u32 nslices, float init,
+                           float mparam) {
+  const int lane = threadIdx.x & 31;
+  const thb_u32 warps_per_block = THB_RD_THREADS / 32;
+  for (thb_u64 s64 = (thb_u64)blockIdx.x * warps_per_block + (threadIdx.x >> 5); s64 < nslices;
+       s64 += (thb_u64)gridDim.x * warps_per_block) {
+    const thb_u32 s = (thb_u32)s64;
+    const float* p = in.data + thb_offset(in, s);
+    float acc[4] = {init, init, init, init};
+    if ((((thb_u64)p) & 15) == 0 && (rsize & 3) == 0) {
+      const float4* p4 = reinterpret_cast<const float4*>(p);
+      const thb_u32 nvec = rsize >> 2;
+      for (thb_u32 i = lane; i < nvec; i += 32 * 4) {
+        float4 v[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u)
+          if (i + u * 32 < nvec) v[u] = p4[i + u * 32];
+#pragma unroll
+        for (int u = 0; u < 4; ++u)
+          if (i + u * 32 < nvec) {
+            acc[0] = Red::apply(acc[0], Mod::apply(v[u].x, mparam, 0.f));
+            acc[1] = Red::apply(acc[1], Mod::apply(v[u].y, mparam, 0.f));
+            acc[2] = Red::apply(acc[2], Mod::apply(v[u].z, mparam, 0.f));
+            acc[3] = Red::apply(acc[3], Mod::apply(v[u].w, mparam, 0.f));
+          }
+      }
+    } else {
+      for (thb_u32 i = lane; i < rsize; i += 32) acc[0] = Red::apply(acc[0], Mod::apply(p[i], mparam, 0.f));
+    }
+    float r = Red::apply(Red::apply(acc[0], acc[1]), Red::apply(acc[2], acc[3]));
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) r = Red::apply(r, __shfl_down_sync(THB_FULL_MASK, r, off));
+    if (lane == 0) out.data[thb_offset(out, s)] = r;
+  }
+}
+
+// rstride != 1: one thread per (slice, chunk of the reduced dimension); adjacent
+// threads take adjacent slices, so the loads coalesce whenever adjacent slices
+// are adjacent in memory. With nchunks == 1 the result goes straight to `out`,
+// otherwise to partial[chunk * nslices + slice] for thb_reduce_dim_fold_chunks.
+template <class Mod, class Red>
+__global__ void __launch_bounds__(THB_RD_THREADS)
+thb_reduce_dim_noncontig(ThbLayout out, ThbLayout in, thb_u32 rsize, thb_u32 rstride, thb_u32 nslices,
+                         thb_u32 chunk_len, thb_u32 nchunks, float init, float mparam, float* partial) {
+  const thb_u32 chunk = blockIdx.y;
+  const thb_u32 r0 = chunk * chunk_len;
+  const thb_u32 r1 = min(rsize, r0 + chunk_len);
+  for (thb_u64 s64 = (thb_u64)blockIdx.x * THB_RD_THREADS + threadIdx.x; s64 < nslices;
+       s64 += (thb_u64)gridDim.x * THB_RD_THREADS) {
+    const thb_u32 s = (thb_u32)s64;
+    const float* p = in.data + thb_offset(in, s);
+    float acc = init;
+    thb_u32 r = r0;
+    for (; r + 8 <= r1; r += 8) {
+      float v[8];
+#pragma unroll
+      for (int u = 0; u < 8; ++u) v[u] = p[(thb_u64)(r + u) * rstride];
+#pragma unroll
+      for (int u = 0; u < 8; ++u) acc = Red::apply(acc, Mod::apply(v[u], mparam, 0.f));
+    }
+    for (; r < r1; ++r) acc = Red::apply(acc, Mod::apply(p[(thb_u64)r * rstride], mparam, 0.f));
+    if (nchunks == 1) out.data[thb_offset(out, s)] = acc;
+    else partial[(thb_u64)chunk * nslices + s] = acc;
+  }
+}
+
+template <class Red>
+__global__ void __launch_bounds__(THB_RD_THREADS)
+thb_reduce_dim_fold_chunks(ThbLayout out, const float* partial, thb_u32 nslices, thb_u32 nchunks, float init) {
+  for (thb_u64 s64 = (thb_u64)blockIdx.x * THB_RD_THREADS + threadIdx.x; s64 < nslices;
+       s64 += (thb_u64)gridDim.x * THB_RD_THREADS) {
+    const thb_u32 s = (thb_u32)s64;
+    float acc = init;
+    for (thb_u32 c = 0; c < nchunks; ++c) acc = Red::apply(acc, partial[(thb_u64)c * nslices + s]);
+    out.data[thb_offset(out, s)] = acc;
+  }
+}
+
+// ---- max / min along one dimension with the position -----------------------
+// A candidate is (value, 0-based position or -1). `Better(a, b)`: a replaces b.
+// Within a thread positions ascend and the comparison is strict, so the first
+// occurrence wins and NaN never replaces the running value; across threads the
+// lower position wins ties, which gives the same answer as one sequential scan.
+template <bool IS_MAX>
+struct ThbArg {
+  static __device__ __forceinline__ float start() { return IS_MAX ? -3.402823466e+38f : 3.402823466e+38f; }
+  static __device__ __forceinline__ bool strictly(float a, float b) { return IS_MAX ? a > b : a < b; }
+  static __device__ __forceinline__ void take(float& v, int& i, float ov, int oi) {
+    if (strictly(ov, v) || (ov == v && oi < i)) { v = ov; i = oi; }
+  }
+};
+
+// src viewed as [rows][n] contiguous; one warp (n < 1024) or one block per row.
+template <bool IS_MAX, bool WARP_PER_ROW>
+__global__ void __launch_bounds__(THB_RD_THREADS)
+thb_argreduce_rows(float* values, float* indices, const float* src, thb_i64 rows, thb_u32 n) {
+  __shared__ float sv[32];
+  __shared__ int si[32];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const thb_i64 rows_per_block = WARP_PER_ROW ? THB_RD_THREADS / 32 : 1;
+  for (thb_i64 row0 = (thb_i64)blockIdx.x * rows_per_block; row0 < rows; row0 += (thb_i64)gridDim.x * rows_per_block) {
+    const thb_i64 row = WARP_PER_ROW ? row0 + warp : row0;
+    float v = ThbArg<IS_MAX>::start();
+    int idx = -1;
+    if (row < rows) {
+      const float* p = src + row * (thb_i64)n;
+      const int t = WARP_PER_ROW ? lane : threadIdx.x;
+      const int nt = WARP_PER_ROW ? 32 : THB_RD_THREADS;
+      if ((((thb_u64)p) & 15) == 0 && (n & 3) == 0) {
+        const float4* p4 = reinterpret_cast<const float4*>(p);
+        const thb_u32 nvec = n >> 2;
+        for (thb_u32 i = t; i < nvec; i += nt * 2) {
+          float4 a = p4[i];
+          float4 b = (i + nt < nvec) ? p4[i + nt] : a;
+          if (ThbArg<IS_MAX>::strictly(a.x, v)) { v = a.x; idx = 4 * i; }
+          if (ThbArg<IS_MAX>::strictly(a.y, v)) { v = a.y; idx = 4 * i + 1; }
+          if (ThbArg<IS_MAX>::strictly(a.z, v)) { v = a.z; idx = 4 * i + 2; }
+          if (ThbArg<IS_MAX>::strictly(a.w, v)) { v = a.w; idx = 4 * i + 3; }
+          if (i + nt < nvec) {
+            const thb_u32 j = i + nt;
+            if (ThbArg<IS_MAX>::strictly(b.x, v)) { v = b.x; idx = 4 * j; }
+            if (ThbArg<IS_MAX>::strictly(b.y, v)) { v = b.y; idx = 4 * j + 1; }
+            if (ThbArg<IS_MAX>::strictly(b.z, v)) { v = b.z; idx = 4 * j + 2; }
+            if (ThbArg<IS_MAX>::strictly(b.w, v)) { v = b.w; idx = 4 * j + 3; }
+          }
+        }
+      } else {
+        for (thb_u32 i = t; i < n; i += nt)
+          if (ThbArg<IS_MAX>::strictly(p[i], v)) { v = p[i]; idx = i; }
+      }
+    }
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) {
+      float ov = __shfl_down_sync(THB_FULL_MASK, v, off);
+      int oi = __shfl_down_sync(THB_FULL_MASK, idx, off);
+      // a real position is only ever recorded for a value strictly beyond the start
+      // value, so a candidate without a position (-1) has nothing to offer
+      if (oi >= 0) ThbArg<IS_MAX>::take(v, idx, ov, oi);
+    }
+    if (WARP_PER_ROW) {
+      if (lane == 0 && row < rows) {
+        values[row] = v;
+        indices[row] = (float)(idx < 0 ? -1 : idx + 1);
+      }
+    } else {
+      if (lane == 0) { sv[warp] = v; si[warp] = idx; }
+      __syncthreads();
+      if (warp == 0) {
+        v = lane < THB_RD_THREADS / 32 ? sv[lane] : ThbArg<IS_MAX>::start();
+        idx = lane < THB_RD_THREADS / 32 ? si[lane] : -1;
+#pragma unroll
+        for (int off = 16; off > 0; off >>= 1) {
+          float ov = __shfl_down_sync(THB_FULL_MASK, v, off);
+          int oi = __shfl_down_sync(THB_FULL_MASK, idx, off);
+          if (oi >= 0) ThbArg<IS_MAX>::take(v, idx, ov, oi);
+        }
+        if (lane == 0) {
+          values[row] = v;
+          indices[row] = (float)(idx < 0 ? -1 : idx + 1);
+        }
+      }
+      __syncthreads();
+    }
+  }
+}
+
+// src viewed as [outer][n][inner] contiguous with inner > 1: one thread per
+// (outer, inner, chunk of n). With nchunks == 1 results go to values/indices,
+// otherwise to pval/pidx[chunk * (outer*inner) + slice] for thb_argreduce_fold_chunks.
+template <bool IS_MAX>
+__global__ void __launch_bounds__(THB_RD_THREADS)
+thb_argreduce_cols(float* values, float* indices, const float* src, thb_i64 outer, thb_u32 n, thb_i64 inner,
+                   thb_u32 chunk_len, thb_u32 nchunks, float* pval, int* pidx) {
+  const thb_i64 nslices = outer * inner;
+  const thb_u32 chunk = blockIdx.y;
+  const thb_u32 r0 = chunk * chunk_len;
+  const thb_u32 r1 = min(n, r0 + chunk_len);
+  for (thb_i64 s = (thb_i64)blockIdx.x * THB_RD_THREADS + threadIdx.x; s < nslices;
+       s += (thb_i64)gridDim.x * THB_RD_THREADS) {
+    const thb_i64 o = s / inner, i = s - o * inner;
+    const float* p = src + (o * n) * inner + i;
+    float v = ThbArg<IS_MAX>::start();
+    int idx = -1;
+    thb_u32 r = r0;
+    for (; r + 8 <= r1; r += 8) {
+      float x[8];
+#pragma unroll
+      for (int u = 0; u < 8; ++u) x[u] = p[(thb_i64)(r + u) * inner];
+#pragma unroll
+      for (int u = 0; u < 8; ++u)
+        if (ThbArg<IS_MAX>::strictly(x[u], v)) { v = x[u]; idx = r + u; }
+    }
+    for (; r < r1; ++r) {
+      float x = p[(thb_i64)r * inner];
+      if (ThbArg<IS_MAX>::strictly(x, v)) { v = x; idx = r; }
+    }
+    if (nchunks == 1) {
+      values[s] = v;
+      indices[s] = (float)(idx < 0 ? -1 : idx + 1);
+    } else {
+      pval[(thb_i64)chunk * nslices + s] = v;
+      pidx[(thb_i64)chunk * nslices + s] = idx;
+    }
+  }
+}
+
+template <bool IS_MAX>
+__global__ void __launch_bounds__(THB_RD_THREADS)
+thb_argreduce_fold_chunks(float* values, float* indices, const float* pval, const int* pidx, thb_i64 nslices,
+                          thb_u32 nchunks) {
+  for (thb_i64 s = (thb_i64)blockIdx.x * THB_RD_THREADS + threadIdx.x; s < nslices;
+       s += (thb_i64)gridDim.x * THB_RD_THREADS) {
+    float v = ThbArg<IS_MAX>::start();
+    int idx = -1;
+    for (thb_u32 c = 0; c < nchunks; ++c) {
+      float ov = pval[(thb_i64)c * nslices + s];
+      int oi = pidx[(thb_i64)c * nslices + s];
+      if (oi >= 0 && ThbArg<IS_MAX>::strictly(ov, v)) { v = ov; idx = oi; }
+    }
+    values[s] = v;
+    indices[s] = (float)(idx < 0 ? -1 : idx + 1);
+  }
+}

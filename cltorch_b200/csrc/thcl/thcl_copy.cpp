@@ -1,0 +1,172 @@
+// Tensor copies (reference src/lib/THClTensorCopy.cpp): device to device with
+// any strides, and host <-> device for the Torch7 host tensor types.
+//
+// Host copies move only the elements the tensor addresses (the reference moves
+// the whole underlying storage through its host mirror on every call).
+#include "thcl_internal.h"
+
+#include <cstdio>
+#include <cstdlib>
+#include <type_traits>
+#include <vector>
+
+using namespace thcl;
+
+namespace {
+
+// Visits the elements of a host tensor in row-major order of its own shape.
+template <class T, class F>
+void for_each_host(long* size, long* stride, int nd, T* base, F&& f) {
+  long n = 1;
+  for (int d = 0; d < nd; ++d) n *= size[d];
+  if (nd <= 0 || n == 0) return;
+  std::vector<long> idx(nd, 0);
+  long off = 0;
+  for (long i = 0; i < n; ++i) {
+    f(base[off], i);
+    for (int d = nd - 1; d >= 0; --d) {
+      off += stride[d];
+      if (++idx[d] < size[d]) break;
+      off -= idx[d] * stride[d];
+      idx[d] = 0;
+    }
+  }
+}
+
+bool host_contiguous(long* size, long* stride, int nd) {
+  long z = 1;
+  for (int d = nd - 1; d >= 0; --d) {
+    if (size[d] != 1) {
+      if (stride[d] != z) return false;
+      z *= size[d];
+    }
+  }
+  return true;
+}
+
+long host_nelement(long* size, int nd) {
+  if (nd <= 0) return 0;
+  long n = 1;
+  for (int d = 0; d < nd; ++d) n *= size[d];
+  return n;
+}
+
+// Uploads `n` floats that are already in linear order into `self` (any strides).
+void upload_linear(THClState* state, THClTensor* self, const float* host, long n) {
+  THClDeviceContext* ctx = context(state, self->device);
+  use_device(self->device);
+  if (state->trace) printf("THCl: host -> device %ld floats\n", n);
+  if (THClTensor_isContiguous(state, self)) {
+    check_cuda(cudaMemcpyAsync(THClTensor_data(state, self), host, (size_t)n * sizeof(float), cudaMemcpyHostToDevice, ctx->stream), "cudaMemcpyAsync");
+    check_cuda(cudaStreamSynchronize(ctx->stream), "cudaStreamSynchronize");
+    return;
+  }
+  THClTensor* tmp = THClTensor_newWithSize1d(state, self->device, n);
+  check_cuda(cudaMemcpyAsync(THClTensor_data(state, tmp), host, (size_t)n * sizeof(float), cudaMemcpyHostToDevice, ctx->stream), "cudaMemcpyAsync");
+  THClTensor_copy(state, self, tmp);
+  check_cuda(cudaStreamSynchronize(ctx->stream), "cudaStreamSynchronize");
+  THClTensor_free(state, tmp);
+}
+
+// Downloads the elements of `src` in linear order into `host`.
+void download_linear(THClState* state, THClTensor* src, float* host, long n) {
+  THClDeviceContext* ctx = context(state, src->device);
+  use_device(src->device);
+  if (state->trace) printf("THCl: device -> host %ld floats\n", n);
+  THClTensor* c = THClTensor_newContiguous(state, src);
+  check_cuda(cudaMemcpyAsync(host, THClTensor_data(state, c), (size_t)n * sizeof(float), cudaMemcpyDeviceToHost, ctx->stream), "cudaMemcpyAsync");
+  check_cuda(cudaStreamSynchronize(ctx->stream), "cudaStreamSynchronize");
+  THClTensor_free(state, c);
+}
+
+template <class HostTensor, class T>
+void copy_from_host(THClState* state, THClTensor* self, HostTensor* src) {
+  const long n = THClTensor_nElement(state, self);
+  arg_check(n == host_nelement(src->size, src->nDimension), 2, "sizes do not match");
+  if (n == 0) return;
+  T* base = src->storage->data + src->storageOffset;
+  if (sizeof(T) == sizeof(float) && std::is_same<T, float>::value && host_contiguous(src->size, src->stride, src->nDimension)) {
+    upload_linear(state, self, reinterpret_cast<const float*>(base), n);
+    return;
+  }
+  std::vector<float> buf(n);
+  for_each_host<T>(src->size, src->stride, src->nDimension, base, [&](T& v, long i) { buf[i] = (float)v; });
+  upload_linear(state, self, buf.data(), n);
+}
+
+template <class HostTensor, class T>
+void copy_to_host(THClState* state, HostTensor* self, THClTensor* src) {
+  const long n = THClTensor_nElement(state, src);
+  arg_check(n == host_nelement(self->size, self->nDimension), 2, "sizes do not match");
+  if (n == 0) return;
+  T* base = self->storage->data + self->storageOffset;
+  if (std::is_same<T, float>::value && host_contiguous(self->size, self->stride, self->nDimension)) {
+    download_linear(state, src, reinterpret_cast<float*>(base), n);
+    return;
+  }
+  std::vector<float> buf(n);
+  download_linear(state, src, buf.data(), n);
+  for_each_host<T>(self->size, self->stride, self->nDimension, base, [&](T& v, long i) { v = (T)buf[i]; });
+}
+
+}  // namespace
+
+extern "C" {
+
+void THClTensor_copy(THClState* state, THClTensor* dst, THClTensor* src) {
+  THCL_BEGIN
+  const long n = THClTensor_nElement(state, dst);
+  arg_check(n == THClTensor_nElement(state, src), 2, "sizes do not match");
+  if (dst->nDimension <= 0 || n == 0) return;
+  if (dst->device != src->device) raise("Not implemented: copy between devices");
+  const bool contig = THClTensor_isContiguous(state, src) && THClTensor_isContiguous(state, dst);
+  // plain device copy when both are one run (or a single element) in different
+  // storages; everything else is the copy operator through apply
+  // (reference src/lib/THClTensorCopy.cpp:144-184)
+  if ((contig || n == 1) && src->storage != dst->storage) {
+    THClDeviceContext* ctx = context(state, dst->device);
+    use_device(dst->device);
+    check_cuda(cudaMemcpyAsync(THClTensor_data(state, dst), THClTensor_data(state, src), (size_t)n * sizeof(float),
+                               cudaMemcpyDeviceToDevice, ctx->stream), "cudaMemcpyAsync");
+    after_launch(state, ctx);
+    return;
+  }
+  THClTensor* t[2] = {dst, src};
+  const bool rw[2] = {true, false};
+  pointwise(state, 2, t, rw, "COPY_2", nullptr, 0.f, 0.f, nullptr);
+  THCL_END_VOID
+}
+
+void THClTensor_copyCl(THClState* state, THClTensor* self, THClTensor* src) { THClTensor_copy(state, self, src); }
+
+// Copy into a destination whose indices overlap without the temporary: which
+// writer wins is unspecified (reference src/lib/THClApply.cpp:17-26).
+void THClTensor_copyIgnoringOverlaps(THClState* state, THClTensor* dst, THClTensor* src) {
+  THCL_BEGIN
+  THClTensor* t[2] = {dst, src};
+  const bool rw[2] = {false, false};
+  pointwise(state, 2, t, rw, "COPY_2", nullptr, 0.f, 0.f, nullptr);
+  THCL_END_VOID
+}
+
+#define THCL_HOST_COPY(Name, T)                                                                  \
+  void THClTensor_copy##Name(THClState* state, THClTensor* self, TH##Name##Tensor* src) {        \
+    THCL_BEGIN                                                                                   \
+    copy_from_host<TH##Name##Tensor, T>(state, self, src);                                       \
+    THCL_END_VOID                                                                                \
+  }                                                                                              \
+  void TH##Name##Tensor_copyCl(THClState* state, TH##Name##Tensor* self, THClTensor* src) {      \
+    THCL_BEGIN                                                                                   \
+    copy_to_host<TH##Name##Tensor, T>(state, self, src);                                         \
+    THCL_END_VOID                                                                                \
+  }
+THCL_HOST_COPY(Byte, unsigned char)
+THCL_HOST_COPY(Char, char)
+THCL_HOST_COPY(Short, short)
+THCL_HOST_COPY(Int, int)
+THCL_HOST_COPY(Long, long)
+THCL_HOST_COPY(Float, float)
+THCL_HOST_COPY(Double, double)
+#undef THCL_HOST_COPY
+
+}  // extern "C"

@@ -1,0 +1,85 @@
+// Internals of the THCl-shaped host layer (include/THCl.h).
+#pragma once
+#include <cuda_runtime.h>
+#include <stdexcept>
+#include <string>
+#include <vector>
+
+#include "THCl.h"
+#include "thb200.h"
+
+struct THClDeviceContext {
+  int device = 0;
+  cudaStream_t stream = nullptr;
+  bool owns_stream = false;
+  float* result = nullptr;        // 64 device floats: results of host-scalar reductions
+  float* result_host = nullptr;   // pinned mirror of `result`
+  float* scratch = nullptr;       // reduction partials
+  size_t scratch_bytes = 0;
+  void* gemm_ws = nullptr;        // split operands of the GEMM
+  size_t gemm_ws_bytes = 0;
+  THClScratchSpace scratch_space{nullptr, nullptr};
+};
+
+namespace thcl {
+
+struct Error : std::runtime_error {
+  using std::runtime_error::runtime_error;
+};
+
+[[noreturn]] void raise(const char* fmt, ...) __attribute__((format(printf, 1, 2)));
+void arg_check(bool cond, int arg, const char* msg);  // THArgCheck
+void check_cuda(cudaError_t e, const char* what);
+void check_thb(int rc);  // non-zero status of a thb200_* call -> Error with its message
+
+// Error reporting at the C boundary: nested API calls rethrow, the outermost
+// one runs the installed handler.
+struct Scope {
+  Scope();
+  ~Scope();
+  static int depth();
+};
+void report(const char* msg);
+void clear_error();
+
+#define THCL_BEGIN        \
+  ::thcl::Scope thcl_scope_; \
+  try {
+#define THCL_END(ret)                         \
+  }                                           \
+  catch (const std::exception& e) {           \
+    if (::thcl::Scope::depth() > 1) throw;    \
+    ::thcl::report(e.what());                 \
+    return ret;                               \
+  }
+#define THCL_END_VOID                         \
+  }                                           \
+  catch (const std::exception& e) {           \
+    if (::thcl::Scope::depth() > 1) throw;    \
+    ::thcl::report(e.what());                 \
+    return;                                   \
+  }
+
+THClDeviceContext* context(THClState* state, int device);  // created on first use
+void use_device(int device);                               // cudaSetDevice if needed
+float* ensure_scratch(THClDeviceContext* ctx, size_t bytes);
+void* ensure_gemm_ws(THClDeviceContext* ctx, size_t bytes);
+void after_launch(THClState* state, THClDeviceContext* ctx);  // addFinish
+
+// View of a tensor for the thin ABI; keeps the int64 copies of size/stride alive.
+struct View {
+  thb200_tensor t;
+  int64_t size[THB200_MAX_DIMS];
+  int64_t stride[THB200_MAX_DIMS];
+  View() { t.data = nullptr; t.ndim = 0; t.size = size; t.stride = stride; }
+  View(const View&) = delete;
+  void set(const THClTensor* x);
+};
+
+// Pointwise apply over 1..3 tensors with overlap handling
+// (THClTensor_pointwiseApply, reference src/lib/THClApply.cpp:145-240).
+// Exactly one of `op` (built-in name) and `expr` (rewritten body) is given.
+void pointwise(THClState* state, int nt, THClTensor** tensors, const bool* read_write, const char* op,
+               const char* expr, float val1, float val2, const THClTensor* point1);
+
+}  // namespace thcl

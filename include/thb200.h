@@ -1,0 +1,154 @@
+/* thb200.h — the thin CUDA C ABI underneath the THCl-shaped host library.
+ *
+ * Plain pointers, sizes and strides only. Every device pointer is an ordinary
+ * CUDA global-memory address on the current device; `stream` is a
+ * cudaStream_t passed as void* (NULL = the legacy default stream). All launches
+ * are asynchronous; nothing here synchronises the host except where stated.
+ *
+ * Return value: 0 on success, non-zero on failure, with the reason available
+ * from thb200_last_error() (thread-local, valid until the next failing call on
+ * the same thread).
+ *
+ * Each entry point names the interface of the reference (hughperkins/cltorch,
+ * paths relative to its root) that it stands in for.
+ */
+#ifndef THB200_H
+#define THB200_H
+
+#include <stdint.h>
+#include <stddef.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define THB200_MAX_DIMS 25 /* MAX_CLTORCH_DIMS, src/lib/THClReduceApplyUtils.h:19 */
+
+/* A strided fp32 view. `data` addresses element (0,...,0), i.e. storage base +
+ * storageOffset; `size`/`stride` are in elements, un-collapsed, row-major
+ * meaning as in THClTensor (src/lib/THClTensor.h:14-27). ndim == 0 is a point
+ * tensor / empty tensor: zero elements for apply, one float for the scalar
+ * arguments named `point`. */
+typedef struct thb200_tensor {
+  float* data;
+  int ndim;
+  const int64_t* size;
+  const int64_t* stride;
+} thb200_tensor;
+
+const char* thb200_last_error(void);
+
+/* ---- host-side index helpers (no GPU needed) ------------------------------ */
+
+/* TensorInfo<IndexType>::TensorInfo, src/lib/THClReduceApplyUtils.h:68-170:
+ * drop size-1 dims, merge dim i into i+1 when stride[i] == size[i+1]*stride[i+1];
+ * `reduce_dim` (or -1) is treated as size 1. Writes at most ndim entries to
+ * out_size/out_stride and returns the collapsed dim count (>= 1), or -1. */
+int thb200_collapse_dims(int ndim, const int64_t* size, const int64_t* stride, int reduce_dim,
+                         int64_t* out_size, int64_t* out_stride);
+/* THCL_canUse32BitIndexMath, src/lib/THClReduceApplyUtils.cpp:9-30. */
+int thb200_can_use_32bit_index(int ndim, const int64_t* size, const int64_t* stride);
+/* THCL_overlappingIndices, src/lib/THClReduceApplyUtils.cpp:69-121 (dims sorted
+ * by ascending stride; the reference's qsort comparator is not a valid ordering). */
+int thb200_overlapping_indices(int ndim, const int64_t* size, const int64_t* stride);
+/* Which kernel thb200_apply_* would pick for these operands, without launching:
+ * 0 = nothing to do, 1 = contiguous 128-bit, 2 = strided, 3 = 2-D tile; < 0 = error. */
+int thb200_apply_plan(int ntensors, const thb200_tensor* t);
+
+/* ---- pointwise apply ------------------------------------------------------ */
+
+/* Code of a built-in operator by name ("ADD_3", "MULC_1", ...; the list is
+ * cltorch_b200/csrc/kernels/apply_ops.def), or -1. */
+int thb200_op_code(const char* name);
+/* Number of tensors a built-in operator takes (1..3), or -1. */
+int thb200_op_arity(int op);
+
+/* THClTensor_pointwiseApply1/2/3 with a built-in operator, src/lib/THClApply.cpp:145-287
+ * and kernel src/lib/THClApply.cl:47-102. t[0] is the read/write operand. All
+ * operands need equal element counts, not equal shapes. Overlapping read/write
+ * operands are the caller's business (the THCl layer routes them through a
+ * contiguous temporary as the reference does). */
+int thb200_apply_op(void* stream, int op, int ntensors, const thb200_tensor* t,
+                    float val1, float val2, const float* point1, const float* point2);
+
+/* THClTensor_apply / _map / _map2 after the x,y,z rewrite,
+ * src/lib/THClTensorMathPointwise.cpp:79-146: `body` is C code over *out, *in1,
+ * *in2 (and val1, val2, *pointTensor1, *pointTensor2), compiled once per
+ * (ntensors, body) with NVRTC for sm_100a and cached for the process. */
+int thb200_apply_expr(void* stream, const char* body, int ntensors, const thb200_tensor* t,
+                      float val1, float val2, const float* point1, const float* point2);
+/* The x/y/z -> (*out)/(*in1)/(*in2) rewrite itself, token-wise; unsuffixed
+ * floating literals get an `f`. Returns the length written (excluding NUL) or
+ * -1 if `cap` is too small. */
+int thb200_rewrite_expr(const char* expr, int ntensors, char* out, size_t cap);
+
+/* ---- reductions ----------------------------------------------------------- */
+
+enum thb200_modify { THB200_MOD_COPY = 0, THB200_MOD_ABSPOW = 1, THB200_MOD_NEZERO = 2, THB200_MOD_SQDEV = 3 };
+enum thb200_reduce { THB200_RED_ADD = 0, THB200_RED_MUL = 1, THB200_RED_MIN = 2, THB200_RED_MAX = 3,
+                     THB200_RED_AND = 4, THB200_RED_OR = 5 };
+enum thb200_final { THB200_FIN_NONE = 0, THB200_FIN_DIV = 1, THB200_FIN_DIV_SQRT = 2 };
+
+/* Bytes of scratch (global memory beyond input and output) that
+ * thb200_reduce_all needs for `n` elements: one float per pass-1 block. */
+size_t thb200_reduce_all_scratch_bytes(int64_t n);
+
+/* THClTensor_reduceAll, src/lib/THClReduceAll.cpp:276-316 with kernels
+ * src/lib/THClReduceAll.cl:24-100: r = init; r = reduce(r, modify(e)) over all
+ * elements; *d_out = finalise(r). Two launches in a fixed order (no atomics):
+ * pass 1 writes one partial per block into `scratch`, pass 2 folds them.
+ * `mod_param` is the exponent of ABSPOW; `mod_point` the device-resident mean of
+ * SQDEV; `fin_param` the divisor of FIN_DIV / FIN_DIV_SQRT. d_out is a device
+ * pointer: the result never visits the host (point tensors, README.md:88-138). */
+int thb200_reduce_all(void* stream, int modify, int reduce, const thb200_tensor* in, float init,
+                      float mod_param, const float* mod_point, int fin, float fin_param,
+                      float* d_out, float* scratch, size_t scratch_bytes);
+
+/* Bytes of scratch thb200_reduce_dim may need for this shape (0 if none). */
+size_t thb200_reduce_dim_scratch_bytes(const thb200_tensor* in, int dim);
+
+/* THClTensor_reduceDim, src/lib/THClReduce.cpp:215-302 with kernels
+ * src/lib/THClReduce.cl:30-111: out[..., 0, ...] = fold over `dim`. `out` must
+ * already have the shape of `in` with size 1 at `dim`. */
+int thb200_reduce_dim(void* stream, int modify, int reduce, const thb200_tensor* out,
+                      const thb200_tensor* in, int dim, float init, float mod_param,
+                      float* scratch, size_t scratch_bytes);
+
+/* THClTensor_reduceDimIndex, src/lib/THClTensorMathTransformReduce.cpp:160-185
+ * with kernels src/lib/THClTensorMathTransformReduce.cl:17-102: per slice the
+ * extreme value and its 1-based position stored as fp32; strict comparison in
+ * ascending position, so the first occurrence wins and NaN never replaces the
+ * running value; start value -/+FLT_MAX with index -1. All three tensors are
+ * contiguous; src is viewed as [outer][n][inner]. is_max: 1 = max, 0 = min. */
+int thb200_reduce_dim_index(void* stream, int is_max, float* values, float* indices, const float* src,
+                            int64_t outer, int64_t n, int64_t inner, float* scratch, size_t scratch_bytes);
+size_t thb200_reduce_dim_index_scratch_bytes(int64_t outer, int64_t n, int64_t inner);
+
+/* Fixed-order fold of `count` device floats into *d_out (count <= 1024): the
+ * last step of a sum sharded over several GPUs, after the per-GPU partials
+ * have been gathered. No counterpart in the reference (it has no collectives). */
+int thb200_fold_partials(void* stream, int reduce, const float* d_partials, int count, float* d_out);
+
+/* ---- GEMM ----------------------------------------------------------------- */
+
+/* clblasSgemm as called from THClBlas_gemm, src/lib/THClBlas.cpp:380-449:
+ * column-major C(m x n) = alpha * op(A) * op(B) + beta * C, transa/transb 'n' or
+ * 't', fp32 in and out. Computed with tcgen05 TF32 tensor-core MMAs on a
+ * three-term split of each operand (hi*hi + hi*lo + lo*hi) accumulated in fp32.
+ * `batch` independent problems at the given element strides (batch = 1 for addmm).
+ * `workspace` holds the split operands; size from thb200_gemm_workspace_bytes. */
+size_t thb200_gemm_workspace_bytes(int64_t m, int64_t n, int64_t k, int64_t batch);
+int thb200_gemm(void* stream, char transa, char transb, int64_t m, int64_t n, int64_t k, float alpha,
+                const float* a, int64_t lda, const float* b, int64_t ldb, float beta, float* c, int64_t ldc,
+                int64_t batch, int64_t stride_a, int64_t stride_b, int64_t stride_c,
+                void* workspace, size_t workspace_bytes);
+/* Every wait inside the GEMM kernel is bounded. Status word of the last
+ * thb200_gemm that used this workspace: 0 = completed, 1/2/3 = a wait of the
+ * load / MMA / store stage gave up (C is then undefined). Synchronises `stream`.
+ * < 0: the status could not be read. */
+int thb200_gemm_status(void* stream, int64_t m, int64_t n, int64_t k, int64_t batch, void* workspace);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* THB200_H */
