@@ -1,0 +1,171 @@
+"""Single-GPU timings of the remaining benchmark configurations (`bench.py --workload c1|c2|c3|c4`).
+
+Every operation is timed on its own with CUDA events on the stream the library launches
+on, after warm-up, with a 512 MiB fill between timed iterations so that nothing is served
+from L2 (126 MB). Rates use the ALGORITHMIC bytes (4 bytes per element an operation must
+read or write) or 2*M*N*K flops, and are quoted against the measured HBM copy rate
+(MEASURED_PEAKS.json) or, for the GEMM, against one third of the nominal dense TF32 rate.
+Inputs are seeded synthetic tensors of the configured shapes.
+"""
+from __future__ import annotations
+
+import json
+import statistics
+from pathlib import Path
+
+import numpy as np
+
+ROOT = Path(__file__).resolve().parent.parent
+TF32_DENSE_TFLOPS_NOMINAL = 1100.0
+
+
+def _peak():
+    p = ROOT / "MEASURED_PEAKS.json"
+    return float(json.loads(p.read_text())["hbm_gbs"]) if p.exists() else 6650.0
+
+
+class Timer:
+    def __init__(self, steps, warmup):
+        import torch
+        import cltorch_b200 as cl
+        self.torch, self.cl = torch, cl
+        torch.cuda.set_device(0)
+        cl.setDevice(1)
+        cl.setStream(torch.cuda.current_stream().cuda_stream)
+        self.steps, self.warmup = steps, warmup
+        self.flush = torch.empty(128 << 20, dtype=torch.float32, device="cuda")
+        self.peak = _peak()
+        self.results = {}
+
+    def time(self, name, fn, nbytes=None, flops=None, setup=None):
+        t = self.torch
+        for _ in range(self.warmup):
+            if setup:
+                setup()
+            fn()
+        ms = []
+        for _ in range(self.steps):
+            if setup:
+                setup()
+            self.flush.fill_(1.0)
+            a, b = t.cuda.Event(enable_timing=True), t.cuda.Event(enable_timing=True)
+            a.record()
+            fn()
+            b.record()
+            b.synchronize()
+            ms.append(a.elapsed_time(b))
+        med = statistics.median(ms)
+        r = {"ms": med}
+        if nbytes is not None:
+            r["GB/s"] = nbytes / (med * 1e-3) / 1e9
+            r["frac_of_measured_hbm"] = r["GB/s"] / self.peak
+        if flops is not None:
+            r["TFLOP/s"] = flops / (med * 1e-3) / 1e12
+            r["frac_of_3xtf32_nominal"] = r["TFLOP/s"] / (TF32_DENSE_TFLOPS_NOMINAL / 3)
+        self.results[name] = r
+        return r
+
+
+def _uniform(g, shape, lo, hi):
+    return (g.random(shape, dtype=np.float32) * np.float32(hi - lo) + np.float32(lo)).astype(np.float32)
+
+
+def c1(T):
+    cl = T.cl
+    g = np.random.Generator(np.random.PCG64(0))
+    n = 4096 * 4096
+    X, Y, Z = (cl.ClTensor(_uniform(g, (4096, 4096), 0, 1)) for _ in range(3))
+    S = cl.ClTensor()
+    T.time("map2 x = sqrt(1000*x + y*10 + z*z)", lambda: X.map2_on_gpu(Y, Z, "x = sqrt(1000*x + y*10 + z*z)"), 16 * n)
+    T.time("sum -> point tensor", lambda: S.sum(X), 4 * n)
+    T.time("div by point tensor", lambda: X.div(S), 8 * n, setup=lambda: X.fill(1.0) and S.sum(X))
+    T.time("sum -> host float (with read-back)", lambda: X.sum(), 4 * n)
+    T.time("div by host float", lambda: X.div(3.0), 8 * n)
+
+    def chain():
+        X.map2_on_gpu(Y, Z, "x = sqrt(1000*x + y*10 + z*z)")
+        S.sum(X)
+        X.div(S)
+    T.time("sequence map2 + sum + div (point tensor)", chain, 28 * n)
+
+
+def c2(T):
+    cl = T.cl
+    n = 8192
+    g = np.random.Generator(np.random.PCG64(1))
+    A, B, Tt = (cl.ClTensor(_uniform(g, (n, n), -1, 1)) for _ in range(3))
+    views = {
+        "T (transpose)": lambda X: X.t(),
+        "S (stride-2 columns)": lambda X: cl.ClTensor(X.storage(), 1, [n, n // 2], [n, 2]),
+        "W (narrow rows)": lambda X: X.narrow(1, 17, 4000),
+        "Wc (narrow columns)": lambda X: X.narrow(2, 17, 4000),
+    }
+    for name, gv in views.items():
+        va, vb, vt = gv(A), gv(B), gv(Tt)
+        cnt = va.nElement()
+        out = cl.ClTensor().resizeAs(va)
+        T.time(f"add {name}", lambda: out.add(va, vb), 12 * cnt)
+        T.time(f"cmul {name}", lambda: out.cmul(va, vb), 12 * cnt)
+        T.time(f"addcmul(0.5) {name} [copy + apply3 = 24 B/elt]", lambda: out.addcmul(vt, 0.5, va, vb), 24 * cnt)
+        T.time(f"copy into fresh contiguous {name}", lambda: out.copy(va), 8 * cnt)
+        T.time(f"apply x = tanh(x)*x (in place, contiguous copy) {name}", lambda: out.apply_on_gpu("x = tanh(x)*x"), 8 * cnt,
+               setup=lambda: out.copy(va))
+    out = cl.ClTensor(n, n)
+    T.time("add contiguous = transpose + contiguous", lambda: out.add(A.t(), B), 12 * n * n)
+
+
+def c3(T):
+    cl = T.cl
+    g = np.random.Generator(np.random.PCG64(2))
+    a = g.standard_normal((16384, 16384), dtype=np.float32)
+    A = cl.ClTensor(a)
+    del a
+    n = 16384 * 16384
+    out = cl.ClTensor()
+    for d in (1, 2):
+        T.time(f"sum(A, {d})", lambda: out.sum(A, d), 4 * n)
+        T.time(f"max(A, {d}) with indices", lambda: A.max(d), 4 * n)
+        T.time(f"min(A, {d}) with indices", lambda: A.min(d), 4 * n)
+    m, s = cl.ClTensor(), cl.ClTensor()
+
+    def chain():
+        for _ in range(100):
+            m.mean(A); A.csub(m); s.std(A); A.div(s)
+    T.time("100 x (mean, sub, std, div) on the device [28 B/elt per iteration: std is two passes]", chain, 100 * 28 * n)
+    del A
+    b = g.standard_normal((256, 1024, 1024), dtype=np.float32)
+    Bt = cl.ClTensor(b)
+    del b
+    for d in (1, 2, 3):
+        T.time(f"sum(B3d, {d})", lambda: out.sum(Bt, d), 4 * n)
+        T.time(f"max(B3d, {d}) with indices", lambda: Bt.max(d), 4 * n)
+
+
+def c4(T):
+    cl = T.cl
+    g = np.random.Generator(np.random.PCG64(3))
+
+    def pair(M, N, K, batch=None):
+        lim = 1.0 / np.sqrt(K)
+        sa = (M, K) if batch is None else (batch, M, K)
+        sb = (K, N) if batch is None else (batch, K, N)
+        return cl.ClTensor(_uniform(g, sa, -lim, lim)), cl.ClTensor(_uniform(g, sb, -lim, lim))
+    for M, N, K in ((8192, 8192, 8192), (512, 4096, 4096)):
+        A, B = pair(M, N, K)
+        C = cl.ClTensor(M, N).zero()
+        T.time(f"addmm {M}x{N}x{K}", lambda: C.addmm(1.0, C, 1.0, A, B), flops=2.0 * M * N * K, setup=lambda: C.zero())
+        del A, B, C
+    A, B = pair(1024, 1024, 128, batch=64)
+    C = cl.ClTensor(64, 1024, 1024).zero()
+    nbytes = 64 * (1024 * 128 + 128 * 1024 + 2 * 1024 * 1024) * 4
+    T.time("baddbmm 64 x (1024x1024x128)", lambda: C.baddbmm(1.0, C, 1.0, A, B), nbytes=nbytes,
+           flops=2.0 * 64 * 1024 * 1024 * 128, setup=lambda: C.zero())
+
+
+def run(workload: str, steps: int, warmup: int) -> None:
+    T = Timer(steps, warmup)
+    {"c1": c1, "c2": c2, "c3": c3, "c4": c4}[workload](T)
+    T.cl.synchronize()
+    print(json.dumps({"workload": workload, "n_gpus": 1, "steps": steps, "warmup": warmup, "dtype": "f32",
+                      "data": "synthetic", "hbm_peak_gbs_measured": T.peak, "l2_flush": "512 MiB fill between iterations",
+                      "results": T.results}))

@@ -27,6 +27,7 @@ static const char* kKernelSource =
 // Function names whose accuracy policy differs from the CUDA fp32 routine
 // (math_policy.cuh); expressions get the same policy as the built-in operators.
 static const char* kPolicyMacros =
+    "#define exp(x) thb_exp(x)\n"
     "#define tan(x) thb_tan(x)\n"
     "#define sinh(x) thb_sinh(x)\n"
     "#define atan2(y, x) thb_atan2(y, x)\n"

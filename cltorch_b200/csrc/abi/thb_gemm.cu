@@ -48,12 +48,13 @@ struct Workspace {
 static Workspace carve(void* ws, int64_t m, int64_t n, int64_t k, int64_t batch) {
   const int64_t Kp = round_up(k, THB_GEMM_BK);
   Workspace w;
+  ws = (void*)(((uintptr_t)ws + 1023) & ~(uintptr_t)1023);  // TMA and the swizzle want 1024-byte aligned bases
   size_t a_bytes = (size_t)round_up(batch * 2 * m * Kp * 4, 1024);
   size_t b_bytes = (size_t)round_up(batch * 2 * n * Kp * 4, 1024);
   w.a = (float*)ws;
   w.b = (float*)((char*)ws + a_bytes);
   w.status = (int*)((char*)ws + a_bytes + b_bytes);
-  w.bytes = a_bytes + b_bytes + 1024;
+  w.bytes = a_bytes + b_bytes + 1024 /*status*/ + 1024 /*alignment slack*/;
   return w;
 }
 
@@ -81,7 +82,6 @@ int thb200_gemm(void* stream, char transa, char transb, int64_t m, int64_t n, in
   if (!a || !b || !c) return fail("gemm: null operand");
   if (lda < (ta ? k : m) || ldb < (tb ? n : k) || ldc < m)
     return fail("gemm: leading dimension too small (lda=%lld ldb=%lld ldc=%lld)", (long long)lda, (long long)ldb, (long long)ldc);
-  if (((uintptr_t)workspace & 1023) != 0) return fail("gemm: workspace must be 1024-byte aligned");
   Workspace w = carve(workspace, m, n, k > 0 ? k : 1, batch);
   if (!workspace || workspace_bytes < w.bytes)
     return fail("gemm: workspace too small (%zu bytes, need %zu)", workspace_bytes, w.bytes);
@@ -134,8 +134,11 @@ int thb200_gemm(void* stream, char transa, char transb, int64_t m, int64_t n, in
 int thb200_gemm_status(void* stream, int64_t m, int64_t n, int64_t k, int64_t batch, void* workspace) {
   Workspace w = carve(workspace, m, n, k > 0 ? k : 1, batch);
   int h = -1;
-  THB_CUDA(cudaMemcpyAsync(&h, w.status, sizeof(int), cudaMemcpyDeviceToHost, (cudaStream_t)stream));
-  THB_CUDA(cudaStreamSynchronize((cudaStream_t)stream));
+  if (cudaMemcpyAsync(&h, w.status, sizeof(int), cudaMemcpyDeviceToHost, (cudaStream_t)stream) != cudaSuccess ||
+      cudaStreamSynchronize((cudaStream_t)stream) != cudaSuccess) {
+    fail("gemm: could not read the status word");
+    return -1;
+  }
   return h;
 }
 

@@ -96,17 +96,17 @@ struct ReduceAllArgs {
   void operator()() {
     const int blocks = (int)reduce_all_blocks(n);
     if (contig) {
-      thb_reduce_all_pass1_contig<Mod, Red><<<blocks, THB_RA_THREADS, 0, st>>>(in->data, n, head, init, mparam,
-                                                                              mpoint, scratch);
+      thb_reduce_all_pass1_contig<Mod, Red><<<blocks, THB_RA_THREADS, 0, st>>>(
+          in->data, n, head, init, mparam, mpoint, (typename Red::acc_t*)scratch);
     } else {
       ThbLayout L;
       fill_layout(&L, in->data, c);
-      thb_reduce_all_pass1_strided<Mod, Red><<<blocks, THB_RA_THREADS, 0, st>>>(L, (thb_u64)n, init, mparam,
-                                                                               mpoint, scratch);
+      thb_reduce_all_pass1_strided<Mod, Red><<<blocks, THB_RA_THREADS, 0, st>>>(
+          L, (thb_u64)n, init, mparam, mpoint, (typename Red::acc_t*)scratch);
     }
     err = cudaGetLastError();
     if (err != cudaSuccess) return;
-    thb_reduce_all_pass2<Red><<<1, 1024, 0, st>>>(scratch, blocks, init, fin, fparam, d_out);
+    thb_reduce_all_pass2<Red><<<1, 1024, 0, st>>>((const typename Red::acc_t*)scratch, blocks, init, fin, fparam, d_out);
     err = cudaGetLastError();
   }
 };
@@ -151,11 +151,12 @@ struct ReduceDimArgs {
     uint64_t bx = ((uint64_t)nslices + THB_RD_THREADS - 1) / THB_RD_THREADS;
     if (bx > 65535u * 16u) bx = 65535u * 16u;
     dim3 grid((unsigned)bx, nchunks);
-    thb_reduce_dim_noncontig<Mod, Red><<<grid, THB_RD_THREADS, 0, st>>>(out, in, rsize, rstride, nslices, chunk_len,
-                                                                       nchunks, init, mparam, scratch);
+    thb_reduce_dim_noncontig<Mod, Red><<<grid, THB_RD_THREADS, 0, st>>>(
+        out, in, rsize, rstride, nslices, chunk_len, nchunks, init, mparam, (typename Red::acc_t*)scratch);
     err = cudaGetLastError();
     if (err != cudaSuccess || nchunks == 1) return;
-    thb_reduce_dim_fold_chunks<Red><<<(unsigned)bx, THB_RD_THREADS, 0, st>>>(out, scratch, nslices, nchunks, init);
+    thb_reduce_dim_fold_chunks<Red><<<(unsigned)bx, THB_RD_THREADS, 0, st>>>(
+        out, (const typename Red::acc_t*)scratch, nslices, nchunks, init);
     err = cudaGetLastError();
   }
 };
@@ -169,7 +170,7 @@ struct FoldArgs {
   cudaError_t err = cudaSuccess;
   template <class Red>
   void operator()() {
-    thb_reduce_all_pass2<Red><<<1, 1024, 0, st>>>(partials, count, init, THB_FIN_NONE, 1.f, d_out);
+    thb_fold_floats<Red><<<1, 1024, 0, st>>>(partials, count, init, d_out);
     err = cudaGetLastError();
   }
 };
@@ -228,7 +229,8 @@ using namespace thb;
 
 extern "C" {
 
-size_t thb200_reduce_all_scratch_bytes(int64_t n) { return (size_t)reduce_all_blocks(n) * sizeof(float); }
+// one partial per pass-1 block; sums keep theirs in double
+size_t thb200_reduce_all_scratch_bytes(int64_t n) { return (size_t)reduce_all_blocks(n) * sizeof(double); }
 
 int thb200_reduce_all(void* stream, int modify, int reduce, const thb200_tensor* in, float init, float mod_param,
                       const float* mod_point, int fin, float fin_param, float* d_out, float* scratch,
@@ -281,7 +283,7 @@ size_t thb200_reduce_dim_scratch_bytes(const thb200_tensor* in, int dim) {
   if (reduce_dim_geometry(in, dim, &nslices, &rsize, &rstride)) return 0;
   if (rstride == 1 || nslices == 0) return 0;
   uint32_t chunks = pick_chunks(nslices, rsize);
-  return chunks > 1 ? (size_t)chunks * nslices * sizeof(float) : 0;
+  return chunks > 1 ? (size_t)chunks * nslices * sizeof(double) : 0;
 }
 
 int thb200_reduce_dim(void* stream, int modify, int reduce, const thb200_tensor* out, const thb200_tensor* in, int dim,
@@ -306,9 +308,9 @@ int thb200_reduce_dim(void* stream, int modify, int reduce, const thb200_tensor*
   a.init = init; a.mparam = mod_param; a.scratch = scratch;
   a.nchunks = rstride == 1 ? 1 : pick_chunks(nslices, rsize);
   a.chunk_len = (uint32_t)((rsize + a.nchunks - 1) / a.nchunks);
-  if (a.nchunks > 1 && (!scratch || scratch_bytes < (size_t)a.nchunks * nslices * sizeof(float)))
+  if (a.nchunks > 1 && (!scratch || scratch_bytes < (size_t)a.nchunks * nslices * sizeof(double)))
     return fail("reduceDim: scratch too small (%zu bytes, need %zu)", scratch_bytes,
-                (size_t)a.nchunks * nslices * sizeof(float));
+                (size_t)a.nchunks * nslices * sizeof(double));
   if (!dispatch_pair(modify, reduce, a)) return fail("reduceDim: unsupported modify/reduce pair (%d, %d)", modify, reduce);
   if (a.err != cudaSuccess) return fail_cuda(a.err, "reduceDim launch");
   return 0;

@@ -266,7 +266,7 @@ thb_apply_tile2d(ThbTile2d P, ThbScalars s) {
 // Whether an operator body reads *out before overwriting it: it does unless
 // "*out" occurs exactly once and is directly followed by a plain '='.
 // ---------------------------------------------------------------------------
-constexpr bool thb_body_reads_out(const char* s) {
+__host__ __device__ constexpr bool thb_body_reads_out(const char* s) {
   int count = 0;
   bool plainAssign = false;
   for (int i = 0; s[i]; ++i) {

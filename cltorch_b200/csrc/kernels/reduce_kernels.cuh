@@ -23,19 +23,26 @@ struct ModSqDev { static __device__ __forceinline__ float apply(float x, float, 
 // reduceOp strings: TensorAddOp, TensorMulOp, MinOp (fmin), MaxOp (fmax)
 // (src/lib/THClTensorMathPointwise.h:62-140), logicalall/any functors
 // "(int)*in1 && (int)*in2" (src/lib/THClTensorMath.cpp:444-460).
-struct RedAdd { static __device__ __forceinline__ float apply(float a, float b) { return a + b; } };
-struct RedMul { static __device__ __forceinline__ float apply(float a, float b) { return a * b; } };
-struct RedMin { static __device__ __forceinline__ float apply(float a, float b) { return fminf(a, b); } };
-struct RedMax { static __device__ __forceinline__ float apply(float a, float b) { return fmaxf(a, b); } };
-struct RedAnd { static __device__ __forceinline__ float apply(float a, float b) { return (float)((int)a && (int)b); } };
-struct RedOr { static __device__ __forceinline__ float apply(float a, float b) { return (float)((int)a || (int)b); } };
+//
+// Sums and products are accumulated in double and rounded to fp32 once, at the
+// very end: the reduction stays bound by HBM (one DADD per 4-byte element is a
+// fraction of the fp64 rate) and the result is within 1e-5 relative of a
+// double-precision evaluation even for zero-mean data, where an fp32 tree loses
+// digits to cancellation. min/max/and/or are exact in fp32.
+struct RedAdd { typedef double acc_t; static __device__ __forceinline__ double apply(double a, double b) { return a + b; } };
+struct RedMul { typedef double acc_t; static __device__ __forceinline__ double apply(double a, double b) { return a * b; } };
+struct RedMin { typedef float acc_t; static __device__ __forceinline__ float apply(float a, float b) { return fminf(a, b); } };
+struct RedMax { typedef float acc_t; static __device__ __forceinline__ float apply(float a, float b) { return fmaxf(a, b); } };
+struct RedAnd { typedef float acc_t; static __device__ __forceinline__ float apply(float a, float b) { return (float)((int)a && (int)b); } };
+struct RedOr { typedef float acc_t; static __device__ __forceinline__ float apply(float a, float b) { return (float)((int)a || (int)b); } };
 
 #define THB_FULL_MASK 0xffffffffu
 
 // Folds the values of the calling block's threads in a fixed order; the result
 // is valid in thread 0. `smem` holds one float per warp.
 template <class Red>
-__device__ __forceinline__ float thb_block_fold(float v, float init, float* smem) {
+__device__ __forceinline__ typename Red::acc_t thb_block_fold(typename Red::acc_t v, typename Red::acc_t init,
+                                                              typename Red::acc_t* smem) {
 #pragma unroll
   for (int off = 16; off > 0; off >>= 1) v = Red::apply(v, __shfl_down_sync(THB_FULL_MASK, v, off));
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -59,12 +66,13 @@ __device__ __forceinline__ float thb_block_fold(float v, float init, float* smem
 template <class Mod, class Red>
 __global__ void __launch_bounds__(THB_RA_THREADS)
 thb_reduce_all_pass1_contig(const float* in, thb_i64 n, int head, float init, float mparam,
-                            const float* mpoint, float* partials) {
-  __shared__ float smem[32];
+                            const float* mpoint, typename Red::acc_t* partials) {
+  typedef typename Red::acc_t acc_t;
+  __shared__ acc_t smem[32];
   const float mp = mpoint ? *mpoint : 0.f;
   const thb_i64 nvec = (n - head) >> 2;
   const float4* in4 = reinterpret_cast<const float4*>(in + head);
-  float acc[4] = {init, init, init, init};
+  acc_t acc[4] = {(acc_t)init, (acc_t)init, (acc_t)init, (acc_t)init};
 
   const thb_i64 step = (thb_i64)gridDim.x * (THB_RA_THREADS * THB_RA_UNROLL);
   for (thb_i64 base = (thb_i64)blockIdx.x * (THB_RA_THREADS * THB_RA_UNROLL) + threadIdx.x; base < nvec;
@@ -93,8 +101,8 @@ thb_reduce_all_pass1_contig(const float* in, thb_i64 n, int head, float init, fl
     if (t < head) acc[0] = Red::apply(acc[0], Mod::apply(in[t], mparam, mp));
     else if (t - head < ntail) acc[0] = Red::apply(acc[0], Mod::apply(in[tail0 + (t - head)], mparam, mp));
   }
-  float r = Red::apply(Red::apply(acc[0], acc[1]), Red::apply(acc[2], acc[3]));
-  r = thb_block_fold<Red>(r, init, smem);
+  acc_t r = Red::apply(Red::apply(acc[0], acc[1]), Red::apply(acc[2], acc[3]));
+  r = thb_block_fold<Red>(r, (acc_t)init, smem);
   if (threadIdx.x == 0) partials[blockIdx.x] = r;
 }
 
@@ -102,10 +110,11 @@ thb_reduce_all_pass1_contig(const float* in, thb_i64 n, int head, float init, fl
 template <class Mod, class Red>
 __global__ void __launch_bounds__(THB_RA_THREADS)
 thb_reduce_all_pass1_strided(ThbLayout L, thb_u64 n, float init, float mparam, const float* mpoint,
-                             float* partials) {
-  __shared__ float smem[32];
+                             typename Red::acc_t* partials) {
+  typedef typename Red::acc_t acc_t;
+  __shared__ acc_t smem[32];
   const float mp = mpoint ? *mpoint : 0.f;
-  float acc = init;
+  acc_t acc = (acc_t)init;
   const thb_u64 step = (thb_u64)gridDim.x * (THB_RA_THREADS * THB_RA_UNROLL);
   for (thb_u64 base = (thb_u64)blockIdx.x * (THB_RA_THREADS * THB_RA_UNROLL) + threadIdx.x; base < n;
        base += step) {
@@ -121,7 +130,7 @@ thb_reduce_all_pass1_strided(ThbLayout L, thb_u64 n, float init, float mparam, c
       if (i < n) acc = Red::apply(acc, Mod::apply(v[u], mparam, mp));
     }
   }
-  acc = thb_block_fold<Red>(acc, init, smem);
+  acc = thb_block_fold<Red>(acc, (acc_t)init, smem);
   if (threadIdx.x == 0) partials[blockIdx.x] = acc;
 }
 
@@ -132,16 +141,29 @@ thb_reduce_all_pass1_strided(ThbLayout L, thb_u64 n, float init, float mparam, c
 // Pass 2: one block folds the pass-1 partials and writes the finished scalar.
 template <class Red>
 __global__ void __launch_bounds__(1024)
-thb_reduce_all_pass2(const float* partials, int count, float init, int fin, float fparam, float* out) {
-  __shared__ float smem[32];
-  float r = init;
+thb_reduce_all_pass2(const typename Red::acc_t* partials, int count, float init, int fin, float fparam, float* out) {
+  typedef typename Red::acc_t acc_t;
+  __shared__ acc_t smem[32];
+  acc_t r = (acc_t)init;
   for (int i = threadIdx.x; i < count; i += blockDim.x) r = Red::apply(r, partials[i]);
-  r = thb_block_fold<Red>(r, init, smem);
+  r = thb_block_fold<Red>(r, (acc_t)init, smem);
   if (threadIdx.x == 0) {
-    if (fin == THB_FIN_DIV) r = r / fparam;
-    else if (fin == THB_FIN_DIV_SQRT) r = sqrtf(r / fparam);
-    out[0] = r;
+    if (fin == THB_FIN_DIV) r = r / (acc_t)fparam;
+    else if (fin == THB_FIN_DIV_SQRT) r = sqrt(r / (acc_t)fparam);
+    out[0] = (float)r;
   }
+}
+
+// The same fold for fp32 inputs (per-GPU results that already are point tensors).
+template <class Red>
+__global__ void __launch_bounds__(1024)
+thb_fold_floats(const float* values, int count, float init, float* out) {
+  typedef typename Red::acc_t acc_t;
+  __shared__ acc_t smem[32];
+  acc_t r = (acc_t)init;
+  for (int i = threadIdx.x; i < count; i += blockDim.x) r = Red::apply(r, (acc_t)values[i]);
+  r = thb_block_fold<Red>(r, (acc_t)init, smem);
+  if (threadIdx.x == 0) out[0] = (float)r;
 }
 
 // ---- reduce along one dimension --------------------------------------------
@@ -155,10 +177,11 @@ template <class Mod, class Red>
 __global__ void __launch_bounds__(THB_RD_THREADS)
 thb_reduce_dim_contig_block(ThbLayout out, ThbLayout in, thb_u32 rsize, thb_u32 nslices, float init,
                             float mparam) {
-  __shared__ float smem[32];
+  typedef typename Red::acc_t acc_t;
+  __shared__ acc_t smem[32];
   for (thb_u32 s = blockIdx.x; s < nslices; s += gridDim.x) {
     const float* p = in.data + thb_offset(in, s);
-    float acc[4] = {init, init, init, init};
+    acc_t acc[4] = {(acc_t)init, (acc_t)init, (acc_t)init, (acc_t)init};
     if ((((thb_u64)p) & 15) == 0 && (rsize & 3) == 0) {
       const float4* p4 = reinterpret_cast<const float4*>(p);
       const thb_u32 nvec = rsize >> 2;
@@ -180,9 +203,9 @@ thb_reduce_dim_contig_block(ThbLayout out, ThbLayout in, thb_u32 rsize, thb_u32 
       for (thb_u32 i = threadIdx.x; i < rsize; i += THB_RD_THREADS)
         acc[0] = Red::apply(acc[0], Mod::apply(p[i], mparam, 0.f));
     }
-    float r = Red::apply(Red::apply(acc[0], acc[1]), Red::apply(acc[2], acc[3]));
-    r = thb_block_fold<Red>(r, init, smem);
-    if (threadIdx.x == 0) out.data[thb_offset(out, s)] = r;
+    acc_t r = Red::apply(Red::apply(acc[0], acc[1]), Red::apply(acc[2], acc[3]));
+    r = thb_block_fold<Red>(r, (acc_t)init, smem);
+    if (threadIdx.x == 0) out.data[thb_offset(out, s)] = (float)r;
     __syncthreads();
   }
 }
@@ -192,13 +215,14 @@ template <class Mod, class Red>
 __global__ void __launch_bounds__(THB_RD_THREADS)
 thb_reduce_dim_contig_warp(ThbLayout out, ThbLayout in, thb_u32 rsize, thb_u32 nslices, float init,
                            float mparam) {
+  typedef typename Red::acc_t acc_t;
   const int lane = threadIdx.x & 31;
   const thb_u32 warps_per_block = THB_RD_THREADS / 32;
   for (thb_u64 s64 = (thb_u64)blockIdx.x * warps_per_block + (threadIdx.x >> 5); s64 < nslices;
        s64 += (thb_u64)gridDim.x * warps_per_block) {
     const thb_u32 s = (thb_u32)s64;
     const float* p = in.data + thb_offset(in, s);
-    float acc[4] = {init, init, init, init};
+    acc_t acc[4] = {(acc_t)init, (acc_t)init, (acc_t)init, (acc_t)init};
     if ((((thb_u64)p) & 15) == 0 && (rsize & 3) == 0) {
       const float4* p4 = reinterpret_cast<const float4*>(p);
       const thb_u32 nvec = rsize >> 2;
@@ -219,10 +243,10 @@ thb_reduce_dim_contig_warp(ThbLayout out, ThbLayout in, thb_u32 rsize, thb_u32 n
     } else {
       for (thb_u32 i = lane; i < rsize; i += 32) acc[0] = Red::apply(acc[0], Mod::apply(p[i], mparam, 0.f));
     }
-    float r = Red::apply(Red::apply(acc[0], acc[1]), Red::apply(acc[2], acc[3]));
+    acc_t r = Red::apply(Red::apply(acc[0], acc[1]), Red::apply(acc[2], acc[3]));
 #pragma unroll
     for (int off = 16; off > 0; off >>= 1) r = Red::apply(r, __shfl_down_sync(THB_FULL_MASK, r, off));
-    if (lane == 0) out.data[thb_offset(out, s)] = r;
+    if (lane == 0) out.data[thb_offset(out, s)] = (float)r;
   }
 }
 
@@ -233,7 +257,9 @@ thb_reduce_dim_contig_warp(ThbLayout out, ThbLayout in, thb_u32 rsize, thb_u32 n
 template <class Mod, class Red>
 __global__ void __launch_bounds__(THB_RD_THREADS)
 thb_reduce_dim_noncontig(ThbLayout out, ThbLayout in, thb_u32 rsize, thb_u32 rstride, thb_u32 nslices,
-                         thb_u32 chunk_len, thb_u32 nchunks, float init, float mparam, float* partial) {
+                         thb_u32 chunk_len, thb_u32 nchunks, float init, float mparam,
+                         typename Red::acc_t* partial) {
+  typedef typename Red::acc_t acc_t;
   const thb_u32 chunk = blockIdx.y;
   const thb_u32 r0 = chunk * chunk_len;
   const thb_u32 r1 = min(rsize, r0 + chunk_len);
@@ -241,7 +267,7 @@ thb_reduce_dim_noncontig(ThbLayout out, ThbLayout in, thb_u32 rsize, thb_u32 rst
        s64 += (thb_u64)gridDim.x * THB_RD_THREADS) {
     const thb_u32 s = (thb_u32)s64;
     const float* p = in.data + thb_offset(in, s);
-    float acc = init;
+    acc_t acc = (acc_t)init;
     thb_u32 r = r0;
     for (; r + 8 <= r1; r += 8) {
       float v[8];
@@ -251,20 +277,22 @@ thb_reduce_dim_noncontig(ThbLayout out, ThbLayout in, thb_u32 rsize, thb_u32 rst
       for (int u = 0; u < 8; ++u) acc = Red::apply(acc, Mod::apply(v[u], mparam, 0.f));
     }
     for (; r < r1; ++r) acc = Red::apply(acc, Mod::apply(p[(thb_u64)r * rstride], mparam, 0.f));
-    if (nchunks == 1) out.data[thb_offset(out, s)] = acc;
+    if (nchunks == 1) out.data[thb_offset(out, s)] = (float)acc;
     else partial[(thb_u64)chunk * nslices + s] = acc;
   }
 }
 
 template <class Red>
 __global__ void __launch_bounds__(THB_RD_THREADS)
-thb_reduce_dim_fold_chunks(ThbLayout out, const float* partial, thb_u32 nslices, thb_u32 nchunks, float init) {
+thb_reduce_dim_fold_chunks(ThbLayout out, const typename Red::acc_t* partial, thb_u32 nslices, thb_u32 nchunks,
+                           float init) {
+  typedef typename Red::acc_t acc_t;
   for (thb_u64 s64 = (thb_u64)blockIdx.x * THB_RD_THREADS + threadIdx.x; s64 < nslices;
        s64 += (thb_u64)gridDim.x * THB_RD_THREADS) {
     const thb_u32 s = (thb_u32)s64;
-    float acc = init;
+    acc_t acc = (acc_t)init;
     for (thb_u32 c = 0; c < nchunks; ++c) acc = Red::apply(acc, partial[(thb_u64)c * nslices + s]);
-    out.data[thb_offset(out, s)] = acc;
+    out.data[thb_offset(out, s)] = (float)acc;
   }
 }
 

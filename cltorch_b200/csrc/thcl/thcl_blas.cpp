@@ -91,6 +91,10 @@ void gemm_front(THClState* state, THClTensor* r_, float beta, THClTensor* t, flo
                        THClTensor_data(state, ob.t), ob.ld, beta, THClTensor_data(state, r), ldc, batch,
                        batched ? oa.t->stride[0] : 0, batched ? ob.t->stride[0] : 0, batched ? r->stride[0] : 0, ws,
                        ctx->gemm_ws_bytes);
+  if (!rc) {
+    ctx->gemm_pending = true;
+    ctx->gemm_shape[0] = m; ctx->gemm_shape[1] = n; ctx->gemm_shape[2] = k; ctx->gemm_shape[3] = batch;
+  }
   std::string err = rc ? thb200_last_error() : "";
   if (oa.owned) THClTensor_free(state, oa.owned);
   if (ob.owned) THClTensor_free(state, ob.owned);

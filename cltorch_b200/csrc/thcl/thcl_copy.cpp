@@ -58,13 +58,13 @@ void upload_linear(THClState* state, THClTensor* self, const float* host, long n
   if (state->trace) printf("THCl: host -> device %ld floats\n", n);
   if (THClTensor_isContiguous(state, self)) {
     check_cuda(cudaMemcpyAsync(THClTensor_data(state, self), host, (size_t)n * sizeof(float), cudaMemcpyHostToDevice, ctx->stream), "cudaMemcpyAsync");
-    check_cuda(cudaStreamSynchronize(ctx->stream), "cudaStreamSynchronize");
+    sync_stream(ctx);
     return;
   }
   THClTensor* tmp = THClTensor_newWithSize1d(state, self->device, n);
   check_cuda(cudaMemcpyAsync(THClTensor_data(state, tmp), host, (size_t)n * sizeof(float), cudaMemcpyHostToDevice, ctx->stream), "cudaMemcpyAsync");
   THClTensor_copy(state, self, tmp);
-  check_cuda(cudaStreamSynchronize(ctx->stream), "cudaStreamSynchronize");
+  sync_stream(ctx);
   THClTensor_free(state, tmp);
 }
 
@@ -75,7 +75,7 @@ void download_linear(THClState* state, THClTensor* src, float* host, long n) {
   if (state->trace) printf("THCl: device -> host %ld floats\n", n);
   THClTensor* c = THClTensor_newContiguous(state, src);
   check_cuda(cudaMemcpyAsync(host, THClTensor_data(state, c), (size_t)n * sizeof(float), cudaMemcpyDeviceToHost, ctx->stream), "cudaMemcpyAsync");
-  check_cuda(cudaStreamSynchronize(ctx->stream), "cudaStreamSynchronize");
+  sync_stream(ctx);
   THClTensor_free(state, c);
 }
 

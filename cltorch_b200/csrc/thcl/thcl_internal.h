@@ -18,6 +18,8 @@ struct THClDeviceContext {
   size_t scratch_bytes = 0;
   void* gemm_ws = nullptr;        // split operands of the GEMM
   size_t gemm_ws_bytes = 0;
+  bool gemm_pending = false;      // a GEMM was enqueued and its status word not read yet
+  long gemm_shape[4] = {0, 0, 0, 0};
   THClScratchSpace scratch_space{nullptr, nullptr};
 };
 
@@ -65,6 +67,10 @@ void use_device(int device);                               // cudaSetDevice if n
 float* ensure_scratch(THClDeviceContext* ctx, size_t bytes);
 void* ensure_gemm_ws(THClDeviceContext* ctx, size_t bytes);
 void after_launch(THClState* state, THClDeviceContext* ctx);  // addFinish
+// cudaStreamSynchronize, then the status word of the last GEMM if one is pending: a
+// GEMM whose bounded waits gave up surfaces here as an error instead of silently
+// leaving an undefined result.
+void sync_stream(THClDeviceContext* ctx);
 
 // View of a tensor for the thin ABI; keeps the int64 copies of size/stride alive.
 struct View {

@@ -148,7 +148,7 @@ static void reduce_all(THClState* state, THClTensor* src, int mod, int red, floa
 static float read_result(THClState* state, THClDeviceContext* ctx, int slot) {
   if (state->trace) printf("THCl: device -> host 1 float (reduction result)\n");
   check_cuda(cudaMemcpyAsync(ctx->result_host + slot, ctx->result + slot, sizeof(float), cudaMemcpyDeviceToHost, ctx->stream), "cudaMemcpyAsync");
-  check_cuda(cudaStreamSynchronize(ctx->stream), "cudaStreamSynchronize");
+  sync_stream(ctx);
   return ctx->result_host[slot];
 }
 

@@ -115,8 +115,18 @@ void* ensure_gemm_ws(THClDeviceContext* ctx, size_t bytes) {
   return ctx->gemm_ws;
 }
 
+void sync_stream(THClDeviceContext* ctx) {
+  check_cuda(cudaStreamSynchronize(ctx->stream), "cudaStreamSynchronize");
+  if (ctx->gemm_pending) {
+    ctx->gemm_pending = false;
+    int st = thb200_gemm_status(ctx->stream, ctx->gemm_shape[0], ctx->gemm_shape[1], ctx->gemm_shape[2],
+                                ctx->gemm_shape[3], ctx->gemm_ws);
+    if (st != 0) raise("GEMM kernel did not complete: a bounded wait gave up (status %d); the result is undefined", st);
+  }
+}
+
 void after_launch(THClState* state, THClDeviceContext* ctx) {
-  if (state->addFinish) check_cuda(cudaStreamSynchronize(ctx->stream), "cudaStreamSynchronize (addFinish)");
+  if (state->addFinish) sync_stream(ctx);
 }
 
 }  // namespace thcl
@@ -204,7 +214,7 @@ void THClSynchronize(THClState* state) {
   THCL_BEGIN
   THClDeviceContext* ctx = context(state, state->currentDevice);
   use_device(ctx->device);
-  check_cuda(cudaStreamSynchronize(ctx->stream), "cudaStreamSynchronize");
+  sync_stream(ctx);
   THCL_END_VOID
 }
 

@@ -91,7 +91,7 @@ static THClStorage* new_with_values(THClState* state, int device, const float* v
   THClStorage* s = THClStorage_newWithSize(state, device, n);
   THClDeviceContext* ctx = context(state, device);
   check_cuda(cudaMemcpyAsync(s->wrapper, v, n * sizeof(float), cudaMemcpyHostToDevice, ctx->stream), "cudaMemcpyAsync");
-  check_cuda(cudaStreamSynchronize(ctx->stream), "cudaStreamSynchronize");  // `v` is on the caller's stack
+  sync_stream(ctx);  // `v` is on the caller's stack
   return s;
 }
 
@@ -126,7 +126,7 @@ THClStorage* THClStorage_newWithData(THClState* state, int device, float* data, 
   if (size > 0) {
     THClDeviceContext* ctx = context(state, device);
     check_cuda(cudaMemcpyAsync(s->wrapper, data, (size_t)size * sizeof(float), cudaMemcpyHostToDevice, ctx->stream), "cudaMemcpyAsync");
-    check_cuda(cudaStreamSynchronize(ctx->stream), "cudaStreamSynchronize");
+    sync_stream(ctx);
   }
   free(data);
   return s;
@@ -201,7 +201,7 @@ float THClStorage_get(THClState* state, const THClStorage* s, long index) {
   THClDeviceContext* ctx = context(state, s->device);
   use_device(s->device);
   check_cuda(cudaMemcpyAsync(ctx->result_host + 32, s->wrapper + index, sizeof(float), cudaMemcpyDeviceToHost, ctx->stream), "cudaMemcpyAsync");
-  check_cuda(cudaStreamSynchronize(ctx->stream), "cudaStreamSynchronize");
+  sync_stream(ctx);
   return ctx->result_host[32];
   THCL_END(0.f)
 }
@@ -213,7 +213,7 @@ void THClStorage_rawCopy(THClState* state, THClStorage* self, float* src) {
   use_device(self->device);
   if (state->trace) printf("THCl: host -> device %ld floats\n", self->size);
   check_cuda(cudaMemcpyAsync(self->wrapper, src, (size_t)self->size * sizeof(float), cudaMemcpyHostToDevice, ctx->stream), "cudaMemcpyAsync");
-  check_cuda(cudaStreamSynchronize(ctx->stream), "cudaStreamSynchronize");
+  sync_stream(ctx);
   THCL_END_VOID
 }
 
@@ -244,7 +244,7 @@ void THFloatStorage_copyCl(THClState* state, struct THFloatStorage* self, struct
   use_device(src->device);
   if (state->trace) printf("THCl: device -> host %ld floats\n", src->size);
   check_cuda(cudaMemcpyAsync(self->data, src->wrapper, (size_t)src->size * sizeof(float), cudaMemcpyDeviceToHost, ctx->stream), "cudaMemcpyAsync");
-  check_cuda(cudaStreamSynchronize(ctx->stream), "cudaStreamSynchronize");
+  sync_stream(ctx);
   THCL_END_VOID
 }
 

@@ -90,13 +90,15 @@ enum thb200_reduce { THB200_RED_ADD = 0, THB200_RED_MUL = 1, THB200_RED_MIN = 2,
 enum thb200_final { THB200_FIN_NONE = 0, THB200_FIN_DIV = 1, THB200_FIN_DIV_SQRT = 2 };
 
 /* Bytes of scratch (global memory beyond input and output) that
- * thb200_reduce_all needs for `n` elements: one float per pass-1 block. */
+ * thb200_reduce_all needs for `n` elements: one 8-byte partial per pass-1 block
+ * (at most 1184 blocks). Must be 8-byte aligned. */
 size_t thb200_reduce_all_scratch_bytes(int64_t n);
 
 /* THClTensor_reduceAll, src/lib/THClReduceAll.cpp:276-316 with kernels
  * src/lib/THClReduceAll.cl:24-100: r = init; r = reduce(r, modify(e)) over all
  * elements; *d_out = finalise(r). Two launches in a fixed order (no atomics):
- * pass 1 writes one partial per block into `scratch`, pass 2 folds them.
+ * pass 1 writes one partial per block into `scratch`, pass 2 folds them. Sums
+ * and products accumulate in double and round to fp32 once at the end.
  * `mod_param` is the exponent of ABSPOW; `mod_point` the device-resident mean of
  * SQDEV; `fin_param` the divisor of FIN_DIV / FIN_DIV_SQRT. d_out is a device
  * pointer: the result never visits the host (point tensors, README.md:88-138). */
