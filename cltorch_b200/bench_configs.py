@@ -162,9 +162,33 @@ def c4(T):
            flops=2.0 * 64 * 1024 * 1024 * 128, setup=lambda: C.zero())
 
 
+def c4small(T):
+    """One mid-sized addmm (2048 x 2048 x 4096): the case used for profiler captures of the GEMM kernels."""
+    cl = T.cl
+    g = np.random.Generator(np.random.PCG64(3))
+    M, N, K = 2048, 2048, 4096
+    lim = 1.0 / np.sqrt(K)
+    A, B = cl.ClTensor(_uniform(g, (M, K), -lim, lim)), cl.ClTensor(_uniform(g, (K, N), -lim, lim))
+    C = cl.ClTensor(M, N).zero()
+    T.time(f"addmm {M}x{N}x{K}", lambda: C.addmm(1.0, C, 1.0, A, B), flops=2.0 * M * N * K, setup=lambda: C.zero())
+
+
+def c2small(T):
+    """Transpose and column-narrowed adds on 4096 x 4096 (profiler captures of the strided kernels)."""
+    cl = T.cl
+    n = 4096
+    g = np.random.Generator(np.random.PCG64(1))
+    A, B = (cl.ClTensor(_uniform(g, (n, n), -1, 1)) for _ in range(2))
+    out = cl.ClTensor(n, n)
+    T.time("add contiguous = transpose + transpose", lambda: out.add(A.t(), B.t()), 12 * n * n)
+    va, vb = A.narrow(2, 17, 2000), B.narrow(2, 17, 2000)
+    out2 = cl.ClTensor().resizeAs(va)
+    T.time("add narrow-columns", lambda: out2.add(va, vb), 12 * n * 2000)
+
+
 def run(workload: str, steps: int, warmup: int) -> None:
     T = Timer(steps, warmup)
-    {"c1": c1, "c2": c2, "c3": c3, "c4": c4}[workload](T)
+    {"c1": c1, "c2": c2, "c3": c3, "c4": c4, "c4small": c4small, "c2small": c2small}[workload](T)
     T.cl.synchronize()
     print(json.dumps({"workload": workload, "n_gpus": 1, "steps": steps, "warmup": warmup, "dtype": "f32",
                       "data": "synthetic", "hbm_peak_gbs_measured": T.peak, "l2_flush": "512 MiB fill between iterations",

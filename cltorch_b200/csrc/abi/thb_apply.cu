@@ -83,7 +83,7 @@ int launch_apply(const ApplyKernels& k, cudaStream_t st, int nt, const thb200_te
     if (!can_use_32bit(t[i].ndim, t[i].size, t[i].stride))
       return fail("apply: tensor %d needs 64-bit index math on a non-contiguous layout: not implemented", i + 1);
 
-  // 2-D tile path: at least one operand is column-major-like and all agree on R x C.
+  // 2-D paths: every operand is the same R x C matrix (a contiguous one counts as R x C).
   {
     int64_t R = 0, C = 0;
     bool ok = true, any_col = false;
@@ -92,6 +92,39 @@ int launch_apply(const ApplyKernels& k, cudaStream_t st, int nt, const thb200_te
         if (R == 0) { R = c[i].size[0]; C = c[i].size[1]; }
         else if (R != c[i].size[0] || C != c[i].size[1]) ok = false;
       } else if (c[i].dims != 1) ok = false;
+    // rows path: unit stride along C everywhere, float4 along the rows
+    if (ok && R > 0 && R * C == n && (C & 3) == 0 && k.rows2d) {
+      ThbRows2d Q;
+      memset(&Q, 0, sizeof Q);
+      bool rows_ok = true;
+      for (int i = 0; i < nt && rows_ok; ++i) {
+        Q.data[i] = t[i].data;
+        if (c[i].dims == 1) {
+          rows_ok = c[i].stride[0] == 1;
+          Q.row_stride[i] = C;
+        } else {
+          rows_ok = c[i].stride[1] == 1 && (c[i].stride[0] & 3) == 0;
+          Q.row_stride[i] = c[i].stride[0];
+        }
+        rows_ok = rows_ok && ((uintptr_t)t[i].data & 15) == 0;
+      }
+      const uint64_t nvec = (uint64_t)R * (uint64_t)(C >> 2);
+      if (rows_ok && nvec < (uint64_t(1) << 32)) {
+        if (plan_out) *plan_out = PLAN_ROWS2D;
+        if (dry_run) return 0;
+        Q.cvec = (uint32_t)(C >> 2);
+        fastdiv_constants(Q.cvec, &Q.magic, &Q.shift);
+        Q.nvec = nvec;
+        uint64_t per_block = THB_CONTIG_THREADS * THB_CONTIG_UNROLL;
+        uint64_t blocks = (nvec + per_block - 1) / per_block;
+        uint64_t cap = (uint64_t)sms * 32;
+        if (blocks > cap) blocks = cap;
+        void* args[] = {&Q, &s};
+        THB_CUDA(cudaLaunchKernel(k.rows2d, dim3((unsigned)blocks), dim3(THB_CONTIG_THREADS), args, 0, st));
+        return 0;
+      }
+    }
+    // tile path: at least one operand is column-major-like
     if (ok && R > 0 && R * C == n && k.tile2d) {
       ThbTile2d P;
       memset(&P, 0, sizeof P);
@@ -159,6 +192,7 @@ int thb200_apply_plan(int ntensors, const thb200_tensor* t) {
   thb::ApplyKernels k;
   k.nt = ntensors;
   k.tile2d = (const void*)1;  // eligibility only; nothing is launched
+  k.rows2d = (const void*)1;
   int plan = 0;
   if (thb::launch_apply(k, nullptr, ntensors, t, 0, 0, nullptr, nullptr, true, &plan)) return -1;
   return plan;

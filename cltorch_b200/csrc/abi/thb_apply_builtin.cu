@@ -1,4 +1,4 @@
-// Instantiates the three apply kernels for every built-in operator of
+// Instantiates the four apply kernels for every built-in operator of
 // apply_ops.def. The file is compiled THB_NPARTS times with -DTHB_PART=k; part k
 // instantiates the operators whose code is congruent to k, so the parts build in
 // parallel. Part 0 also owns the table and the lookup functions.
@@ -42,6 +42,7 @@ static void register_part(ApplyKernels* table) {
     k.contig = (const void*)&thb_apply_contig<Op_##NAME, NT>;                        \
     k.strided = (const void*)&thb_apply_strided<Op_##NAME, NT>;                      \
     k.tile2d = (const void*)&thb_apply_tile2d<Op_##NAME, NT>;                        \
+    k.rows2d = (const void*)&thb_apply_rows2d<Op_##NAME, NT>;                        \
     k.nt = NT;                                                                       \
     k.reads_out = Op_##NAME::kReadsOut;                                              \
     k.name = #NAME;                                                                  \

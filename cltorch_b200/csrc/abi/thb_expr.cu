@@ -5,7 +5,7 @@
 // compiles it on first use, caching by a key made of the operand count and the
 // string (src/lib/THClApply.cpp:54-112). Here the text of apply_kernels.cuh is
 // embedded in the library, the body becomes the `apply` member of a struct, and
-// the three kernel templates are instantiated for it in one NVRTC program; the
+// the four kernel templates are instantiated for it in one NVRTC program; the
 // cubin is loaded through the CUDA runtime's library API and cached for the
 // process by (operand count, body).
 #include "thb_internal.h"
@@ -28,6 +28,7 @@ static const char* kKernelSource =
 // (math_policy.cuh); expressions get the same policy as the built-in operators.
 static const char* kPolicyMacros =
     "#define exp(x) thb_exp(x)\n"
+    "#define tanh(x) thb_tanh(x)\n"
     "#define tan(x) thb_tan(x)\n"
     "#define sinh(x) thb_sinh(x)\n"
     "#define atan2(y, x) thb_atan2(y, x)\n"
@@ -75,8 +76,8 @@ int expr_kernels(int nt, const std::string& body, const ApplyKernels** out) {
   nvrtcResult r = nvrtcCreateProgram(&prog, src.c_str(), "thb_user_expr.cu", 0, nullptr, nullptr);
   if (r != NVRTC_SUCCESS) return fail_nvrtc(r, "nvrtcCreateProgram");
   const std::string nts = std::to_string(nt);
-  const std::string names[3] = {"thb_apply_contig<UserOp, " + nts + ">", "thb_apply_strided<UserOp, " + nts + ">",
-                                "thb_apply_tile2d<UserOp, " + nts + ">"};
+  const std::string names[4] = {"thb_apply_contig<UserOp, " + nts + ">", "thb_apply_strided<UserOp, " + nts + ">",
+                                "thb_apply_tile2d<UserOp, " + nts + ">", "thb_apply_rows2d<UserOp, " + nts + ">"};
   for (const std::string& n : names) {
     r = nvrtcAddNameExpression(prog, n.c_str());
     if (r != NVRTC_SUCCESS) { nvrtcDestroyProgram(&prog); return fail_nvrtc(r, "nvrtcAddNameExpression"); }
@@ -99,8 +100,8 @@ int expr_kernels(int nt, const std::string& body, const ApplyKernels** out) {
   std::vector<char> cubin(n);
   r = nvrtcGetCUBIN(prog, cubin.data());
   if (r != NVRTC_SUCCESS) { nvrtcDestroyProgram(&prog); return fail_nvrtc(r, "nvrtcGetCUBIN"); }
-  std::string lowered[3];
-  for (int i = 0; i < 3; ++i) {
+  std::string lowered[4];
+  for (int i = 0; i < 4; ++i) {
     const char* ln = nullptr;
     r = nvrtcGetLoweredName(prog, names[i].c_str(), &ln);
     if (r != NVRTC_SUCCESS || !ln) { nvrtcDestroyProgram(&prog); return fail_nvrtc(r, "nvrtcGetLoweredName"); }
@@ -112,11 +113,12 @@ int expr_kernels(int nt, const std::string& body, const ApplyKernels** out) {
   e->body = body;
   e->name = "expr";
   THB_CUDA(cudaLibraryLoadData(&e->lib, cubin.data(), nullptr, nullptr, 0, nullptr, nullptr, 0));
-  cudaKernel_t kern[3];
-  for (int i = 0; i < 3; ++i) THB_CUDA(cudaLibraryGetKernel(&kern[i], e->lib, lowered[i].c_str()));
+  cudaKernel_t kern[4];
+  for (int i = 0; i < 4; ++i) THB_CUDA(cudaLibraryGetKernel(&kern[i], e->lib, lowered[i].c_str()));
   e->k.contig = (const void*)kern[0];
   e->k.strided = (const void*)kern[1];
   e->k.tile2d = (const void*)kern[2];
+  e->k.rows2d = (const void*)kern[3];
   e->k.nt = nt;
   e->k.reads_out = thb_body_reads_out(body.c_str());
   e->k.name = e->name.c_str();

@@ -3,6 +3,7 @@
 #include "../kernels/gemm_kernels.cuh"
 
 #include <cudaTypedefs.h>
+#include <cstdlib>
 #include <mutex>
 
 namespace thb {
@@ -23,16 +24,20 @@ static PFN_cuTensorMapEncodeTiled_v12000 tensor_map_encoder() {
   return fn;
 }
 
-// [parts = 2 * batch][rows][Kp] fp32, box 32 x box_rows x 1, 128-byte swizzle.
-static int make_operand_map(CUtensorMap* map, const float* base, int64_t rows, int64_t Kp, int64_t parts, int box_rows) {
+static const int kKPad = 32;  // K is padded to this in the split operands (a multiple of every BK)
+
+// [parts = 2 * batch][rows][Kp] fp32, box bk x box_rows x 1, swizzle span = one box row.
+static int make_operand_map(CUtensorMap* map, const float* base, int64_t rows, int64_t Kp, int64_t parts, int box_rows,
+                            int bk) {
   auto enc = tensor_map_encoder();
   if (!enc) return fail("gemm: cuTensorMapEncodeTiled is not available from this driver");
   cuuint64_t dims[3] = {(cuuint64_t)Kp, (cuuint64_t)rows, (cuuint64_t)parts};
   cuuint64_t strides[2] = {(cuuint64_t)Kp * 4, (cuuint64_t)Kp * 4 * (cuuint64_t)rows};
-  cuuint32_t box[3] = {THB_GEMM_BK, (cuuint32_t)box_rows, 1};
+  cuuint32_t box[3] = {(cuuint32_t)bk, (cuuint32_t)box_rows, 1};
   cuuint32_t estr[3] = {1, 1, 1};
   CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, (void*)base, dims, strides, box, estr,
-                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                   CU_TENSOR_MAP_INTERLEAVE_NONE, bk == 32 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B,
+                   CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) return fail("gemm: cuTensorMapEncodeTiled failed with %d", (int)r);
   return 0;
@@ -46,7 +51,7 @@ struct Workspace {
 };
 
 static Workspace carve(void* ws, int64_t m, int64_t n, int64_t k, int64_t batch) {
-  const int64_t Kp = round_up(k, THB_GEMM_BK);
+  const int64_t Kp = round_up(k, kKPad);
   Workspace w;
   ws = (void*)(((uintptr_t)ws + 1023) & ~(uintptr_t)1023);  // TMA and the swizzle want 1024-byte aligned bases
   size_t a_bytes = (size_t)round_up(batch * 2 * m * Kp * 4, 1024);
@@ -86,7 +91,7 @@ int thb200_gemm(void* stream, char transa, char transb, int64_t m, int64_t n, in
   if (!workspace || workspace_bytes < w.bytes)
     return fail("gemm: workspace too small (%zu bytes, need %zu)", workspace_bytes, w.bytes);
 
-  const int64_t Kp = round_up(k > 0 ? k : 1, THB_GEMM_BK);
+  const int64_t Kp = round_up(k > 0 ? k : 1, kKPad);
   // op(A)(i, kk): column-major A, 'n': a[i + kk*lda] (unit stride along i), 't': a[kk + i*lda]
   {
     dim3 grid((unsigned)(Kp / 32), (unsigned)((m + 31) / 32), (unsigned)batch);
@@ -103,11 +108,15 @@ int thb200_gemm(void* stream, char transa, char transb, int64_t m, int64_t n, in
   }
   THB_CUDA(cudaMemsetAsync(w.status, 0, sizeof(int), st));
 
+  // k-block depth: 32 floats (128-byte swizzle, 2-stage ring) or 16 floats (64-byte swizzle,
+  // 4-stage ring: more loads in flight). THB200_GEMM_BK overrides the default for experiments.
+  static const int bk = [] {
+    const char* e = getenv("THB200_GEMM_BK");
+    return (e && atoi(e) == 32) ? 32 : 16;
+  }();
   CUtensorMap map_a, map_b;
-  if (int rc = make_operand_map(&map_a, w.a, m, Kp, 2 * batch, THB_GEMM_BM)) return rc;
-  if (int rc = make_operand_map(&map_b, w.b, n, Kp, 2 * batch, THB_GEMM_BN)) return rc;
-
-  THB_CUDA(cudaFuncSetAttribute(thb_gemm_3xtf32, cudaFuncAttributeMaxDynamicSharedMemorySize, THB_GEMM_SMEM_BYTES));
+  if (int rc = make_operand_map(&map_a, w.a, m, Kp, 2 * batch, THB_GEMM_BM, bk)) return rc;
+  if (int rc = make_operand_map(&map_b, w.b, n, Kp, 2 * batch, THB_GEMM_BN, bk)) return rc;
 
   ThbGemmParams p;
   p.c = c;
@@ -115,15 +124,23 @@ int thb200_gemm(void* stream, char transa, char transb, int64_t m, int64_t n, in
   p.batch_stride_c = stride_c;
   p.m = (int)m;
   p.n = (int)n;
-  p.kblocks = k > 0 ? (int)(Kp / THB_GEMM_BK) : 0;
+  p.kblocks = (int)(Kp / bk);  // k == 0: the split wrote zeros, so C = beta * C
   p.alpha = alpha;
   p.beta = beta;
   p.tiles_m = (int)((m + THB_GEMM_BM - 1) / THB_GEMM_BM);
   p.tiles_n = (int)((n + THB_GEMM_BN - 1) / THB_GEMM_BN);
+  p.batch = (int)batch;
   p.status = w.status;
-  if (p.kblocks == 0) { p.kblocks = 1; }  // k == 0: the split wrote zeros, so C = beta * C
-  dim3 grid((unsigned)(p.tiles_m * p.tiles_n), 1, (unsigned)batch);
-  thb_gemm_3xtf32<<<grid, THB_GEMM_THREADS, THB_GEMM_SMEM_BYTES, st>>>(map_a, map_b, p);
+  const int64_t total_tiles = (int64_t)p.tiles_m * p.tiles_n * batch;
+  if (total_tiles > INT32_MAX) return fail("gemm: too many tiles");
+  const int64_t ctas = total_tiles < sm_count() ? total_tiles : sm_count();
+  if (bk == 32) {
+    THB_CUDA(cudaFuncSetAttribute(thb_gemm_3xtf32<32, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, ThbGemmCfg<32, 2>::kSmem));
+    thb_gemm_3xtf32<32, 2><<<(unsigned)ctas, THB_GEMM_THREADS, ThbGemmCfg<32, 2>::kSmem, st>>>(map_a, map_b, p);
+  } else {
+    THB_CUDA(cudaFuncSetAttribute(thb_gemm_3xtf32<16, 4>, cudaFuncAttributeMaxDynamicSharedMemorySize, ThbGemmCfg<16, 4>::kSmem));
+    thb_gemm_3xtf32<16, 4><<<(unsigned)ctas, THB_GEMM_THREADS, ThbGemmCfg<16, 4>::kSmem, st>>>(map_a, map_b, p);
+  }
   THB_CUDA(cudaGetLastError());
   return 0;
 }

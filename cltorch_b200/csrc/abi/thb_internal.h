@@ -36,13 +36,14 @@ struct ApplyKernels {
   const void* contig = nullptr;
   const void* strided = nullptr;
   const void* tile2d = nullptr;
+  const void* rows2d = nullptr;
   int nt = 0;
   bool reads_out = true;
   const char* name = nullptr;
   const char* body = nullptr;
 };
 
-enum ApplyPlan { PLAN_NONE = 0, PLAN_CONTIG = 1, PLAN_STRIDED = 2, PLAN_TILE2D = 3 };
+enum ApplyPlan { PLAN_NONE = 0, PLAN_CONTIG = 1, PLAN_STRIDED = 2, PLAN_TILE2D = 3, PLAN_ROWS2D = 4 };
 
 // Chooses the kernel for these operands and launches it.
 int launch_apply(const ApplyKernels& k, cudaStream_t st, int nt, const thb200_tensor* t, float val1,

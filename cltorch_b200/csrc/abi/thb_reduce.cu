@@ -114,7 +114,7 @@ struct ReduceAllArgs {
 // How many chunks the reduced dimension is cut into so that a reduction with few
 // slices still fills the GPU.
 static uint32_t pick_chunks(int64_t nslices, int64_t rsize) {
-  const int64_t want_threads = (int64_t)sm_count() * 1024;
+  const int64_t want_threads = (int64_t)sm_count() * 2048;
   if (nslices >= want_threads || rsize < 256) return 1;
   int64_t chunks = (want_threads + nslices - 1) / nslices;
   int64_t max_chunks = rsize / 64;
@@ -137,7 +137,7 @@ struct ReduceDimArgs {
   void operator()() {
     const int sms = sm_count();
     if (rstride == 1) {
-      if (rsize >= 1024) {
+      if (rsize >= 8192) {
         unsigned blocks = nslices < (unsigned)sms * 64u ? nslices : (unsigned)sms * 64u;
         thb_reduce_dim_contig_block<Mod, Red><<<blocks, THB_RD_THREADS, 0, st>>>(out, in, rsize, nslices, init, mparam);
       } else {
@@ -192,7 +192,7 @@ static int argreduce(cudaStream_t st, float* values, float* indices, const float
                      int64_t inner, float* scratch, size_t scratch_bytes) {
   const int sms = sm_count();
   if (inner == 1) {
-    if (n < 1024) {
+    if (n < 8192) {
       int64_t blocks = (outer + 7) / 8;
       if (blocks > (int64_t)sms * 64) blocks = (int64_t)sms * 64;
       thb_argreduce_rows<IS_MAX, true><<<(unsigned)blocks, THB_RD_THREADS, 0, st>>>(values, indices, src, outer, (thb_u32)n);

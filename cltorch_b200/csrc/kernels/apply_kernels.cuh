@@ -17,9 +17,11 @@
 // (src/lib/THClTensorMathPointwise.h, src/lib/THClApply.cl:33-45), so those
 // strings paste in unchanged.
 //
-// Three kernels:
+// Four kernels:
 //   thb_apply_contig   every operand is one contiguous run: 128-bit loads and
 //                      stores, 4 vectors in flight per thread, 64-bit counts.
+//   thb_apply_rows2d   the same R x C matrix in every operand with unit stride
+//                      along C (column-narrowed views): 128-bit along the rows.
 //   thb_apply_strided  any collapsed layout up to 25 dims, 32-bit index math
 //                      with multiply-shift division instead of % and /.
 //   thb_apply_tile2d   operands are the same logical R x C matrix, each either
@@ -174,6 +176,57 @@ thb_apply_strided(ThbLayout A, ThbLayout B, ThbLayout C, thb_u64 n, ThbScalars s
       if (i < n) {
         Op::apply(&o[u], &x[u], &y[u], s.val1, s.val2, &p1, &p2);
         A.data[oa[u]] = o[u];
+      }
+    }
+  }
+}
+
+// ---------------------------------------------------------------------------
+// Same logical R x C matrix in every operand, unit stride along C and any row
+// stride (column-narrowed views, or a contiguous tensor seen as R x C): float4
+// along the rows, one division per vector shared by all operands. Needs
+// C % 4 == 0, 16-byte aligned row starts, and fewer than 2^32 vectors.
+// ---------------------------------------------------------------------------
+struct ThbRows2d {
+  float* data[3];
+  thb_i64 row_stride[3];  // elements
+  thb_u32 cvec;           // C / 4
+  thb_u32 magic, shift;   // division by cvec
+  thb_u64 nvec;           // R * cvec
+};
+
+template <class Op, int NT>
+__global__ void __launch_bounds__(THB_CONTIG_THREADS)
+thb_apply_rows2d(ThbRows2d P, ThbScalars s) {
+  float p1 = 0.f, p2 = 0.f;
+  if (s.pointTensor1) p1 = *s.pointTensor1;
+  if (s.pointTensor2) p2 = *s.pointTensor2;
+  const thb_u64 step = (thb_u64)gridDim.x * (THB_CONTIG_THREADS * THB_CONTIG_UNROLL);
+  for (thb_u64 base = (thb_u64)blockIdx.x * (THB_CONTIG_THREADS * THB_CONTIG_UNROLL) + threadIdx.x;
+       base < P.nvec; base += step) {
+    float4 va[THB_CONTIG_UNROLL], vb[THB_CONTIG_UNROLL], vc[THB_CONTIG_UNROLL];
+    float4* pa[THB_CONTIG_UNROLL];
+#pragma unroll
+    for (int u = 0; u < THB_CONTIG_UNROLL; ++u) {
+      const thb_u64 i = base + (thb_u64)u * THB_CONTIG_THREADS;
+      if (i < P.nvec) {
+        const thb_u32 r = thb_fastdiv((thb_u32)i, P.magic, P.shift);
+        const thb_u32 c = ((thb_u32)i - r * P.cvec) << 2;
+        pa[u] = reinterpret_cast<float4*>(P.data[0] + (thb_i64)r * P.row_stride[0] + c);
+        if (Op::kReadsOut) va[u] = *pa[u];
+        if (NT >= 2) vb[u] = *reinterpret_cast<const float4*>(P.data[1] + (thb_i64)r * P.row_stride[1] + c);
+        if (NT >= 3) vc[u] = *reinterpret_cast<const float4*>(P.data[2] + (thb_i64)r * P.row_stride[2] + c);
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < THB_CONTIG_UNROLL; ++u) {
+      const thb_u64 i = base + (thb_u64)u * THB_CONTIG_THREADS;
+      if (i < P.nvec) {
+        Op::apply(&va[u].x, &vb[u].x, &vc[u].x, s.val1, s.val2, &p1, &p2);
+        Op::apply(&va[u].y, &vb[u].y, &vc[u].y, s.val1, s.val2, &p1, &p2);
+        Op::apply(&va[u].z, &vb[u].z, &vc[u].z, s.val1, s.val2, &p1, &p2);
+        Op::apply(&va[u].w, &vb[u].w, &vc[u].w, s.val1, s.val2, &p1, &p2);
+        *pa[u] = va[u];
       }
     }
   }

@@ -14,14 +14,15 @@
 //                   row-major [rows][Kp] matrices ("K-major"), Kp = K rounded
 //                   up to 32 and zero-filled, so that the GEMM kernel needs a
 //                   single operand layout whatever transa/transb were.
-//  thb_gemm_3xtf32  one 128 x 256 output tile per CTA. Warp 0 lane 0 issues TMA
-//                   loads (cp.async.bulk.tensor, 128-byte swizzle, no
+//  thb_gemm_3xtf32  persistent, one CTA per SM, 128 x 256 output tiles. Warp 0
+//                   lane 0 issues TMA loads (cp.async.bulk.tensor, swizzled, no
 //                   multicast) of the four operand tiles of a k block into a
-//                   2-stage shared-memory ring; warp 1 lane 0 issues
+//                   shared-memory ring; warp 1 lane 0 issues
 //                   tcgen05.mma.kind::tf32 (M=128, N=256, K=8), three per k
-//                   step, into a 128-lane x 256-column TMEM accumulator and
-//                   commits to mbarriers; warps 2-5 read the accumulator with
-//                   tcgen05.ld and write C with coalesced stores.
+//                   step, into one of two 128-lane x 256-column TMEM
+//                   accumulators and commits to mbarriers; warps 2-5 read the
+//                   other accumulator with tcgen05.ld and write C with
+//                   coalesced stores while the next tile's k loop runs.
 //
 // Every wait is bounded: after THB_GEMM_WAIT_LIMIT_NS a waiter records a
 // code in *status, raises the CTA's abort flag and everybody falls through to
@@ -33,16 +34,20 @@
 
 #define THB_GEMM_BM 128
 #define THB_GEMM_BN 256
-#define THB_GEMM_BK 32
-#define THB_GEMM_STAGES 2
 #define THB_GEMM_THREADS 192
-#define THB_GEMM_TILE_A_BYTES (THB_GEMM_BM * THB_GEMM_BK * 4)
-#define THB_GEMM_TILE_B_BYTES (THB_GEMM_BN * THB_GEMM_BK * 4)
-#define THB_GEMM_STAGE_BYTES (2 * THB_GEMM_TILE_A_BYTES + 2 * THB_GEMM_TILE_B_BYTES)
-#define THB_GEMM_SMEM_BYTES (THB_GEMM_STAGES * THB_GEMM_STAGE_BYTES + 1024 /*alignment slack*/ + 256 /*barriers*/)
-#define THB_GEMM_TMEM_COLS 256
+#define THB_GEMM_TMEM_COLS 512  // two 128 x 256 fp32 accumulators
 #define THB_GEMM_WAIT_LIMIT_NS 2000000000ull  // 2 s
 #define THB_GEMM_GROUP_M 16
+
+// Shared-memory budget of one configuration: k-block depth BK (32 = 128-byte
+// swizzle, 16 = 64-byte swizzle) and ring length STAGES.
+template <int BK, int STAGES>
+struct ThbGemmCfg {
+  static constexpr int kTileA = THB_GEMM_BM * BK * 4;
+  static constexpr int kTileB = THB_GEMM_BN * BK * 4;
+  static constexpr int kStage = 2 * kTileA + 2 * kTileB;  // A_hi, A_lo, B_hi, B_lo
+  static constexpr int kSmem = STAGES * kStage + 1024 /*alignment slack*/ + 256 /*barriers*/;
+};
 
 // ---- operand split ----------------------------------------------------------
 // src element (r, k) is at src[r * sr + k * sk]; TRANS selects which of the two
@@ -140,15 +145,19 @@ __device__ __forceinline__ void thb_tma_load_3d(uint32_t dst, const CUtensorMap*
       ::"r"(dst), "l"(map), "r"(bar), "r"(x), "r"(y), "r"(z)
       : "memory");
 }
-// Shared-memory matrix descriptor: K-major tile, rows of 128 bytes, 128-byte
-// swizzle, 8-row groups 1024 bytes apart.
-__device__ __forceinline__ uint64_t thb_umma_desc_sw128(uint32_t smem_addr) {
+// Shared-memory matrix descriptor of a K-major tile whose rows are one swizzle
+// span long: BK = 32 floats -> 128-byte swizzle (8-row groups 1024 bytes apart),
+// BK = 16 floats -> 64-byte swizzle (8-row groups 512 bytes apart).
+template <int BK>
+__device__ __forceinline__ uint64_t thb_umma_desc(uint32_t smem_addr) {
+  constexpr uint64_t kSbo = (BK == 32) ? 1024 : 512;
+  constexpr uint64_t kLayout = (BK == 32) ? 2 : 4;  // 2 = SWIZZLE_128B, 4 = SWIZZLE_64B
   uint64_t d = 0;
   d |= (uint64_t)((smem_addr & 0x3FFFFu) >> 4);  // start address, bits [0,14)
   d |= (uint64_t)1 << 16;                        // leading byte offset (unused for swizzled K-major)
-  d |= (uint64_t)(1024 >> 4) << 32;              // stride byte offset, bits [32,46)
+  d |= (kSbo >> 4) << 32;                        // stride byte offset, bits [32,46)
   d |= (uint64_t)1 << 46;                        // descriptor version of sm_100
-  d |= (uint64_t)2 << 61;                        // layout: 128-byte swizzle
+  d |= kLayout << 61;
   return d;
 }
 // Instruction descriptor of tcgen05.mma.kind::tf32: fp32 accumulate, TF32 A and
@@ -167,46 +176,52 @@ __device__ __forceinline__ void thb_umma_tf32(uint32_t d_tmem, uint64_t a_desc, 
 __device__ __forceinline__ void thb_umma_commit(uint32_t bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
 }
+__device__ __forceinline__ void thb_mbar_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
 
 struct ThbGemmParams {
   float* c;
   long long ldc, batch_stride_c;
   int m, n, kblocks;
   float alpha, beta;
-  int tiles_m, tiles_n;
+  int tiles_m, tiles_n, batch;
   int* status;  // 0 = fine; otherwise the code of the first wait that gave up
 };
 
+// Persistent: CTA i works on tiles i, i + gridDim.x, ... The k loop of tile t+1
+// overlaps the epilogue of tile t through two TMEM accumulators.
+template <int BK, int STAGES>
 __global__ void __launch_bounds__(THB_GEMM_THREADS, 1)
 thb_gemm_3xtf32(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                 ThbGemmParams p) {
+  typedef ThbGemmCfg<BK, STAGES> Cfg;
   extern __shared__ uint8_t smem_raw[];
-  // tiles need 1024-byte alignment for the 128-byte swizzle
+  // tiles need 1024-byte alignment for the swizzle
   uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
-  uint64_t* bars = (uint64_t*)(smem + THB_GEMM_STAGES * THB_GEMM_STAGE_BYTES);
-  // bars[0..S): full, bars[S..2S): empty, bars[2S]: accumulator ready
-  uint32_t* tmem_slot = (uint32_t*)(bars + 2 * THB_GEMM_STAGES + 1);
+  uint64_t* bars = (uint64_t*)(smem + STAGES * Cfg::kStage);
+  uint64_t* bar_full = bars;                     // [STAGES] TMA -> MMA
+  uint64_t* bar_empty = bars + STAGES;           // [STAGES] MMA -> TMA
+  uint64_t* bar_acc_full = bars + 2 * STAGES;    // [2] MMA -> epilogue
+  uint64_t* bar_acc_empty = bars + 2 * STAGES + 2;  // [2] epilogue -> MMA (4 arrivals: one per warp)
+  uint32_t* tmem_slot = (uint32_t*)(bars + 2 * STAGES + 4);
   volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
   volatile int* never_set = abort_flag + 1;  // stays 0: for the waits of the exit path
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-
-  // grouped tile order: THB_GEMM_GROUP_M row tiles share their B tiles in L2
-  const int tile = blockIdx.x;
+  const int tiles_per_batch = p.tiles_m * p.tiles_n;
+  const int total_tiles = tiles_per_batch * p.batch;
   const int group_sz = THB_GEMM_GROUP_M * p.tiles_n;
-  const int group = tile / group_sz;
-  const int first_m = group * THB_GEMM_GROUP_M;
-  const int gm = min(THB_GEMM_GROUP_M, p.tiles_m - first_m);
-  const int tile_m = first_m + (tile % group_sz) % gm;
-  const int tile_n = (tile % group_sz) / gm;
-  const int batch = blockIdx.z;
 
   if (threadIdx.x == 0) {
-    for (int s = 0; s < THB_GEMM_STAGES; ++s) {
-      thb_mbar_init(thb_smem_u32(&bars[s]), 1);
-      thb_mbar_init(thb_smem_u32(&bars[THB_GEMM_STAGES + s]), 1);
+    for (int s = 0; s < STAGES; ++s) {
+      thb_mbar_init(thb_smem_u32(&bar_full[s]), 1);
+      thb_mbar_init(thb_smem_u32(&bar_empty[s]), 1);
     }
-    thb_mbar_init(thb_smem_u32(&bars[2 * THB_GEMM_STAGES]), 1);
+    for (int a = 0; a < 2; ++a) {
+      thb_mbar_init(thb_smem_u32(&bar_acc_full[a]), 1);
+      thb_mbar_init(thb_smem_u32(&bar_acc_empty[a]), 4);
+    }
     abort_flag[0] = 0;
     abort_flag[1] = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -221,81 +236,115 @@ thb_gemm_3xtf32(const __grid_constant__ CUtensorMap map_a, const __grid_constant
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
   const uint32_t tmem_base = *tmem_slot;
 
+  // tile index -> (batch, tile_m, tile_n): within a batch, THB_GEMM_GROUP_M row tiles
+  // share their B tiles in L2
+#define THB_GEMM_TILE_COORDS(tile)                                          \
+  const int batch = (tile) / tiles_per_batch;                               \
+  const int rem_ = (tile) % tiles_per_batch;                                \
+  const int first_m_ = (rem_ / group_sz) * THB_GEMM_GROUP_M;                \
+  const int gm_ = min(THB_GEMM_GROUP_M, p.tiles_m - first_m_);              \
+  const int tile_m = first_m_ + (rem_ % group_sz) % gm_;                    \
+  const int tile_n = (rem_ % group_sz) / gm_;
+
   if (warp == 0) {
     if (lane == 0) {
       // ---- TMA producer ----
-      int issued = 0;
-      for (int kb = 0; kb < p.kblocks; ++kb) {
-        const int s = kb % THB_GEMM_STAGES;
-        const uint32_t round = kb / THB_GEMM_STAGES;
-        if (kb >= THB_GEMM_STAGES &&
-            !thb_mbar_wait(thb_smem_u32(&bars[THB_GEMM_STAGES + s]), (round - 1) & 1, abort_flag)) {
-          if (!*abort_flag) { *abort_flag = 1; atomicCAS(p.status, 0, 1); }
-          break;
+      long long it = 0;  // k blocks issued so far, over all tiles of this CTA
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+        THB_GEMM_TILE_COORDS(tile)
+        for (int kb = 0; kb < p.kblocks; ++kb, ++it) {
+          const int s = (int)(it % STAGES);
+          const uint32_t round = (uint32_t)(it / STAGES);
+          if (it >= STAGES && !thb_mbar_wait(thb_smem_u32(&bar_empty[s]), (round - 1) & 1, abort_flag)) {
+            if (!*abort_flag) { *abort_flag = 1; atomicCAS(p.status, 0, 1); }
+            ok = false;
+            break;
+          }
+          const uint32_t full = thb_smem_u32(&bar_full[s]);
+          uint8_t* st = smem + s * Cfg::kStage;
+          thb_mbar_expect_tx(full, Cfg::kStage);
+          const int k0 = kb * BK;
+          thb_tma_load_3d(thb_smem_u32(st), &map_a, full, k0, tile_m * THB_GEMM_BM, batch * 2 + 0);
+          thb_tma_load_3d(thb_smem_u32(st + Cfg::kTileA), &map_a, full, k0, tile_m * THB_GEMM_BM, batch * 2 + 1);
+          thb_tma_load_3d(thb_smem_u32(st + 2 * Cfg::kTileA), &map_b, full, k0, tile_n * THB_GEMM_BN, batch * 2 + 0);
+          thb_tma_load_3d(thb_smem_u32(st + 2 * Cfg::kTileA + Cfg::kTileB), &map_b, full, k0, tile_n * THB_GEMM_BN,
+                          batch * 2 + 1);
         }
-        const uint32_t full = thb_smem_u32(&bars[s]);
-        uint8_t* st = smem + s * THB_GEMM_STAGE_BYTES;
-        thb_mbar_expect_tx(full, THB_GEMM_STAGE_BYTES);
-        const int k0 = kb * THB_GEMM_BK;
-        thb_tma_load_3d(thb_smem_u32(st), &map_a, full, k0, tile_m * THB_GEMM_BM, batch * 2 + 0);
-        thb_tma_load_3d(thb_smem_u32(st + THB_GEMM_TILE_A_BYTES), &map_a, full, k0, tile_m * THB_GEMM_BM, batch * 2 + 1);
-        thb_tma_load_3d(thb_smem_u32(st + 2 * THB_GEMM_TILE_A_BYTES), &map_b, full, k0, tile_n * THB_GEMM_BN, batch * 2 + 0);
-        thb_tma_load_3d(thb_smem_u32(st + 2 * THB_GEMM_TILE_A_BYTES + THB_GEMM_TILE_B_BYTES), &map_b, full, k0,
-                        tile_n * THB_GEMM_BN, batch * 2 + 1);
-        issued = kb + 1;
       }
       if (*abort_flag) {
         // do not leave while copies into this CTA's shared memory are in flight
-        for (int kb = max(0, issued - THB_GEMM_STAGES); kb < issued; ++kb)
-          thb_mbar_wait(thb_smem_u32(&bars[kb % THB_GEMM_STAGES]), (kb / THB_GEMM_STAGES) & 1, never_set);
+        for (long long j = (it > STAGES ? it - STAGES : 0); j < it; ++j)
+          thb_mbar_wait(thb_smem_u32(&bar_full[j % STAGES]), (uint32_t)(j / STAGES) & 1, never_set);
       }
     }
   } else if (warp == 1) {
     if (lane == 0) {
       // ---- MMA issuer ----
       const uint32_t idesc = thb_umma_idesc_tf32(THB_GEMM_BM, THB_GEMM_BN);
+      long long it = 0;
+      int t = 0;  // tiles done by this CTA
+      int fail_t = 0;
       bool ok = true;
-      for (int kb = 0; kb < p.kblocks && ok; ++kb) {
-        const int s = kb % THB_GEMM_STAGES;
-        const uint32_t round = kb / THB_GEMM_STAGES;
-        if (!thb_mbar_wait(thb_smem_u32(&bars[s]), round & 1, abort_flag)) {
-          if (!*abort_flag) { *abort_flag = 1; atomicCAS(p.status, 0, 2); }
+      for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++t) {
+        const int acc = t & 1;
+        fail_t = t;
+        const uint32_t d_tmem = tmem_base + (uint32_t)(acc * THB_GEMM_BN);
+        if (t >= 2 && !thb_mbar_wait(thb_smem_u32(&bar_acc_empty[acc]), ((uint32_t)(t >> 1) - 1) & 1, abort_flag)) {
+          if (!*abort_flag) { *abort_flag = 1; atomicCAS(p.status, 0, 4); }
           ok = false;
           break;
         }
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        const uint32_t st = thb_smem_u32(smem + s * THB_GEMM_STAGE_BYTES);
-        const uint64_t a_hi = thb_umma_desc_sw128(st);
-        const uint64_t a_lo = thb_umma_desc_sw128(st + THB_GEMM_TILE_A_BYTES);
-        const uint64_t b_hi = thb_umma_desc_sw128(st + 2 * THB_GEMM_TILE_A_BYTES);
-        const uint64_t b_lo = thb_umma_desc_sw128(st + 2 * THB_GEMM_TILE_A_BYTES + THB_GEMM_TILE_B_BYTES);
+        for (int kb = 0; kb < p.kblocks; ++kb, ++it) {
+          const int s = (int)(it % STAGES);
+          const uint32_t round = (uint32_t)(it / STAGES);
+          if (!thb_mbar_wait(thb_smem_u32(&bar_full[s]), round & 1, abort_flag)) {
+            if (!*abort_flag) { *abort_flag = 1; atomicCAS(p.status, 0, 2); }
+            ok = false;
+            break;
+          }
+          asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+          const uint32_t st = thb_smem_u32(smem + s * Cfg::kStage);
+          const uint64_t a_hi = thb_umma_desc<BK>(st);
+          const uint64_t a_lo = thb_umma_desc<BK>(st + Cfg::kTileA);
+          const uint64_t b_hi = thb_umma_desc<BK>(st + 2 * Cfg::kTileA);
+          const uint64_t b_lo = thb_umma_desc<BK>(st + 2 * Cfg::kTileA + Cfg::kTileB);
 #pragma unroll
-        for (int kk = 0; kk < THB_GEMM_BK / 8; ++kk) {
-          const uint64_t adv = (uint64_t)((kk * 32) >> 4);  // 8 tf32 = 32 bytes further along K
-          thb_umma_tf32(tmem_base, a_lo + adv, b_hi + adv, idesc, (kb | kk) != 0);
-          thb_umma_tf32(tmem_base, a_hi + adv, b_lo + adv, idesc, 1);
-          thb_umma_tf32(tmem_base, a_hi + adv, b_hi + adv, idesc, 1);
+          for (int kk = 0; kk < BK / 8; ++kk) {
+            const uint64_t adv = (uint64_t)((kk * 32) >> 4);  // 8 tf32 = 32 bytes further along K
+            thb_umma_tf32(d_tmem, a_lo + adv, b_hi + adv, idesc, (kb | kk) != 0);
+            thb_umma_tf32(d_tmem, a_hi + adv, b_lo + adv, idesc, 1);
+            thb_umma_tf32(d_tmem, a_hi + adv, b_hi + adv, idesc, 1);
+          }
+          thb_umma_commit(thb_smem_u32(&bar_empty[s]));  // stage may be refilled
         }
-        thb_umma_commit(thb_smem_u32(&bars[THB_GEMM_STAGES + s]));  // stage may be refilled
+        if (ok) thb_umma_commit(thb_smem_u32(&bar_acc_full[acc]));  // accumulator complete
       }
-      thb_umma_commit(thb_smem_u32(&bars[2 * THB_GEMM_STAGES]));  // accumulator complete
-      // after giving up: let the MMAs already issued drain before tensor memory is released
-      if (!ok) thb_mbar_wait(thb_smem_u32(&bars[2 * THB_GEMM_STAGES]), 0, never_set);
+      if (!ok) {
+        // after giving up: let the MMAs already issued drain before tensor memory is released
+        thb_umma_commit(thb_smem_u32(&bar_acc_full[fail_t & 1]));
+        thb_mbar_wait(thb_smem_u32(&bar_acc_full[fail_t & 1]), (uint32_t)(fail_t >> 1) & 1, never_set);
+      }
     }
   } else {
     // ---- epilogue: warps 2..5 own TMEM lanes 32*(warp%4) .. +31 ----
     const int lane_group = warp & 3;
-    bool ok = thb_mbar_wait(thb_smem_u32(&bars[2 * THB_GEMM_STAGES]), 0, abort_flag);
-    if (!ok && !*abort_flag) { *abort_flag = 1; atomicCAS(p.status, 0, 3); }
-    ok = __all_sync(0xffffffffu, ok);
-    if (ok) {
+    int t = 0;
+    for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, ++t) {
+      THB_GEMM_TILE_COORDS(tile)
+      const int acc = t & 1;
+      bool ok = thb_mbar_wait(thb_smem_u32(&bar_acc_full[acc]), (uint32_t)(t >> 1) & 1, abort_flag);
+      if (!ok && !*abort_flag) { *abort_flag = 1; atomicCAS(p.status, 0, 3); }
+      ok = __all_sync(0xffffffffu, ok);
+      if (!ok) break;
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
       const int row = tile_m * THB_GEMM_BM + lane_group * 32 + lane;
-      float* cb = p.c + (long long)batch * p.batch_stride_c;
+      float* cb = p.c + (long long)batch * p.batch_stride_c + row;
 #pragma unroll 1
       for (int c0 = 0; c0 < THB_GEMM_BN; c0 += 32) {
         uint32_t r[32];
-        const uint32_t taddr = tmem_base + ((uint32_t)(lane_group * 32) << 16) + (uint32_t)c0;
+        const uint32_t taddr = tmem_base + ((uint32_t)(lane_group * 32) << 16) + (uint32_t)(acc * THB_GEMM_BN + c0);
         asm volatile(
             "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
             "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
@@ -306,21 +355,31 @@ thb_gemm_3xtf32(const __grid_constant__ CUtensorMap map_a, const __grid_constant
               "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
             : "r"(taddr));
         asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-        if (row < p.m) {
+        const int col0 = tile_n * THB_GEMM_BN + c0;
+        if (row < p.m && col0 < p.n) {
+          // all reads of C first (32 independent loads in flight), then the stores
+          float cv[32];
+          if (p.beta != 0.f) {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) cv[j] = (col0 + j < p.n) ? cb[(long long)(col0 + j) * p.ldc] : 0.f;
+          }
 #pragma unroll
           for (int j = 0; j < 32; ++j) {
-            const int col = tile_n * THB_GEMM_BN + c0 + j;
-            if (col < p.n) {
-              float* dst = cb + row + (long long)col * p.ldc;
+            if (col0 + j < p.n) {
               float v = p.alpha * __uint_as_float(r[j]);
-              if (p.beta != 0.f) v += p.beta * *dst;
-              *dst = v;
+              if (p.beta != 0.f) v += p.beta * cv[j];
+              cb[(long long)(col0 + j) * p.ldc] = v;
             }
           }
         }
       }
+      // this warp is done reading the accumulator: hand it back to the MMA issuer
+      asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+      __syncwarp();
+      if (lane == 0) thb_mbar_arrive(thb_smem_u32(&bar_acc_empty[acc]));
     }
   }
+#undef THB_GEMM_TILE_COORDS
 
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
   __syncthreads();

@@ -58,13 +58,17 @@ __device__ __forceinline__ typename Red::acc_t thb_block_fold(typename Red::acc_
 }
 
 // ---- reduceAll --------------------------------------------------------------
+// 256 threads x 8 float4 loads in flight per thread, 4 blocks per SM (<= 64 registers):
+// 128 KB of loads in flight per SM, and 592 = 4 x 148 blocks are one full wave on a B200.
+// The block count is a constant so that the summation order never depends on the device.
 #define THB_RA_THREADS 256
-#define THB_RA_UNROLL 4
-#define THB_RA_MAX_BLOCKS 1184  // fixed, so that the summation order does not depend on the device
+#define THB_RA_UNROLL 8
+#define THB_RA_BLOCKS_PER_SM 4
+#define THB_RA_MAX_BLOCKS 592
 
 // Pass 1 over one contiguous run. `head` as in thb_apply_contig.
 template <class Mod, class Red>
-__global__ void __launch_bounds__(THB_RA_THREADS)
+__global__ void __launch_bounds__(THB_RA_THREADS, THB_RA_BLOCKS_PER_SM)
 thb_reduce_all_pass1_contig(const float* in, thb_i64 n, int head, float init, float mparam,
                             const float* mpoint, typename Red::acc_t* partials) {
   typedef typename Red::acc_t acc_t;
@@ -269,12 +273,12 @@ thb_reduce_dim_noncontig(ThbLayout out, ThbLayout in, thb_u32 rsize, thb_u32 rst
     const float* p = in.data + thb_offset(in, s);
     acc_t acc = (acc_t)init;
     thb_u32 r = r0;
-    for (; r + 8 <= r1; r += 8) {
-      float v[8];
+    for (; r + 16 <= r1; r += 16) {
+      float v[16];
 #pragma unroll
-      for (int u = 0; u < 8; ++u) v[u] = p[(thb_u64)(r + u) * rstride];
+      for (int u = 0; u < 16; ++u) v[u] = p[(thb_u64)(r + u) * rstride];
 #pragma unroll
-      for (int u = 0; u < 8; ++u) acc = Red::apply(acc, Mod::apply(v[u], mparam, 0.f));
+      for (int u = 0; u < 16; ++u) acc = Red::apply(acc, Mod::apply(v[u], mparam, 0.f));
     }
     for (; r < r1; ++r) acc = Red::apply(acc, Mod::apply(p[(thb_u64)r * rstride], mparam, 0.f));
     if (nchunks == 1) out.data[thb_offset(out, s)] = (float)acc;
@@ -402,12 +406,12 @@ thb_argreduce_cols(float* values, float* indices, const float* src, thb_i64 oute
     float v = ThbArg<IS_MAX>::start();
     int idx = -1;
     thb_u32 r = r0;
-    for (; r + 8 <= r1; r += 8) {
-      float x[8];
+    for (; r + 16 <= r1; r += 16) {
+      float x[16];
 #pragma unroll
-      for (int u = 0; u < 8; ++u) x[u] = p[(thb_i64)(r + u) * inner];
+      for (int u = 0; u < 16; ++u) x[u] = p[(thb_i64)(r + u) * inner];
 #pragma unroll
-      for (int u = 0; u < 8; ++u)
+      for (int u = 0; u < 16; ++u)
         if (ThbArg<IS_MAX>::strictly(x[u], v)) { v = x[u]; idx = r + u; }
     }
     for (; r < r1; ++r) {

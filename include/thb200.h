@@ -52,7 +52,8 @@ int thb200_can_use_32bit_index(int ndim, const int64_t* size, const int64_t* str
  * by ascending stride; the reference's qsort comparator is not a valid ordering). */
 int thb200_overlapping_indices(int ndim, const int64_t* size, const int64_t* stride);
 /* Which kernel thb200_apply_* would pick for these operands, without launching:
- * 0 = nothing to do, 1 = contiguous 128-bit, 2 = strided, 3 = 2-D tile; < 0 = error. */
+ * 0 = nothing to do, 1 = contiguous 128-bit, 2 = strided, 3 = 2-D tile (transposed
+ * operands), 4 = 2-D rows (unit inner stride, 128-bit); < 0 = error. */
 int thb200_apply_plan(int ntensors, const thb200_tensor* t);
 
 /* ---- pointwise apply ------------------------------------------------------ */
@@ -91,7 +92,7 @@ enum thb200_final { THB200_FIN_NONE = 0, THB200_FIN_DIV = 1, THB200_FIN_DIV_SQRT
 
 /* Bytes of scratch (global memory beyond input and output) that
  * thb200_reduce_all needs for `n` elements: one 8-byte partial per pass-1 block
- * (at most 1184 blocks). Must be 8-byte aligned. */
+ * (at most 592 blocks). Must be 8-byte aligned. */
 size_t thb200_reduce_all_scratch_bytes(int64_t n);
 
 /* THClTensor_reduceAll, src/lib/THClReduceAll.cpp:276-316 with kernels

@@ -198,6 +198,23 @@ def test_contiguous_ragged_sizes(n, offset):
     a.check(0, f"n={n} offset={offset}")
 
 
+@pytest.mark.parametrize("rows,cols,pitch", [(30, 28, 40), (257, 1028, 1200), (1, 8, 8), (70, 4, 12)])
+def test_column_narrowed_views_take_the_row_vector_path(rows, cols, pitch):
+    """R x C views with unit inner stride, 16-byte aligned rows and C % 4 == 0 (128-bit row kernel)."""
+    import cltorch_b200 as cl
+    a = Pair(rng_uniform(41, (rows * pitch + 8,), -1, 1), 4, [rows, cols], [pitch, 1])
+    b = Pair(rng_uniform(42, (rows * pitch + 8,), -1, 1), 8, [rows, cols], [pitch, 1])
+    c = Pair(rng_uniform(43, (rows * cols,), -1, 1), 0, [rows, cols], [cols, 1])
+    a.cl.addcmul(0.5, b.cl, c.cl); O.apply("ADDCMUL_3", [a.view, b.view, c.view], 0.5)
+    a.check(0, "narrowed += 0.5 * narrowed * contiguous")
+    c.cl.add(a.cl); O.apply("ADD_2", [c.view, a.view])
+    c.check(0, "contiguous += narrowed")
+    a.cl.map_on_gpu(b.cl, "x = x * y + 0.25")
+    want = O.eval_expr("x = x * y + 0.25", a.view.numpy(), b.view.numpy())
+    a.view.numpy()[...] = want
+    a.check(0, "expression on narrowed views")
+
+
 def test_mixed_alignment_falls_back_to_strided():
     a = Pair(rng_uniform(10, (5000,)), 1, [4000], None)
     b = Pair(rng_uniform(11, (5000,)), 2, [4000], None)

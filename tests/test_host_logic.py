@@ -135,7 +135,10 @@ def test_kernel_plan(lib):
     assert plan(lib, [(A, [n, n], [1, n]), contig, contig]) == 3                       # transposed destination
     assert plan(lib, [(A, [n, n // 2], [n, 1]), (A, [n, n // 2], [n, 2])]) == 2        # stride-2 slice: 1-D strided
     assert plan(lib, [(A, [4000, n], [n, 1]), (A + 64 * n, [4000, n], [n, 1])]) == 1   # narrowed rows stay one run
-    assert plan(lib, [(A, [n, 4000], [n, 1]), (A, [n, 4000], [n, 1])]) == 2            # narrowed columns: strided
+    assert plan(lib, [(A, [n, 4000], [n, 1]), (A, [n, 4000], [n, 1])]) == 4            # narrowed columns: 128-bit rows
+    assert plan(lib, [(A, [n, 4000], [n, 1]), contig[:1] + ([n, 4000], [4000, 1])]) == 4 # ... mixed with a contiguous one
+    assert plan(lib, [(A, [n, 4001], [n, 1]), (A, [n, 4001], [n, 1])]) == 2            # ragged rows: generic strided
+    assert plan(lib, [(A + 4, [n, 4000], [n, 1]), (A, [n, 4000], [n, 1])]) == 2        # misaligned rows: generic strided
     assert plan(lib, [(A, [n, 4000], [n, 1]), (A, [n, 4000], [1, n])]) == 3
     assert plan(lib, [(A, [], []), (A, [], [])]) == 0                                  # 0-dim: nothing to do
     assert plan(lib, [(A, [6], [1]), (A, [2, 3], [3, 1])]) == 1                        # equal counts, different shapes
@@ -175,7 +178,7 @@ def test_operator_table(lib):
 
 def test_scratch_and_workspace_sizes(lib):
     assert lib.thb200_reduce_all_scratch_bytes(1) == 8
-    assert lib.thb200_reduce_all_scratch_bytes(1 << 31) == 1184 * 8      # the fixed maximum number of pass-1 blocks
+    assert lib.thb200_reduce_all_scratch_bytes(1 << 31) == 592 * 8       # the fixed maximum number of pass-1 blocks
     assert lib.thb200_gemm_workspace_bytes(8192, 8192, 8192, 1) >= 4 * 8192 * 8192 * 4
     assert lib.thb200_reduce_dim_index_scratch_bytes(16384, 16384, 1) == 0
 
