@@ -205,6 +205,8 @@ PROTOTYPES = {
     "THClTensor_norm": (v, [S, T, T, f, l]),
     "THClTensor_max": (v, [S, T, T, T, l]), "THClTensor_min": (v, [S, T, T, T, l]),
     "THClTensor_addmm": (v, [S, T, f, T, f, T, T]), "THClTensor_baddbmm": (v, [S, T, f, T, f, T, T]),
+    "THClTensor_addmv": (v, [S, T, f, T, f, T, T]), "THClTensor_addr": (v, [S, T, f, T, f, T, T]),
+    "THClTensor_dot": (f, [S, T, T]),
     # thin ABI
     "thb200_last_error": (cp, []),
     "thb200_collapse_dims": (i, [i, c_int64_p, c_int64_p, i, c_int64_p, c_int64_p]),
@@ -230,6 +232,11 @@ PROTOTYPES = {
                         C.c_void_p, C.c_int64, f, C.c_void_p, C.c_int64, C.c_int64, C.c_int64, C.c_int64, C.c_int64,
                         C.c_void_p, C.c_size_t]),
     "thb200_gemm_status": (i, [C.c_void_p, C.c_int64, C.c_int64, C.c_int64, C.c_int64, C.c_void_p]),
+    "thb200_dot_scratch_bytes": (C.c_size_t, [C.c_int64]),
+    "thb200_dot": (i, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_void_p, C.c_void_p, C.c_size_t]),
+    "thb200_gemv_scratch_bytes": (C.c_size_t, [C.c_char, C.c_int64, C.c_int64]),
+    "thb200_gemv": (i, [C.c_void_p, C.c_char, C.c_int64, C.c_int64, f, C.c_void_p, C.c_int64, C.c_void_p, C.c_int64, f,
+                        C.c_void_p, C.c_int64, C.c_void_p, C.c_size_t]),
 }
 for _n in _UNARY:
     PROTOTYPES[f"THClTensor_{_n}"] = (v, [S, T, T])

@@ -1,0 +1,91 @@
+// Host side of thb200_dot and thb200_gemv.
+#include "thb_internal.h"
+#include "../kernels/math_policy.cuh"
+#include "../kernels/blas_kernels.cuh"
+
+using namespace thb;
+
+extern "C" {
+
+size_t thb200_dot_scratch_bytes(int64_t n) {
+  (void)n;
+  return (size_t)THB_RA_MAX_BLOCKS * sizeof(double);
+}
+
+int thb200_dot(void* stream, const float* a, const float* b, int64_t n, float* d_out, void* scratch,
+               size_t scratch_bytes) {
+  if (n < 0) return fail("dot: negative length");
+  if (!d_out) return fail("dot: null output");
+  if (n > 0 && (!a || !b)) return fail("dot: null operand");
+  if (!scratch || scratch_bytes < thb200_dot_scratch_bytes(n)) return fail("dot: scratch too small");
+  cudaStream_t st = (cudaStream_t)stream;
+  int64_t per_block = (int64_t)THB_RA_THREADS * 16;
+  int64_t blocks = (n + per_block - 1) / per_block;
+  if (blocks > THB_RA_MAX_BLOCKS) blocks = THB_RA_MAX_BLOCKS;
+  if (blocks < 1) blocks = 1;
+  const int vec_ok = ((((uintptr_t)a) | ((uintptr_t)b)) & 15) == 0;
+  thb_dot_pass1<<<(unsigned)blocks, THB_RA_THREADS, 0, st>>>(a, b, n, vec_ok, (double*)scratch);
+  THB_CUDA(cudaGetLastError());
+  thb_reduce_all_pass2<RedAdd><<<1, 1024, 0, st>>>((const double*)scratch, (int)blocks, 0.f, THB_FIN_NONE, 1.f, d_out);
+  THB_CUDA(cudaGetLastError());
+  return 0;
+}
+
+static uint32_t gemv_chunks(int64_t m, int64_t n) {
+  const int64_t want = (int64_t)sm_count() * 2048;
+  if (m >= want || n < 256) return 1;
+  int64_t chunks = (want + m - 1) / m;
+  if (chunks > n / 64) chunks = n / 64;
+  if (chunks > 1024) chunks = 1024;
+  return (uint32_t)(chunks < 1 ? 1 : chunks);
+}
+
+size_t thb200_gemv_scratch_bytes(char trans, int64_t m, int64_t n) {
+  if (trans == 't' || trans == 'T' || m <= 0 || n <= 0) return 0;
+  uint32_t c = gemv_chunks(m, n);
+  return c > 1 ? (size_t)c * m * sizeof(double) : 0;
+}
+
+int thb200_gemv(void* stream, char trans, int64_t m, int64_t n, float alpha, const float* a, int64_t lda, const float* x,
+                int64_t incx, float beta, float* y, int64_t incy, void* scratch, size_t scratch_bytes) {
+  const bool t = (trans == 't' || trans == 'T');
+  if (!t && trans != 'n' && trans != 'N') return fail("gemv: trans must be 'n' or 't'");
+  if (m < 0 || n < 0) return fail("gemv: negative extent");
+  if (m > UINT32_MAX || n > UINT32_MAX) return fail("gemv: extent too large");
+  if (lda < (m > 1 ? m : 1)) return fail("gemv: lda %lld < m %lld", (long long)lda, (long long)m);
+  const int64_t ylen = t ? n : m;
+  if (ylen == 0) return 0;
+  if (!a || !x || !y) return fail("gemv: null operand");
+  cudaStream_t st = (cudaStream_t)stream;
+  const int sms = sm_count();
+  if (t) {
+    // y (n) = alpha * A^T x + beta * y: one contiguous column of A (length m) per output
+    if (m < 8192) {
+      int64_t blocks = (n + 7) / 8;
+      if (blocks > (int64_t)sms * 64) blocks = (int64_t)sms * 64;
+      thb_gemv_t<true><<<(unsigned)blocks, THB_RD_THREADS, 0, st>>>(a, lda, x, incx, y, incy, (thb_u32)m, (thb_u32)n, alpha, beta);
+    } else {
+      int64_t blocks = n < (int64_t)sms * 64 ? n : (int64_t)sms * 64;
+      thb_gemv_t<false><<<(unsigned)blocks, THB_RD_THREADS, 0, st>>>(a, lda, x, incx, y, incy, (thb_u32)m, (thb_u32)n, alpha, beta);
+    }
+    THB_CUDA(cudaGetLastError());
+    return 0;
+  }
+  const uint32_t nchunks = gemv_chunks(m, n);
+  const uint32_t chunk_len = (uint32_t)((n + nchunks - 1) / nchunks);
+  if (nchunks > 1 && (!scratch || scratch_bytes < (size_t)nchunks * m * sizeof(double)))
+    return fail("gemv: scratch too small (%zu bytes, need %zu)", scratch_bytes, (size_t)nchunks * m * sizeof(double));
+  int64_t bx = (m + THB_RD_THREADS - 1) / THB_RD_THREADS;
+  if (bx > 65535 * 16) bx = 65535 * 16;
+  dim3 grid((unsigned)bx, nchunks ? nchunks : 1);
+  thb_gemv_n<<<grid, THB_RD_THREADS, 0, st>>>(a, lda, x, incx, y, incy, (thb_u32)m, (thb_u32)n, alpha, beta, chunk_len,
+                                             nchunks, (double*)scratch);
+  THB_CUDA(cudaGetLastError());
+  if (nchunks > 1) {
+    thb_gemv_n_fold<<<(unsigned)bx, THB_RD_THREADS, 0, st>>>((const double*)scratch, y, incy, (thb_u32)m, nchunks, alpha, beta);
+    THB_CUDA(cudaGetLastError());
+  }
+  return 0;
+}
+
+}  // extern "C"

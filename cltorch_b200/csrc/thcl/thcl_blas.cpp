@@ -119,4 +119,95 @@ void THClTensor_baddbmm(THClState* state, THClTensor* result, float beta, THClTe
   THCL_END_VOID
 }
 
+float THClTensor_dot(THClState* state, THClTensor* self, THClTensor* src) {
+  THCL_BEGIN
+  arg_check(THClTensor_nElement(state, self) == THClTensor_nElement(state, src), 2, "sizes do not match");
+  if (self->device != src->device) raise("tensors are on different devices");
+  // contiguous copies of strided operands, as the reference does
+  THClTensor* a = THClTensor_newContiguous(state, self);
+  THClTensor* b = THClTensor_newContiguous(state, src);
+  THClDeviceContext* ctx = context(state, self->device);
+  use_device(self->device);
+  const long n = THClTensor_nElement(state, a);
+  float* scratch = ensure_scratch(ctx, thb200_dot_scratch_bytes(n));
+  int rc = thb200_dot(ctx->stream, THClTensor_data(state, a), THClTensor_data(state, b), n, ctx->result, scratch,
+                      ctx->scratch_bytes);
+  std::string err = rc ? thb200_last_error() : "";
+  THClTensor_free(state, a);
+  THClTensor_free(state, b);
+  if (rc) raise("%s", err.c_str());
+  check_cuda(cudaMemcpyAsync(ctx->result_host, ctx->result, sizeof(float), cudaMemcpyDeviceToHost, ctx->stream), "cudaMemcpyAsync");
+  sync_stream(ctx);
+  return ctx->result_host[0];
+  THCL_END(0.f)
+}
+
+void THClTensor_addmv(THClState* state, THClTensor* r_, float beta, THClTensor* t, float alpha, THClTensor* mat, THClTensor* vec) {
+  THCL_BEGIN
+  if (mat->nDimension != 2 || vec->nDimension != 1) raise("matrix and vector expected");
+  if (mat->size[1] != vec->size[0]) raise("size mismatch");
+  if (t->nDimension != 1) raise("size mismatch");
+  if (t->size[0] != mat->size[0]) raise("size mismatch");
+  if (r_->device != t->device || mat->device != t->device || vec->device != t->device) raise("tensors are on different devices");
+  if (r_ != t) {
+    THClTensor_resizeAs(state, r_, t);
+    THClTensor_copy(state, r_, t);
+  }
+  // a matrix with unit stride along its rows index is the column-major 'n' case;
+  // a row-major one is its transpose; anything else goes through a contiguous copy
+  THClTensor* owned = nullptr;
+  char trans;
+  long m, n, lda;
+  if (mat->stride[0] == 1 && mat->stride[1] >= (mat->size[0] > 1 ? mat->size[0] : 1)) {
+    trans = 'n'; m = mat->size[0]; n = mat->size[1]; lda = mat->stride[1];
+  } else {
+    if (!(mat->stride[1] == 1 && mat->stride[0] >= (mat->size[1] > 1 ? mat->size[1] : 1))) {
+      owned = THClTensor_newContiguous(state, mat);
+      mat = owned;
+    }
+    trans = 't'; m = mat->size[1]; n = mat->size[0]; lda = mat->stride[0];
+    if (lda < (m > 1 ? m : 1)) lda = (m > 1 ? m : 1);
+  }
+  THClDeviceContext* ctx = context(state, r_->device);
+  use_device(r_->device);
+  float* scratch = ensure_scratch(ctx, thb200_gemv_scratch_bytes(trans, m, n));
+  int rc = thb200_gemv(ctx->stream, trans, m, n, alpha, THClTensor_data(state, mat), lda, THClTensor_data(state, vec),
+                       vec->stride[0], beta, THClTensor_data(state, r_), r_->stride[0], scratch, ctx->scratch_bytes);
+  std::string err = rc ? thb200_last_error() : "";
+  if (owned) THClTensor_free(state, owned);
+  if (rc) raise("%s", err.c_str());
+  after_launch(state, ctx);
+  THCL_END_VOID
+}
+
+void THClTensor_addr(THClState* state, THClTensor* r_, float beta, THClTensor* t, float alpha, THClTensor* vec1, THClTensor* vec2) {
+  THCL_BEGIN
+  if (vec1->nDimension != 1 || vec2->nDimension != 1) raise("vector and vector expected");
+  if (t->nDimension != 2) raise("size mismatch");
+  if (t->size[0] != vec1->size[0] || t->size[1] != vec2->size[0]) raise("size mismatch");
+  if (r_ != t) {
+    THClTensor_resizeAs(state, r_, t);
+    THClTensor_copy(state, r_, t);
+  }
+  if (beta != 1) THClTensor_mul(state, r_, r_, beta);
+  // the rank-1 update r += alpha * vec1 (x) vec2 is the pointwise operator
+  // "*out += val1 * *in1 * *in2" over broadcast (stride-0) views of the two vectors
+  THClTensor* a = THClTensor_newWithStorage2d(state, vec1->device, vec1->storage, vec1->storageOffset, vec1->size[0],
+                                              vec1->stride[0], vec2->size[0], 0);
+  THClTensor* b = THClTensor_newWithStorage2d(state, vec2->device, vec2->storage, vec2->storageOffset, vec1->size[0], 0,
+                                              vec2->size[0], vec2->stride[0]);
+  try {
+    THClTensor* ts[3] = {r_, a, b};
+    const bool rw[3] = {true, false, false};
+    pointwise(state, 3, ts, rw, "ADDCMUL_3", nullptr, alpha, 0.f, nullptr);
+  } catch (...) {
+    THClTensor_free(state, a);
+    THClTensor_free(state, b);
+    throw;
+  }
+  THClTensor_free(state, a);
+  THClTensor_free(state, b);
+  THCL_END_VOID
+}
+
 }  // extern "C"

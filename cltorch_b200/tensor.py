@@ -687,6 +687,27 @@ class ClTensor:
     def baddbmm(self, *args) -> "ClTensor":
         return self._addm("THClTensor_baddbmm", args)
 
+    def addmv(self, *args) -> "ClTensor":
+        """[res] addmv([beta,] [v,] [alpha,] mat, vec): res = beta*v + alpha*mat*vec."""
+        return self._addm("THClTensor_addmv", args)
+
+    def addr(self, *args) -> "ClTensor":
+        """[res] addr([beta,] [M,] [alpha,] vec1, vec2): res = beta*M + alpha * vec1 (x) vec2."""
+        return self._addm("THClTensor_addr", args)
+
+    def mv(self, mat: "ClTensor", vec: "ClTensor") -> "ClTensor":
+        self.resize(mat.size(1))
+        call("THClTensor_addmv", state(), self._p, 0.0, self._p, 1.0, mat._p, vec._p)
+        return self
+
+    def ger(self, v1: "ClTensor", v2: "ClTensor") -> "ClTensor":
+        self.resize(v1.size(1), v2.size(1)).zero()
+        call("THClTensor_addr", state(), self._p, 1.0, self._p, 1.0, v1._p, v2._p)
+        return self
+
+    def dot(self, other: "ClTensor") -> float:
+        return call("THClTensor_dot", state(), self._p, other._p)
+
     def mm(self, m1: "ClTensor", m2: "ClTensor") -> "ClTensor":
         # torch.mm: result zero-initialised, beta = 0 (reference src/TensorMath.lua:827-845)
         self.resize(m1.size(1), m2.size(2))

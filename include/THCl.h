@@ -358,5 +358,11 @@ THCL_API void THClTensor_min(THClState* state, THClTensor* values, THClTensor* i
 
 THCL_API void THClTensor_addmm(THClState* state, THClTensor* self, float beta, THClTensor* t, float alpha, THClTensor* mat1, THClTensor* mat2);
 THCL_API void THClTensor_baddbmm(THClState* state, THClTensor* result, float beta, THClTensor* t, float alpha, THClTensor* batch1, THClTensor* batch2);
+/* self = beta * t + alpha * mat * vec (src/lib/THClTensorMathBlas.cpp:43-105) */
+THCL_API void THClTensor_addmv(THClState* state, THClTensor* self, float beta, THClTensor* t, float alpha, THClTensor* mat, THClTensor* vec);
+/* self = beta * t + alpha * vec1 (x) vec2 (src/lib/THClTensorMathBlas.cpp:216-277) */
+THCL_API void THClTensor_addr(THClState* state, THClTensor* self, float beta, THClTensor* t, float alpha, THClTensor* vec1, THClTensor* vec2);
+/* sum of self[i] * src[i] over all elements, returned to the host (src/lib/THClTensorMathBlas.cpp:17-41) */
+THCL_API float THClTensor_dot(THClState* state, THClTensor* self, THClTensor* src);
 
 #endif /* THCL_B200_INC */

@@ -151,6 +151,21 @@ int thb200_gemm(void* stream, char transa, char transb, int64_t m, int64_t n, in
  * < 0: the status could not be read. */
 int thb200_gemm_status(void* stream, int64_t m, int64_t n, int64_t k, int64_t batch, void* workspace);
 
+/* clblasSdot as called from THClBlas_dot, src/lib/THClBlas.cpp:149-192: *d_out =
+ * sum a[i] * b[i] over two contiguous vectors, exact products accumulated in
+ * double. The result stays on the device. */
+size_t thb200_dot_scratch_bytes(int64_t n);
+int thb200_dot(void* stream, const float* a, const float* b, int64_t n, float* d_out, void* scratch,
+               size_t scratch_bytes);
+
+/* clblasSgemv as called from THClBlas_gemv, src/lib/THClBlas.cpp:194-262, column-major
+ * A (m x n, unit stride along m, leading dimension lda): trans 'n': y(m) = alpha*A*x + beta*y;
+ * trans 't': y(n) = alpha*A^T*x + beta*y. HBM-bound: A is read exactly once. */
+size_t thb200_gemv_scratch_bytes(char trans, int64_t m, int64_t n);
+int thb200_gemv(void* stream, char trans, int64_t m, int64_t n, float alpha, const float* a, int64_t lda,
+                const float* x, int64_t incx, float beta, float* y, int64_t incy, void* scratch,
+                size_t scratch_bytes);
+
 #ifdef __cplusplus
 }
 #endif

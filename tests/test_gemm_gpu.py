@@ -98,3 +98,54 @@ def test_gemm_status_word_reports_completion():
     r = cl.ClTensor().mm(a, a)
     cl.synchronize()
     assert np.isfinite(r.float()).all()
+
+
+def test_dot_addmv_addr_fixtures_from_reference_tests():
+    import cltorch_b200 as cl
+    c, d = cl.ClTensor(np.array([3, 5, 1], np.float32)), cl.ClTensor(np.array([2, 4, 8], np.float32))
+    assert c.dot(d) == 34.0                                             # unit_tensor.lua:437-443
+    C = np.array([[3, 1, 7], [3, 2, 4], [8, 5, 3]], np.float32)         # unit_tensor.lua:455-460
+    dd, e = np.array([3, 2, 5], np.float32), np.array([3, 1, 2], np.float32)
+    r = cl.ClTensor().addr(cl.ClTensor(C), cl.ClTensor(dd), cl.ClTensor(e))
+    assert np.array_equal(r.float(), C + np.outer(dd, e))
+    r = cl.ClTensor().addr(0.5, cl.ClTensor(C), 2.0, cl.ClTensor(dd), cl.ClTensor(e))
+    assert np.array_equal(r.float(), 0.5 * C + 2.0 * np.outer(dd, e))
+    assert np.array_equal(cl.ClTensor().ger(cl.ClTensor(dd), cl.ClTensor(e)).float(), np.outer(dd, e))
+
+
+@pytest.mark.parametrize("M,K", [(1, 1), (5, 3), (300, 70), (70, 9000), (9000, 70), (20000, 33), (129, 1025)])
+def test_addmv_layouts(M, K):
+    import cltorch_b200 as cl
+    a = rng_uniform(51, (M, K), -1, 1)
+    x = rng_uniform(52, (K,), -1, 1)
+    t = rng_uniform(53, (M,), -1, 1)
+    want = 0.5 * t.astype(np.float64) + 2.0 * (a.astype(np.float64) @ x.astype(np.float64))
+    scale = np.abs(a.astype(np.float64)) @ np.abs(x.astype(np.float64)) + 1.0
+    A, X, T = cl.ClTensor(a), cl.ClTensor(x), cl.ClTensor(t)
+    At = cl.ClTensor(np.ascontiguousarray(a.T)).t()                      # column-major matrix
+    for name, mat in (("row-major", A), ("column-major", At)):
+        r = cl.ClTensor().addmv(0.5, T, 2.0, mat, X)
+        assert np.all(np.abs(r.float() - want) <= 1e-5 * scale), name
+    assert np.all(np.abs(cl.ClTensor().mv(A, X).float() - a.astype(np.float64) @ x.astype(np.float64)) <= 1e-5 * scale)
+    # strided vector and a matrix with neither stride 1
+    x2 = cl.ClTensor(rng_uniform(54, (K, 2), -1, 1))
+    xs = x2.select(2, 1)
+    wide = cl.ClTensor(rng_uniform(55, (M, 2 * K), -1, 1))
+    ms = cl.ClTensor(wide.storage(), 1, [M, K], [2 * K, 2])
+    want2 = wide.float()[:, ::2].astype(np.float64) @ x2.float()[:, 0].astype(np.float64)
+    r = cl.ClTensor(M).zero().addmv(0.0, 1.0, ms, xs)
+    assert np.all(np.abs(r.float() - want2) <= 1e-5 * (np.abs(wide.float()[:, ::2].astype(np.float64)) @ np.abs(x2.float()[:, 0].astype(np.float64)) + 1))
+    with pytest.raises(cl.ClError, match="size mismatch"):
+        cl.ClTensor().addmv(T, A, T if K != M else cl.ClTensor(K + 1))
+
+
+def test_dot_large_and_strided():
+    import cltorch_b200 as cl
+    a, b = rng_uniform(56, (3000, 1001), -1, 1), rng_uniform(57, (3000, 1001), -1, 1)
+    want = float(np.sum(a.astype(np.float64) * b.astype(np.float64)))
+    scale = float(np.sum(np.abs(a.astype(np.float64) * b.astype(np.float64))))
+    assert abs(cl.ClTensor(a).dot(cl.ClTensor(b)) - want) <= 1e-6 * scale
+    A, B = cl.ClTensor(a), cl.ClTensor(np.ascontiguousarray(b.T))
+    assert abs(A.t().dot(B) - want) <= 1e-6 * scale                    # strided operand: contiguous copy first
+    with pytest.raises(cl.ClError, match="sizes do not match"):
+        A.dot(cl.ClTensor(5))
