@@ -223,6 +223,8 @@ PROTOTYPES = {
     "thb200_reduce_dim_scratch_bytes": (C.c_size_t, [C.POINTER(thb200_tensor), i]),
     "thb200_reduce_dim": (i, [C.c_void_p, i, i, C.POINTER(thb200_tensor), C.POINTER(thb200_tensor), i, f, f,
                               C.c_void_p, C.c_size_t]),
+    "thb200_reduce_dim_noalloc_capacity": (C.c_size_t, []),
+    "thb200_reduce_dim_noalloc": (i, [C.c_void_p, i, i, C.POINTER(thb200_tensor), C.POINTER(thb200_tensor), i, f, f]),
     "thb200_reduce_dim_index": (i, [C.c_void_p, i, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_int64,
                                     C.c_int64, C.c_void_p, C.c_size_t]),
     "thb200_reduce_dim_index_scratch_bytes": (C.c_size_t, [C.c_int64, C.c_int64, C.c_int64]),

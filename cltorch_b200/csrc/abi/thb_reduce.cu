@@ -5,6 +5,7 @@
 #include "../kernels/reduce_kernels.cuh"
 
 #include <cstring>
+#include <mutex>
 
 namespace thb {
 
@@ -331,6 +332,52 @@ int thb200_reduce_dim_index(void* stream, int is_max, float* values, float* indi
   if (n >= (int64_t(1) << 31)) return fail("max/min: dimension too large");
   return is_max ? argreduce<true>((cudaStream_t)stream, values, indices, src, outer, n, inner, scratch, scratch_bytes)
                 : argreduce<false>((cudaStream_t)stream, values, indices, src, outer, n, inner, scratch, scratch_bytes);
+}
+
+}  // extern "C"
+
+// ---- thb200_reduce_dim_noalloc ------------------------------------------------------
+// Built-in scratch for callers that may not allocate device memory. It lives in the
+// library's device image: every GPU that loads the library holds these 4 MiB until
+// the process exits. In host code the array's name is only a handle for the runtime,
+// not a device address: the address a kernel can use comes from cudaGetSymbolAddress,
+// asked once per device with that device current.
+#define THB_NOALLOC_SCRATCH_BYTES (4u << 20)
+static __device__ __align__(256) unsigned char thb_noalloc_scratch[THB_NOALLOC_SCRATCH_BYTES];
+
+namespace thb {
+static std::mutex g_noalloc_mu;
+static void* g_noalloc_addr[64];  // per device ordinal; nullptr until the first call on that device
+}  // namespace thb
+
+extern "C" {
+
+size_t thb200_reduce_dim_noalloc_capacity(void) { return THB_NOALLOC_SCRATCH_BYTES; }
+
+int thb200_reduce_dim_noalloc(void* stream, int modify, int reduce, const thb200_tensor* out, const thb200_tensor* in,
+                              int dim, float init, float mod_param) {
+  const size_t need = thb200_reduce_dim_scratch_bytes(in, dim);
+  if (need > THB_NOALLOC_SCRATCH_BYTES)
+    return fail("reduceDim (no-alloc): this shape needs %zu bytes of scratch but the built-in scratch holds %u bytes; "
+                "use thb200_reduce_dim with scratch of your own",
+                need, (unsigned)THB_NOALLOC_SCRATCH_BYTES);
+  int dev = 0;
+  THB_CUDA(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= 64) return fail("reduceDim (no-alloc): device ordinal %d not supported", dev);
+  void* scratch = nullptr;
+  {
+    std::lock_guard<std::mutex> lock(g_noalloc_mu);
+    if (!g_noalloc_addr[dev]) {
+      void* p = nullptr;
+      cudaError_t e = cudaGetSymbolAddress(&p, thb_noalloc_scratch);
+      if (e != cudaSuccess || !p) return fail_cuda(e, "cudaGetSymbolAddress(built-in scratch)");
+      g_noalloc_addr[dev] = p;
+    }
+    scratch = g_noalloc_addr[dev];
+  }
+  // Nothing in the scratch has to start at zero: pass 1 writes every partial that pass 2 reads.
+  return thb200_reduce_dim(stream, modify, reduce, out, in, dim, init, mod_param, (float*)scratch,
+                           THB_NOALLOC_SCRATCH_BYTES);
 }
 
 }  // extern "C"

@@ -117,6 +117,28 @@ int thb200_reduce_dim(void* stream, int modify, int reduce, const thb200_tensor*
                       const thb200_tensor* in, int dim, float init, float mod_param,
                       float* scratch, size_t scratch_bytes);
 
+/* thb200_reduce_dim for hosts that are not allowed to allocate device memory: no
+ * counterpart in the reference. Some embedders plan every device buffer up front and
+ * forbid allocation afterwards — an inference server with a fixed memory budget, a
+ * plugin loaded into another framework's process, a latency-critical loop where
+ * cudaMalloc's implicit device synchronisation is unacceptable — so they cannot hand
+ * over scratch of their own and the library may not go and get some. Here the scratch
+ * is a 4 MiB array inside the library's own device image (held by every GPU that loads
+ * the library, until the process exits); the call itself allocates and frees nothing.
+ *  - Shapes whose reduction needs more than thb200_reduce_dim_noalloc_capacity() bytes
+ *    (see thb200_reduce_dim_scratch_bytes) are refused with an error; use
+ *    thb200_reduce_dim with your own scratch for those.
+ *  - The first call on each device looks up the array's device address (a one-time
+ *    host-side query, done with that device current). Make that first call before
+ *    starting any stream capture.
+ *  - All calls on a device share the one array and it keeps the previous call's bytes.
+ *    Nothing in it has to start at zero (every partial is written before it is read),
+ *    but two calls that overlap on the GPU — different streams, or different host
+ *    threads without ordering — race on it: keep them on one stream or order them. */
+size_t thb200_reduce_dim_noalloc_capacity(void);
+int thb200_reduce_dim_noalloc(void* stream, int modify, int reduce, const thb200_tensor* out,
+                              const thb200_tensor* in, int dim, float init, float mod_param);
+
 /* THClTensor_reduceDimIndex, src/lib/THClTensorMathTransformReduce.cpp:160-185
  * with kernels src/lib/THClTensorMathTransformReduce.cl:17-102: per slice the
  * extreme value and its 1-based position stored as fp32; strict comparison in
