@@ -186,9 +186,21 @@ def c2small(T):
     T.time("add narrow-columns", lambda: out2.add(va, vb), 12 * n * 2000)
 
 
+def c3small(T):
+    """Sums and max-with-indices along both dimensions of 8192 x 8192 (profiler captures of the reductions)."""
+    cl = T.cl
+    g = np.random.Generator(np.random.PCG64(2))
+    n = 8192
+    A = cl.ClTensor(g.standard_normal((n, n), dtype=np.float32))
+    out = cl.ClTensor()
+    for d in (1, 2):
+        T.time(f"sum(A, {d})", lambda: out.sum(A, d), 4 * n * n)
+        T.time(f"max(A, {d}) with indices", lambda: A.max(d), 4 * n * n)
+
+
 def run(workload: str, steps: int, warmup: int) -> None:
     T = Timer(steps, warmup)
-    {"c1": c1, "c2": c2, "c3": c3, "c4": c4, "c4small": c4small, "c2small": c2small}[workload](T)
+    {"c1": c1, "c2": c2, "c3": c3, "c4": c4, "c4small": c4small, "c2small": c2small, "c3small": c3small}[workload](T)
     T.cl.synchronize()
     print(json.dumps({"workload": workload, "n_gpus": 1, "steps": steps, "warmup": warmup, "dtype": "f32",
                       "data": "synthetic", "hbm_peak_gbs_measured": T.peak, "l2_flush": "512 MiB fill between iterations",

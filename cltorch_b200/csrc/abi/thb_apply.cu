@@ -144,6 +144,24 @@ int launch_apply(const ApplyKernels& k, cudaStream_t st, int nt, const thb200_te
         if (plan_out) *plan_out = PLAN_TILE2D;
         if (dry_run) return 0;
         P.R = (uint32_t)R; P.C = (uint32_t)C;
+        // 128-bit variant when every access it makes is 16-byte aligned
+        bool v4 = k.tile2d_v4 != nullptr;
+        for (int i = 0; i < nt && v4; ++i) {
+          v4 = ((uintptr_t)t[i].data & 15) == 0;
+          if ((P.colmajor >> i) & 1) v4 = v4 && (R & 3) == 0 && (P.sc[i] & 3) == 0;
+          else v4 = v4 && (C & 3) == 0 && (P.sr[i] & 3) == 0;
+        }
+        if (v4) {
+          P.tilesC = (uint32_t)((C + THB_T4_C - 1) / THB_T4_C);
+          uint64_t ntiles = (uint64_t)((R + THB_T4_R - 1) / THB_T4_R) * P.tilesC;
+          P.ntiles = (uint32_t)ntiles;
+          uint64_t blocks = ntiles;
+          uint64_t cap = (uint64_t)sms * 64;
+          if (blocks > cap) blocks = cap;
+          void* args[] = {&P, &s};
+          THB_CUDA(cudaLaunchKernel(k.tile2d_v4, dim3((unsigned)blocks), dim3(256), args, 0, st));
+          return 0;
+        }
         P.tilesC = (uint32_t)((C + THB_TILE - 1) / THB_TILE);
         uint64_t ntiles = (uint64_t)((R + THB_TILE - 1) / THB_TILE) * P.tilesC;
         P.ntiles = (uint32_t)ntiles;

@@ -43,6 +43,7 @@ static void register_part(ApplyKernels* table) {
     k.strided = (const void*)&thb_apply_strided<Op_##NAME, NT>;                      \
     k.tile2d = (const void*)&thb_apply_tile2d<Op_##NAME, NT>;                        \
     k.rows2d = (const void*)&thb_apply_rows2d<Op_##NAME, NT>;                        \
+    k.tile2d_v4 = (const void*)&thb_apply_tile2d_v4<Op_##NAME, NT>;                  \
     k.nt = NT;                                                                       \
     k.reads_out = Op_##NAME::kReadsOut;                                              \
     k.name = #NAME;                                                                  \

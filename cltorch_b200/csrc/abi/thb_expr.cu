@@ -5,7 +5,7 @@
 // compiles it on first use, caching by a key made of the operand count and the
 // string (src/lib/THClApply.cpp:54-112). Here the text of apply_kernels.cuh is
 // embedded in the library, the body becomes the `apply` member of a struct, and
-// the four kernel templates are instantiated for it in one NVRTC program; the
+// the five kernel templates are instantiated for it in one NVRTC program; the
 // cubin is loaded through the CUDA runtime's library API and cached for the
 // process by (operand count, body).
 #include "thb_internal.h"
@@ -76,8 +76,11 @@ int expr_kernels(int nt, const std::string& body, const ApplyKernels** out) {
   nvrtcResult r = nvrtcCreateProgram(&prog, src.c_str(), "thb_user_expr.cu", 0, nullptr, nullptr);
   if (r != NVRTC_SUCCESS) return fail_nvrtc(r, "nvrtcCreateProgram");
   const std::string nts = std::to_string(nt);
-  const std::string names[4] = {"thb_apply_contig<UserOp, " + nts + ">", "thb_apply_strided<UserOp, " + nts + ">",
-                                "thb_apply_tile2d<UserOp, " + nts + ">", "thb_apply_rows2d<UserOp, " + nts + ">"};
+  const int kNumKernels = 5;
+  const std::string names[kNumKernels] = {
+      "thb_apply_contig<UserOp, " + nts + ">", "thb_apply_strided<UserOp, " + nts + ">",
+      "thb_apply_tile2d<UserOp, " + nts + ">", "thb_apply_rows2d<UserOp, " + nts + ">",
+      "thb_apply_tile2d_v4<UserOp, " + nts + ">"};
   for (const std::string& n : names) {
     r = nvrtcAddNameExpression(prog, n.c_str());
     if (r != NVRTC_SUCCESS) { nvrtcDestroyProgram(&prog); return fail_nvrtc(r, "nvrtcAddNameExpression"); }
@@ -100,8 +103,8 @@ int expr_kernels(int nt, const std::string& body, const ApplyKernels** out) {
   std::vector<char> cubin(n);
   r = nvrtcGetCUBIN(prog, cubin.data());
   if (r != NVRTC_SUCCESS) { nvrtcDestroyProgram(&prog); return fail_nvrtc(r, "nvrtcGetCUBIN"); }
-  std::string lowered[4];
-  for (int i = 0; i < 4; ++i) {
+  std::string lowered[kNumKernels];
+  for (int i = 0; i < kNumKernels; ++i) {
     const char* ln = nullptr;
     r = nvrtcGetLoweredName(prog, names[i].c_str(), &ln);
     if (r != NVRTC_SUCCESS || !ln) { nvrtcDestroyProgram(&prog); return fail_nvrtc(r, "nvrtcGetLoweredName"); }
@@ -113,12 +116,13 @@ int expr_kernels(int nt, const std::string& body, const ApplyKernels** out) {
   e->body = body;
   e->name = "expr";
   THB_CUDA(cudaLibraryLoadData(&e->lib, cubin.data(), nullptr, nullptr, 0, nullptr, nullptr, 0));
-  cudaKernel_t kern[4];
-  for (int i = 0; i < 4; ++i) THB_CUDA(cudaLibraryGetKernel(&kern[i], e->lib, lowered[i].c_str()));
+  cudaKernel_t kern[kNumKernels];
+  for (int i = 0; i < kNumKernels; ++i) THB_CUDA(cudaLibraryGetKernel(&kern[i], e->lib, lowered[i].c_str()));
   e->k.contig = (const void*)kern[0];
   e->k.strided = (const void*)kern[1];
   e->k.tile2d = (const void*)kern[2];
   e->k.rows2d = (const void*)kern[3];
+  e->k.tile2d_v4 = (const void*)kern[4];
   e->k.nt = nt;
   e->k.reads_out = thb_body_reads_out(body.c_str());
   e->k.name = e->name.c_str();

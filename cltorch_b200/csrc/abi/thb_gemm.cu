@@ -114,9 +114,19 @@ int thb200_gemm(void* stream, char transa, char transb, int64_t m, int64_t n, in
     const char* e = getenv("THB200_GEMM_BK");
     return (e && atoi(e) == 32) ? 32 : 16;
   }();
+  // 128 x 128 tiles when 128 x 256 ones would leave SMs idle and the narrower tiling yields more work items
+  const int sms = sm_count();
+  const int64_t tm = (m + THB_GEMM_BM - 1) / THB_GEMM_BM;
+  const int64_t tiles256 = tm * ((n + 255) / 256) * batch, tiles128 = tm * ((n + 127) / 128) * batch;
+  static const int forced_bn = [] {  // THB200_GEMM_BN=128|256 pins the tile width (tests, experiments)
+    const char* e = getenv("THB200_GEMM_BN");
+    const int v = e ? atoi(e) : 0;
+    return (v == 128 || v == 256) ? v : 0;
+  }();
+  const int bn = forced_bn ? forced_bn : ((tiles256 < sms && tiles128 > tiles256) ? 128 : 256);
   CUtensorMap map_a, map_b;
   if (int rc = make_operand_map(&map_a, w.a, m, Kp, 2 * batch, THB_GEMM_BM, bk)) return rc;
-  if (int rc = make_operand_map(&map_b, w.b, n, Kp, 2 * batch, THB_GEMM_BN, bk)) return rc;
+  if (int rc = make_operand_map(&map_b, w.b, n, Kp, 2 * batch, bn, bk)) return rc;
 
   ThbGemmParams p;
   p.c = c;
@@ -127,20 +137,24 @@ int thb200_gemm(void* stream, char transa, char transb, int64_t m, int64_t n, in
   p.kblocks = (int)(Kp / bk);  // k == 0: the split wrote zeros, so C = beta * C
   p.alpha = alpha;
   p.beta = beta;
-  p.tiles_m = (int)((m + THB_GEMM_BM - 1) / THB_GEMM_BM);
-  p.tiles_n = (int)((n + THB_GEMM_BN - 1) / THB_GEMM_BN);
+  p.tiles_m = (int)tm;
+  p.tiles_n = (int)((n + bn - 1) / bn);
   p.batch = (int)batch;
   p.status = w.status;
   const int64_t total_tiles = (int64_t)p.tiles_m * p.tiles_n * batch;
   if (total_tiles > INT32_MAX) return fail("gemm: too many tiles");
-  const int64_t ctas = total_tiles < sm_count() ? total_tiles : sm_count();
-  if (bk == 32) {
-    THB_CUDA(cudaFuncSetAttribute(thb_gemm_3xtf32<32, 2>, cudaFuncAttributeMaxDynamicSharedMemorySize, ThbGemmCfg<32, 2>::kSmem));
-    thb_gemm_3xtf32<32, 2><<<(unsigned)ctas, THB_GEMM_THREADS, ThbGemmCfg<32, 2>::kSmem, st>>>(map_a, map_b, p);
-  } else {
-    THB_CUDA(cudaFuncSetAttribute(thb_gemm_3xtf32<16, 4>, cudaFuncAttributeMaxDynamicSharedMemorySize, ThbGemmCfg<16, 4>::kSmem));
-    thb_gemm_3xtf32<16, 4><<<(unsigned)ctas, THB_GEMM_THREADS, ThbGemmCfg<16, 4>::kSmem, st>>>(map_a, map_b, p);
-  }
+  const unsigned ctas = (unsigned)(total_tiles < sms ? total_tiles : sms);
+#define THB_LAUNCH_GEMM(BN_, BK_, ST_)                                                                                   \
+  do {                                                                                                                   \
+    THB_CUDA(cudaFuncSetAttribute(thb_gemm_3xtf32<BN_, BK_, ST_>, cudaFuncAttributeMaxDynamicSharedMemorySize,           \
+                                  ThbGemmCfg<BN_, BK_, ST_>::kSmem));                                                    \
+    thb_gemm_3xtf32<BN_, BK_, ST_><<<ctas, THB_GEMM_THREADS, ThbGemmCfg<BN_, BK_, ST_>::kSmem, st>>>(map_a, map_b, p);   \
+  } while (0)
+  if (bn == 256 && bk == 32) THB_LAUNCH_GEMM(256, 32, 2);
+  else if (bn == 256) THB_LAUNCH_GEMM(256, 16, 4);
+  else if (bk == 32) THB_LAUNCH_GEMM(128, 32, 3);
+  else THB_LAUNCH_GEMM(128, 16, 6);
+#undef THB_LAUNCH_GEMM
   THB_CUDA(cudaGetLastError());
   return 0;
 }

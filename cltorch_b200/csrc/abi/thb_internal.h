@@ -36,6 +36,7 @@ struct ApplyKernels {
   const void* contig = nullptr;
   const void* strided = nullptr;
   const void* tile2d = nullptr;
+  const void* tile2d_v4 = nullptr;
   const void* rows2d = nullptr;
   int nt = 0;
   bool reads_out = true;

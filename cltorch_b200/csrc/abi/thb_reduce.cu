@@ -125,6 +125,17 @@ static uint32_t pick_chunks(int64_t nslices, int64_t rsize) {
   return (uint32_t)chunks;
 }
 
+// Whether 4 adjacent slices of a strided-dimension reduction are 4 consecutive, 16-byte
+// aligned floats in every row: then one thread takes 4 slices with 128-bit loads.
+static bool slices_vectorise(const float* data, const Collapsed& in_wo_rdim, int64_t rstride) {
+  const int d = in_wo_rdim.dims;
+  if (((uintptr_t)data & 15) != 0 || (rstride & 3) != 0) return false;
+  if (in_wo_rdim.stride[d - 1] != 1 || (in_wo_rdim.size[d - 1] & 3) != 0) return false;
+  for (int i = 0; i + 1 < d; ++i)
+    if ((in_wo_rdim.stride[i] & 3) != 0) return false;
+  return true;
+}
+
 struct ReduceDimArgs {
   cudaStream_t st;
   ThbLayout out, in;
@@ -132,6 +143,7 @@ struct ReduceDimArgs {
   float init, mparam;
   float* scratch;
   uint32_t nchunks, chunk_len;
+  bool vec4 = false;
   cudaError_t err = cudaSuccess;
 
   template <class Mod, class Red>
@@ -151,9 +163,15 @@ struct ReduceDimArgs {
     }
     uint64_t bx = ((uint64_t)nslices + THB_RD_THREADS - 1) / THB_RD_THREADS;
     if (bx > 65535u * 16u) bx = 65535u * 16u;
-    dim3 grid((unsigned)bx, nchunks);
-    thb_reduce_dim_noncontig<Mod, Red><<<grid, THB_RD_THREADS, 0, st>>>(
-        out, in, rsize, rstride, nslices, chunk_len, nchunks, init, mparam, (typename Red::acc_t*)scratch);
+    if (vec4) {
+      uint64_t bq = ((uint64_t)(nslices >> 2) + THB_RD_THREADS - 1) / THB_RD_THREADS;
+      if (bq > 65535u * 16u) bq = 65535u * 16u;
+      thb_reduce_dim_noncontig_v4<Mod, Red><<<dim3((unsigned)bq, nchunks), THB_RD_THREADS, 0, st>>>(
+          out, in, rsize, rstride, nslices, chunk_len, nchunks, init, mparam, (typename Red::acc_t*)scratch);
+    } else {
+      thb_reduce_dim_noncontig<Mod, Red><<<dim3((unsigned)bx, nchunks), THB_RD_THREADS, 0, st>>>(
+          out, in, rsize, rstride, nslices, chunk_len, nchunks, init, mparam, (typename Red::acc_t*)scratch);
+    }
     err = cudaGetLastError();
     if (err != cudaSuccess || nchunks == 1) return;
     thb_reduce_dim_fold_chunks<Red><<<(unsigned)bx, THB_RD_THREADS, 0, st>>>(
@@ -205,7 +223,8 @@ static int argreduce(cudaStream_t st, float* values, float* indices, const float
     return 0;
   }
   const int64_t nslices = outer * inner;
-  const uint32_t nchunks = pick_chunks(nslices, n);
+  const bool vec4 = (inner & 3) == 0 && ((uintptr_t)src & 15) == 0;
+  const uint32_t nchunks = pick_chunks(vec4 ? nslices >> 2 : nslices, n);
   const uint32_t chunk_len = (uint32_t)((n + nchunks - 1) / nchunks);
   float* pval = scratch;
   int* pidx = reinterpret_cast<int*>(scratch + (size_t)nchunks * nslices);
@@ -213,9 +232,15 @@ static int argreduce(cudaStream_t st, float* values, float* indices, const float
     return fail("max/min: scratch too small (%zu bytes, need %zu)", scratch_bytes, (size_t)nchunks * nslices * 8);
   int64_t bx = (nslices + THB_RD_THREADS - 1) / THB_RD_THREADS;
   if (bx > 65535 * 16) bx = 65535 * 16;
-  dim3 grid((unsigned)bx, nchunks);
-  thb_argreduce_cols<IS_MAX><<<grid, THB_RD_THREADS, 0, st>>>(values, indices, src, outer, (thb_u32)n, inner, chunk_len,
-                                                             nchunks, pval, pidx);
+  if (vec4) {
+    int64_t bq = ((nslices >> 2) + THB_RD_THREADS - 1) / THB_RD_THREADS;
+    if (bq > 65535 * 16) bq = 65535 * 16;
+    thb_argreduce_cols_v4<IS_MAX><<<dim3((unsigned)bq, nchunks), THB_RD_THREADS, 0, st>>>(
+        values, indices, src, outer, (thb_u32)n, inner, chunk_len, nchunks, pval, pidx);
+  } else {
+    thb_argreduce_cols<IS_MAX><<<dim3((unsigned)bx, nchunks), THB_RD_THREADS, 0, st>>>(
+        values, indices, src, outer, (thb_u32)n, inner, chunk_len, nchunks, pval, pidx);
+  }
   THB_CUDA(cudaGetLastError());
   if (nchunks > 1) {
     thb_argreduce_fold_chunks<IS_MAX><<<(unsigned)bx, THB_RD_THREADS, 0, st>>>(values, indices, pval, pidx, nslices, nchunks);
@@ -283,7 +308,10 @@ size_t thb200_reduce_dim_scratch_bytes(const thb200_tensor* in, int dim) {
   int64_t nslices, rsize, rstride;
   if (reduce_dim_geometry(in, dim, &nslices, &rsize, &rstride)) return 0;
   if (rstride == 1 || nslices == 0) return 0;
-  uint32_t chunks = pick_chunks(nslices, rsize);
+  Collapsed ci;
+  if (!collapse(in->ndim, in->size, in->stride, dim, &ci)) return 0;
+  const bool vec4 = slices_vectorise(in->data, ci, rstride);
+  uint32_t chunks = pick_chunks(vec4 ? nslices >> 2 : nslices, rsize);
   return chunks > 1 ? (size_t)chunks * nslices * sizeof(double) : 0;
 }
 
@@ -307,7 +335,8 @@ int thb200_reduce_dim(void* stream, int modify, int reduce, const thb200_tensor*
   fill_layout(&a.in, in->data, ci);
   a.rsize = (uint32_t)rsize; a.rstride = (uint32_t)rstride; a.nslices = (uint32_t)nslices;
   a.init = init; a.mparam = mod_param; a.scratch = scratch;
-  a.nchunks = rstride == 1 ? 1 : pick_chunks(nslices, rsize);
+  a.vec4 = rstride != 1 && slices_vectorise(in->data, ci, rstride);
+  a.nchunks = rstride == 1 ? 1 : pick_chunks(a.vec4 ? nslices >> 2 : nslices, rsize);
   a.chunk_len = (uint32_t)((rsize + a.nchunks - 1) / a.nchunks);
   if (a.nchunks > 1 && (!scratch || scratch_bytes < (size_t)a.nchunks * nslices * sizeof(double)))
     return fail("reduceDim: scratch too small (%zu bytes, need %zu)", scratch_bytes,
@@ -319,7 +348,8 @@ int thb200_reduce_dim(void* stream, int modify, int reduce, const thb200_tensor*
 
 size_t thb200_reduce_dim_index_scratch_bytes(int64_t outer, int64_t n, int64_t inner) {
   if (inner <= 1 || outer * inner == 0) return 0;
-  uint32_t chunks = pick_chunks(outer * inner, n);
+  // sized for the 128-bit variant (4 slices per thread, hence up to 4 times the chunks)
+  uint32_t chunks = pick_chunks((inner & 3) == 0 ? (outer * inner) >> 2 : outer * inner, n);
   return chunks > 1 ? (size_t)chunks * outer * inner * (sizeof(float) + sizeof(int)) : 0;
 }
 

@@ -316,6 +316,107 @@ thb_apply_tile2d(ThbTile2d P, ThbScalars s) {
 }
 
 // ---------------------------------------------------------------------------
+// The same job with 128-bit global accesses on both sides: tiles of 64 rows x
+// 32 columns, 256 threads. A column-major-like operand is read as float4 along r
+// (16 threads cover the 64 rows of one column: 256 contiguous bytes), kept in
+// shared memory as tile[c][r], and picked up per element by the row-major
+// mapping, in which a thread owns 4 consecutive columns of one row. Needs every
+// operand 16-byte aligned, row-major ones with C % 4 == 0 and a row stride that
+// is a multiple of 4, column-major ones with R % 4 == 0 and a column stride that
+// is a multiple of 4; the host falls back to thb_apply_tile2d otherwise.
+// ---------------------------------------------------------------------------
+#define THB_T4_R 64
+#define THB_T4_C 32
+#define THB_T4_PITCH 66  // 66 % 32 == 2: the per-element reads below are at most 2-way bank conflicts
+
+template <class Op, int NT>
+__global__ void __launch_bounds__(256)
+thb_apply_tile2d_v4(ThbTile2d P, ThbScalars s) {
+  __shared__ float tile[3][THB_T4_C][THB_T4_PITCH];
+  float p1 = 0.f, p2 = 0.f;
+  if (s.pointTensor1) p1 = *s.pointTensor1;
+  if (s.pointTensor2) p2 = *s.pointTensor2;
+
+  const int tid = threadIdx.x;
+  const int cr = tid & 15, cc = tid >> 4;  // column-major mapping: rows 4cr..4cr+3 of columns cc, cc+16
+  const int rc = tid & 7, rr = tid >> 3;   // row-major mapping: columns 4rc..4rc+3 of rows rr, rr+32
+  for (thb_u32 t = blockIdx.x; t < P.ntiles; t += gridDim.x) {
+    const thb_u32 r0 = (t / P.tilesC) * THB_T4_R;
+    const thb_u32 c0 = (t % P.tilesC) * THB_T4_C;
+
+#pragma unroll
+    for (int q = 0; q < NT; ++q) {
+      if (((P.colmajor >> q) & 1) && (q > 0 || Op::kReadsOut)) {
+#pragma unroll
+        for (int pass = 0; pass < 2; ++pass) {
+          const thb_u32 r = r0 + 4 * cr, c = c0 + cc + 16 * pass;
+          if (r < P.R && c < P.C) {
+            const float4 v = *reinterpret_cast<const float4*>(P.data[q] + r + (thb_i64)c * P.sc[q]);
+            float2* dst = reinterpret_cast<float2*>(&tile[q][cc + 16 * pass][4 * cr]);
+            dst[0] = make_float2(v.x, v.y);
+            dst[1] = make_float2(v.z, v.w);
+          }
+        }
+      }
+    }
+    __syncthreads();
+
+    float4 v[3][2];
+#pragma unroll
+    for (int pass = 0; pass < 2; ++pass) {
+      const thb_u32 r = r0 + rr + 32 * pass, c = c0 + 4 * rc;
+      const bool in = (r < P.R && c < P.C);
+#pragma unroll
+      for (int q = 0; q < NT; ++q) {
+        v[q][pass] = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (in && (q > 0 || Op::kReadsOut)) {
+          if ((P.colmajor >> q) & 1) {
+            v[q][pass].x = tile[q][4 * rc + 0][rr + 32 * pass];
+            v[q][pass].y = tile[q][4 * rc + 1][rr + 32 * pass];
+            v[q][pass].z = tile[q][4 * rc + 2][rr + 32 * pass];
+            v[q][pass].w = tile[q][4 * rc + 3][rr + 32 * pass];
+          } else {
+            v[q][pass] = *reinterpret_cast<const float4*>(P.data[q] + (thb_i64)r * P.sr[q] + c);
+          }
+        }
+      }
+      if (in) {
+        float4& o = v[0][pass];
+        const float4& x = v[NT >= 2 ? 1 : 0][pass];
+        const float4& y = v[NT >= 3 ? 2 : 0][pass];
+        Op::apply(&o.x, &x.x, &y.x, s.val1, s.val2, &p1, &p2);
+        Op::apply(&o.y, &x.y, &y.y, s.val1, s.val2, &p1, &p2);
+        Op::apply(&o.z, &x.z, &y.z, s.val1, s.val2, &p1, &p2);
+        Op::apply(&o.w, &x.w, &y.w, s.val1, s.val2, &p1, &p2);
+        if (!(P.colmajor & 1)) *reinterpret_cast<float4*>(P.data[0] + (thb_i64)r * P.sr[0] + c) = o;
+      }
+    }
+
+    if (P.colmajor & 1) {
+      __syncthreads();  // everyone has taken its inputs out of tile[0]
+#pragma unroll
+      for (int pass = 0; pass < 2; ++pass) {
+        tile[0][4 * rc + 0][rr + 32 * pass] = v[0][pass].x;
+        tile[0][4 * rc + 1][rr + 32 * pass] = v[0][pass].y;
+        tile[0][4 * rc + 2][rr + 32 * pass] = v[0][pass].z;
+        tile[0][4 * rc + 3][rr + 32 * pass] = v[0][pass].w;
+      }
+      __syncthreads();
+#pragma unroll
+      for (int pass = 0; pass < 2; ++pass) {
+        const thb_u32 r = r0 + 4 * cr, c = c0 + cc + 16 * pass;
+        if (r < P.R && c < P.C) {
+          const float2* src = reinterpret_cast<const float2*>(&tile[0][cc + 16 * pass][4 * cr]);
+          const float2 lo = src[0], hi = src[1];
+          *reinterpret_cast<float4*>(P.data[0] + r + (thb_i64)c * P.sc[0]) = make_float4(lo.x, lo.y, hi.x, hi.y);
+        }
+      }
+    }
+    __syncthreads();  // tiles are reused by the next iteration
+  }
+}
+
+// ---------------------------------------------------------------------------
 // Whether an operator body reads *out before overwriting it: it does unless
 // "*out" occurs exactly once and is directly followed by a plain '='.
 // ---------------------------------------------------------------------------

@@ -33,18 +33,18 @@
 #include <stdint.h>
 
 #define THB_GEMM_BM 128
-#define THB_GEMM_BN 256
 #define THB_GEMM_THREADS 192
-#define THB_GEMM_TMEM_COLS 512  // two 128 x 256 fp32 accumulators
 #define THB_GEMM_WAIT_LIMIT_NS 2000000000ull  // 2 s
 #define THB_GEMM_GROUP_M 16
 
-// Shared-memory budget of one configuration: k-block depth BK (32 = 128-byte
+// Shared-memory budget of one configuration: tile width BN (256, or 128 for problems
+// with too few 128 x 256 tiles to fill the GPU), k-block depth BK (32 = 128-byte
 // swizzle, 16 = 64-byte swizzle) and ring length STAGES.
-template <int BK, int STAGES>
+template <int BN, int BK, int STAGES>
 struct ThbGemmCfg {
   static constexpr int kTileA = THB_GEMM_BM * BK * 4;
-  static constexpr int kTileB = THB_GEMM_BN * BK * 4;
+  static constexpr int kTileB = BN * BK * 4;
+  static constexpr int kTmemCols = 2 * BN;  // two 128 x BN fp32 accumulators
   static constexpr int kStage = 2 * kTileA + 2 * kTileB;  // A_hi, A_lo, B_hi, B_lo
   static constexpr int kSmem = STAGES * kStage + 1024 /*alignment slack*/ + 256 /*barriers*/;
 };
@@ -191,11 +191,11 @@ struct ThbGemmParams {
 
 // Persistent: CTA i works on tiles i, i + gridDim.x, ... The k loop of tile t+1
 // overlaps the epilogue of tile t through two TMEM accumulators.
-template <int BK, int STAGES>
+template <int BN, int BK, int STAGES>
 __global__ void __launch_bounds__(THB_GEMM_THREADS, 1)
 thb_gemm_3xtf32(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                 ThbGemmParams p) {
-  typedef ThbGemmCfg<BK, STAGES> Cfg;
+  typedef ThbGemmCfg<BN, BK, STAGES> Cfg;
   extern __shared__ uint8_t smem_raw[];
   // tiles need 1024-byte alignment for the swizzle
   uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
@@ -228,7 +228,7 @@ thb_gemm_3xtf32(const __grid_constant__ CUtensorMap map_a, const __grid_constant
   }
   if (warp == 1) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(thb_smem_u32(tmem_slot)),
-                 "r"(THB_GEMM_TMEM_COLS) : "memory");
+                 "r"(Cfg::kTmemCols) : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
   }
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -267,8 +267,8 @@ thb_gemm_3xtf32(const __grid_constant__ CUtensorMap map_a, const __grid_constant
           const int k0 = kb * BK;
           thb_tma_load_3d(thb_smem_u32(st), &map_a, full, k0, tile_m * THB_GEMM_BM, batch * 2 + 0);
           thb_tma_load_3d(thb_smem_u32(st + Cfg::kTileA), &map_a, full, k0, tile_m * THB_GEMM_BM, batch * 2 + 1);
-          thb_tma_load_3d(thb_smem_u32(st + 2 * Cfg::kTileA), &map_b, full, k0, tile_n * THB_GEMM_BN, batch * 2 + 0);
-          thb_tma_load_3d(thb_smem_u32(st + 2 * Cfg::kTileA + Cfg::kTileB), &map_b, full, k0, tile_n * THB_GEMM_BN,
+          thb_tma_load_3d(thb_smem_u32(st + 2 * Cfg::kTileA), &map_b, full, k0, tile_n * BN, batch * 2 + 0);
+          thb_tma_load_3d(thb_smem_u32(st + 2 * Cfg::kTileA + Cfg::kTileB), &map_b, full, k0, tile_n * BN,
                           batch * 2 + 1);
         }
       }
@@ -281,7 +281,7 @@ thb_gemm_3xtf32(const __grid_constant__ CUtensorMap map_a, const __grid_constant
   } else if (warp == 1) {
     if (lane == 0) {
       // ---- MMA issuer ----
-      const uint32_t idesc = thb_umma_idesc_tf32(THB_GEMM_BM, THB_GEMM_BN);
+      const uint32_t idesc = thb_umma_idesc_tf32(THB_GEMM_BM, BN);
       long long it = 0;
       int t = 0;  // tiles done by this CTA
       int fail_t = 0;
@@ -289,7 +289,7 @@ thb_gemm_3xtf32(const __grid_constant__ CUtensorMap map_a, const __grid_constant
       for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, ++t) {
         const int acc = t & 1;
         fail_t = t;
-        const uint32_t d_tmem = tmem_base + (uint32_t)(acc * THB_GEMM_BN);
+        const uint32_t d_tmem = tmem_base + (uint32_t)(acc * BN);
         if (t >= 2 && !thb_mbar_wait(thb_smem_u32(&bar_acc_empty[acc]), ((uint32_t)(t >> 1) - 1) & 1, abort_flag)) {
           if (!*abort_flag) { *abort_flag = 1; atomicCAS(p.status, 0, 4); }
           ok = false;
@@ -342,9 +342,9 @@ thb_gemm_3xtf32(const __grid_constant__ CUtensorMap map_a, const __grid_constant
       const int row = tile_m * THB_GEMM_BM + lane_group * 32 + lane;
       float* cb = p.c + (long long)batch * p.batch_stride_c + row;
 #pragma unroll 1
-      for (int c0 = 0; c0 < THB_GEMM_BN; c0 += 32) {
+      for (int c0 = 0; c0 < BN; c0 += 32) {
         uint32_t r[32];
-        const uint32_t taddr = tmem_base + ((uint32_t)(lane_group * 32) << 16) + (uint32_t)(acc * THB_GEMM_BN + c0);
+        const uint32_t taddr = tmem_base + ((uint32_t)(lane_group * 32) << 16) + (uint32_t)(acc * BN + c0);
         asm volatile(
             "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
             "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
@@ -355,7 +355,7 @@ thb_gemm_3xtf32(const __grid_constant__ CUtensorMap map_a, const __grid_constant
               "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
             : "r"(taddr));
         asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-        const int col0 = tile_n * THB_GEMM_BN + c0;
+        const int col0 = tile_n * BN + c0;
         if (row < p.m && col0 < p.n) {
           // all reads of C first (32 independent loads in flight), then the stores
           float cv[32];
@@ -385,6 +385,6 @@ thb_gemm_3xtf32(const __grid_constant__ CUtensorMap map_a, const __grid_constant
   __syncthreads();
   if (warp == 1) {
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(THB_GEMM_TMEM_COLS) : "memory");
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(Cfg::kTmemCols) : "memory");
   }
 }

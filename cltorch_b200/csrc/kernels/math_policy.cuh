@@ -21,7 +21,8 @@ __device__ __forceinline__ float thb_atan(float x) { return atanf(x); }
 __device__ __forceinline__ float thb_cosh(float x) { return coshf(x); }
 // tanh to within 1 ulp, so that products such as tanh(x)*x stay within 2 ulp of a
 // correctly rounded evaluation (tanhf alone is documented at 2 ulp and measured
-// 3 ulp in that product). em = expm1(2|x|) in double from a degree-9 polynomial
+// 3 ulp in that product). |x| <= 1 uses a Pade approximant in double; beyond that,
+// em = expm1(2|x|) in double from a degree-9 polynomial
 // after the usual ln2 range reduction (relative error < 1e-12), then
 // em / (em + 2) with a float reciprocal refined by one Newton step in double:
 // about 25 fp64 instructions, a fraction of the library tanh(double).
@@ -29,6 +30,17 @@ __device__ __forceinline__ float thb_tanh(float xf) {
   const float ax = fabsf(xf);
   if (!(ax <= 20.0f)) return (ax != ax) ? xf : copysignf(1.0f, xf);  // NaN, or saturated
   if (ax < 2.44140625e-4f) return fmaf(xf * xf * xf, -0.333333343f, xf);  // |x| < 2^-12: x - x^3/3
+  if (ax <= 1.0f) {
+    // |x| <= 1: the [7/6] Pade approximant x*(135135 + 17325 x^2 + 378 x^4 + x^6) /
+    // (135135 + 62370 x^2 + 3150 x^4 + 28 x^6), relative error < 3e-12 on this range,
+    // about 11 fp64 instructions
+    const double x = (double)xf, q = x * x;
+    const double num = x * fma(fma(fma(q, 1.0, 378.0), q, 17325.0), q, 135135.0);
+    const double den = fma(fma(fma(q, 28.0, 3150.0), q, 62370.0), q, 135135.0);
+    double y = (double)__frcp_rn((float)den);
+    y = y * fma(-den, y, 2.0);
+    return (float)(num * y);
+  }
   const double x2 = 2.0 * (double)ax;
   const double n = rint(x2 * 1.4426950408889634);
   double r = fma(n, -6.93147180369123816490e-01, x2);

@@ -78,6 +78,10 @@ thb_reduce_all_pass1_contig(const float* in, thb_i64 n, int head, float init, fl
   const float4* in4 = reinterpret_cast<const float4*>(in + head);
   acc_t acc[4] = {(acc_t)init, (acc_t)init, (acc_t)init, (acc_t)init};
 
+  // Grid-stride over 32 KB pieces (256 threads x 8 vectors): at any moment the grid streams
+  // through one window of consecutive pieces. Measured on 8 GiB: 7.1 TB/s, against 6.6 TB/s
+  // with the 8 vectors of a thread spread 2.4 MB apart and 5.7 TB/s with one contiguous
+  // share per block.
   const thb_i64 step = (thb_i64)gridDim.x * (THB_RA_THREADS * THB_RA_UNROLL);
   for (thb_i64 base = (thb_i64)blockIdx.x * (THB_RA_THREADS * THB_RA_UNROLL) + threadIdx.x; base < nvec;
        base += step) {
@@ -286,6 +290,52 @@ thb_reduce_dim_noncontig(ThbLayout out, ThbLayout in, thb_u32 rsize, thb_u32 rst
   }
 }
 
+// The same with one thread per 4 adjacent slices (128-bit loads): for layouts in which
+// slices 4k..4k+3 are 4 consecutive floats at a 16-byte aligned address in every row of
+// the reduced dimension. 8 rows in flight per thread.
+template <class Mod, class Red>
+__global__ void __launch_bounds__(THB_RD_THREADS)
+thb_reduce_dim_noncontig_v4(ThbLayout out, ThbLayout in, thb_u32 rsize, thb_u32 rstride, thb_u32 nslices,
+                            thb_u32 chunk_len, thb_u32 nchunks, float init, float mparam,
+                            typename Red::acc_t* partial) {
+  typedef typename Red::acc_t acc_t;
+  const thb_u32 chunk = blockIdx.y;
+  const thb_u32 r0 = chunk * chunk_len;
+  const thb_u32 r1 = min(rsize, r0 + chunk_len);
+  const thb_u32 nquads = nslices >> 2;
+  for (thb_u64 q64 = (thb_u64)blockIdx.x * THB_RD_THREADS + threadIdx.x; q64 < nquads;
+       q64 += (thb_u64)gridDim.x * THB_RD_THREADS) {
+    const thb_u32 s = (thb_u32)q64 << 2;
+    const float* p = in.data + thb_offset(in, s);
+    acc_t acc[4] = {(acc_t)init, (acc_t)init, (acc_t)init, (acc_t)init};
+    thb_u32 r = r0;
+    for (; r + 8 <= r1; r += 8) {
+      float4 v[8];
+#pragma unroll
+      for (int u = 0; u < 8; ++u) v[u] = *reinterpret_cast<const float4*>(p + (thb_u64)(r + u) * rstride);
+#pragma unroll
+      for (int u = 0; u < 8; ++u) {
+        acc[0] = Red::apply(acc[0], Mod::apply(v[u].x, mparam, 0.f));
+        acc[1] = Red::apply(acc[1], Mod::apply(v[u].y, mparam, 0.f));
+        acc[2] = Red::apply(acc[2], Mod::apply(v[u].z, mparam, 0.f));
+        acc[3] = Red::apply(acc[3], Mod::apply(v[u].w, mparam, 0.f));
+      }
+    }
+    for (; r < r1; ++r) {
+      const float4 v = *reinterpret_cast<const float4*>(p + (thb_u64)r * rstride);
+      acc[0] = Red::apply(acc[0], Mod::apply(v.x, mparam, 0.f));
+      acc[1] = Red::apply(acc[1], Mod::apply(v.y, mparam, 0.f));
+      acc[2] = Red::apply(acc[2], Mod::apply(v.z, mparam, 0.f));
+      acc[3] = Red::apply(acc[3], Mod::apply(v.w, mparam, 0.f));
+    }
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      if (nchunks == 1) out.data[thb_offset(out, s + j)] = (float)acc[j];
+      else partial[(thb_u64)chunk * nslices + s + j] = acc[j];
+    }
+  }
+}
+
 template <class Red>
 __global__ void __launch_bounds__(THB_RD_THREADS)
 thb_reduce_dim_fold_chunks(ThbLayout out, const typename Red::acc_t* partial, thb_u32 nslices, thb_u32 nchunks,
@@ -424,6 +474,58 @@ thb_argreduce_cols(float* values, float* indices, const float* src, thb_i64 oute
     } else {
       pval[(thb_i64)chunk * nslices + s] = v;
       pidx[(thb_i64)chunk * nslices + s] = idx;
+    }
+  }
+}
+
+// The same with one thread per 4 adjacent inner positions (inner % 4 == 0, src 16-byte aligned).
+template <bool IS_MAX>
+__global__ void __launch_bounds__(THB_RD_THREADS)
+thb_argreduce_cols_v4(float* values, float* indices, const float* src, thb_i64 outer, thb_u32 n, thb_i64 inner,
+                      thb_u32 chunk_len, thb_u32 nchunks, float* pval, int* pidx) {
+  const thb_i64 nslices = outer * inner;
+  const thb_i64 nquads = nslices >> 2;
+  const thb_u32 chunk = blockIdx.y;
+  const thb_u32 r0 = chunk * chunk_len;
+  const thb_u32 r1 = min(n, r0 + chunk_len);
+  for (thb_i64 q = (thb_i64)blockIdx.x * THB_RD_THREADS + threadIdx.x; q < nquads;
+       q += (thb_i64)gridDim.x * THB_RD_THREADS) {
+    const thb_i64 s = q << 2;
+    const thb_i64 o = s / inner, i = s - o * inner;
+    const float* p = src + (o * n) * inner + i;
+    float v[4];
+    int idx[4];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) { v[j] = ThbArg<IS_MAX>::start(); idx[j] = -1; }
+    thb_u32 r = r0;
+    for (; r + 8 <= r1; r += 8) {
+      float4 x[8];
+#pragma unroll
+      for (int u = 0; u < 8; ++u) x[u] = *reinterpret_cast<const float4*>(p + (thb_i64)(r + u) * inner);
+#pragma unroll
+      for (int u = 0; u < 8; ++u) {
+        if (ThbArg<IS_MAX>::strictly(x[u].x, v[0])) { v[0] = x[u].x; idx[0] = r + u; }
+        if (ThbArg<IS_MAX>::strictly(x[u].y, v[1])) { v[1] = x[u].y; idx[1] = r + u; }
+        if (ThbArg<IS_MAX>::strictly(x[u].z, v[2])) { v[2] = x[u].z; idx[2] = r + u; }
+        if (ThbArg<IS_MAX>::strictly(x[u].w, v[3])) { v[3] = x[u].w; idx[3] = r + u; }
+      }
+    }
+    for (; r < r1; ++r) {
+      const float4 x = *reinterpret_cast<const float4*>(p + (thb_i64)r * inner);
+      if (ThbArg<IS_MAX>::strictly(x.x, v[0])) { v[0] = x.x; idx[0] = r; }
+      if (ThbArg<IS_MAX>::strictly(x.y, v[1])) { v[1] = x.y; idx[1] = r; }
+      if (ThbArg<IS_MAX>::strictly(x.z, v[2])) { v[2] = x.z; idx[2] = r; }
+      if (ThbArg<IS_MAX>::strictly(x.w, v[3])) { v[3] = x.w; idx[3] = r; }
+    }
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      if (nchunks == 1) {
+        values[s + j] = v[j];
+        indices[s + j] = (float)(idx[j] < 0 ? -1 : idx[j] + 1);
+      } else {
+        pval[(thb_i64)chunk * nslices + s + j] = v[j];
+        pidx[(thb_i64)chunk * nslices + s + j] = idx[j];
+      }
     }
   }
 }

@@ -215,6 +215,29 @@ def test_column_narrowed_views_take_the_row_vector_path(rows, cols, pitch):
     a.check(0, "expression on narrowed views")
 
 
+@pytest.mark.parametrize("rows,cols", [(64, 32), (128, 96), (68, 36), (200, 132), (4, 4), (1028, 516)])
+def test_transposed_operands_take_the_tile_path(rows, cols):
+    """Transpose views with 16-byte friendly extents (128-bit tile kernel), destination row- or column-major."""
+    import cltorch_b200 as cl
+    n = rows * cols
+    # contiguous (rows x cols) destination, two transposed sources
+    a = Pair(rng_uniform(44, (n,), -1, 1), 0, [rows, cols], [cols, 1])
+    b = Pair(rng_uniform(45, (n,), -1, 1), 0, [rows, cols], [1, rows])
+    c = Pair(rng_uniform(46, (n,), -1, 1), 0, [rows, cols], [1, rows])
+    a.cl.addcmul(0.5, b.cl, c.cl); O.apply("ADDCMUL_3", [a.view, b.view, c.view], 0.5)
+    a.check(0, "row-major += 0.5 * transposed * transposed")
+    # transposed destination
+    b.cl.add(a.cl); O.apply("ADD_2", [b.view, a.view])
+    b.check(0, "transposed += row-major")
+    b.cl.addcmul(2.0, c.cl, a.cl); O.apply("ADDCMUL_3", [b.view, c.view, a.view], 2.0)
+    b.check(0, "transposed += 2 * transposed * row-major")
+    # write-only transposed destination through an expression
+    b.cl.map_on_gpu(a.cl, "x = y * 3")
+    b.view.numpy()[...] = a.view.numpy() * np.float32(3)
+    b.check(0, "transposed = row-major * 3")
+    a.check(0, "source untouched")
+
+
 def test_mixed_alignment_falls_back_to_strided():
     a = Pair(rng_uniform(10, (5000,)), 1, [4000], None)
     b = Pair(rng_uniform(11, (5000,)), 2, [4000], None)
