@@ -99,6 +99,7 @@ def cpu_chain(sample_elems: int, reps: int):
     import numpy as np
     from oracle import oracle as O
     L = O.lib()
+    L.orc_set_num_threads(len(os.sched_getaffinity(0)))  # torchrun exports OMP_NUM_THREADS=1 to its ranks
     g = np.random.Generator(np.random.PCG64(4))
     x = g.random(sample_elems, dtype=np.float32)
     ptr = C.c_void_p(x.ctypes.data)

@@ -112,18 +112,25 @@ struct ReduceAllArgs {
   }
 };
 
-// How many chunks the reduced dimension is cut into so that a reduction with few
-// slices still fills the GPU.
-static uint32_t pick_chunks(int64_t nslices, int64_t rsize) {
-  const int64_t want_threads = (int64_t)sm_count() * 2048;
-  if (nslices >= want_threads || rsize < 256) return 1;
-  int64_t chunks = (want_threads + nslices - 1) / nslices;
-  int64_t max_chunks = rsize / 64;
+// How many chunks the reduced dimension is cut into so that a reduction with few slices
+// still fills the GPU: as many as fit one wave of resident blocks (`threads` worker threads
+// per chunk in blocks of THB_RD_THREADS, `blocks_per_sm` of them resident), never a
+// fraction of a wave more, and none when the slices alone fill half the GPU.
+static uint32_t pick_chunks(int64_t threads, int64_t rsize, int blocks_per_sm) {
+  const int64_t wave = (int64_t)sm_count() * blocks_per_sm;
+  const int64_t bx = (threads + THB_RD_THREADS - 1) / THB_RD_THREADS;
+  if (bx * 2 > wave || rsize < 256) return 1;
+  int64_t chunks = wave / bx;
+  const int64_t max_chunks = rsize / 64;
   if (chunks > max_chunks) chunks = max_chunks;
   if (chunks > 1024) chunks = 1024;
   if (chunks < 1) chunks = 1;
-  return (uint32_t)chunks;
+  // equal chunk lengths may need fewer chunks than asked for
+  const int64_t len = (rsize + chunks - 1) / chunks;
+  return (uint32_t)((rsize + len - 1) / len);
 }
+// resident blocks per SM of the column kernels (their __launch_bounds__)
+static const int kOccSumV4 = 6, kOccArgV4 = 4, kOccScalar = 8;
 
 // Whether 4 adjacent slices of a strided-dimension reduction are 4 consecutive, 16-byte
 // aligned floats in every row: then one thread takes 4 slices with 128-bit loads.
@@ -174,8 +181,15 @@ struct ReduceDimArgs {
     }
     err = cudaGetLastError();
     if (err != cudaSuccess || nchunks == 1) return;
-    thb_reduce_dim_fold_chunks<Red><<<(unsigned)bx, THB_RD_THREADS, 0, st>>>(
-        out, (const typename Red::acc_t*)scratch, nslices, nchunks, init);
+    if (nchunks >= 8) {  // 32 slices x 8 chunk lanes per block
+      uint64_t bf = ((uint64_t)nslices + 31) / 32;
+      if (bf > 65535u * 16u) bf = 65535u * 16u;
+      thb_reduce_dim_fold_chunks<Red, 8><<<(unsigned)bf, THB_RD_THREADS, 0, st>>>(
+          out, (const typename Red::acc_t*)scratch, nslices, nchunks, init);
+    } else {
+      thb_reduce_dim_fold_chunks<Red, 1><<<(unsigned)bx, THB_RD_THREADS, 0, st>>>(
+          out, (const typename Red::acc_t*)scratch, nslices, nchunks, init);
+    }
     err = cudaGetLastError();
   }
 };
@@ -224,7 +238,7 @@ static int argreduce(cudaStream_t st, float* values, float* indices, const float
   }
   const int64_t nslices = outer * inner;
   const bool vec4 = (inner & 3) == 0 && ((uintptr_t)src & 15) == 0;
-  const uint32_t nchunks = pick_chunks(vec4 ? nslices >> 2 : nslices, n);
+  const uint32_t nchunks = vec4 ? pick_chunks(nslices >> 2, n, kOccArgV4) : pick_chunks(nslices, n, kOccScalar);
   const uint32_t chunk_len = (uint32_t)((n + nchunks - 1) / nchunks);
   float* pval = scratch;
   int* pidx = reinterpret_cast<int*>(scratch + (size_t)nchunks * nslices);
@@ -243,7 +257,13 @@ static int argreduce(cudaStream_t st, float* values, float* indices, const float
   }
   THB_CUDA(cudaGetLastError());
   if (nchunks > 1) {
-    thb_argreduce_fold_chunks<IS_MAX><<<(unsigned)bx, THB_RD_THREADS, 0, st>>>(values, indices, pval, pidx, nslices, nchunks);
+    if (nchunks >= 8) {  // 32 slices x 8 chunk lanes per block
+      int64_t bf = (nslices + 31) / 32;
+      if (bf > 65535 * 16) bf = 65535 * 16;
+      thb_argreduce_fold_chunks<IS_MAX, 8><<<(unsigned)bf, THB_RD_THREADS, 0, st>>>(values, indices, pval, pidx, nslices, nchunks);
+    } else {
+      thb_argreduce_fold_chunks<IS_MAX, 1><<<(unsigned)bx, THB_RD_THREADS, 0, st>>>(values, indices, pval, pidx, nslices, nchunks);
+    }
     THB_CUDA(cudaGetLastError());
   }
   return 0;
@@ -311,7 +331,7 @@ size_t thb200_reduce_dim_scratch_bytes(const thb200_tensor* in, int dim) {
   Collapsed ci;
   if (!collapse(in->ndim, in->size, in->stride, dim, &ci)) return 0;
   const bool vec4 = slices_vectorise(in->data, ci, rstride);
-  uint32_t chunks = pick_chunks(vec4 ? nslices >> 2 : nslices, rsize);
+  uint32_t chunks = vec4 ? pick_chunks(nslices >> 2, rsize, kOccSumV4) : pick_chunks(nslices, rsize, kOccScalar);
   return chunks > 1 ? (size_t)chunks * nslices * sizeof(double) : 0;
 }
 
@@ -336,7 +356,7 @@ int thb200_reduce_dim(void* stream, int modify, int reduce, const thb200_tensor*
   a.rsize = (uint32_t)rsize; a.rstride = (uint32_t)rstride; a.nslices = (uint32_t)nslices;
   a.init = init; a.mparam = mod_param; a.scratch = scratch;
   a.vec4 = rstride != 1 && slices_vectorise(in->data, ci, rstride);
-  a.nchunks = rstride == 1 ? 1 : pick_chunks(a.vec4 ? nslices >> 2 : nslices, rsize);
+  a.nchunks = rstride == 1 ? 1 : (a.vec4 ? pick_chunks(nslices >> 2, rsize, kOccSumV4) : pick_chunks(nslices, rsize, kOccScalar));
   a.chunk_len = (uint32_t)((rsize + a.nchunks - 1) / a.nchunks);
   if (a.nchunks > 1 && (!scratch || scratch_bytes < (size_t)a.nchunks * nslices * sizeof(double)))
     return fail("reduceDim: scratch too small (%zu bytes, need %zu)", scratch_bytes,
@@ -349,7 +369,7 @@ int thb200_reduce_dim(void* stream, int modify, int reduce, const thb200_tensor*
 size_t thb200_reduce_dim_index_scratch_bytes(int64_t outer, int64_t n, int64_t inner) {
   if (inner <= 1 || outer * inner == 0) return 0;
   // sized for the 128-bit variant (4 slices per thread, hence up to 4 times the chunks)
-  uint32_t chunks = pick_chunks((inner & 3) == 0 ? (outer * inner) >> 2 : outer * inner, n);
+  uint32_t chunks = (inner & 3) == 0 ? pick_chunks((outer * inner) >> 2, n, kOccArgV4) : pick_chunks(outer * inner, n, kOccScalar);
   return chunks > 1 ? (size_t)chunks * outer * inner * (sizeof(float) + sizeof(int)) : 0;
 }
 

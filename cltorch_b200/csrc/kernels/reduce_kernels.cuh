@@ -294,7 +294,7 @@ thb_reduce_dim_noncontig(ThbLayout out, ThbLayout in, thb_u32 rsize, thb_u32 rst
 // slices 4k..4k+3 are 4 consecutive floats at a 16-byte aligned address in every row of
 // the reduced dimension. 8 rows in flight per thread.
 template <class Mod, class Red>
-__global__ void __launch_bounds__(THB_RD_THREADS)
+__global__ void __launch_bounds__(THB_RD_THREADS, 6)
 thb_reduce_dim_noncontig_v4(ThbLayout out, ThbLayout in, thb_u32 rsize, thb_u32 rstride, thb_u32 nslices,
                             thb_u32 chunk_len, thb_u32 nchunks, float init, float mparam,
                             typename Red::acc_t* partial) {
@@ -336,17 +336,44 @@ thb_reduce_dim_noncontig_v4(ThbLayout out, ThbLayout in, thb_u32 rsize, thb_u32 
   }
 }
 
-template <class Red>
+// Folds the chunk partials of every slice in chunk order. A block is (256 / LANES) slices x
+// LANES lanes; lane k folds the k-th run of consecutive chunks, then lane 0 folds the run
+// results in order, so LANES times as many threads share the latency-bound walk over the
+// chunks (LANES = 8 when there are many chunks, 1 for a handful).
+template <class Red, int LANES>
 __global__ void __launch_bounds__(THB_RD_THREADS)
 thb_reduce_dim_fold_chunks(ThbLayout out, const typename Red::acc_t* partial, thb_u32 nslices, thb_u32 nchunks,
                            float init) {
   typedef typename Red::acc_t acc_t;
-  for (thb_u64 s64 = (thb_u64)blockIdx.x * THB_RD_THREADS + threadIdx.x; s64 < nslices;
-       s64 += (thb_u64)gridDim.x * THB_RD_THREADS) {
-    const thb_u32 s = (thb_u32)s64;
+  constexpr int SL = THB_RD_THREADS / LANES;
+  __shared__ acc_t runs[LANES][SL + 1];
+  const int tx = threadIdx.x % SL, ty = threadIdx.x / SL;
+  const thb_u32 per = (nchunks + LANES - 1) / LANES;
+  const thb_u32 c0 = min(nchunks, ty * per), c1 = min(nchunks, c0 + per);
+  for (thb_u64 s0 = (thb_u64)blockIdx.x * SL; s0 < nslices; s0 += (thb_u64)gridDim.x * SL) {
+    const thb_u64 s = s0 + tx;
     acc_t acc = (acc_t)init;
-    for (thb_u32 c = 0; c < nchunks; ++c) acc = Red::apply(acc, partial[(thb_u64)c * nslices + s]);
-    out.data[thb_offset(out, s)] = (float)acc;
+    if (s < nslices) {
+      thb_u32 c = c0;
+      for (; c + 4 <= c1; c += 4) {
+        acc_t v[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) v[u] = partial[(thb_u64)(c + u) * nslices + s];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) acc = Red::apply(acc, v[u]);
+      }
+      for (; c < c1; ++c) acc = Red::apply(acc, partial[(thb_u64)c * nslices + s]);
+    }
+    if (LANES > 1) {
+      runs[ty][tx] = acc;
+      __syncthreads();
+      if (ty == 0) {
+#pragma unroll
+        for (int k = 1; k < LANES; ++k) acc = Red::apply(acc, runs[k][tx]);
+      }
+    }
+    if (ty == 0 && s < nslices) out.data[thb_offset(out, (thb_u32)s)] = (float)acc;
+    if (LANES > 1) __syncthreads();
   }
 }
 
@@ -480,7 +507,7 @@ thb_argreduce_cols(float* values, float* indices, const float* src, thb_i64 oute
 
 // The same with one thread per 4 adjacent inner positions (inner % 4 == 0, src 16-byte aligned).
 template <bool IS_MAX>
-__global__ void __launch_bounds__(THB_RD_THREADS)
+__global__ void __launch_bounds__(THB_RD_THREADS, 4)
 thb_argreduce_cols_v4(float* values, float* indices, const float* src, thb_i64 outer, thb_u32 n, thb_i64 inner,
                       thb_u32 chunk_len, thb_u32 nchunks, float* pval, int* pidx) {
   const thb_i64 nslices = outer * inner;
@@ -530,20 +557,43 @@ thb_argreduce_cols_v4(float* values, float* indices, const float* src, thb_i64 o
   }
 }
 
-template <bool IS_MAX>
+// Chunk candidates of every slice, folded in chunk order with the strict comparison (an
+// earlier chunk keeps a tie); lanes as in thb_reduce_dim_fold_chunks.
+template <bool IS_MAX, int LANES>
 __global__ void __launch_bounds__(THB_RD_THREADS)
 thb_argreduce_fold_chunks(float* values, float* indices, const float* pval, const int* pidx, thb_i64 nslices,
                           thb_u32 nchunks) {
-  for (thb_i64 s = (thb_i64)blockIdx.x * THB_RD_THREADS + threadIdx.x; s < nslices;
-       s += (thb_i64)gridDim.x * THB_RD_THREADS) {
+  constexpr int SL = THB_RD_THREADS / LANES;
+  __shared__ float rv[LANES][SL + 1];
+  __shared__ int ri[LANES][SL + 1];
+  const int tx = threadIdx.x % SL, ty = threadIdx.x / SL;
+  const thb_u32 per = (nchunks + LANES - 1) / LANES;
+  const thb_u32 c0 = min(nchunks, ty * per), c1 = min(nchunks, c0 + per);
+  for (thb_i64 s0 = (thb_i64)blockIdx.x * SL; s0 < nslices; s0 += (thb_i64)gridDim.x * SL) {
+    const thb_i64 s = s0 + tx;
     float v = ThbArg<IS_MAX>::start();
     int idx = -1;
-    for (thb_u32 c = 0; c < nchunks; ++c) {
-      float ov = pval[(thb_i64)c * nslices + s];
-      int oi = pidx[(thb_i64)c * nslices + s];
-      if (oi >= 0 && ThbArg<IS_MAX>::strictly(ov, v)) { v = ov; idx = oi; }
+    if (s < nslices) {
+      for (thb_u32 c = c0; c < c1; ++c) {
+        const float ov = pval[(thb_i64)c * nslices + s];
+        const int oi = pidx[(thb_i64)c * nslices + s];
+        if (oi >= 0 && ThbArg<IS_MAX>::strictly(ov, v)) { v = ov; idx = oi; }
+      }
     }
-    values[s] = v;
-    indices[s] = (float)(idx < 0 ? -1 : idx + 1);
+    if (LANES > 1) {
+      rv[ty][tx] = v;
+      ri[ty][tx] = idx;
+      __syncthreads();
+      if (ty == 0) {
+#pragma unroll
+        for (int k = 1; k < LANES; ++k)
+          if (ri[k][tx] >= 0 && ThbArg<IS_MAX>::strictly(rv[k][tx], v)) { v = rv[k][tx]; idx = ri[k][tx]; }
+      }
+    }
+    if (ty == 0 && s < nslices) {
+      values[s] = v;
+      indices[s] = (float)(idx < 0 ? -1 : idx + 1);
+    }
+    if (LANES > 1) __syncthreads();
   }
 }

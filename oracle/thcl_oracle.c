@@ -47,6 +47,16 @@ int orc_num_threads(void) {
 #endif
 }
 
+/* Thread count of the timing loops; a launcher that exports OMP_NUM_THREADS=1 to every
+ * rank would otherwise pin the CPU baseline to one core. */
+void orc_set_num_threads(int n) {
+#ifdef _OPENMP
+  if (n > 0) omp_set_num_threads(n);
+#else
+  (void)n;
+#endif
+}
+
 /* TensorInfo<IndexType>::TensorInfo, src/lib/THClReduceApplyUtils.h:68-170. Written as the
  * reference writes it (two passes: count the collapsed dims, then fill), not as the
  * CUDA library does, so that the two are independent. */
