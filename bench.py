@@ -92,6 +92,11 @@ class ClockSampler:
                 "samples": len(sm), "reasons": sorted(reasons)}
 
 
+# dram__bytes_read.sum + dram__bytes_write.sum of thb_apply_contig for 2^28 elements, per element
+# (profiles/apply_contig_and_reduce_all_2p28.md); DRAM traffic of this kernel grows in proportion.
+NCU_DRAM_BYTES_PER_ELT_APPLY = (1.073753e9 + 1.016120e9) / 268435456
+
+
 # ---- CPU leg (oracle port) ---------------------------------------------------------------------
 
 def cpu_chain(sample_elems: int, reps: int):
@@ -259,7 +264,10 @@ def run_gpu(args):
                        "l2": f"inputs larger than L2 ({4 * n_local >> 20} MiB per GPU vs 126 MiB)"},
             "roofline": {"bound": "hbm", "kernel": "thb_apply_contig<UserOp,1> (x = x*1.0001 + 0.5)",
                          "achieved": achieved, "peak": peaks["hbm_gbs"], "unit": "GB/s",
-                         "frac": achieved / peaks["hbm_gbs"], "peak_source": peaks["source"], "traffic": None,
+                         "frac": achieved / peaks["hbm_gbs"], "peak_source": peaks["source"],
+                         "traffic": NCU_DRAM_BYTES_PER_ELT_APPLY * n_local,
+                         "traffic_note": "bytes per launch: dram__bytes_read.sum + dram__bytes_write.sum of one ncu "
+                                         "capture at 2^28 elements (2.0899 GB), scaled by the elements of a launch",
                          "per_kernel_gbs": {"apply_axpb": achieved, "apply_sqrt": 8 * n_local / (k_apply2 * 1e-3) / 1e9,
                                             "reduce_all_sum": 4 * n_local / (k_sum * 1e-3) / 1e9}},
             "e2e": {"value": BYTES_PER_ELT * n_total / (e2e_ms / e2e_steps * 1e-3) / 1e9, "unit": "GB/s",

@@ -155,6 +155,25 @@ def c4(T):
         C = cl.ClTensor(M, N).zero()
         T.time(f"addmm {M}x{N}x{K}", lambda: C.addmm(1.0, C, 1.0, A, B), flops=2.0 * M * N * K, setup=lambda: C.zero())
         del A, B, C
+    # Library reference points on the same box and stream: cuBLAS single-pass TF32 (the tensor
+    # pipe's measured ceiling; a 3xTF32 GEMM can reach at most a third of it) and cuBLAS fp32.
+    try:
+        t = T.torch
+        ta = t.rand(8192, 8192, device="cuda") - 0.5
+        tb = t.rand(8192, 8192, device="cuda") - 0.5
+        tc = t.empty(8192, 8192, device="cuda")
+        was = t.backends.cuda.matmul.allow_tf32
+        t.backends.cuda.matmul.allow_tf32 = True
+        r = T.time("library: cuBLAS TF32 (1 pass) 8192x8192x8192", lambda: t.matmul(ta, tb, out=tc), flops=2.0 * 8192 ** 3)
+        r["third_of_measured_tf32_TFLOP/s"] = r["TFLOP/s"] / 3
+        t.backends.cuda.matmul.allow_tf32 = False
+        T.time("library: cuBLAS fp32 8192x8192x8192", lambda: t.matmul(ta, tb, out=tc), flops=2.0 * 8192 ** 3)
+        t.backends.cuda.matmul.allow_tf32 = was
+        big = T.results["addmm 8192x8192x8192"]
+        big["frac_of_third_of_measured_tf32"] = big["TFLOP/s"] / r["third_of_measured_tf32_TFLOP/s"]
+        del ta, tb, tc
+    except Exception as e:  # a torch build without these switches: the library points are optional
+        T.results["library reference points"] = {"ms": 0.0, "error": str(e)[:200]}
     A, B = pair(1024, 1024, 128, batch=64)
     C = cl.ClTensor(64, 1024, 1024).zero()
     nbytes = 64 * (1024 * 128 + 128 * 1024 + 2 * 1024 * 1024) * 4

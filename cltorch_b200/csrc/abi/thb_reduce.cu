@@ -65,6 +65,21 @@ static bool dispatch_pair(int modify, int reduce, F&& f) {
   return false;
 }
 
+// Internal reduce codes of thb200_var_dim / thb200_var_all (not part of the public enum).
+enum { kRedVar = 100, kRedVarBiased = 101, kRedStd = 102, kRedStdBiased = 103 };
+static int moments_code(int biased, int apply_sqrt) { return 100 + (biased ? 1 : 0) + (apply_sqrt ? 2 : 0); }
+
+template <class F>
+static bool dispatch_moments(int code, F&& f) {
+  switch (code) {
+    case kRedVar: f.template operator()<ModCopy, RedMoments<false, false> >(); return true;
+    case kRedVarBiased: f.template operator()<ModCopy, RedMoments<true, false> >(); return true;
+    case kRedStd: f.template operator()<ModCopy, RedMoments<false, true> >(); return true;
+    case kRedStdBiased: f.template operator()<ModCopy, RedMoments<true, true> >(); return true;
+  }
+  return false;
+}
+
 template <class F>
 static bool dispatch_red(int reduce, F&& f) {
   switch (reduce) {
@@ -77,6 +92,9 @@ static bool dispatch_red(int reduce, F&& f) {
   }
   return false;
 }
+
+template <class Red> struct IsMoments { static const bool value = false; };
+template <bool B, bool S> struct IsMoments<RedMoments<B, S> > { static const bool value = true; };
 
 struct ReduceAllArgs {
   cudaStream_t st;
@@ -93,6 +111,14 @@ struct ReduceAllArgs {
   Collapsed c;
   cudaError_t err = cudaSuccess;
 
+  template <class Red>
+  void launch_pass2(int blocks) {
+    if constexpr (IsMoments<Red>::value)
+      thb_moments_all_pass2<Red><<<1, 1024, 0, st>>>((const ThbMoments*)scratch, blocks, fparam, d_out);
+    else
+      thb_reduce_all_pass2<Red><<<1, 1024, 0, st>>>((const typename Red::acc_t*)scratch, blocks, init, fin, fparam, d_out);
+  }
+
   template <class Mod, class Red>
   void operator()() {
     const int blocks = (int)reduce_all_blocks(n);
@@ -107,7 +133,7 @@ struct ReduceAllArgs {
     }
     err = cudaGetLastError();
     if (err != cudaSuccess) return;
-    thb_reduce_all_pass2<Red><<<1, 1024, 0, st>>>((const typename Red::acc_t*)scratch, blocks, init, fin, fparam, d_out);
+    launch_pass2<Red>(blocks);
     err = cudaGetLastError();
   }
 };
@@ -185,10 +211,10 @@ struct ReduceDimArgs {
       uint64_t bf = ((uint64_t)nslices + 31) / 32;
       if (bf > 65535u * 16u) bf = 65535u * 16u;
       thb_reduce_dim_fold_chunks<Red, 8><<<(unsigned)bf, THB_RD_THREADS, 0, st>>>(
-          out, (const typename Red::acc_t*)scratch, nslices, nchunks, init);
+          out, (const typename Red::acc_t*)scratch, nslices, nchunks, init, rsize);
     } else {
       thb_reduce_dim_fold_chunks<Red, 1><<<(unsigned)bx, THB_RD_THREADS, 0, st>>>(
-          out, (const typename Red::acc_t*)scratch, nslices, nchunks, init);
+          out, (const typename Red::acc_t*)scratch, nslices, nchunks, init, rsize);
     }
     err = cudaGetLastError();
   }
@@ -335,8 +361,10 @@ size_t thb200_reduce_dim_scratch_bytes(const thb200_tensor* in, int dim) {
   return chunks > 1 ? (size_t)chunks * nslices * sizeof(double) : 0;
 }
 
-int thb200_reduce_dim(void* stream, int modify, int reduce, const thb200_tensor* out, const thb200_tensor* in, int dim,
-                      float init, float mod_param, float* scratch, size_t scratch_bytes) {
+// `reduce` is a THB200_RED_* code or one of the internal moments codes; `acc_bytes` the size
+// of one chunk partial (8 for every public operator, 16 for the moments).
+static int reduce_dim_impl(void* stream, int modify, int reduce, const thb200_tensor* out, const thb200_tensor* in,
+                           int dim, float init, float mod_param, float* scratch, size_t scratch_bytes, size_t acc_bytes) {
   int64_t nslices, rsize, rstride;
   if (int rc = reduce_dim_geometry(in, dim, &nslices, &rsize, &rstride)) return rc;
   if (!out) return fail("reduceDim: null output");
@@ -358,11 +386,53 @@ int thb200_reduce_dim(void* stream, int modify, int reduce, const thb200_tensor*
   a.vec4 = rstride != 1 && slices_vectorise(in->data, ci, rstride);
   a.nchunks = rstride == 1 ? 1 : (a.vec4 ? pick_chunks(nslices >> 2, rsize, kOccSumV4) : pick_chunks(nslices, rsize, kOccScalar));
   a.chunk_len = (uint32_t)((rsize + a.nchunks - 1) / a.nchunks);
-  if (a.nchunks > 1 && (!scratch || scratch_bytes < (size_t)a.nchunks * nslices * sizeof(double)))
+  if (a.nchunks > 1 && (!scratch || scratch_bytes < (size_t)a.nchunks * nslices * acc_bytes))
     return fail("reduceDim: scratch too small (%zu bytes, need %zu)", scratch_bytes,
-                (size_t)a.nchunks * nslices * sizeof(double));
-  if (!dispatch_pair(modify, reduce, a)) return fail("reduceDim: unsupported modify/reduce pair (%d, %d)", modify, reduce);
+                (size_t)a.nchunks * nslices * acc_bytes);
+  const bool known = reduce >= 100 ? dispatch_moments(reduce, a) : dispatch_pair(modify, reduce, a);
+  if (!known) return fail("reduceDim: unsupported modify/reduce pair (%d, %d)", modify, reduce);
   if (a.err != cudaSuccess) return fail_cuda(a.err, "reduceDim launch");
+  return 0;
+}
+
+int thb200_reduce_dim(void* stream, int modify, int reduce, const thb200_tensor* out, const thb200_tensor* in, int dim,
+                      float init, float mod_param, float* scratch, size_t scratch_bytes) {
+  if (reduce >= 100) return fail("reduceDim: unknown reduce op %d", reduce);
+  return reduce_dim_impl(stream, modify, reduce, out, in, dim, init, mod_param, scratch, scratch_bytes, sizeof(double));
+}
+
+size_t thb200_var_dim_scratch_bytes(const thb200_tensor* in, int dim) { return 2 * thb200_reduce_dim_scratch_bytes(in, dim); }
+
+int thb200_var_dim(void* stream, const thb200_tensor* out, const thb200_tensor* in, int dim, int biased, int apply_sqrt,
+                   float* scratch, size_t scratch_bytes) {
+  return reduce_dim_impl(stream, THB200_MOD_COPY, moments_code(biased, apply_sqrt), out, in, dim, 0.f, 0.f, scratch,
+                         scratch_bytes, sizeof(ThbMoments));
+}
+
+size_t thb200_var_all_scratch_bytes(int64_t n) { return (size_t)reduce_all_blocks(n) * sizeof(ThbMoments); }
+
+int thb200_var_all(void* stream, const thb200_tensor* in, int biased, int apply_sqrt, float* d_out, float* scratch,
+                   size_t scratch_bytes) {
+  if (!in || !d_out) return fail("varall: null argument");
+  if (in->ndim > THB200_MAX_DIMS) return fail("varall: too many dimensions");
+  ReduceAllArgs a;
+  a.st = (cudaStream_t)stream;
+  a.in = in;
+  a.n = num_elements(*in);
+  a.init = 0.f; a.mparam = 0.f; a.mpoint = nullptr;
+  a.fin = THB_FIN_NONE; a.fparam = (float)a.n;
+  a.d_out = d_out; a.scratch = scratch;
+  if (a.n > 0 && !in->data) return fail("varall: input has no device memory");
+  if (!scratch || scratch_bytes < thb200_var_all_scratch_bytes(a.n))
+    return fail("varall: scratch too small (%zu bytes, need %zu)", scratch_bytes, thb200_var_all_scratch_bytes(a.n));
+  if (!collapse(in->ndim, in->size, in->stride, -1, &a.c)) return fail("varall: bad layout");
+  a.contig = a.n == 0 || (a.c.contiguous() && ((uintptr_t)in->data & 3) == 0);
+  a.head = a.contig && a.n > 0 ? (int)(((16 - ((uintptr_t)in->data & 15)) & 15) >> 2) : 0;
+  if (a.head > a.n) a.head = (int)a.n;
+  if (!a.contig && !can_use_32bit(in->ndim, in->size, in->stride))
+    return fail("varall: non-contiguous tensor needs 64-bit index math: not implemented");
+  dispatch_moments(moments_code(biased, apply_sqrt), a);
+  if (a.err != cudaSuccess) return fail_cuda(a.err, "varall launch");
   return 0;
 }
 

@@ -29,12 +29,72 @@ struct ModSqDev { static __device__ __forceinline__ float apply(float x, float, 
 // fraction of the fp64 rate) and the result is within 1e-5 relative of a
 // double-precision evaluation even for zero-mean data, where an fp32 tree loses
 // digits to cancellation. min/max/and/or are exact in fp32.
-struct RedAdd { typedef double acc_t; static __device__ __forceinline__ double apply(double a, double b) { return a + b; } };
-struct RedMul { typedef double acc_t; static __device__ __forceinline__ double apply(double a, double b) { return a * b; } };
-struct RedMin { typedef float acc_t; static __device__ __forceinline__ float apply(float a, float b) { return fminf(a, b); } };
-struct RedMax { typedef float acc_t; static __device__ __forceinline__ float apply(float a, float b) { return fmaxf(a, b); } };
-struct RedAnd { typedef float acc_t; static __device__ __forceinline__ float apply(float a, float b) { return (float)((int)a && (int)b); } };
-struct RedOr { typedef float acc_t; static __device__ __forceinline__ float apply(float a, float b) { return (float)((int)a || (int)b); } };
+struct RedAdd {
+  typedef double acc_t;
+  static __device__ __forceinline__ double apply(double a, double b) { return a + b; }
+  static __device__ __forceinline__ float result(double a, float) { return (float)a; }
+};
+struct RedMul {
+  typedef double acc_t;
+  static __device__ __forceinline__ double apply(double a, double b) { return a * b; }
+  static __device__ __forceinline__ float result(double a, float) { return (float)a; }
+};
+struct RedMin {
+  typedef float acc_t;
+  static __device__ __forceinline__ float apply(float a, float b) { return fminf(a, b); }
+  static __device__ __forceinline__ float result(float a, float) { return a; }
+};
+struct RedMax {
+  typedef float acc_t;
+  static __device__ __forceinline__ float apply(float a, float b) { return fmaxf(a, b); }
+  static __device__ __forceinline__ float result(float a, float) { return a; }
+};
+struct RedAnd {
+  typedef float acc_t;
+  static __device__ __forceinline__ float apply(float a, float b) { return (float)((int)a && (int)b); }
+  static __device__ __forceinline__ float result(float a, float) { return a; }
+};
+struct RedOr {
+  typedef float acc_t;
+  static __device__ __forceinline__ float apply(float a, float b) { return (float)((int)a || (int)b); }
+  static __device__ __forceinline__ float result(float a, float) { return a; }
+};
+
+// Sum and sum of squares of a slice in one pass, for the variance / standard deviation of
+// THClTensor_computeVar (src/lib/THClTensorMath2.cl:5-23): BIASED divides by n, otherwise by
+// n - 1; negative results of the subtraction are clamped to 0; SQRT gives the standard
+// deviation. Both sums are kept in double, so the subtraction loses nothing that fp32
+// inputs could show. An element enters as ThbMoments(x) = (x, x * x).
+struct ThbMoments {
+  double s, q;
+  __device__ __forceinline__ ThbMoments() {}
+  __device__ __forceinline__ ThbMoments(float x) : s((double)x), q((double)x * (double)x) {}
+};
+template <bool BIASED, bool SQRT>
+struct RedMoments {
+  typedef ThbMoments acc_t;
+  static __device__ __forceinline__ ThbMoments apply(ThbMoments a, ThbMoments b) {
+    a.s += b.s;
+    a.q += b.q;
+    return a;
+  }
+  // n = number of elements of the slice
+  static __device__ __forceinline__ float result(ThbMoments a, float n_f) {
+    const double n = (double)n_f;
+    const double mean = a.s / n;
+    double v = BIASED ? a.q / n - mean * mean : a.q / (n - 1.0) - n / (n - 1.0) * mean * mean;
+    v = v < 0.0 ? 0.0 : v;
+    return (float)(SQRT ? sqrt(v) : v);
+  }
+};
+
+__device__ __forceinline__ float thb_shfl_down(float v, int off) { return __shfl_down_sync(0xffffffffu, v, off); }
+__device__ __forceinline__ double thb_shfl_down(double v, int off) { return __shfl_down_sync(0xffffffffu, v, off); }
+__device__ __forceinline__ ThbMoments thb_shfl_down(ThbMoments v, int off) {
+  v.s = __shfl_down_sync(0xffffffffu, v.s, off);
+  v.q = __shfl_down_sync(0xffffffffu, v.q, off);
+  return v;
+}
 
 #define THB_FULL_MASK 0xffffffffu
 
@@ -44,7 +104,7 @@ template <class Red>
 __device__ __forceinline__ typename Red::acc_t thb_block_fold(typename Red::acc_t v, typename Red::acc_t init,
                                                               typename Red::acc_t* smem) {
 #pragma unroll
-  for (int off = 16; off > 0; off >>= 1) v = Red::apply(v, __shfl_down_sync(THB_FULL_MASK, v, off));
+  for (int off = 16; off > 0; off >>= 1) v = Red::apply(v, thb_shfl_down(v, off));
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int nwarps = (blockDim.x + 31) >> 5;
   if (lane == 0) smem[warp] = v;
@@ -52,7 +112,7 @@ __device__ __forceinline__ typename Red::acc_t thb_block_fold(typename Red::acc_
   if (warp == 0) {
     v = lane < nwarps ? smem[lane] : init;
 #pragma unroll
-    for (int off = 16; off > 0; off >>= 1) v = Red::apply(v, __shfl_down_sync(THB_FULL_MASK, v, off));
+    for (int off = 16; off > 0; off >>= 1) v = Red::apply(v, thb_shfl_down(v, off));
   }
   return v;
 }
@@ -162,6 +222,17 @@ thb_reduce_all_pass2(const typename Red::acc_t* partials, int count, float init,
   }
 }
 
+// Pass 2 of the whole-tensor variance / standard deviation from single-pass moments.
+template <class Red>
+__global__ void __launch_bounds__(1024)
+thb_moments_all_pass2(const ThbMoments* partials, int count, float n, float* out) {
+  __shared__ ThbMoments smem[32];
+  ThbMoments r(0.f);
+  for (int i = threadIdx.x; i < count; i += blockDim.x) r = Red::apply(r, partials[i]);
+  r = thb_block_fold<Red>(r, ThbMoments(0.f), smem);
+  if (threadIdx.x == 0) out[0] = Red::result(r, n);
+}
+
 // The same fold for fp32 inputs (per-GPU results that already are point tensors).
 template <class Red>
 __global__ void __launch_bounds__(1024)
@@ -186,6 +257,7 @@ __global__ void __launch_bounds__(THB_RD_THREADS)
 thb_reduce_dim_contig_block(ThbLayout out, ThbLayout in, thb_u32 rsize, thb_u32 nslices, float init,
                             float mparam) {
   typedef typename Red::acc_t acc_t;
+  const float fin_n = (float)rsize;
   __shared__ acc_t smem[32];
   for (thb_u32 s = blockIdx.x; s < nslices; s += gridDim.x) {
     const float* p = in.data + thb_offset(in, s);
@@ -213,7 +285,7 @@ thb_reduce_dim_contig_block(ThbLayout out, ThbLayout in, thb_u32 rsize, thb_u32 
     }
     acc_t r = Red::apply(Red::apply(acc[0], acc[1]), Red::apply(acc[2], acc[3]));
     r = thb_block_fold<Red>(r, (acc_t)init, smem);
-    if (threadIdx.x == 0) out.data[thb_offset(out, s)] = (float)r;
+    if (threadIdx.x == 0) out.data[thb_offset(out, s)] = Red::result(r, fin_n);
     __syncthreads();
   }
 }
@@ -224,6 +296,7 @@ __global__ void __launch_bounds__(THB_RD_THREADS)
 thb_reduce_dim_contig_warp(ThbLayout out, ThbLayout in, thb_u32 rsize, thb_u32 nslices, float init,
                            float mparam) {
   typedef typename Red::acc_t acc_t;
+  const float fin_n = (float)rsize;
   const int lane = threadIdx.x & 31;
   const thb_u32 warps_per_block = THB_RD_THREADS / 32;
   for (thb_u64 s64 = (thb_u64)blockIdx.x * warps_per_block + (threadIdx.x >> 5); s64 < nslices;
@@ -253,8 +326,8 @@ thb_reduce_dim_contig_warp(ThbLayout out, ThbLayout in, thb_u32 rsize, thb_u32 n
     }
     acc_t r = Red::apply(Red::apply(acc[0], acc[1]), Red::apply(acc[2], acc[3]));
 #pragma unroll
-    for (int off = 16; off > 0; off >>= 1) r = Red::apply(r, __shfl_down_sync(THB_FULL_MASK, r, off));
-    if (lane == 0) out.data[thb_offset(out, s)] = (float)r;
+    for (int off = 16; off > 0; off >>= 1) r = Red::apply(r, thb_shfl_down(r, off));
+    if (lane == 0) out.data[thb_offset(out, s)] = Red::result(r, fin_n);
   }
 }
 
@@ -268,6 +341,7 @@ thb_reduce_dim_noncontig(ThbLayout out, ThbLayout in, thb_u32 rsize, thb_u32 rst
                          thb_u32 chunk_len, thb_u32 nchunks, float init, float mparam,
                          typename Red::acc_t* partial) {
   typedef typename Red::acc_t acc_t;
+  const float fin_n = (float)rsize;
   const thb_u32 chunk = blockIdx.y;
   const thb_u32 r0 = chunk * chunk_len;
   const thb_u32 r1 = min(rsize, r0 + chunk_len);
@@ -285,7 +359,7 @@ thb_reduce_dim_noncontig(ThbLayout out, ThbLayout in, thb_u32 rsize, thb_u32 rst
       for (int u = 0; u < 16; ++u) acc = Red::apply(acc, Mod::apply(v[u], mparam, 0.f));
     }
     for (; r < r1; ++r) acc = Red::apply(acc, Mod::apply(p[(thb_u64)r * rstride], mparam, 0.f));
-    if (nchunks == 1) out.data[thb_offset(out, s)] = (float)acc;
+    if (nchunks == 1) out.data[thb_offset(out, s)] = Red::result(acc, fin_n);
     else partial[(thb_u64)chunk * nslices + s] = acc;
   }
 }
@@ -299,6 +373,7 @@ thb_reduce_dim_noncontig_v4(ThbLayout out, ThbLayout in, thb_u32 rsize, thb_u32 
                             thb_u32 chunk_len, thb_u32 nchunks, float init, float mparam,
                             typename Red::acc_t* partial) {
   typedef typename Red::acc_t acc_t;
+  const float fin_n = (float)rsize;
   const thb_u32 chunk = blockIdx.y;
   const thb_u32 r0 = chunk * chunk_len;
   const thb_u32 r1 = min(rsize, r0 + chunk_len);
@@ -330,7 +405,7 @@ thb_reduce_dim_noncontig_v4(ThbLayout out, ThbLayout in, thb_u32 rsize, thb_u32 
     }
 #pragma unroll
     for (int j = 0; j < 4; ++j) {
-      if (nchunks == 1) out.data[thb_offset(out, s + j)] = (float)acc[j];
+      if (nchunks == 1) out.data[thb_offset(out, s + j)] = Red::result(acc[j], fin_n);
       else partial[(thb_u64)chunk * nslices + s + j] = acc[j];
     }
   }
@@ -343,8 +418,9 @@ thb_reduce_dim_noncontig_v4(ThbLayout out, ThbLayout in, thb_u32 rsize, thb_u32 
 template <class Red, int LANES>
 __global__ void __launch_bounds__(THB_RD_THREADS)
 thb_reduce_dim_fold_chunks(ThbLayout out, const typename Red::acc_t* partial, thb_u32 nslices, thb_u32 nchunks,
-                           float init) {
+                           float init, thb_u32 rsize) {
   typedef typename Red::acc_t acc_t;
+  const float fin_n = (float)rsize;
   constexpr int SL = THB_RD_THREADS / LANES;
   __shared__ acc_t runs[LANES][SL + 1];
   const int tx = threadIdx.x % SL, ty = threadIdx.x / SL;
@@ -372,7 +448,7 @@ thb_reduce_dim_fold_chunks(ThbLayout out, const typename Red::acc_t* partial, th
         for (int k = 1; k < LANES; ++k) acc = Red::apply(acc, runs[k][tx]);
       }
     }
-    if (ty == 0 && s < nslices) out.data[thb_offset(out, (thb_u32)s)] = (float)acc;
+    if (ty == 0 && s < nslices) out.data[thb_offset(out, (thb_u32)s)] = Red::result(acc, fin_n);
     if (LANES > 1) __syncthreads();
   }
 }
