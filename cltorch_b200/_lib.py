@@ -203,6 +203,10 @@ PROTOTYPES = {
     "THClTensor_stdall_gpu": (v, [S, T, T]),
     "THClTensor_sum": (v, [S, T, T, l]), "THClTensor_prod": (v, [S, T, T, l]), "THClTensor_mean": (v, [S, T, T, l]),
     "THClTensor_norm": (v, [S, T, T, f, l]),
+    "THClTensor_var": (v, [S, T, T, l, i]), "THClTensor_std": (v, [S, T, T, l, i]),
+    "THClTensor_cumsum": (v, [S, T, T, l]), "THClTensor_cumprod": (v, [S, T, T, l]),
+    "THClTensor_renorm": (v, [S, T, T, f, l, f]),
+    "THClTensor_dist": (f, [S, T, T, f]), "THClTensor_dist_gpu": (v, [S, T, T, T, f]),
     "THClTensor_max": (v, [S, T, T, T, l]), "THClTensor_min": (v, [S, T, T, T, l]),
     "THClTensor_addmm": (v, [S, T, f, T, f, T, T]), "THClTensor_baddbmm": (v, [S, T, f, T, f, T, T]),
     "THClTensor_addmv": (v, [S, T, f, T, f, T, T]), "THClTensor_addr": (v, [S, T, f, T, f, T, T]),
@@ -234,6 +238,16 @@ PROTOTYPES = {
                         C.c_void_p, C.c_int64, f, C.c_void_p, C.c_int64, C.c_int64, C.c_int64, C.c_int64, C.c_int64,
                         C.c_void_p, C.c_size_t]),
     "thb200_gemm_status": (i, [C.c_void_p, C.c_int64, C.c_int64, C.c_int64, C.c_int64, C.c_void_p]),
+    "thb200_var_dim_scratch_bytes": (C.c_size_t, [C.POINTER(thb200_tensor), i]),
+    "thb200_var_dim": (i, [C.c_void_p, C.POINTER(thb200_tensor), C.POINTER(thb200_tensor), i, i, i, C.c_void_p, C.c_size_t]),
+    "thb200_var_all_scratch_bytes": (C.c_size_t, [C.c_int64]),
+    "thb200_var_all": (i, [C.c_void_p, C.POINTER(thb200_tensor), i, i, C.c_void_p, C.c_void_p, C.c_size_t]),
+    "thb200_scan_scratch_bytes": (C.c_size_t, [C.c_void_p, C.c_void_p, C.c_int64, C.c_int64, C.c_int64]),
+    "thb200_scan": (i, [C.c_void_p, i, C.c_void_p, C.c_void_p, C.c_int64, C.c_int64, C.c_int64, C.c_void_p, C.c_size_t]),
+    "thb200_renorm_rows_scratch_bytes": (C.c_size_t, [C.c_int64, C.c_int64]),
+    "thb200_renorm_rows": (i, [C.c_void_p, C.c_void_p, C.c_int64, C.c_int64, f, f, C.c_void_p, C.c_size_t]),
+    "thb200_dist_scratch_bytes": (C.c_size_t, [C.c_int64]),
+    "thb200_dist": (i, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, f, C.c_void_p, C.c_void_p, C.c_size_t]),
     "thb200_dot_scratch_bytes": (C.c_size_t, [C.c_int64]),
     "thb200_dot": (i, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_void_p, C.c_void_p, C.c_size_t]),
     "thb200_gemv_scratch_bytes": (C.c_size_t, [C.c_char, C.c_int64, C.c_int64]),

@@ -131,7 +131,7 @@ def c3(T):
     def chain():
         for _ in range(100):
             m.mean(A); A.csub(m); s.std(A); A.div(s)
-    T.time("100 x (mean, sub, std, div) on the device [28 B/elt per iteration: std is two passes]", chain, 100 * 28 * n)
+    T.time("100 x (mean, sub, std, div) on the device [24 B/elt per iteration: std is one pass]", chain, 100 * 24 * n)
     del A
     b = g.standard_normal((256, 1024, 1024), dtype=np.float32)
     Bt = cl.ClTensor(b)
@@ -217,9 +217,41 @@ def c3small(T):
         T.time(f"max(A, {d}) with indices", lambda: A.max(d), 4 * n * n)
 
 
+def n3(T):
+    """var/std along a dimension, scans, renorm and dist on 16384 x 16384 (1 GiB)."""
+    cl = T.cl
+    g = np.random.Generator(np.random.PCG64(5))
+    rows = 16384
+    n = rows * rows
+    a = g.standard_normal((rows, rows), dtype=np.float32)
+    A = cl.ClTensor(a)
+    del a
+    out = cl.ClTensor()
+    for d in (1, 2):
+        T.time(f"var(A, {d})", lambda: out.var(A, d), 4 * n)
+        T.time(f"std(A, {d}, true)", lambda: out.std(A, d, True), 4 * n)
+    pt = cl.ClTensor()
+    T.time("std -> point tensor (one pass)", lambda: pt.std(A), 4 * n)
+    T.time("norm(2) -> host float", lambda: A.norm(2), 4 * n)
+    T.time("norm(3) -> host float [general power: fp64 pow per element]", lambda: A.norm(3), 4 * n)
+    B = cl.ClTensor(rows, rows)
+    for d in (1, 2):
+        T.time(f"cumsum(A, {d}) [8 B/elt; the chunked form moves 12]", lambda: B.cumsum(A, d), 8 * n)
+    T.time("cumprod(A, 2)", lambda: B.cumprod(A, 2), 8 * n)
+    V = cl.ClTensor(g.standard_normal((n,), dtype=np.float32))
+    W = cl.ClTensor(n)
+    T.time("cumsum of a 2^28 vector [8 B/elt; chunked: 12 moved]", lambda: W.cumsum(V, 1), 8 * n)
+    T.time("dist(A, B, 2) -> point tensor", lambda: pt.dist_gpu(A, B, 2), 8 * n)
+    # renorm in place along dimension 1 (rows of 16384 normal values have 2-norms close to 128:
+    # about half of them exceed the limit and are rescaled); A is restored before every call
+    A0 = cl.ClTensor(rows, rows).copy(A)
+    T.time("renorm(A, 2, 1, 128) in place [4 B/elt norms + 8 B/elt for the half of the rows rescaled]",
+           lambda: A.renorm(A, 2, 1, 128.0), 4 * n + 4 * n, setup=lambda: A.copy(A0))
+
+
 def run(workload: str, steps: int, warmup: int) -> None:
     T = Timer(steps, warmup)
-    {"c1": c1, "c2": c2, "c3": c3, "c4": c4, "c4small": c4small, "c2small": c2small, "c3small": c3small}[workload](T)
+    {"c1": c1, "c2": c2, "c3": c3, "c4": c4, "c4small": c4small, "c2small": c2small, "c3small": c3small, "n3": n3}[workload](T)
     T.cl.synchronize()
     print(json.dumps({"workload": workload, "n_gpus": 1, "steps": steps, "warmup": warmup, "dtype": "f32",
                       "data": "synthetic", "hbm_peak_gbs_measured": T.peak, "l2_flush": "512 MiB fill between iterations",

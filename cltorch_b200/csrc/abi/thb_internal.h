@@ -30,6 +30,11 @@ bool collapse(int ndim, const int64_t* size, const int64_t* stride, int reduce_d
 bool can_use_32bit(int ndim, const int64_t* size, const int64_t* stride);
 int sm_count();  // of the current device, cached per device
 
+// Number of chunks to cut a reduced / scanned dimension of `rsize` elements into when only
+// `threads` worker threads (blocks of 256, `blocks_per_sm` resident) exist per chunk: as many
+// as fit one wave of resident blocks, 1 when the threads alone fill half the GPU.
+uint32_t pick_chunks(int64_t threads, int64_t rsize, int blocks_per_sm);
+
 // Kernel handles of one pointwise operator: device function pointers usable
 // with cudaLaunchKernel (nvcc-compiled symbols or cudaKernel_t from NVRTC).
 struct ApplyKernels {

@@ -72,10 +72,10 @@ static int moments_code(int biased, int apply_sqrt) { return 100 + (biased ? 1 :
 template <class F>
 static bool dispatch_moments(int code, F&& f) {
   switch (code) {
-    case kRedVar: f.template operator()<ModCopy, RedMoments<false, false> >(); return true;
-    case kRedVarBiased: f.template operator()<ModCopy, RedMoments<true, false> >(); return true;
-    case kRedStd: f.template operator()<ModCopy, RedMoments<false, true> >(); return true;
-    case kRedStdBiased: f.template operator()<ModCopy, RedMoments<true, true> >(); return true;
+    case kRedVar: f.template operator()<ModShift, RedMoments<false, false> >(); return true;
+    case kRedVarBiased: f.template operator()<ModShift, RedMoments<true, false> >(); return true;
+    case kRedStd: f.template operator()<ModShift, RedMoments<false, true> >(); return true;
+    case kRedStdBiased: f.template operator()<ModShift, RedMoments<true, true> >(); return true;
   }
   return false;
 }
@@ -142,7 +142,7 @@ struct ReduceAllArgs {
 // still fills the GPU: as many as fit one wave of resident blocks (`threads` worker threads
 // per chunk in blocks of THB_RD_THREADS, `blocks_per_sm` of them resident), never a
 // fraction of a wave more, and none when the slices alone fill half the GPU.
-static uint32_t pick_chunks(int64_t threads, int64_t rsize, int blocks_per_sm) {
+uint32_t pick_chunks(int64_t threads, int64_t rsize, int blocks_per_sm) {
   const int64_t wave = (int64_t)sm_count() * blocks_per_sm;
   const int64_t bx = (threads + THB_RD_THREADS - 1) / THB_RD_THREADS;
   if (bx * 2 > wave || rsize < 256) return 1;
@@ -156,7 +156,8 @@ static uint32_t pick_chunks(int64_t threads, int64_t rsize, int blocks_per_sm) {
   return (uint32_t)((rsize + len - 1) / len);
 }
 // resident blocks per SM of the column kernels (their __launch_bounds__)
-static const int kOccSumV4 = 6, kOccArgV4 = 4, kOccScalar = 8;
+static const int kOccSumV4 = RedAdd::kColsBlocks, kOccMomentsV4 = RedMoments<false, false>::kColsBlocks, kOccArgV4 = 4,
+                 kOccScalar = 8;
 
 // Whether 4 adjacent slices of a strided-dimension reduction are 4 consecutive, 16-byte
 // aligned floats in every row: then one thread takes 4 slices with 128-bit loads.
@@ -350,15 +351,19 @@ static int reduce_dim_geometry(const thb200_tensor* in, int dim, int64_t* nslice
   return 0;
 }
 
-size_t thb200_reduce_dim_scratch_bytes(const thb200_tensor* in, int dim) {
+static size_t reduce_dim_scratch(const thb200_tensor* in, int dim, int occ_v4, size_t acc_bytes) {
   int64_t nslices, rsize, rstride;
   if (reduce_dim_geometry(in, dim, &nslices, &rsize, &rstride)) return 0;
   if (rstride == 1 || nslices == 0) return 0;
   Collapsed ci;
   if (!collapse(in->ndim, in->size, in->stride, dim, &ci)) return 0;
   const bool vec4 = slices_vectorise(in->data, ci, rstride);
-  uint32_t chunks = vec4 ? pick_chunks(nslices >> 2, rsize, kOccSumV4) : pick_chunks(nslices, rsize, kOccScalar);
-  return chunks > 1 ? (size_t)chunks * nslices * sizeof(double) : 0;
+  uint32_t chunks = vec4 ? pick_chunks(nslices >> 2, rsize, occ_v4) : pick_chunks(nslices, rsize, kOccScalar);
+  return chunks > 1 ? (size_t)chunks * nslices * acc_bytes : 0;
+}
+
+size_t thb200_reduce_dim_scratch_bytes(const thb200_tensor* in, int dim) {
+  return reduce_dim_scratch(in, dim, kOccSumV4, sizeof(double));
 }
 
 // `reduce` is a THB200_RED_* code or one of the internal moments codes; `acc_bytes` the size
@@ -384,7 +389,8 @@ static int reduce_dim_impl(void* stream, int modify, int reduce, const thb200_te
   a.rsize = (uint32_t)rsize; a.rstride = (uint32_t)rstride; a.nslices = (uint32_t)nslices;
   a.init = init; a.mparam = mod_param; a.scratch = scratch;
   a.vec4 = rstride != 1 && slices_vectorise(in->data, ci, rstride);
-  a.nchunks = rstride == 1 ? 1 : (a.vec4 ? pick_chunks(nslices >> 2, rsize, kOccSumV4) : pick_chunks(nslices, rsize, kOccScalar));
+  const int occ_v4 = reduce >= 100 ? kOccMomentsV4 : kOccSumV4;
+  a.nchunks = rstride == 1 ? 1 : (a.vec4 ? pick_chunks(nslices >> 2, rsize, occ_v4) : pick_chunks(nslices, rsize, kOccScalar));
   a.chunk_len = (uint32_t)((rsize + a.nchunks - 1) / a.nchunks);
   if (a.nchunks > 1 && (!scratch || scratch_bytes < (size_t)a.nchunks * nslices * acc_bytes))
     return fail("reduceDim: scratch too small (%zu bytes, need %zu)", scratch_bytes,
@@ -401,7 +407,9 @@ int thb200_reduce_dim(void* stream, int modify, int reduce, const thb200_tensor*
   return reduce_dim_impl(stream, modify, reduce, out, in, dim, init, mod_param, scratch, scratch_bytes, sizeof(double));
 }
 
-size_t thb200_var_dim_scratch_bytes(const thb200_tensor* in, int dim) { return 2 * thb200_reduce_dim_scratch_bytes(in, dim); }
+size_t thb200_var_dim_scratch_bytes(const thb200_tensor* in, int dim) {
+  return reduce_dim_scratch(in, dim, kOccMomentsV4, sizeof(ThbMoments));
+}
 
 int thb200_var_dim(void* stream, const thb200_tensor* out, const thb200_tensor* in, int dim, int biased, int apply_sqrt,
                    float* scratch, size_t scratch_bytes) {
@@ -419,7 +427,8 @@ int thb200_var_all(void* stream, const thb200_tensor* in, int biased, int apply_
   a.st = (cudaStream_t)stream;
   a.in = in;
   a.n = num_elements(*in);
-  a.init = 0.f; a.mparam = 0.f; a.mpoint = nullptr;
+  a.init = 0.f; a.mparam = 0.f;
+  a.mpoint = a.n > 0 ? in->data : nullptr;  // the first element: the shift of ModShift
   a.fin = THB_FIN_NONE; a.fparam = (float)a.n;
   a.d_out = d_out; a.scratch = scratch;
   if (a.n > 0 && !in->data) return fail("varall: input has no device memory");

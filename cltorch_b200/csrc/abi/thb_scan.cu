@@ -1,0 +1,165 @@
+// Host side of the scans, renorm and dist entries of include/thb200.h.
+#include "thb_internal.h"
+#include "../kernels/math_policy.cuh"
+#include "../kernels/scan_kernels.cuh"
+
+namespace thb {
+
+struct ScanPlan {
+  bool rows;        // inner == 1
+  int vec;          // 4 or 1
+  uint32_t nchunks, chunk_len;
+};
+
+static ScanPlan plan_scan(const float* dst, const float* src, int64_t outer, int64_t n, int64_t inner) {
+  ScanPlan p;
+  p.rows = inner == 1;
+  const bool aligned = (((uintptr_t)dst | (uintptr_t)src) & 15) == 0;
+  if (p.rows) {
+    p.vec = (aligned && (n & 3) == 0) ? 4 : 1;
+    const int64_t piece = 32 * p.vec * THB_SC_ROW_UNROLL;  // elements one warp step covers
+    // one warp per (row, chunk): aim at 8 blocks of 8 warps per SM, chunks of at least 4 pieces
+    const int64_t target_warps = (int64_t)sm_count() * 64;
+    int64_t chunks = outer * 2 > target_warps ? 1 : target_warps / outer;
+    const int64_t max_chunks = n / (4 * piece);
+    if (chunks > max_chunks) chunks = max_chunks;
+    if (chunks < 1) chunks = 1;
+    int64_t len = (n + chunks - 1) / chunks;
+    len = (len + piece - 1) / piece * piece;
+    p.chunk_len = (uint32_t)len;
+    p.nchunks = (uint32_t)((n + len - 1) / len);
+  } else {
+    p.vec = (aligned && (inner & 3) == 0) ? 4 : 1;
+    p.nchunks = pick_chunks(outer * inner / p.vec, n, 8);
+    p.chunk_len = (uint32_t)((n + p.nchunks - 1) / p.nchunks);
+  }
+  return p;
+}
+
+template <class Op>
+static int run_scan(cudaStream_t st, float* dst, const float* src, int64_t outer, int64_t n, int64_t inner, double* carry,
+                    const ScanPlan& p) {
+  const int sms = sm_count();
+  if (p.rows) {
+    const int64_t work = outer * p.nchunks;  // warps
+    int64_t blocks = (work + THB_SC_THREADS / 32 - 1) / (THB_SC_THREADS / 32);
+    if (blocks > (int64_t)sms * 64) blocks = (int64_t)sms * 64;
+    if (p.nchunks > 1) {
+      if (p.vec == 4) thb_scan_rows<Op, 4, true><<<(unsigned)blocks, THB_SC_THREADS, 0, st>>>(dst, src, outer, (thb_u32)n, p.chunk_len, p.nchunks, carry);
+      else thb_scan_rows<Op, 1, true><<<(unsigned)blocks, THB_SC_THREADS, 0, st>>>(dst, src, outer, (thb_u32)n, p.chunk_len, p.nchunks, carry);
+      THB_CUDA(cudaGetLastError());
+      if (p.nchunks >= 64) {  // few long rows: a block per row
+        int64_t cb = outer < (int64_t)sms * 8 ? outer : (int64_t)sms * 8;
+        thb_scan_carries_rows<Op><<<(unsigned)cb, THB_SC_THREADS, 0, st>>>(carry, outer, p.nchunks);
+      } else {
+        int64_t cb = (outer + THB_SC_THREADS - 1) / THB_SC_THREADS;
+        if (cb > (int64_t)sms * 64) cb = (int64_t)sms * 64;
+        thb_scan_carries<Op><<<(unsigned)cb, THB_SC_THREADS, 0, st>>>(carry, outer, p.nchunks, 1);
+      }
+      THB_CUDA(cudaGetLastError());
+    }
+    if (p.vec == 4) thb_scan_rows<Op, 4, false><<<(unsigned)blocks, THB_SC_THREADS, 0, st>>>(dst, src, outer, (thb_u32)n, p.chunk_len, p.nchunks, carry);
+    else thb_scan_rows<Op, 1, false><<<(unsigned)blocks, THB_SC_THREADS, 0, st>>>(dst, src, outer, (thb_u32)n, p.chunk_len, p.nchunks, carry);
+    THB_CUDA(cudaGetLastError());
+    return 0;
+  }
+  const int64_t threads = outer * inner / p.vec;
+  int64_t bx = (threads + THB_SC_THREADS - 1) / THB_SC_THREADS;
+  if (bx > (int64_t)sms * 64) bx = (int64_t)sms * 64;
+  const dim3 grid((unsigned)bx, p.nchunks);
+  if (p.nchunks > 1) {
+    if (p.vec == 4) thb_scan_cols<Op, 4, true><<<grid, THB_SC_THREADS, 0, st>>>(dst, src, outer, (thb_u32)n, inner, p.chunk_len, p.nchunks, carry);
+    else thb_scan_cols<Op, 1, true><<<grid, THB_SC_THREADS, 0, st>>>(dst, src, outer, (thb_u32)n, inner, p.chunk_len, p.nchunks, carry);
+    THB_CUDA(cudaGetLastError());
+    int64_t cb = (outer * inner + THB_SC_THREADS - 1) / THB_SC_THREADS;
+    if (cb > (int64_t)sms * 64) cb = (int64_t)sms * 64;
+    thb_scan_carries<Op><<<(unsigned)cb, THB_SC_THREADS, 0, st>>>(carry, outer, p.nchunks, inner);
+    THB_CUDA(cudaGetLastError());
+  }
+  if (p.vec == 4) thb_scan_cols<Op, 4, false><<<grid, THB_SC_THREADS, 0, st>>>(dst, src, outer, (thb_u32)n, inner, p.chunk_len, p.nchunks, carry);
+  else thb_scan_cols<Op, 1, false><<<grid, THB_SC_THREADS, 0, st>>>(dst, src, outer, (thb_u32)n, inner, p.chunk_len, p.nchunks, carry);
+  THB_CUDA(cudaGetLastError());
+  return 0;
+}
+
+static int64_t dist_blocks(int64_t n) {
+  const int64_t per_block = (int64_t)THB_RA_THREADS * 16;
+  int64_t blocks = (n + per_block - 1) / per_block;
+  if (blocks > THB_RA_MAX_BLOCKS) blocks = THB_RA_MAX_BLOCKS;
+  return blocks < 1 ? 1 : blocks;
+}
+
+}  // namespace thb
+
+using namespace thb;
+
+extern "C" {
+
+size_t thb200_scan_scratch_bytes(const float* dst, const float* src, int64_t outer, int64_t n, int64_t inner) {
+  if (outer <= 0 || n <= 0 || inner <= 0) return 0;
+  const ScanPlan p = plan_scan(dst, src, outer, n, inner);
+  return p.nchunks > 1 ? (size_t)outer * p.nchunks * inner * sizeof(double) : 0;
+}
+
+int thb200_scan(void* stream, int op, float* dst, const float* src, int64_t outer, int64_t n, int64_t inner,
+                void* scratch, size_t scratch_bytes) {
+  if (outer < 0 || n < 0 || inner < 0) return fail("scan: negative extent");
+  if (outer == 0 || n == 0 || inner == 0) return 0;
+  if (!dst || !src) return fail("scan: null pointer");
+  if (n >= (int64_t(1) << 31)) return fail("scan: dimension of %lld elements is too long", (long long)n);
+  if (op != THB200_RED_ADD && op != THB200_RED_MUL) return fail("scan: operator %d is neither add nor mul", op);
+  const ScanPlan p = plan_scan(dst, src, outer, n, inner);
+  const size_t need = p.nchunks > 1 ? (size_t)outer * p.nchunks * inner * sizeof(double) : 0;
+  if (need && (!scratch || scratch_bytes < need || ((uintptr_t)scratch & 7)))
+    return fail("scan: scratch too small or misaligned (%zu bytes, need %zu)", scratch_bytes, need);
+  return op == THB200_RED_ADD ? run_scan<ScanAdd>((cudaStream_t)stream, dst, src, outer, n, inner, (double*)scratch, p)
+                              : run_scan<ScanMul>((cudaStream_t)stream, dst, src, outer, n, inner, (double*)scratch, p);
+}
+
+size_t thb200_renorm_rows_scratch_bytes(int64_t rows, int64_t size) {
+  if (rows <= 0 || size <= 0) return 0;
+  return (size_t)rows * sizeof(float);
+}
+
+int thb200_renorm_rows(void* stream, float* data, int64_t rows, int64_t size, float p, float maxnorm, void* scratch,
+                       size_t scratch_bytes) {
+  if (rows < 0 || size < 0) return fail("renorm: negative extent");
+  if (rows == 0 || size == 0) return 0;
+  if (!data) return fail("renorm: null pointer");
+  if (!(p > 0.f)) return fail("renorm: non-positive-norm not supported");
+  if (rows >= (int64_t(1) << 31) || size >= (int64_t(1) << 31)) return fail("renorm: extent too large");
+  if (!scratch || scratch_bytes < (size_t)rows * sizeof(float)) return fail("renorm: scratch too small");
+  // sum |x|^p of every row: the contiguous-dimension reduction, [rows][size] -> [rows][1]
+  const int64_t in_size[2] = {rows, size}, in_stride[2] = {size, 1};
+  const int64_t out_size[2] = {rows, 1}, out_stride[2] = {1, 1};
+  thb200_tensor tin = {data, 2, in_size, in_stride}, tout = {(float*)scratch, 2, out_size, out_stride};
+  if (int rc = thb200_reduce_dim(stream, THB200_MOD_ABSPOW, THB200_RED_ADD, &tout, &tin, 1, 0.f, p, nullptr, 0)) return rc;
+  const int64_t pieces = (size + THB_RN_PIECE - 1) / THB_RN_PIECE;
+  int64_t blocks = rows * pieces;
+  const int64_t cap = (int64_t)sm_count() * 64;
+  if (blocks > cap) blocks = cap;
+  thb_renorm_scale<<<(unsigned)blocks, THB_SC_THREADS, 0, (cudaStream_t)stream>>>(data, (const float*)scratch, rows, size, p,
+                                                                                   maxnorm, pieces);
+  THB_CUDA(cudaGetLastError());
+  return 0;
+}
+
+size_t thb200_dist_scratch_bytes(int64_t n) { return (size_t)dist_blocks(n) * sizeof(double); }
+
+int thb200_dist(void* stream, const float* a, const float* b, int64_t n, float p, float* d_out, void* scratch,
+                size_t scratch_bytes) {
+  if (n < 0) return fail("dist: negative length");
+  if (!d_out) return fail("dist: null output");
+  if (n > 0 && (!a || !b)) return fail("dist: null pointer");
+  const int blocks = (int)dist_blocks(n);
+  if (!scratch || scratch_bytes < (size_t)blocks * sizeof(double) || ((uintptr_t)scratch & 7))
+    return fail("dist: scratch too small or misaligned");
+  const int vec_ok = (((uintptr_t)a | (uintptr_t)b) & 15) == 0;
+  thb_dist_pass1<<<blocks, THB_RA_THREADS, 0, (cudaStream_t)stream>>>(a, b, n, p, vec_ok, (double*)scratch);
+  THB_CUDA(cudaGetLastError());
+  thb_dist_pass2<<<1, 1024, 0, (cudaStream_t)stream>>>((const double*)scratch, blocks, p, d_out);
+  THB_CUDA(cudaGetLastError());
+  return 0;
+}
+
+}  // extern "C"

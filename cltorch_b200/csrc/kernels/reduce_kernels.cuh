@@ -16,10 +16,27 @@
 // "pow(fabs(*in1), p)"; PartialNotEqualFunctor "*in1 != 0"
 // (src/lib/THClTensorMath2.cpp:336-356); the squared deviation is the
 // square_functor of the commented varall (src/lib/THClTensorMath2.cpp:197-207).
-struct ModCopy { static __device__ __forceinline__ float apply(float x, float, float) { return x; } };
-struct ModAbsPow { static __device__ __forceinline__ float apply(float x, float p, float) { return thb_pow(fabsf(x), p); } };
-struct ModNeZero { static __device__ __forceinline__ float apply(float x, float, float) { return x != 0.0f; } };
-struct ModSqDev { static __device__ __forceinline__ float apply(float x, float, float m) { return (x - m) * (x - m); } };
+// |d|^p as a term of a norm or a distance. These terms are summed over many elements and
+// the sum is held to 1e-5 relative, so the general power is exp2(p * log2(d)) on the
+// special-function unit (relative error about 1e-6 for the exponents and magnitudes norms
+// are taken with), unlike in the pointwise pow operator: a double-precision pow per element
+// (about a hundred fp64 instructions) would make these reductions compute-bound.
+__device__ __forceinline__ float thb_abs_pow(float d, float p) {
+  d = fabsf(d);
+  if (p == 2.0f) return d * d;
+  if (p == 1.0f) return d;
+  if (p == 0.0f) return 1.0f;  // pow(x, 0) = 1, also for x = 0
+  return __powf(d, p);
+}
+
+// kFirst: the operator wants the first element of the slice as its third argument.
+struct ModCopy { static constexpr bool kFirst = false; static __device__ __forceinline__ float apply(float x, float, float) { return x; } };
+struct ModAbsPow { static constexpr bool kFirst = false; static __device__ __forceinline__ float apply(float x, float p, float) { return thb_abs_pow(x, p); } };
+struct ModNeZero { static constexpr bool kFirst = false; static __device__ __forceinline__ float apply(float x, float, float) { return x != 0.0f; } };
+struct ModSqDev { static constexpr bool kFirst = false; static __device__ __forceinline__ float apply(float x, float, float m) { return (x - m) * (x - m); } };
+// Deviation from the first element of the slice: the single-pass variance accumulates the
+// sums of (x - k) and (x - k)^2, which keeps them small when the mean is far from zero.
+struct ModShift { static constexpr bool kFirst = true; static __device__ __forceinline__ float apply(float x, float, float k) { return x - k; } };
 // reduceOp strings: TensorAddOp, TensorMulOp, MinOp (fmin), MaxOp (fmax)
 // (src/lib/THClTensorMathPointwise.h:62-140), logicalall/any functors
 // "(int)*in1 && (int)*in2" (src/lib/THClTensorMath.cpp:444-460).
@@ -30,31 +47,37 @@ struct ModSqDev { static __device__ __forceinline__ float apply(float x, float, 
 // double-precision evaluation even for zero-mean data, where an fp32 tree loses
 // digits to cancellation. min/max/and/or are exact in fp32.
 struct RedAdd {
+  static constexpr int kColsBlocks = 6;  // resident blocks per SM of the 128-bit column kernel
   typedef double acc_t;
   static __device__ __forceinline__ double apply(double a, double b) { return a + b; }
   static __device__ __forceinline__ float result(double a, float) { return (float)a; }
 };
 struct RedMul {
+  static constexpr int kColsBlocks = 6;  // resident blocks per SM of the 128-bit column kernel
   typedef double acc_t;
   static __device__ __forceinline__ double apply(double a, double b) { return a * b; }
   static __device__ __forceinline__ float result(double a, float) { return (float)a; }
 };
 struct RedMin {
+  static constexpr int kColsBlocks = 6;  // resident blocks per SM of the 128-bit column kernel
   typedef float acc_t;
   static __device__ __forceinline__ float apply(float a, float b) { return fminf(a, b); }
   static __device__ __forceinline__ float result(float a, float) { return a; }
 };
 struct RedMax {
+  static constexpr int kColsBlocks = 6;  // resident blocks per SM of the 128-bit column kernel
   typedef float acc_t;
   static __device__ __forceinline__ float apply(float a, float b) { return fmaxf(a, b); }
   static __device__ __forceinline__ float result(float a, float) { return a; }
 };
 struct RedAnd {
+  static constexpr int kColsBlocks = 6;  // resident blocks per SM of the 128-bit column kernel
   typedef float acc_t;
   static __device__ __forceinline__ float apply(float a, float b) { return (float)((int)a && (int)b); }
   static __device__ __forceinline__ float result(float a, float) { return a; }
 };
 struct RedOr {
+  static constexpr int kColsBlocks = 6;  // resident blocks per SM of the 128-bit column kernel
   typedef float acc_t;
   static __device__ __forceinline__ float apply(float a, float b) { return (float)((int)a || (int)b); }
   static __device__ __forceinline__ float result(float a, float) { return a; }
@@ -72,6 +95,7 @@ struct ThbMoments {
 };
 template <bool BIASED, bool SQRT>
 struct RedMoments {
+  static constexpr int kColsBlocks = 4;  // 16-byte accumulators: 64 registers per thread
   typedef ThbMoments acc_t;
   static __device__ __forceinline__ ThbMoments apply(ThbMoments a, ThbMoments b) {
     a.s += b.s;
@@ -261,6 +285,7 @@ thb_reduce_dim_contig_block(ThbLayout out, ThbLayout in, thb_u32 rsize, thb_u32 
   __shared__ acc_t smem[32];
   for (thb_u32 s = blockIdx.x; s < nslices; s += gridDim.x) {
     const float* p = in.data + thb_offset(in, s);
+    const float k0 = Mod::kFirst ? p[0] : 0.f;
     acc_t acc[4] = {(acc_t)init, (acc_t)init, (acc_t)init, (acc_t)init};
     if ((((thb_u64)p) & 15) == 0 && (rsize & 3) == 0) {
       const float4* p4 = reinterpret_cast<const float4*>(p);
@@ -273,15 +298,15 @@ thb_reduce_dim_contig_block(ThbLayout out, ThbLayout in, thb_u32 rsize, thb_u32 
 #pragma unroll
         for (int u = 0; u < 4; ++u)
           if (i + u * THB_RD_THREADS < nvec) {
-            acc[0] = Red::apply(acc[0], Mod::apply(v[u].x, mparam, 0.f));
-            acc[1] = Red::apply(acc[1], Mod::apply(v[u].y, mparam, 0.f));
-            acc[2] = Red::apply(acc[2], Mod::apply(v[u].z, mparam, 0.f));
-            acc[3] = Red::apply(acc[3], Mod::apply(v[u].w, mparam, 0.f));
+            acc[0] = Red::apply(acc[0], Mod::apply(v[u].x, mparam, k0));
+            acc[1] = Red::apply(acc[1], Mod::apply(v[u].y, mparam, k0));
+            acc[2] = Red::apply(acc[2], Mod::apply(v[u].z, mparam, k0));
+            acc[3] = Red::apply(acc[3], Mod::apply(v[u].w, mparam, k0));
           }
       }
     } else {
       for (thb_u32 i = threadIdx.x; i < rsize; i += THB_RD_THREADS)
-        acc[0] = Red::apply(acc[0], Mod::apply(p[i], mparam, 0.f));
+        acc[0] = Red::apply(acc[0], Mod::apply(p[i], mparam, k0));
     }
     acc_t r = Red::apply(Red::apply(acc[0], acc[1]), Red::apply(acc[2], acc[3]));
     r = thb_block_fold<Red>(r, (acc_t)init, smem);
@@ -303,6 +328,7 @@ thb_reduce_dim_contig_warp(ThbLayout out, ThbLayout in, thb_u32 rsize, thb_u32 n
        s64 += (thb_u64)gridDim.x * warps_per_block) {
     const thb_u32 s = (thb_u32)s64;
     const float* p = in.data + thb_offset(in, s);
+    const float k0 = Mod::kFirst ? p[0] : 0.f;
     acc_t acc[4] = {(acc_t)init, (acc_t)init, (acc_t)init, (acc_t)init};
     if ((((thb_u64)p) & 15) == 0 && (rsize & 3) == 0) {
       const float4* p4 = reinterpret_cast<const float4*>(p);
@@ -315,14 +341,14 @@ thb_reduce_dim_contig_warp(ThbLayout out, ThbLayout in, thb_u32 rsize, thb_u32 n
 #pragma unroll
         for (int u = 0; u < 4; ++u)
           if (i + u * 32 < nvec) {
-            acc[0] = Red::apply(acc[0], Mod::apply(v[u].x, mparam, 0.f));
-            acc[1] = Red::apply(acc[1], Mod::apply(v[u].y, mparam, 0.f));
-            acc[2] = Red::apply(acc[2], Mod::apply(v[u].z, mparam, 0.f));
-            acc[3] = Red::apply(acc[3], Mod::apply(v[u].w, mparam, 0.f));
+            acc[0] = Red::apply(acc[0], Mod::apply(v[u].x, mparam, k0));
+            acc[1] = Red::apply(acc[1], Mod::apply(v[u].y, mparam, k0));
+            acc[2] = Red::apply(acc[2], Mod::apply(v[u].z, mparam, k0));
+            acc[3] = Red::apply(acc[3], Mod::apply(v[u].w, mparam, k0));
           }
       }
     } else {
-      for (thb_u32 i = lane; i < rsize; i += 32) acc[0] = Red::apply(acc[0], Mod::apply(p[i], mparam, 0.f));
+      for (thb_u32 i = lane; i < rsize; i += 32) acc[0] = Red::apply(acc[0], Mod::apply(p[i], mparam, k0));
     }
     acc_t r = Red::apply(Red::apply(acc[0], acc[1]), Red::apply(acc[2], acc[3]));
 #pragma unroll
@@ -349,6 +375,7 @@ thb_reduce_dim_noncontig(ThbLayout out, ThbLayout in, thb_u32 rsize, thb_u32 rst
        s64 += (thb_u64)gridDim.x * THB_RD_THREADS) {
     const thb_u32 s = (thb_u32)s64;
     const float* p = in.data + thb_offset(in, s);
+    const float k0 = Mod::kFirst ? p[0] : 0.f;
     acc_t acc = (acc_t)init;
     thb_u32 r = r0;
     for (; r + 16 <= r1; r += 16) {
@@ -356,9 +383,9 @@ thb_reduce_dim_noncontig(ThbLayout out, ThbLayout in, thb_u32 rsize, thb_u32 rst
 #pragma unroll
       for (int u = 0; u < 16; ++u) v[u] = p[(thb_u64)(r + u) * rstride];
 #pragma unroll
-      for (int u = 0; u < 16; ++u) acc = Red::apply(acc, Mod::apply(v[u], mparam, 0.f));
+      for (int u = 0; u < 16; ++u) acc = Red::apply(acc, Mod::apply(v[u], mparam, k0));
     }
-    for (; r < r1; ++r) acc = Red::apply(acc, Mod::apply(p[(thb_u64)r * rstride], mparam, 0.f));
+    for (; r < r1; ++r) acc = Red::apply(acc, Mod::apply(p[(thb_u64)r * rstride], mparam, k0));
     if (nchunks == 1) out.data[thb_offset(out, s)] = Red::result(acc, fin_n);
     else partial[(thb_u64)chunk * nslices + s] = acc;
   }
@@ -368,7 +395,7 @@ thb_reduce_dim_noncontig(ThbLayout out, ThbLayout in, thb_u32 rsize, thb_u32 rst
 // slices 4k..4k+3 are 4 consecutive floats at a 16-byte aligned address in every row of
 // the reduced dimension. 8 rows in flight per thread.
 template <class Mod, class Red>
-__global__ void __launch_bounds__(THB_RD_THREADS, 6)
+__global__ void __launch_bounds__(THB_RD_THREADS, Red::kColsBlocks)
 thb_reduce_dim_noncontig_v4(ThbLayout out, ThbLayout in, thb_u32 rsize, thb_u32 rstride, thb_u32 nslices,
                             thb_u32 chunk_len, thb_u32 nchunks, float init, float mparam,
                             typename Red::acc_t* partial) {
@@ -382,6 +409,7 @@ thb_reduce_dim_noncontig_v4(ThbLayout out, ThbLayout in, thb_u32 rsize, thb_u32 
        q64 += (thb_u64)gridDim.x * THB_RD_THREADS) {
     const thb_u32 s = (thb_u32)q64 << 2;
     const float* p = in.data + thb_offset(in, s);
+    const float4 kq = Mod::kFirst ? *reinterpret_cast<const float4*>(p) : make_float4(0.f, 0.f, 0.f, 0.f);
     acc_t acc[4] = {(acc_t)init, (acc_t)init, (acc_t)init, (acc_t)init};
     thb_u32 r = r0;
     for (; r + 8 <= r1; r += 8) {
@@ -390,18 +418,18 @@ thb_reduce_dim_noncontig_v4(ThbLayout out, ThbLayout in, thb_u32 rsize, thb_u32 
       for (int u = 0; u < 8; ++u) v[u] = *reinterpret_cast<const float4*>(p + (thb_u64)(r + u) * rstride);
 #pragma unroll
       for (int u = 0; u < 8; ++u) {
-        acc[0] = Red::apply(acc[0], Mod::apply(v[u].x, mparam, 0.f));
-        acc[1] = Red::apply(acc[1], Mod::apply(v[u].y, mparam, 0.f));
-        acc[2] = Red::apply(acc[2], Mod::apply(v[u].z, mparam, 0.f));
-        acc[3] = Red::apply(acc[3], Mod::apply(v[u].w, mparam, 0.f));
+        acc[0] = Red::apply(acc[0], Mod::apply(v[u].x, mparam, kq.x));
+        acc[1] = Red::apply(acc[1], Mod::apply(v[u].y, mparam, kq.y));
+        acc[2] = Red::apply(acc[2], Mod::apply(v[u].z, mparam, kq.z));
+        acc[3] = Red::apply(acc[3], Mod::apply(v[u].w, mparam, kq.w));
       }
     }
     for (; r < r1; ++r) {
       const float4 v = *reinterpret_cast<const float4*>(p + (thb_u64)r * rstride);
-      acc[0] = Red::apply(acc[0], Mod::apply(v.x, mparam, 0.f));
-      acc[1] = Red::apply(acc[1], Mod::apply(v.y, mparam, 0.f));
-      acc[2] = Red::apply(acc[2], Mod::apply(v.z, mparam, 0.f));
-      acc[3] = Red::apply(acc[3], Mod::apply(v.w, mparam, 0.f));
+      acc[0] = Red::apply(acc[0], Mod::apply(v.x, mparam, kq.x));
+      acc[1] = Red::apply(acc[1], Mod::apply(v.y, mparam, kq.y));
+      acc[2] = Red::apply(acc[2], Mod::apply(v.z, mparam, kq.z));
+      acc[3] = Red::apply(acc[3], Mod::apply(v.w, mparam, kq.w));
     }
 #pragma unroll
     for (int j = 0; j < 4; ++j) {

@@ -172,10 +172,15 @@ static void moments_point(THClState* state, THClTensor* src, int what /*0 mean, 
     reduce_all(state, src, THB200_MOD_COPY, THB200_RED_ADD, 0.f, 0.f, nullptr, THB200_FIN_DIV, (float)n, d_out);
     return;
   }
-  float* mean = ctx->result + 8;
-  reduce_all(state, src, THB200_MOD_COPY, THB200_RED_ADD, 0.f, 0.f, nullptr, THB200_FIN_DIV, (float)n, mean);
-  reduce_all(state, src, THB200_MOD_SQDEV, THB200_RED_ADD, 0.f, 0.f, mean,
-             what == 1 ? THB200_FIN_DIV : THB200_FIN_DIV_SQRT, (float)(n - 1), d_out);
+  // one pass over the input (shifted sums of x and x^2 in double) instead of the reference's
+  // mean pass followed by a squared-deviation pass (src/lib/THClTensorMath2.cpp:209-229)
+  if (src->nDimension > THB200_MAX_DIMS) raise("tensor too large or too many (>%d) dimensions", THB200_MAX_DIMS);
+  use_device(src->device);
+  View v;
+  v.set(src);
+  float* scratch = ensure_scratch(ctx, thb200_var_all_scratch_bytes(n));
+  check_thb(thb200_var_all(ctx->stream, &v.t, 0, what == 2, d_out, scratch, ctx->scratch_bytes));
+  after_launch(state, ctx);
 }
 
 static void reduce_dim(THClState* state, THClTensor* self, THClTensor* src, int mod, int red, float init, float mparam,
@@ -656,6 +661,151 @@ void THClTensor_max(THClState* state, THClTensor* values, THClTensor* indices, T
 void THClTensor_min(THClState* state, THClTensor* values, THClTensor* indices, THClTensor* src, long dim) {
   THCL_BEGIN
   reduce_dim_index(state, values, indices, src, dim, 0);
+  THCL_END_VOID
+}
+
+}  // extern "C"
+
+// ---- variance / standard deviation along one dimension, scans, renorm, dist ---------------
+
+static void var_dim(THClState* state, THClTensor* self, THClTensor* src, long dim, int flag, int apply_sqrt) {
+  if (self->device != src->device) raise("tensors are on different devices");
+  if (src->nDimension > THB200_MAX_DIMS) raise("tensor too large or too many (>%d) dimensions", THB200_MAX_DIMS);
+  arg_check(dim >= 0 && dim < src->nDimension, 3, "dimension out of range");
+  // the result keeps the dimension with size 1 (src/lib/THClTensorMath2.cpp:296-299)
+  THLongStorage* sizes = THClTensor_newSizeOf(state, src);
+  sizes->data[dim] = 1;
+  THClTensor_resize(state, self, sizes, nullptr);
+  THLongStorage_free(sizes);
+  THClDeviceContext* ctx = context(state, src->device);
+  use_device(src->device);
+  View vo, vi;
+  vo.set(self);
+  vi.set(src);
+  float* scratch = ensure_scratch(ctx, thb200_var_dim_scratch_bytes(&vi.t, (int)dim));
+  check_thb(thb200_var_dim(ctx->stream, &vo.t, &vi.t, (int)dim, flag, apply_sqrt, scratch, ctx->scratch_bytes));
+  after_launch(state, ctx);
+}
+
+static void scan_dim(THClState* state, THClTensor* self_, THClTensor* src, long dim, int op) {
+  if (self_->device != src->device) raise("tensors are on different devices");
+  arg_check(dim >= 0 && dim < src->nDimension, 3, "dimension out of range");
+  // THClTensor_scanDim, src/lib/THClTensorMathScan.cpp:127-142: resize, contiguous copies of both
+  THClTensor_resizeAs(state, self_, src);
+  THClTensor* self = THClTensor_newContiguous(state, self_);
+  THClTensor* in = THClTensor_newContiguous(state, src);
+  int64_t outer = 1, inner = 1;
+  for (int d = 0; d < dim; ++d) outer *= in->size[d];
+  for (int d = (int)dim + 1; d < in->nDimension; ++d) inner *= in->size[d];
+  const int64_t n = in->size[dim];
+  THClDeviceContext* ctx = context(state, src->device);
+  use_device(src->device);
+  float* dst = THClTensor_data(state, self);
+  const float* sp = THClTensor_data(state, in);
+  void* scratch = ensure_scratch(ctx, thb200_scan_scratch_bytes(dst, sp, outer, n, inner));
+  int rc = thb200_scan(ctx->stream, op, dst, sp, outer, n, inner, scratch, ctx->scratch_bytes);
+  std::string err = rc ? thb200_last_error() : "";
+  THClTensor_free(state, in);
+  THClTensor_freeCopyTo(state, self, self_);
+  if (rc) raise("%s", err.c_str());
+  after_launch(state, ctx);
+}
+
+extern "C" {
+
+void THClTensor_var(THClState* state, THClTensor* self, THClTensor* src, long dimension, int flag) {
+  THCL_BEGIN
+  var_dim(state, self, src, dimension, flag, 0);
+  THCL_END_VOID
+}
+void THClTensor_std(THClState* state, THClTensor* self, THClTensor* src, long dimension, int flag) {
+  THCL_BEGIN
+  var_dim(state, self, src, dimension, flag, 1);
+  THCL_END_VOID
+}
+void THClTensor_cumsum(THClState* state, THClTensor* self, THClTensor* src, long dimension) {
+  THCL_BEGIN
+  scan_dim(state, self, src, dimension, THB200_RED_ADD);
+  THCL_END_VOID
+}
+void THClTensor_cumprod(THClState* state, THClTensor* self, THClTensor* src, long dimension) {
+  THCL_BEGIN
+  scan_dim(state, self, src, dimension, THB200_RED_MUL);
+  THCL_END_VOID
+}
+
+void THClTensor_renorm(THClState* state, THClTensor* self, THClTensor* src, float value, long dimension, float maxnorm) {
+  THCL_BEGIN
+  if (self->device != src->device) raise("tensors are on different devices");
+  arg_check(dimension >= 0 && dimension < THClTensor_nDimension(state, src), 3, "invalid dimension");
+  arg_check(value > 0, 2, "non-positive-norm not supported");
+  arg_check(THClTensor_nDimension(state, src) > 1, 1, "need at least 2 dimensions");
+  THClDeviceContext* ctx = context(state, src->device);
+  use_device(src->device);
+  // src/lib/THClTensorMath2.cpp:414-446: the sub-tensors along `dimension` become the rows of a
+  // contiguous clone of the transposed source, are rescaled in place, and the clone is copied
+  // back transposed. In place on a contiguous tensor along dimension 0 the clone is not needed.
+  const bool direct = self == src && dimension == 0 && THClTensor_isContiguous(state, src);
+  THClTensor* data = nullptr;
+  if (direct) {
+    data = self;
+  } else {
+    THClTensor* src_t = THClTensor_newTranspose(state, src, (int)dimension, 0);
+    data = THClTensor_newClone(state, src_t);
+    THClTensor_free(state, src_t);
+  }
+  const int64_t rows = data->size[0];
+  const int64_t size = rows > 0 ? THClTensor_nElement(state, data) / rows : 0;
+  void* scratch = ensure_scratch(ctx, thb200_renorm_rows_scratch_bytes(rows, size));
+  int rc = thb200_renorm_rows(ctx->stream, THClTensor_data(state, data), rows, size, value, maxnorm, scratch,
+                              ctx->scratch_bytes);
+  std::string err = rc ? thb200_last_error() : "";
+  if (!direct) {
+    if (!rc) {
+      THClTensor* back = THClTensor_newTranspose(state, data, (int)dimension, 0);
+      THClTensor_resizeAs(state, self, back);
+      THClTensor_copy(state, self, back);
+      THClTensor_free(state, back);
+    }
+    THClTensor_free(state, data);
+  }
+  if (rc) raise("%s", err.c_str());
+  after_launch(state, ctx);
+  THCL_END_VOID
+}
+
+static void dist_into(THClState* state, THClTensor* self, THClTensor* src, float value, float* d_out) {
+  if (self->device != src->device) raise("tensors are on different devices");
+  arg_check(THClTensor_nElement(state, self) == THClTensor_nElement(state, src), 2, "sizes do not match");
+  THClDeviceContext* ctx = context(state, self->device);
+  use_device(self->device);
+  // contiguous copies of both, as src/lib/THClTensorMath2.cpp:463-465
+  THClTensor* a = THClTensor_newContiguous(state, self);
+  THClTensor* b = THClTensor_newContiguous(state, src);
+  const long n = THClTensor_nElement(state, a);
+  void* scratch = ensure_scratch(ctx, thb200_dist_scratch_bytes(n));
+  int rc = thb200_dist(ctx->stream, THClTensor_data(state, a), THClTensor_data(state, b), n, value, d_out, scratch,
+                       ctx->scratch_bytes);
+  std::string err = rc ? thb200_last_error() : "";
+  THClTensor_free(state, a);
+  THClTensor_free(state, b);
+  if (rc) raise("%s", err.c_str());
+  after_launch(state, ctx);
+}
+
+float THClTensor_dist(THClState* state, THClTensor* self, THClTensor* src, float value) {
+  THCL_BEGIN
+  THClDeviceContext* ctx = context(state, self->device);
+  dist_into(state, self, src, value, ctx->result);
+  return read_result(state, ctx, 0);
+  THCL_END(0.f)
+}
+// The distance as a point tensor: no host synchronisation.
+void THClTensor_dist_gpu(THClState* state, THClTensor* res, THClTensor* self, THClTensor* src, float value) {
+  THCL_BEGIN
+  if (res->device != self->device) raise("tensors are on different devices");
+  THClTensor_resize0d(state, res);
+  dist_into(state, self, src, value, res->storage->wrapper + res->storageOffset);
   THCL_END_VOID
 }
 

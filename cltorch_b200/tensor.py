@@ -610,16 +610,62 @@ class ClTensor:
     def mean(self, *args):
         return self._reduce("mean", args)
 
-    def std(self, *args):
+    def _moment(self, name, args):
+        """`x:std()` -> float; `r:std(x)` -> point tensor r; `x:std(dim [, flag])` -> new tensor;
+        `r:std(x, dim [, flag])` -> r (reference src/TensorMath.lua:1110-1121)."""
         if len(args) == 0:
-            return call("THClTensor_stdall", state(), self._p)
-        call("THClTensor_stdall_gpu", state(), self._p, args[0]._p)
-        return self
+            return call(f"THClTensor_{name}all", state(), self._p)
+        if _is_tensor(args[0]):
+            if len(args) == 1:
+                call(f"THClTensor_{name}all_gpu", state(), self._p, args[0]._p)
+                return self
+            flag = bool(args[2]) if len(args) > 2 else False
+            call(f"THClTensor_{name}", state(), self._p, args[0]._p, int(args[1]) - 1, int(flag))
+            return self
+        flag = bool(args[1]) if len(args) > 1 else False
+        out = self._new()
+        call(f"THClTensor_{name}", state(), out._p, self._p, int(args[0]) - 1, int(flag))
+        return out
+
+    def std(self, *args):
+        return self._moment("std", args)
 
     def var(self, *args):
-        if len(args) == 0:
-            return call("THClTensor_varall", state(), self._p)
-        call("THClTensor_varall_gpu", state(), self._p, args[0]._p)
+        return self._moment("var", args)
+
+    def _scan(self, name, args):
+        """`x:cumsum(dim)` -> new tensor; `r:cumsum(x, dim)` -> r (reference src/TensorMath.lua:955-962)."""
+        if args and _is_tensor(args[0]):
+            call(f"THClTensor_{name}", state(), self._p, args[0]._p, int(args[1]) - 1 if len(args) > 1 else 0)
+            return self
+        out = self._new()
+        call(f"THClTensor_{name}", state(), out._p, self._p, int(args[0]) - 1 if args else 0)
+        return out
+
+    def cumsum(self, *args):
+        return self._scan("cumsum", args)
+
+    def cumprod(self, *args):
+        return self._scan("cumprod", args)
+
+    def renorm(self, *args):
+        """`x:renorm(p, dim, maxnorm)` -> new tensor; `r:renorm(x, p, dim, maxnorm)` -> r, where r may be x
+        (reference src/TensorMath.lua:1136-1142)."""
+        if args and _is_tensor(args[0]):
+            src, p_, dim, maxnorm = args
+            call("THClTensor_renorm", state(), self._p, src._p, float(p_), int(dim) - 1, float(maxnorm))
+            return self
+        p_, dim, maxnorm = args
+        out = self._new()
+        call("THClTensor_renorm", state(), out._p, self._p, float(p_), int(dim) - 1, float(maxnorm))
+        return out
+
+    def dist(self, other: "ClTensor", value: float = 2.0) -> float:
+        return call("THClTensor_dist", state(), self._p, other._p, float(value))
+
+    def dist_gpu(self, a: "ClTensor", b: "ClTensor", value: float = 2.0) -> "ClTensor":
+        """self becomes the point tensor holding dist(a, b); no host synchronisation."""
+        call("THClTensor_dist_gpu", state(), self._p, a._p, b._p, float(value))
         return self
 
     def norm(self, value: float = 2.0, dim: Optional[int] = None):

@@ -340,7 +340,8 @@ THCL_API void THClTensor_logicalany_gpu(THClState* state, THClTensor* self, THCl
 /* mean / var / std as point tensors. The reference declares meanall/varall/stdall
  * (src/lib/THClTensorMath.h:88-93) but ships only the host-scalar meanall; these
  * follow its commented specification (src/lib/THClTensorMath2.cpp:181-229):
- * mean = sum / n, var = sum((x - mean)^2) / (n - 1), std = sqrt(var). */
+ * mean = sum / n, var = sum((x - mean)^2) / (n - 1), std = sqrt(var). var and std read the
+ * input once (shifted sums of x and x^2 kept in double) instead of twice. */
 THCL_API void THClTensor_meanall_gpu(THClState* state, THClTensor* self, THClTensor* src);
 THCL_API void THClTensor_varall_gpu(THClState* state, THClTensor* self, THClTensor* src);
 THCL_API void THClTensor_stdall_gpu(THClState* state, THClTensor* self, THClTensor* src);
@@ -353,6 +354,23 @@ THCL_API void THClTensor_norm(THClState* state, THClTensor* self, THClTensor* sr
 /* indices are 1-based positions stored as fp32; first occurrence wins ties */
 THCL_API void THClTensor_max(THClState* state, THClTensor* values, THClTensor* indices, THClTensor* src, long dim);
 THCL_API void THClTensor_min(THClState* state, THClTensor* values, THClTensor* indices, THClTensor* src, long dim);
+
+/* Variance / standard deviation along `dim` (0-based); flag != 0 divides by n instead of n - 1.
+ * Declared in src/lib/THClTensorMath.h:93-95; the reference's implementation
+ * (src/lib/THClTensorMath2.cpp:293-333, kernels src/lib/THClTensorMath2.cl:5-108) is commented
+ * out and serves as the specification. `self` keeps the dimension with size 1. */
+THCL_API void THClTensor_var(THClState* state, THClTensor* self, THClTensor* src, long dim, int flag);
+THCL_API void THClTensor_std(THClState* state, THClTensor* self, THClTensor* src, long dim, int flag);
+/* Inclusive scans along `dim` (src/lib/THClTensorMathScan.cpp:144-156); self is resized like src. */
+THCL_API void THClTensor_cumsum(THClState* state, THClTensor* self, THClTensor* src, long dim);
+THCL_API void THClTensor_cumprod(THClState* state, THClTensor* self, THClTensor* src, long dim);
+/* Every sub-tensor along `dimension` whose p-norm (p = value > 0) exceeds max_norm is scaled to
+ * max_norm (src/lib/THClTensorMath.h:98; specification src/lib/THClTensorMath2.cpp:414-446). */
+THCL_API void THClTensor_renorm(THClState* state, THClTensor* self, THClTensor* src, float value, long dimension, float max_norm);
+/* (sum |self - src|^value)^(1/value) (src/lib/THClTensorMath.h:99; specification
+ * src/lib/THClTensorMath2.cpp:448-475); the _gpu form leaves the result in a point tensor. */
+THCL_API float THClTensor_dist(THClState* state, THClTensor* self, THClTensor* src, float value);
+THCL_API void THClTensor_dist_gpu(THClState* state, THClTensor* res, THClTensor* self, THClTensor* src, float value);
 
 /* ---- BLAS front-ends: src/lib/THClTensorMathBlas.cpp ----------------------- */
 

@@ -149,6 +149,52 @@ int thb200_reduce_dim_index(void* stream, int is_max, float* values, float* indi
                             int64_t outer, int64_t n, int64_t inner, float* scratch, size_t scratch_bytes);
 size_t thb200_reduce_dim_index_scratch_bytes(int64_t outer, int64_t n, int64_t inner);
 
+/* Variance / standard deviation along one dimension in ONE pass over the input:
+ * THClTensor_var / THClTensor_std with kernels THClTensor_kernel_varOuterDim /
+ * varInnermostDim and THClTensor_computeVar (src/lib/THClTensorMath2.cl:5-108; host side
+ * src/lib/THClTensorMath2.cpp:293-333, commented out in the reference and served from there
+ * as the specification). biased != 0 divides by n, otherwise by n - 1; negative results of
+ * the final subtraction are clamped to 0; apply_sqrt != 0 gives the standard deviation.
+ * The sums of (x - k) and (x - k)^2, k = first element of the slice, are kept in double.
+ * `out` has the shape of `in` with size 1 at `dim`; any strided layouts. */
+size_t thb200_var_dim_scratch_bytes(const thb200_tensor* in, int dim);
+int thb200_var_dim(void* stream, const thb200_tensor* out, const thb200_tensor* in, int dim, int biased,
+                   int apply_sqrt, float* scratch, size_t scratch_bytes);
+
+/* The same over the whole tensor into *d_out (device pointer): THClTensor_varall /
+ * stdall, src/lib/THClTensorMath2.cpp:197-231 (biased = 0 there), in one pass instead of
+ * the reference's mean pass followed by a squared-deviation pass. */
+size_t thb200_var_all_scratch_bytes(int64_t n);
+int thb200_var_all(void* stream, const thb200_tensor* in, int biased, int apply_sqrt, float* d_out,
+                   float* scratch, size_t scratch_bytes);
+
+/* Inclusive scan along n of a contiguous tensor viewed as [outer][n][inner]:
+ * THClTensor_scanDim with kernels THClTensor_kernel_scanOuterDim / scanInnermostDim
+ * (src/lib/THClTensorMathScan.cpp:29-142, src/lib/THClTensorMathScan.cl:27-139); op is
+ * THB200_RED_ADD (cumsum, start 0) or THB200_RED_MUL (cumprod, start 1). Running values are
+ * kept in double and rounded at each store. dst may be src. When the other dimensions are
+ * too small to fill the GPU, n is cut into chunks (totals, scan of totals, scan with carry)
+ * and `scratch` (8-byte aligned) holds the carries; the pointers matter to the size because
+ * 16-byte aligned operands take a different path. */
+size_t thb200_scan_scratch_bytes(const float* dst, const float* src, int64_t outer, int64_t n, int64_t inner);
+int thb200_scan(void* stream, int op, float* dst, const float* src, int64_t outer, int64_t n, int64_t inner,
+                void* scratch, size_t scratch_bytes);
+
+/* THClTensor_kernel_renorm, src/lib/THClTensorMath2.cl:110-143 (host side
+ * src/lib/THClTensorMath2.cpp:414-446, commented out in the reference): every row of the
+ * contiguous [rows][size] matrix whose p-norm exceeds maxnorm is multiplied in place by
+ * maxnorm / (norm + 1e-7); other rows are not touched. `scratch` holds one float per row. */
+size_t thb200_renorm_rows_scratch_bytes(int64_t rows, int64_t size);
+int thb200_renorm_rows(void* stream, float* data, int64_t rows, int64_t size, float p, float maxnorm,
+                       void* scratch, size_t scratch_bytes);
+
+/* THClTensor_dist, src/lib/THClTensorMath2.cpp:448-475 (commented out in the reference):
+ * *d_out = (sum |a[i] - b[i]|^p)^(1/p) over two contiguous vectors; the sum is kept in
+ * double. The result stays on the device. `scratch` must be 8-byte aligned. */
+size_t thb200_dist_scratch_bytes(int64_t n);
+int thb200_dist(void* stream, const float* a, const float* b, int64_t n, float p, float* d_out, void* scratch,
+                size_t scratch_bytes);
+
 /* Fixed-order fold of `count` device floats into *d_out (count <= 1024): the
  * last step of a sum sharded over several GPUs, after the per-GPU partials
  * have been gathered. No counterpart in the reference (it has no collectives). */

@@ -55,6 +55,11 @@ def lib() -> C.CDLL:
         L.orc_overlapping.argtypes = [C.c_int, C.POINTER(C.c_int64), C.POINTER(C.c_int64)]
         L.orc_index_to_offset.restype = C.c_int64
         L.orc_index_to_offset.argtypes = [C.c_int, C.POINTER(C.c_int64), C.POINTER(C.c_int64), C.c_int64]
+        L.orc_var_dim.argtypes = [C.c_int, C.c_int, C.c_void_p, C.c_void_p, C.c_int64, C.c_int64, C.c_int64]
+        L.orc_scan.argtypes = [C.c_int, C.c_void_p, C.c_void_p, C.c_int64, C.c_int64, C.c_int64]
+        L.orc_renorm_rows.argtypes = [C.c_void_p, C.c_int64, C.c_int64, C.c_float, C.c_float]
+        L.orc_dist.restype = C.c_double
+        L.orc_dist.argtypes = [C.c_void_p, C.c_void_p, C.c_int64, C.c_float]
         L.orc_time_sum.restype = C.c_double
         L.orc_time_sum.argtypes = [C.c_void_p, C.c_int64]
         L.orc_time_map2_sqrt.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64]
@@ -167,6 +172,47 @@ def reduce_dim_index(arr: np.ndarray, dim: int, is_max: bool):
     indices = np.empty(shape, dtype=np.float32)
     lib().orc_reduce_dim_index(int(is_max), values.ctypes.data, indices.ctypes.data, a.ctypes.data, outer, n, inner)
     return values, indices
+
+
+def _outer_n_inner(a: np.ndarray, dim: int):
+    outer = int(np.prod(a.shape[:dim])) if dim > 0 else 1
+    inner = int(np.prod(a.shape[dim + 1:])) if dim + 1 < a.ndim else 1
+    return outer, a.shape[dim], inner
+
+
+def var_dim(arr: np.ndarray, dim: int, flag: bool = False, apply_sqrt: bool = False) -> np.ndarray:
+    """var / std along `dim` (size 1 kept), reference src/lib/THClTensorMath2.cl:5-108."""
+    a = np.ascontiguousarray(arr, dtype=np.float32)
+    outer, n, inner = _outer_n_inner(a, dim)
+    shape = list(a.shape)
+    shape[dim] = 1
+    out = np.empty(shape, dtype=np.float32)
+    lib().orc_var_dim(int(flag), int(apply_sqrt), out.ctypes.data, a.ctypes.data, outer, n, inner)
+    return out
+
+
+def scan(arr: np.ndarray, dim: int, is_mul: bool = False) -> np.ndarray:
+    """cumsum / cumprod along `dim`, reference src/lib/THClTensorMathScan.cl:27-50."""
+    a = np.ascontiguousarray(arr, dtype=np.float32)
+    outer, n, inner = _outer_n_inner(a, dim)
+    out = np.empty_like(a)
+    lib().orc_scan(int(is_mul), out.ctypes.data, a.ctypes.data, outer, n, inner)
+    return out
+
+
+def renorm(arr: np.ndarray, value: float, dim: int, maxnorm: float) -> np.ndarray:
+    """renorm as src/lib/THClTensorMath2.cpp:414-446: transpose(dim, 0), contiguous clone, rows rescaled, transposed back."""
+    a = np.asarray(arr, dtype=np.float32)
+    data = np.array(np.swapaxes(a, dim, 0), dtype=np.float32, order="C", copy=True)
+    rows = data.shape[0]
+    lib().orc_renorm_rows(data.ctypes.data, rows, data.size // max(rows, 1), value, maxnorm)
+    return np.ascontiguousarray(np.swapaxes(data, dim, 0))
+
+
+def dist(a: np.ndarray, b: np.ndarray, value: float = 2.0) -> float:
+    x = np.ascontiguousarray(a, dtype=np.float32).ravel()
+    y = np.ascontiguousarray(b, dtype=np.float32).ravel()
+    return float(lib().orc_dist(x.ctypes.data, y.ctypes.data, x.size, value))
 
 
 def addmm(beta: float, t: np.ndarray, alpha: float, m1: np.ndarray, m2: np.ndarray) -> np.ndarray:

@@ -389,6 +389,77 @@ void orc_reduce_dim_index(int is_max, float* values, float* indices, const float
   }
 }
 
+/* THClTensor_kernel_varOuterDim / varInnermostDim + THClTensor_computeVar
+ * (src/lib/THClTensorMath2.cl:5-108; host side src/lib/THClTensorMath2.cpp:293-333, commented out
+ * in the reference) on a contiguous [outer][n][inner] source: per slice sum and sum of squares,
+ * then flag ? sum2/n - mean^2 : sum2/(n-1) - n/(n-1)*mean^2, clamped at 0, optional sqrt.
+ * Evaluated in double (the reference accumulates in fp32). */
+void orc_var_dim(int flag, int apply_sqrt, float* tgt, const float* src, int64_t outer, int64_t n, int64_t inner) {
+#pragma omp parallel for schedule(static)
+  for (int64_t s = 0; s < outer * inner; ++s) {
+    int64_t o = s / inner, i = s % inner;
+    const float* p = src + o * n * inner + i;
+    /* computeVar's sum2/n - mean^2 (flag) or sum2/(n-1) - n/(n-1)*mean^2 equals the mean of the
+     * squared deviations over n (flag) or n-1; that form is evaluated here, in two passes, because
+     * it does not cancel when the mean is far from zero */
+    double mean = 0;
+    for (int64_t c = 0; c < n; ++c) mean += (double)p[c * inner];
+    mean /= (double)n;
+    double sum2 = 0;
+    for (int64_t c = 0; c < n; ++c) {
+      double d = (double)p[c * inner] - mean;
+      sum2 += d * d;
+    }
+    sum2 /= flag ? (double)n : (double)n - 1;
+    sum2 = sum2 < 0 ? 0 : sum2;
+    tgt[s] = (float)(apply_sqrt ? sqrt(sum2) : sum2);
+  }
+}
+
+/* THClTensor_kernel_scanOuterDim (src/lib/THClTensorMathScan.cl:27-50): inclusive scan along n of
+ * a contiguous [outer][n][inner] tensor, acc = init; acc = op(acc, x); store. is_mul selects
+ * TensorMulOp (cumprod, init 1) over TensorAddOp (cumsum, init 0), src/lib/THClTensorMathScan.cpp:144-156.
+ * The running value is kept in double (the reference keeps fp32). */
+void orc_scan(int is_mul, float* tgt, const float* src, int64_t outer, int64_t n, int64_t inner) {
+#pragma omp parallel for schedule(static)
+  for (int64_t s = 0; s < outer * inner; ++s) {
+    int64_t o = s / inner, i = s % inner;
+    const float* p = src + o * n * inner + i;
+    float* t = tgt + o * n * inner + i;
+    double acc = is_mul ? 1.0 : 0.0;
+    for (int64_t c = 0; c < n; ++c) {
+      acc = is_mul ? acc * (double)p[c * inner] : acc + (double)p[c * inner];
+      t[c * inner] = (float)acc;
+    }
+  }
+}
+
+/* THClTensor_kernel_renorm (src/lib/THClTensorMath2.cl:110-143) on a contiguous [rows][size]
+ * matrix, in place: norm = (sum |x|^value)^(1/value); rows with norm > maxnorm are multiplied by
+ * maxnorm / (norm + 1e-7). Sums in double. */
+void orc_renorm_rows(float* data, int64_t rows, int64_t size, float value, float maxnorm) {
+#pragma omp parallel for schedule(static)
+  for (int64_t r = 0; r < rows; ++r) {
+    float* row = data + r * size;
+    double acc = 0;
+    for (int64_t i = 0; i < size; ++i) acc += pow(fabs((double)row[i]), (double)value);
+    float norm = (float)pow((double)(float)acc, 1.0 / (double)value);
+    if (norm > maxnorm) {
+      float f = (float)((double)maxnorm / ((double)norm + 1e-7));
+      for (int64_t i = 0; i < size; ++i) row[i] *= f;
+    }
+  }
+}
+
+/* THClTensor_dist (src/lib/THClTensorMath2.cpp:448-475): (sum |a - b|^value)^(1/value) over two
+ * contiguous vectors; the difference is taken in fp32 as the functor does, the sum in double. */
+double orc_dist(const float* a, const float* b, int64_t n, float value) {
+  double acc = 0;
+#pragma omp parallel for schedule(static) reduction(+ : acc)
+  for (int64_t i = 0; i < n; ++i) acc += pow(fabs((double)(float)(a[i] - b[i])), (double)value);
+  return pow(acc, 1.0 / (double)value);
+}
+
 /* r = beta * t + alpha * m1 * m2 (THClTensor_addmm, src/lib/THClTensorMathBlas.cpp:107-214) on 2-D
  * strided views, fp64 accumulation. Batched form: the same for every index of a leading dim. */
 void orc_addmm(float* r, int64_t r_s0, int64_t r_s1, float beta, const float* t, int64_t t_s0, int64_t t_s1, float alpha,

@@ -132,6 +132,46 @@ with np.errstate(all="ignore"):
         case(f"min_dim{dim + 1}", "src/test/unit_tensor.lua:810-832", "min", {"a": Mx, "dim": dim},
              mx.min(axis=dim, keepdims=True), 0, indices=lst(np.expand_dims(mx.argmin(axis=dim) + 1, dim)))
 
+    # scans: the literal matrix of src/test/test-tensor.lua:612-626 (exact), and the seeded 50 x 60 of
+    # src/test/unit_tensor.lua:876-888 (default dimension = first, src/TensorMath.lua:955-961)
+    Asc = [[3, 1, 7], [3, 2, 4]]
+    asc = np.array(Asc, dtype=np.float64)
+    for dim in (0, 1):
+        case(f"cumsum_dim{dim + 1}", "src/test/test-tensor.lua:612-617", "cumsum", {"a": Asc, "dim": dim}, np.cumsum(asc, axis=dim), 0)
+        case(f"cumprod_dim{dim + 1}", "src/test/test-tensor.lua:619-626", "cumprod", {"a": Asc, "dim": dim}, np.cumprod(asc, axis=dim), 0)
+    X = uniform(108, (50, 60))
+    for dim in (0, 1):
+        case(f"cumsum_uniform_dim{dim + 1}", "src/test/unit_tensor.lua:876-881", "cumsum", {"seed": 108, "shape": [50, 60], "dim": dim},
+             np.cumsum(X.astype(np.float64), axis=dim), TOL)
+        case(f"cumprod_uniform_dim{dim + 1}", "src/test/unit_tensor.lua:883-888", "cumprod", {"seed": 108, "shape": [50, 60], "dim": dim},
+             np.cumprod(X.astype(np.float64), axis=dim), TOL)
+
+    # var / std along a dimension: THClTensor_computeVar, src/lib/THClTensorMath2.cl:5-23 (flag: divide by n)
+    for dim in (0, 1):
+        for flag in (False, True):
+            case(f"var_dim{dim + 1}_flag{int(flag)}", "src/lib/THClTensorMath2.cl:5-23", "var", {"a": M23, "dim": dim, "flag": flag},
+                 m.var(axis=dim, ddof=0 if flag else 1, keepdims=True), 1e-6)
+            case(f"std_dim{dim + 1}_flag{int(flag)}", "src/lib/THClTensorMath2.cl:5-23", "std", {"a": M23, "dim": dim, "flag": flag},
+                 m.std(axis=dim, ddof=0 if flag else 1, keepdims=True), 1e-6)
+    case("var_all", "src/lib/THClTensorMath2.cpp:209-223", "varall", {"a": M23}, [m.var(ddof=1)], 1e-6)
+    case("std_all", "src/lib/THClTensorMath2.cpp:225-229", "stdall", {"a": M23}, [m.std(ddof=1)], 1e-6)
+
+    # renorm (src/lib/THClTensorMath2.cl:110-143): rows of norm > maxnorm scaled by maxnorm / (norm + 1e-7)
+    R = [[3, 4, 0], [0.3, 0.4, 0], [1, 2, 2]]                     # 2-norms of the rows: 5, 0.5, 3
+    r = np.array(R, dtype=np.float64)
+    nr = np.sqrt((r * r).sum(axis=1, keepdims=True))
+    case("renorm_rows", "src/lib/THClTensorMath2.cl:110-143", "renorm", {"a": R, "p": 2, "dim": 0, "maxnorm": 1},
+         np.where(nr > 1, r * (1 / (nr + 1e-7)), r), 1e-6)
+    nc = np.abs(r).sum(axis=0, keepdims=True)                      # 1-norms of the columns: 4.3, 6.4, 2
+    case("renorm_cols", "src/lib/THClTensorMath2.cl:110-143", "renorm", {"a": R, "p": 1, "dim": 1, "maxnorm": 3},
+         np.where(nc > 3, r * (3 / (nc + 1e-7)), r), 1e-6)
+
+    # dist (src/lib/THClTensorMath2.cpp:448-475)
+    cd, dd = f32(C23).astype(np.float64), f32(D23).astype(np.float64)
+    for pv in (1, 2, 3):
+        case(f"dist_p{pv}", "src/lib/THClTensorMath2.cpp:448-475", "dist", {"a": C23, "b": D23, "p": pv},
+             [(np.abs(cd - dd) ** pv).sum() ** (1.0 / pv)], 1e-5)
+
 # Dimension collapsing (src/lib/THClReduceApplyUtils.h:68-170), worked by hand from the rule
 # "drop size-1 dims; merge dim i into i+1 when stride[i] == size[i+1]*stride[i+1]".
 collapse = [

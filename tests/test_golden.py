@@ -77,6 +77,17 @@ def run_oracle(case):
             O.apply(op.upper() + "_3", [O.View(a), O.View(b), O.View(c)], inp["v"]); return a
         if op in ("max", "min"):
             return O.reduce_dim_index(f("a"), inp["dim"], op == "max")
+        if op in ("cumsum", "cumprod"):
+            a = f("a") if "a" in inp else _uniform(inp["seed"], inp["shape"])
+            return O.scan(a, inp["dim"], op == "cumprod")
+        if op in ("var", "std"):
+            return O.var_dim(f("a"), inp["dim"], inp["flag"], op == "std")
+        if op in ("varall", "stdall"):
+            return O.var_dim(f("a").reshape(1, -1), 1, False, op == "stdall").reshape(1)
+        if op == "renorm":
+            return O.renorm(f("a"), inp["p"], inp["dim"], inp["maxnorm"])
+        if op == "dist":
+            return np.array([O.dist(f("a"), f("b"), inp["p"])])
     raise AssertionError(f"no oracle runner for {op}")
 
 
@@ -122,6 +133,17 @@ def run_gpu(case):
     if op in ("max", "min"):
         v, i = getattr(T("a"), op)(inp["dim"] + 1)
         return v.float(), i.float()
+    if op in ("cumsum", "cumprod"):
+        a = T("a") if "a" in inp else cl.ClTensor(_uniform(inp["seed"], inp["shape"]))
+        return getattr(a, op)(inp["dim"] + 1).float()
+    if op in ("var", "std"):
+        return getattr(T("a"), op)(inp["dim"] + 1, inp["flag"]).float()
+    if op in ("varall", "stdall"):
+        return np.array([getattr(T("a"), op[:3])()])
+    if op == "renorm":
+        return T("a").renorm(inp["p"], inp["dim"] + 1, inp["maxnorm"]).float()
+    if op == "dist":
+        return np.array([T("a").dist(T("b"), inp["p"])])
     raise AssertionError(f"no GPU runner for {op}")
 
 
