@@ -8,5 +8,7 @@ package does not load the library; the first use does, and fails loudly if it is
 from .tensor import (ClError, ClStorage, ClTensor, finish, getDevice, getDeviceCount, getStream, lib, setAddFinish,
                      setDevice, setStream, setTrace, state, synchronize)
 
-__all__ = ["ClError", "ClStorage", "ClTensor", "finish", "getDevice", "getDeviceCount", "getStream", "lib",
+from .user_kernel import ClKernel
+
+__all__ = ["ClError", "ClKernel", "ClStorage", "ClTensor", "finish", "getDevice", "getDeviceCount", "getStream", "lib",
            "setAddFinish", "setDevice", "setStream", "setTrace", "state", "synchronize"]

@@ -87,6 +87,11 @@ class thb200_tensor(C.Structure):
     _fields_ = [("data", c_float_p), ("ndim", C.c_int), ("size", c_int64_p), ("stride", c_int64_p)]
 
 
+class thb200_user_arg(C.Structure):
+    _fields_ = [("i", C.c_int), ("f", C.c_float), ("storage", c_float_p), ("offset", C.c_int64), ("ndim", C.c_int),
+                ("size", c_int64_p), ("stride", c_int64_p)]
+
+
 S = C.POINTER(THClState)
 ST = C.POINTER(THClStorage)
 T = C.POINTER(THClTensor)
@@ -248,6 +253,10 @@ PROTOTYPES = {
     "thb200_renorm_rows": (i, [C.c_void_p, C.c_void_p, C.c_int64, C.c_int64, f, f, C.c_void_p, C.c_size_t]),
     "thb200_dist_scratch_bytes": (C.c_size_t, [C.c_int64]),
     "thb200_dist": (i, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, f, C.c_void_p, C.c_void_p, C.c_size_t]),
+    "thb200_user_kernel_create": (i, [cp, cp, cp, i, C.POINTER(C.c_char_p), C.POINTER(C.c_int), C.POINTER(C.c_void_p)]),
+    "thb200_user_kernel_rendered": (cp, [C.c_void_p]),
+    "thb200_user_kernel_run": (i, [C.c_void_p, C.c_void_p, C.POINTER(thb200_user_arg), i, i, C.c_int64]),
+    "thb200_user_kernel_free": (v, [C.c_void_p]),
     "thb200_dot_scratch_bytes": (C.c_size_t, [C.c_int64]),
     "thb200_dot": (i, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_void_p, C.c_void_p, C.c_size_t]),
     "thb200_gemv_scratch_bytes": (C.c_size_t, [C.c_char, C.c_int64, C.c_int64]),

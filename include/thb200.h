@@ -234,6 +234,37 @@ int thb200_gemv(void* stream, char trans, int64_t m, int64_t n, float alpha, con
                 const float* x, int64_t incx, float beta, float* y, int64_t incy, void* scratch,
                 size_t scratch_bytes);
 
+/* ---- user kernels ---------------------------------------------------------- */
+
+/* torch.ClKernel, src/UserKernel.cpp:217-381: a kernel whose body the caller writes, with
+ * named arguments. A tensor argument `t` appears in the body as `t_info` (pointer to struct
+ * THClTensorInfoCl: sizes[25], strides[25], offset, dims; src/lib/THClTensorInfoCl.cl) and
+ * `t_data` (start of the storage: the body adds t_info->offset itself), an int or float by
+ * its name. The body is compiled by NVRTC as CUDA C++ behind a prelude that defines the
+ * OpenCL C words such kernels use (get_global_id(0), get_local_id, get_group_id,
+ * get_local_size, get_num_groups, barrier(CLK_LOCAL_MEM_FENCE), global, local, mad);
+ * `funcs` is extra source placed before the kernel (functions without a qualifier are
+ * device functions). The kernel runs as num_workgroups blocks of workgroup_size threads. */
+typedef struct thb200_user_kernel thb200_user_kernel;
+enum thb200_arg_kind { THB200_ARG_INT = 0, THB200_ARG_FLOAT = 1, THB200_ARG_TENSOR_IN = 2,
+                       THB200_ARG_TENSOR_OUT = 3, THB200_ARG_TENSOR_INOUT = 4 };
+typedef struct thb200_user_arg {
+  int i;                  /* THB200_ARG_INT */
+  float f;                /* THB200_ARG_FLOAT */
+  float* storage;         /* tensors: device address of the start of the storage */
+  int64_t offset;         /* storage offset of the tensor, in elements */
+  int ndim;
+  const int64_t* size;
+  const int64_t* stride;
+} thb200_user_arg;
+int thb200_user_kernel_create(const char* name, const char* src, const char* funcs, int nargs,
+                              const char* const* arg_names, const int* arg_kinds, thb200_user_kernel** out);
+/* The full source that was compiled (ClKernel:getRenderedKernel()). */
+const char* thb200_user_kernel_rendered(const thb200_user_kernel* k);
+int thb200_user_kernel_run(void* stream, thb200_user_kernel* k, const thb200_user_arg* args, int nargs,
+                           int workgroup_size, int64_t num_workgroups);
+void thb200_user_kernel_free(thb200_user_kernel* k);
+
 #ifdef __cplusplus
 }
 #endif
