@@ -99,12 +99,14 @@ NCU_DRAM_BYTES_PER_ELT_APPLY = (1.073753e9 + 1.016120e9) / 268435456
 
 # ---- CPU leg (oracle port) ---------------------------------------------------------------------
 
-def cpu_chain(sample_elems: int, reps: int):
-    """The same chain on the host cores with the oracle's fp32 loops; returns (GB/s, threads)."""
+def cpu_chain(sample_elems: int, reps: int, threads: int = 0):
+    """The same chain on the host cores with the oracle's fp32 loops; returns (GB/s, threads).
+    threads = 0: every core this process may use."""
     import numpy as np
     from oracle import oracle as O
     L = O.lib()
-    L.orc_set_num_threads(len(os.sched_getaffinity(0)))  # torchrun exports OMP_NUM_THREADS=1 to its ranks
+    # torchrun exports OMP_NUM_THREADS=1 to its ranks: set the count explicitly
+    L.orc_set_num_threads(threads if threads > 0 else len(os.sched_getaffinity(0)))
     g = np.random.Generator(np.random.PCG64(4))
     x = g.random(sample_elems, dtype=np.float32)
     ptr = C.c_void_p(x.ctypes.data)
@@ -117,6 +119,25 @@ def cpu_chain(sample_elems: int, reps: int):
         L.orc_time_sum(ptr, sample_elems)
         times.append(time.perf_counter() - t0)
     return BYTES_PER_ELT * sample_elems / statistics.median(times) / 1e9, L.orc_num_threads()
+
+
+def torch_cpu_chain(sample_elems: int, reps: int):
+    """A second, independent CPU number: the same chain with PyTorch's CPU kernels on all cores."""
+    import numpy as np
+    import torch
+    threads = len(os.sched_getaffinity(0))
+    torch.set_num_threads(threads)
+    g = np.random.Generator(np.random.PCG64(4))
+    x = torch.from_numpy(g.random(sample_elems, dtype=np.float32))
+    x.mul_(1.0001).add_(0.5)
+    times = []
+    for _ in range(reps):
+        t0 = time.perf_counter()
+        x.mul_(1.0001).add_(0.5)            # two passes: PyTorch has no fused a*x+b in place (28 B/elt moved)
+        x.sqrt_()
+        float(x.sum())
+        times.append(time.perf_counter() - t0)
+    return BYTES_PER_ELT * sample_elems / statistics.median(times) / 1e9, threads
 
 
 def run_reference(args):
@@ -277,8 +298,15 @@ def run_gpu(args):
         }
         if world == 1:
             gbs, threads = cpu_chain(1 << 27, 12)
+            one, _ = cpu_chain(1 << 25, 3, threads=1)
+            tgbs, tthreads = torch_cpu_chain(1 << 27, 5)
             line["cpu_baseline"] = {"value": gbs, "unit": "GB/s", "cores": threads, "kind": "port",
-                                    "sample": f"2^27 of the 2^31 elements, median of 12 repetitions, OpenMP on {threads} threads"}
+                                    "sample": f"2^27 of the 2^31 elements, median of 12 repetitions, OpenMP on {threads} threads",
+                                    "one_thread": {"value": one, "unit": "GB/s", "cores": 1,
+                                                   "sample": "2^25 elements, median of 3 repetitions"},
+                                    "torch_cpu": {"value": tgbs, "unit": "GB/s", "cores": tthreads,
+                                                  "sample": "2^27 elements, median of 5 repetitions, counted at the same "
+                                                            "20 algorithmic bytes per element"}}
         print(json.dumps(line))
     if world > 1:
         dist.destroy_process_group()

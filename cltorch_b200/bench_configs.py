@@ -181,6 +181,21 @@ def c4(T):
            flops=2.0 * 64 * 1024 * 1024 * 128, setup=lambda: C.zero())
 
 
+def c4batched(T):
+    """The batched K = 128 shape alone, with and without the read of C (profiler captures, experiments)."""
+    cl = T.cl
+    g = np.random.Generator(np.random.PCG64(3))
+    lim = 1.0 / np.sqrt(128)
+    A = cl.ClTensor(_uniform(g, (64, 1024, 128), -lim, lim))
+    B = cl.ClTensor(_uniform(g, (64, 128, 1024), -lim, lim))
+    C = cl.ClTensor(64, 1024, 1024).zero()
+    flops = 2.0 * 64 * 1024 * 1024 * 128
+    T.time("baddbmm 64 x (1024x1024x128), beta = 1", lambda: C.baddbmm(1.0, C, 1.0, A, B),
+           nbytes=64 * (1024 * 128 + 128 * 1024 + 2 * 1024 * 1024) * 4, flops=flops, setup=lambda: C.zero())
+    T.time("bmm 64 x (1024x1024x128), beta = 0", lambda: C.bmm(A, B),
+           nbytes=64 * (1024 * 128 + 128 * 1024 + 1024 * 1024) * 4, flops=flops)
+
+
 def c4small(T):
     """One mid-sized addmm (2048 x 2048 x 4096): the case used for profiler captures of the GEMM kernels."""
     cl = T.cl
@@ -251,7 +266,7 @@ def n3(T):
 
 def run(workload: str, steps: int, warmup: int) -> None:
     T = Timer(steps, warmup)
-    {"c1": c1, "c2": c2, "c3": c3, "c4": c4, "c4small": c4small, "c2small": c2small, "c3small": c3small, "n3": n3}[workload](T)
+    {"c1": c1, "c2": c2, "c3": c3, "c4": c4, "c4small": c4small, "c4batched": c4batched, "c2small": c2small, "c3small": c3small, "n3": n3}[workload](T)
     T.cl.synchronize()
     print(json.dumps({"workload": workload, "n_gpus": 1, "steps": steps, "warmup": warmup, "dtype": "f32",
                       "data": "synthetic", "hbm_peak_gbs_measured": T.peak, "l2_flush": "512 MiB fill between iterations",

@@ -20,9 +20,11 @@
 //                   shared-memory ring; warp 1 lane 0 issues
 //                   tcgen05.mma.kind::tf32 (M=128, N=256, K=8), three per k
 //                   step, into one of two 128-lane x 256-column TMEM
-//                   accumulators and commits to mbarriers; warps 2-5 read the
-//                   other accumulator with tcgen05.ld and write C with
-//                   coalesced stores while the next tile's k loop runs.
+//                   accumulators and commits to mbarriers; warps 2-9 read the
+//                   other accumulator with tcgen05.ld (each warp its 32 TMEM lanes
+//                   and half of the columns) and write C with coalesced stores
+//                   while the next tile's k loop runs; the old C of the next
+//                   32 columns is already in flight while a block is stored.
 //
 // Every wait is bounded: after THB_GEMM_WAIT_LIMIT_NS a waiter records a
 // code in *status, raises the CTA's abort flag and everybody falls through to
@@ -33,7 +35,8 @@
 #include <stdint.h>
 
 #define THB_GEMM_BM 128
-#define THB_GEMM_THREADS 192
+// threads of a CTA: warp 0 TMA, warp 1 MMA issuer, then EW (4 or 8) epilogue warps
+#define THB_GEMM_THREADS(EW) (64 + 32 * (EW))
 #define THB_GEMM_WAIT_LIMIT_NS 2000000000ull  // 2 s
 #define THB_GEMM_GROUP_M 16
 
@@ -187,12 +190,18 @@ struct ThbGemmParams {
   float alpha, beta;
   int tiles_m, tiles_n, batch;
   int* status;  // 0 = fine; otherwise the code of the first wait that gave up
+  // split-K: work item w = (tile, split); split s takes k blocks [s * kb_per_split, ...) and
+  // stores its raw accumulators to partial[s][batch][n][m] (leading dimension m) for
+  // thb_gemm_splitk_fixup. splits == 1: results go straight to C.
+  int splits, kb_per_split;
+  float* partial;
+  long long partial_split_stride;
 };
 
 // Persistent: CTA i works on tiles i, i + gridDim.x, ... The k loop of tile t+1
 // overlaps the epilogue of tile t through two TMEM accumulators.
-template <int BN, int BK, int STAGES>
-__global__ void __launch_bounds__(THB_GEMM_THREADS, 1)
+template <int BN, int BK, int STAGES, int EW, bool PREFETCH_C>
+__global__ void __launch_bounds__(THB_GEMM_THREADS(EW), 1)
 thb_gemm_3xtf32(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                 ThbGemmParams p) {
   typedef ThbGemmCfg<BN, BK, STAGES> Cfg;
@@ -203,14 +212,14 @@ thb_gemm_3xtf32(const __grid_constant__ CUtensorMap map_a, const __grid_constant
   uint64_t* bar_full = bars;                     // [STAGES] TMA -> MMA
   uint64_t* bar_empty = bars + STAGES;           // [STAGES] MMA -> TMA
   uint64_t* bar_acc_full = bars + 2 * STAGES;    // [2] MMA -> epilogue
-  uint64_t* bar_acc_empty = bars + 2 * STAGES + 2;  // [2] epilogue -> MMA (4 arrivals: one per warp)
+  uint64_t* bar_acc_empty = bars + 2 * STAGES + 2;  // [2] epilogue -> MMA (8 arrivals: one per warp)
   uint32_t* tmem_slot = (uint32_t*)(bars + 2 * STAGES + 4);
   volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
   volatile int* never_set = abort_flag + 1;  // stays 0: for the waits of the exit path
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int tiles_per_batch = p.tiles_m * p.tiles_n;
-  const int total_tiles = tiles_per_batch * p.batch;
+  const int total_tiles = tiles_per_batch * p.batch * p.splits;  // work items
   const int group_sz = THB_GEMM_GROUP_M * p.tiles_n;
 
   if (threadIdx.x == 0) {
@@ -220,7 +229,7 @@ thb_gemm_3xtf32(const __grid_constant__ CUtensorMap map_a, const __grid_constant
     }
     for (int a = 0; a < 2; ++a) {
       thb_mbar_init(thb_smem_u32(&bar_acc_full[a]), 1);
-      thb_mbar_init(thb_smem_u32(&bar_acc_empty[a]), 4);
+      thb_mbar_init(thb_smem_u32(&bar_acc_empty[a]), EW);
     }
     abort_flag[0] = 0;
     abort_flag[1] = 0;
@@ -238,9 +247,13 @@ thb_gemm_3xtf32(const __grid_constant__ CUtensorMap map_a, const __grid_constant
 
   // tile index -> (batch, tile_m, tile_n): within a batch, THB_GEMM_GROUP_M row tiles
   // share their B tiles in L2
-#define THB_GEMM_TILE_COORDS(tile)                                          \
-  const int batch = (tile) / tiles_per_batch;                               \
-  const int rem_ = (tile) % tiles_per_batch;                                \
+#define THB_GEMM_TILE_COORDS(work)                                          \
+  const int split = (work) % p.splits;                                      \
+  const int tile_ = (work) / p.splits;                                      \
+  const int kb_begin = split * p.kb_per_split;                              \
+  const int kb_end = min(p.kblocks, kb_begin + p.kb_per_split);             \
+  const int batch = tile_ / tiles_per_batch;                                \
+  const int rem_ = tile_ % tiles_per_batch;                                 \
   const int first_m_ = (rem_ / group_sz) * THB_GEMM_GROUP_M;                \
   const int gm_ = min(THB_GEMM_GROUP_M, p.tiles_m - first_m_);              \
   const int tile_m = first_m_ + (rem_ % group_sz) % gm_;                    \
@@ -253,7 +266,7 @@ thb_gemm_3xtf32(const __grid_constant__ CUtensorMap map_a, const __grid_constant
       bool ok = true;
       for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
         THB_GEMM_TILE_COORDS(tile)
-        for (int kb = 0; kb < p.kblocks; ++kb, ++it) {
+        for (int kb = kb_begin; kb < kb_end; ++kb, ++it) {
           const int s = (int)(it % STAGES);
           const uint32_t round = (uint32_t)(it / STAGES);
           if (it >= STAGES && !thb_mbar_wait(thb_smem_u32(&bar_empty[s]), (round - 1) & 1, abort_flag)) {
@@ -296,7 +309,10 @@ thb_gemm_3xtf32(const __grid_constant__ CUtensorMap map_a, const __grid_constant
           break;
         }
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        for (int kb = 0; kb < p.kblocks; ++kb, ++it) {
+        const int split = tile % p.splits;
+        const int kb_begin = split * p.kb_per_split;
+        const int kb_end = min(p.kblocks, kb_begin + p.kb_per_split);
+        for (int kb = kb_begin; kb < kb_end; ++kb, ++it) {
           const int s = (int)(it % STAGES);
           const uint32_t round = (uint32_t)(it / STAGES);
           if (!thb_mbar_wait(thb_smem_u32(&bar_full[s]), round & 1, abort_flag)) {
@@ -313,7 +329,7 @@ thb_gemm_3xtf32(const __grid_constant__ CUtensorMap map_a, const __grid_constant
 #pragma unroll
           for (int kk = 0; kk < BK / 8; ++kk) {
             const uint64_t adv = (uint64_t)((kk * 32) >> 4);  // 8 tf32 = 32 bytes further along K
-            thb_umma_tf32(d_tmem, a_lo + adv, b_hi + adv, idesc, (kb | kk) != 0);
+            thb_umma_tf32(d_tmem, a_lo + adv, b_hi + adv, idesc, (kb != kb_begin) || (kk != 0));
             thb_umma_tf32(d_tmem, a_hi + adv, b_lo + adv, idesc, 1);
             thb_umma_tf32(d_tmem, a_hi + adv, b_hi + adv, idesc, 1);
           }
@@ -328,21 +344,50 @@ thb_gemm_3xtf32(const __grid_constant__ CUtensorMap map_a, const __grid_constant
       }
     }
   } else {
-    // ---- epilogue: warps 2..5 own TMEM lanes 32*(warp%4) .. +31 ----
+    // ---- epilogue: warps 2..9; warp w reads TMEM lanes 32*(w%4) .. +31 (the lanes a warp may
+    // touch), warps 2-5 the first half of the tile's columns, warps 6-9 the second half ----
     const int lane_group = warp & 3;
+    constexpr int kColsPerWarp = BN / (EW / 4);
+    const int col_begin = ((warp - 2) >> 2) * kColsPerWarp, col_end = col_begin + kColsPerWarp;
+    // with split-K the raw accumulators go to the partial buffer (leading dimension m)
+    const bool to_partial = p.splits > 1;
+    const bool use_c = !to_partial && p.beta != 0.f;
+    const float alpha = to_partial ? 1.0f : p.alpha;
+    const long long ldc = to_partial ? (long long)p.m : p.ldc;
     int t = 0;
     for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, ++t) {
       THB_GEMM_TILE_COORDS(tile)
       const int acc = t & 1;
+      const int row = tile_m * THB_GEMM_BM + lane_group * 32 + lane;
+      float* cb = (to_partial ? p.partial + (long long)split * p.partial_split_stride + (long long)batch * p.m * p.n
+                              : p.c + (long long)batch * p.batch_stride_c) + row;
+      const bool row_ok = row < p.m;
+      // a tile that lies wholly inside C needs no per-element bounds checks
+      const bool full = (tile_m + 1) * THB_GEMM_BM <= p.m && (tile_n + 1) * BN <= p.n;
+      // Old values of C, 32 columns of this thread's row. They are read past L1 (ld.global.cg):
+      // the 32 lines of one such block are ldc * 4 bytes apart and would fight for a few L1 sets.
+      auto load_c = [&](float* dst, int col) {
+        if (!use_c) return;
+        const float* q = cb + (long long)col * ldc;
+        if (full) {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) { dst[j] = __ldcg(q); q += ldc; }
+        } else {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) { dst[j] = (row_ok && col + j < p.n) ? __ldcg(q) : 0.f; q += ldc; }
+        }
+      };
+      // C does not depend on the MMAs: with PREFETCH_C the first block of it is requested before
+      // the wait, and each further block while the previous one is being combined and stored
+      float cv[32], cn[32];
+      if (PREFETCH_C) load_c(cv, tile_n * BN + col_begin);
       bool ok = thb_mbar_wait(thb_smem_u32(&bar_acc_full[acc]), (uint32_t)(t >> 1) & 1, abort_flag);
       if (!ok && !*abort_flag) { *abort_flag = 1; atomicCAS(p.status, 0, 3); }
       ok = __all_sync(0xffffffffu, ok);
       if (!ok) break;
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-      const int row = tile_m * THB_GEMM_BM + lane_group * 32 + lane;
-      float* cb = p.c + (long long)batch * p.batch_stride_c + row;
 #pragma unroll 1
-      for (int c0 = 0; c0 < BN; c0 += 32) {
+      for (int c0 = col_begin; c0 < col_end; c0 += 32) {
         uint32_t r[32];
         const uint32_t taddr = tmem_base + ((uint32_t)(lane_group * 32) << 16) + (uint32_t)(acc * BN + c0);
         asm volatile(
@@ -354,23 +399,44 @@ thb_gemm_3xtf32(const __grid_constant__ CUtensorMap map_a, const __grid_constant
               "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
               "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
             : "r"(taddr));
-        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
         const int col0 = tile_n * BN + c0;
-        if (row < p.m && col0 < p.n) {
-          // all reads of C first (32 independent loads in flight), then the stores
-          float cv[32];
-          if (p.beta != 0.f) {
+        if (PREFETCH_C) {
+          if (c0 + 32 < col_end) load_c(cn, col0 + 32);
+        } else {
+          load_c(cv, col0);
+        }
+        // the accumulator registers are named as operands so that no use of them can be
+        // scheduled before the wait
+        asm volatile("tcgen05.wait::ld.sync.aligned;"
+                     : "+r"(r[0]), "+r"(r[1]), "+r"(r[2]), "+r"(r[3]), "+r"(r[4]), "+r"(r[5]), "+r"(r[6]), "+r"(r[7]),
+                       "+r"(r[8]), "+r"(r[9]), "+r"(r[10]), "+r"(r[11]), "+r"(r[12]), "+r"(r[13]), "+r"(r[14]), "+r"(r[15]),
+                       "+r"(r[16]), "+r"(r[17]), "+r"(r[18]), "+r"(r[19]), "+r"(r[20]), "+r"(r[21]), "+r"(r[22]), "+r"(r[23]),
+                       "+r"(r[24]), "+r"(r[25]), "+r"(r[26]), "+r"(r[27]), "+r"(r[28]), "+r"(r[29]), "+r"(r[30]), "+r"(r[31])
+                     :
+                     : "memory");
+        float* q = cb + (long long)col0 * ldc;
+        if (full) {
+          if (use_c) {
 #pragma unroll
-            for (int j = 0; j < 32; ++j) cv[j] = (col0 + j < p.n) ? cb[(long long)(col0 + j) * p.ldc] : 0.f;
+            for (int j = 0; j < 32; ++j) { *q = alpha * __uint_as_float(r[j]) + p.beta * cv[j]; q += ldc; }
+          } else {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) { *q = alpha * __uint_as_float(r[j]); q += ldc; }
           }
+        } else if (row_ok && col0 < p.n) {
 #pragma unroll
           for (int j = 0; j < 32; ++j) {
             if (col0 + j < p.n) {
-              float v = p.alpha * __uint_as_float(r[j]);
-              if (p.beta != 0.f) v += p.beta * cv[j];
-              cb[(long long)(col0 + j) * p.ldc] = v;
+              float v = alpha * __uint_as_float(r[j]);
+              if (use_c) v += p.beta * cv[j];
+              *q = v;
             }
+            q += ldc;
           }
+        }
+        if (PREFETCH_C) {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) cv[j] = cn[j];
         }
       }
       // this warp is done reading the accumulator: hand it back to the MMA issuer
@@ -386,5 +452,24 @@ thb_gemm_3xtf32(const __grid_constant__ CUtensorMap map_a, const __grid_constant
   if (warp == 1) {
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(Cfg::kTmemCols) : "memory");
+  }
+}
+
+// Split-K fix-up: C = alpha * (P_0 + P_1 + ... in split order) + beta * C, one thread per
+// element, adjacent threads on adjacent rows (C and the partials are column-major).
+__global__ void __launch_bounds__(256)
+thb_gemm_splitk_fixup(float* c, long long ldc, long long batch_stride_c, const float* partial,
+                      long long partial_split_stride, int splits, int m, int n, int batch, float alpha, float beta) {
+  const long long per_batch = (long long)m * n;
+  const long long total = per_batch * batch;
+  for (long long e = (long long)blockIdx.x * 256 + threadIdx.x; e < total; e += (long long)gridDim.x * 256) {
+    const long long b = e / per_batch, r = e - b * per_batch;
+    const long long col = r / m, row = r - col * m;
+    float acc = partial[e];
+    for (int s = 1; s < splits; ++s) acc += partial[(long long)s * partial_split_stride + e];
+    float* dst = c + b * batch_stride_c + col * ldc + row;
+    float v = alpha * acc;
+    if (beta != 0.f) v += beta * *dst;
+    *dst = v;
   }
 }

@@ -30,8 +30,9 @@ def test_blas_fixture_from_reference_tests():
 
 
 @pytest.mark.parametrize("M,N,K", [(1, 1, 1), (2, 3, 4), (17, 5, 33), (128, 256, 32), (129, 257, 31), (300, 500, 70),
-                                   (512, 1024, 256), (1000, 130, 1000)])
+                                   (512, 1024, 256), (1000, 130, 1000), (300, 500, 4100), (128, 256, 2048)])
 def test_addmm_shapes(M, N, K):
+    # the last three have few output tiles and a long K: they run split along K (2, 4 and 4 ways)
     import cltorch_b200 as cl
     a = rng_uniform(31, (M, K), -1, 1)
     b = rng_uniform(32, (K, N), -1, 1)
@@ -89,6 +90,13 @@ def test_baddbmm_and_bmm():
     at = cl.ClTensor(np.ascontiguousarray(a.transpose(0, 2, 1))).transpose(2, 3)
     r = cl.ClTensor(t.copy()).baddbmm(at, cl.ClTensor(b))
     check(r.float(), want, "baddbmm with a transposed batch operand")
+    # few tiles per batch and a long K: the batched split-K path (partials per batch, then the fix-up)
+    Bn, M, N, K = 3, 130, 260, 1100
+    a = rng_uniform(45, (Bn, M, K), -1, 1)
+    b = rng_uniform(46, (Bn, K, N), -1, 1)
+    t = rng_uniform(47, (Bn, M, N), -1, 1)
+    r = cl.ClTensor(t.copy()).baddbmm(0.5, 2.0, cl.ClTensor(a), cl.ClTensor(b))
+    check(r.float(), O.addmm(0.5, t, 2.0, a, b), "baddbmm, split along K")
 
 
 def test_gemm_status_word_reports_completion():
