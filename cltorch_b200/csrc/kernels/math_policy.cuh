@@ -19,12 +19,20 @@ __device__ __forceinline__ float thb_acos(float x) { return acosf(x); }
 __device__ __forceinline__ float thb_asin(float x) { return asinf(x); }
 __device__ __forceinline__ float thb_atan(float x) { return atanf(x); }
 __device__ __forceinline__ float thb_cosh(float x) { return coshf(x); }
+// Reciprocal seed in double, good to about 20 bits (one Newton step then gives 40): the
+// special-function unit's approximation, which spares the two fp64 <-> fp32 conversions
+// that a float reciprocal would cost.
+__device__ __forceinline__ double thb_rcp_seed(double d) {
+  double y;
+  asm("rcp.approx.ftz.f64 %0, %1;" : "=d"(y) : "d"(d));
+  return y;
+}
 // tanh to within 1 ulp, so that products such as tanh(x)*x stay within 2 ulp of a
 // correctly rounded evaluation (tanhf alone is documented at 2 ulp and measured
 // 3 ulp in that product). |x| <= 1 uses a Pade approximant in double; beyond that,
 // em = expm1(2|x|) in double from a degree-9 polynomial
 // after the usual ln2 range reduction (relative error < 1e-12), then
-// em / (em + 2) with a float reciprocal refined by one Newton step in double:
+// em / (em + 2) with an approximate reciprocal refined by one Newton step in double:
 // about 25 fp64 instructions, a fraction of the library tanh(double).
 __device__ __forceinline__ float thb_tanh(float xf) {
   const float ax = fabsf(xf);
@@ -37,7 +45,7 @@ __device__ __forceinline__ float thb_tanh(float xf) {
     const double x = (double)xf, q = x * x;
     const double num = x * fma(fma(fma(q, 1.0, 378.0), q, 17325.0), q, 135135.0);
     const double den = fma(fma(fma(q, 28.0, 3150.0), q, 62370.0), q, 135135.0);
-    double y = (double)__frcp_rn((float)den);
+    double y = thb_rcp_seed(den);
     y = y * fma(-den, y, 2.0);
     return (float)(num * y);
   }
@@ -59,7 +67,7 @@ __device__ __forceinline__ float thb_tanh(float xf) {
   const double s = __longlong_as_double(((long long)n + 1023ll) << 52);  // 2^n, 0 <= n <= 58
   const double em = fma(s, pm, s - 1.0);        // expm1(2|x|)
   const double d = em + 2.0;
-  double y = (double)__frcp_rn((float)d);
+  double y = thb_rcp_seed(d);
   y = y * fma(-d, y, 2.0);
   return copysignf((float)(em * y), xf);
 }
