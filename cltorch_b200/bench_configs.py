@@ -264,9 +264,23 @@ def n3(T):
            lambda: A.renorm(A, 2, 1, 128.0), 4 * n + 4 * n, setup=lambda: A.copy(A0))
 
 
+def n3small(T):
+    """var, cumsum and dist on 8192 x 8192 (profiler captures of the moments and scan kernels)."""
+    cl = T.cl
+    g = np.random.Generator(np.random.PCG64(5))
+    n = 8192
+    A = cl.ClTensor(g.standard_normal((n, n), dtype=np.float32))
+    B = cl.ClTensor(n, n)
+    out, pt = cl.ClTensor(), cl.ClTensor()
+    for d in (1, 2):
+        T.time(f"var(A, {d})", lambda: out.var(A, d), 4 * n * n)
+        T.time(f"cumsum(A, {d})", lambda: B.cumsum(A, d), 8 * n * n)
+    T.time("dist(A, B, 2) -> point tensor", lambda: pt.dist_gpu(A, B, 2), 8 * n * n)
+
+
 def run(workload: str, steps: int, warmup: int) -> None:
     T = Timer(steps, warmup)
-    {"c1": c1, "c2": c2, "c3": c3, "c4": c4, "c4small": c4small, "c4batched": c4batched, "c2small": c2small, "c3small": c3small, "n3": n3}[workload](T)
+    {"c1": c1, "c2": c2, "c3": c3, "c4": c4, "c4small": c4small, "c4batched": c4batched, "c2small": c2small, "c3small": c3small, "n3": n3, "n3small": n3small}[workload](T)
     T.cl.synchronize()
     print(json.dumps({"workload": workload, "n_gpus": 1, "steps": steps, "warmup": warmup, "dtype": "f32",
                       "data": "synthetic", "hbm_peak_gbs_measured": T.peak, "l2_flush": "512 MiB fill between iterations",

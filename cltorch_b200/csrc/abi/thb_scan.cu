@@ -30,7 +30,7 @@ static ScanPlan plan_scan(const float* dst, const float* src, int64_t outer, int
     p.nchunks = (uint32_t)((n + len - 1) / len);
   } else {
     p.vec = (aligned && (inner & 3) == 0) ? 4 : 1;
-    p.nchunks = pick_chunks(outer * inner / p.vec, n, 8);
+    p.nchunks = pick_chunks(outer * inner / p.vec, n, THB_SC_COLS_BLOCKS);
     p.chunk_len = (uint32_t)((n + p.nchunks - 1) / p.nchunks);
   }
   return p;
@@ -52,7 +52,7 @@ static int run_scan(cudaStream_t st, float* dst, const float* src, int64_t outer
         int64_t cb = outer < (int64_t)sms * 8 ? outer : (int64_t)sms * 8;
         thb_scan_carries_rows<Op><<<(unsigned)cb, THB_SC_THREADS, 0, st>>>(carry, outer, p.nchunks);
       } else {
-        int64_t cb = (outer + THB_SC_THREADS - 1) / THB_SC_THREADS;
+        int64_t cb = (outer + 31) / 32;
         if (cb > (int64_t)sms * 64) cb = (int64_t)sms * 64;
         thb_scan_carries<Op><<<(unsigned)cb, THB_SC_THREADS, 0, st>>>(carry, outer, p.nchunks, 1);
       }
@@ -71,7 +71,7 @@ static int run_scan(cudaStream_t st, float* dst, const float* src, int64_t outer
     if (p.vec == 4) thb_scan_cols<Op, 4, true><<<grid, THB_SC_THREADS, 0, st>>>(dst, src, outer, (thb_u32)n, inner, p.chunk_len, p.nchunks, carry);
     else thb_scan_cols<Op, 1, true><<<grid, THB_SC_THREADS, 0, st>>>(dst, src, outer, (thb_u32)n, inner, p.chunk_len, p.nchunks, carry);
     THB_CUDA(cudaGetLastError());
-    int64_t cb = (outer * inner + THB_SC_THREADS - 1) / THB_SC_THREADS;
+    int64_t cb = (outer * inner + 31) / 32;  // 32 positions x 8 lanes per block
     if (cb > (int64_t)sms * 64) cb = (int64_t)sms * 64;
     thb_scan_carries<Op><<<(unsigned)cb, THB_SC_THREADS, 0, st>>>(carry, outer, p.nchunks, inner);
     THB_CUDA(cudaGetLastError());

@@ -31,8 +31,9 @@ struct ScanMul {
 // inner > 1: one thread per VEC adjacent inner positions and chunk (blockIdx.y) walks the
 // rows of its chunk; adjacent threads read adjacent addresses. TOTALS: only the chunk total
 // is produced (phase 1 of a chunked scan), nothing is stored to dst.
+#define THB_SC_COLS_BLOCKS 4  // resident blocks per SM of thb_scan_cols (<= 64 registers)
 template <class Op, int VEC, bool TOTALS>
-__global__ void __launch_bounds__(THB_SC_THREADS)
+__global__ void __launch_bounds__(THB_SC_THREADS, THB_SC_COLS_BLOCKS)
 thb_scan_cols(float* dst, const float* src, thb_i64 outer, thb_u32 n, thb_i64 inner, thb_u32 chunk_len,
               thb_u32 nchunks, double* carry) {
   const thb_u32 chunk = blockIdx.y;
@@ -93,32 +94,46 @@ thb_scan_cols(float* dst, const float* src, thb_i64 outer, thb_u32 n, thb_i64 in
 }
 
 // Phase 2 of a chunked scan: the chunk totals of every (outer, inner) position become
-// the carries (exclusive scan over the chunks, in chunk order).
+// the carries (exclusive scan over the chunks, in chunk order). A block is 32 positions x 8
+// lanes; lane k first folds the k-th run of consecutive chunks, the 8 run totals are
+// scanned through shared memory, then every lane rewrites its run with the running carry.
 template <class Op>
 __global__ void __launch_bounds__(THB_SC_THREADS)
 thb_scan_carries(double* carry, thb_i64 outer, thb_u32 nchunks, thb_i64 inner) {
+  __shared__ double runs[8][33];
+  const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
+  const thb_u32 per = (nchunks + 7) >> 3;
+  const thb_u32 k0 = min(nchunks, ty * per), k1 = min(nchunks, k0 + per);
   const thb_i64 total = outer * inner;
-  for (thb_i64 q = (thb_i64)blockIdx.x * THB_SC_THREADS + threadIdx.x; q < total;
-       q += (thb_i64)gridDim.x * THB_SC_THREADS) {
-    const thb_i64 o = q / inner, i = q - o * inner;
+  for (thb_i64 q0 = (thb_i64)blockIdx.x * 32; q0 < total; q0 += (thb_i64)gridDim.x * 32) {
+    const thb_i64 q = q0 + tx;
+    const bool live = q < total;
+    const thb_i64 o = live ? q / inner : 0, i = live ? q - o * inner : 0;
     double* c = carry + o * nchunks * inner + i;
-    double run = Op::identity();
-    thb_u32 k = 0;
-    for (; k + 8 <= nchunks; k += 8) {
-      double t[8];
+    double tot = Op::identity();
+    if (live) {
+      thb_u32 k = k0;
+      for (; k + 4 <= k1; k += 4) {
+        double t[4];
 #pragma unroll
-      for (int u = 0; u < 8; ++u) t[u] = c[(thb_i64)(k + u) * inner];
+        for (int u = 0; u < 4; ++u) t[u] = c[(thb_i64)(k + u) * inner];
 #pragma unroll
-      for (int u = 0; u < 8; ++u) {
-        c[(thb_i64)(k + u) * inner] = run;
-        run = Op::apply(run, t[u]);
+        for (int u = 0; u < 4; ++u) tot = Op::apply(tot, t[u]);
+      }
+      for (; k < k1; ++k) tot = Op::apply(tot, c[(thb_i64)k * inner]);
+    }
+    runs[ty][tx] = tot;
+    __syncthreads();
+    if (live) {
+      double run = Op::identity();
+      for (int w = 0; w < ty; ++w) run = Op::apply(run, runs[w][tx]);
+      for (thb_u32 k = k0; k < k1; ++k) {
+        const double t = c[(thb_i64)k * inner];
+        c[(thb_i64)k * inner] = run;
+        run = Op::apply(run, t);
       }
     }
-    for (; k < nchunks; ++k) {
-      const double t = c[(thb_i64)k * inner];
-      c[(thb_i64)k * inner] = run;
-      run = Op::apply(run, t);
-    }
+    __syncthreads();
   }
 }
 
