@@ -8,7 +8,8 @@ package does not load the library; the first use does, and fails loudly if it is
 from .tensor import (ClError, ClStorage, ClTensor, finish, getDevice, getDeviceCount, getStream, lib, setAddFinish,
                      setDevice, setStream, setTrace, state, synchronize)
 
+from .serialization import load, save
 from .user_kernel import ClKernel
 
-__all__ = ["ClError", "ClKernel", "ClStorage", "ClTensor", "finish", "getDevice", "getDeviceCount", "getStream", "lib",
+__all__ = ["ClError", "ClKernel", "ClStorage", "ClTensor", "finish", "getDevice", "getDeviceCount", "getStream", "lib", "load", "save",
            "setAddFinish", "setDevice", "setStream", "setTrace", "state", "synchronize"]

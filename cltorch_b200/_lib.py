@@ -248,7 +248,8 @@ PROTOTYPES = {
     "thb200_var_all_scratch_bytes": (C.c_size_t, [C.c_int64]),
     "thb200_var_all": (i, [C.c_void_p, C.POINTER(thb200_tensor), i, i, C.c_void_p, C.c_void_p, C.c_size_t]),
     "thb200_scan_scratch_bytes": (C.c_size_t, [C.c_void_p, C.c_void_p, C.c_int64, C.c_int64, C.c_int64]),
-    "thb200_scan": (i, [C.c_void_p, i, C.c_void_p, C.c_void_p, C.c_int64, C.c_int64, C.c_int64, C.c_void_p, C.c_size_t]),
+    "thb200_scan": (i, [C.c_void_p, i, C.c_void_p, C.c_void_p, C.c_int64, C.c_int64, C.c_int64, C.c_void_p, C.c_size_t,
+                        C.c_void_p]),
     "thb200_renorm_rows_scratch_bytes": (C.c_size_t, [C.c_int64, C.c_int64]),
     "thb200_renorm_rows": (i, [C.c_void_p, C.c_void_p, C.c_int64, C.c_int64, f, f, C.c_void_p, C.c_size_t]),
     "thb200_dist_scratch_bytes": (C.c_size_t, [C.c_int64]),

@@ -11,7 +11,9 @@ namespace thb {
 static int64_t round_up(int64_t x, int64_t m) { return (x + m - 1) / m * m; }
 
 // cuTensorMapEncodeTiled through the runtime, so that the library does not link libcuda.
-static PFN_cuTensorMapEncodeTiled_v12000 tensor_map_encoder() {
+void* tensor_map_encoder_ptr();
+static PFN_cuTensorMapEncodeTiled_v12000 tensor_map_encoder() { return (PFN_cuTensorMapEncodeTiled_v12000)tensor_map_encoder_ptr(); }
+void* tensor_map_encoder_ptr() {
   static PFN_cuTensorMapEncodeTiled_v12000 fn = nullptr;
   static std::once_flag once;
   std::call_once(once, [] {
@@ -21,7 +23,7 @@ static PFN_cuTensorMapEncodeTiled_v12000 tensor_map_encoder() {
         q == cudaDriverEntryPointSuccess)
       fn = (PFN_cuTensorMapEncodeTiled_v12000)p;
   });
-  return fn;
+  return (void*)fn;
 }
 
 static const int kKPad = 32;  // K is padded to this in the split operands (a multiple of every BK)

@@ -30,6 +30,10 @@ bool collapse(int ndim, const int64_t* size, const int64_t* stride, int reduce_d
 bool can_use_32bit(int ndim, const int64_t* size, const int64_t* stride);
 int sm_count();  // of the current device, cached per device
 
+// cuTensorMapEncodeTiled obtained through the runtime (PFN_cuTensorMapEncodeTiled_v12000 as void*),
+// so that the library does not link libcuda; nullptr if the driver does not offer it.
+void* tensor_map_encoder_ptr();
+
 // Number of chunks to cut a reduced / scanned dimension of `rsize` elements into when only
 // `threads` worker threads (blocks of 256, `blocks_per_sm` resident) exist per chunk: as many
 // as fit one wave of resident blocks, 1 when the threads alone fill half the GPU.

@@ -1,7 +1,9 @@
 // Host side of the scans, renorm and dist entries of include/thb200.h.
 #include "thb_internal.h"
 #include "../kernels/math_policy.cuh"
-#include "../kernels/scan_kernels.cuh"
+#include "../kernels/scan_strip_kernels.cuh"
+
+#include <cudaTypedefs.h>
 
 namespace thb {
 
@@ -9,10 +11,14 @@ struct ScanPlan {
   bool rows;        // inner == 1
   int vec;          // 4 or 1
   uint32_t nchunks, chunk_len;
+  bool strips;      // single pass over 128-column strips through a TMA pipeline
+  int strips_per_outer, total_strips;
 };
 
 static ScanPlan plan_scan(const float* dst, const float* src, int64_t outer, int64_t n, int64_t inner) {
   ScanPlan p;
+  p.strips = false;
+  p.strips_per_outer = p.total_strips = 0;
   p.rows = inner == 1;
   const bool aligned = (((uintptr_t)dst | (uintptr_t)src) & 15) == 0;
   if (p.rows) {
@@ -32,13 +38,49 @@ static ScanPlan plan_scan(const float* dst, const float* src, int64_t outer, int
     p.vec = (aligned && (inner & 3) == 0) ? 4 : 1;
     p.nchunks = pick_chunks(outer * inner / p.vec, n, THB_SC_COLS_BLOCKS);
     p.chunk_len = (uint32_t)((n + p.nchunks - 1) / p.nchunks);
+    // Where the one-thread-per-column kernel would have to cut the rows into chunks (three
+    // phases, 12 bytes per element), a strip per CTA does it in one pass, provided there are
+    // enough strips to keep HBM busy and the layout suits TMA (16-byte aligned rows).
+    const int64_t spo = (inner + THB_SS_COLS - 1) / THB_SS_COLS;
+    const int64_t total = spo * outer;
+    if (p.nchunks > 1 && ((uintptr_t)src & 15) == 0 && (inner & 3) == 0 && total >= 24 && total < (int64_t(1) << 31) &&
+        n >= 2 * THB_SS_ROWS && inner < (int64_t(1) << 31) && outer < (int64_t(1) << 31) &&
+        n * inner * 4 < (int64_t(1) << 40) && tensor_map_encoder_ptr() != nullptr) {
+      p.strips = true;
+      p.strips_per_outer = (int)spo;
+      p.total_strips = (int)total;
+      p.nchunks = 1;  // no carries, no scratch
+    }
   }
   return p;
 }
 
 template <class Op>
+static int run_scan_strips(cudaStream_t st, float* dst, const float* src, int64_t outer, int64_t n, int64_t inner,
+                           const ScanPlan& p, int* d_status) {
+  auto enc = (PFN_cuTensorMapEncodeTiled_v12000)tensor_map_encoder_ptr();
+  CUtensorMap map;
+  cuuint64_t dims[3] = {(cuuint64_t)inner, (cuuint64_t)n, (cuuint64_t)outer};
+  cuuint64_t strides[2] = {(cuuint64_t)inner * 4, (cuuint64_t)inner * 4 * (cuuint64_t)n};
+  cuuint32_t box[3] = {THB_SS_COLS, THB_SS_ROWS, 1};
+  cuuint32_t estr[3] = {1, 1, 1};
+  CUresult r = enc(&map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, (void*)src, dims, strides, box, estr,
+                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return fail("scan: cuTensorMapEncodeTiled failed with %d", (int)r);
+  THB_CUDA(cudaFuncSetAttribute(thb_scan_strips<Op>, cudaFuncAttributeMaxDynamicSharedMemorySize, THB_SS_SMEM));
+  const int sms = sm_count();
+  const int ctas = p.total_strips < sms ? p.total_strips : sms;
+  thb_scan_strips<Op><<<ctas, THB_SS_THREADS, THB_SS_SMEM, st>>>(map, dst, (thb_u32)n, inner, p.strips_per_outer,
+                                                                  p.total_strips, d_status);
+  THB_CUDA(cudaGetLastError());
+  return 0;
+}
+
+template <class Op>
 static int run_scan(cudaStream_t st, float* dst, const float* src, int64_t outer, int64_t n, int64_t inner, double* carry,
-                    const ScanPlan& p) {
+                    const ScanPlan& p, int* d_status) {
+  if (p.strips) return run_scan_strips<Op>(st, dst, src, outer, n, inner, p, d_status);
   const int sms = sm_count();
   if (p.rows) {
     const int64_t work = outer * p.nchunks;  // warps
@@ -102,7 +144,7 @@ size_t thb200_scan_scratch_bytes(const float* dst, const float* src, int64_t out
 }
 
 int thb200_scan(void* stream, int op, float* dst, const float* src, int64_t outer, int64_t n, int64_t inner,
-                void* scratch, size_t scratch_bytes) {
+                void* scratch, size_t scratch_bytes, int* d_status) {
   if (outer < 0 || n < 0 || inner < 0) return fail("scan: negative extent");
   if (outer == 0 || n == 0 || inner == 0) return 0;
   if (!dst || !src) return fail("scan: null pointer");
@@ -112,8 +154,9 @@ int thb200_scan(void* stream, int op, float* dst, const float* src, int64_t oute
   const size_t need = p.nchunks > 1 ? (size_t)outer * p.nchunks * inner * sizeof(double) : 0;
   if (need && (!scratch || scratch_bytes < need || ((uintptr_t)scratch & 7)))
     return fail("scan: scratch too small or misaligned (%zu bytes, need %zu)", scratch_bytes, need);
-  return op == THB200_RED_ADD ? run_scan<ScanAdd>((cudaStream_t)stream, dst, src, outer, n, inner, (double*)scratch, p)
-                              : run_scan<ScanMul>((cudaStream_t)stream, dst, src, outer, n, inner, (double*)scratch, p);
+  return op == THB200_RED_ADD
+             ? run_scan<ScanAdd>((cudaStream_t)stream, dst, src, outer, n, inner, (double*)scratch, p, d_status)
+             : run_scan<ScanMul>((cudaStream_t)stream, dst, src, outer, n, inner, (double*)scratch, p, d_status);
 }
 
 size_t thb200_renorm_rows_scratch_bytes(int64_t rows, int64_t size) {

@@ -457,7 +457,7 @@ thb_gemm_3xtf32(const __grid_constant__ CUtensorMap map_a, const __grid_constant
 
 // Split-K fix-up: C = alpha * (P_0 + P_1 + ... in split order) + beta * C, one thread per
 // element, adjacent threads on adjacent rows (C and the partials are column-major).
-__global__ void __launch_bounds__(256)
+static __global__ void __launch_bounds__(256)
 thb_gemm_splitk_fixup(float* c, long long ldc, long long batch_stride_c, const float* partial,
                       long long partial_split_stride, int splits, int m, int n, int batch, float alpha, float beta) {
   const long long per_batch = (long long)m * n;

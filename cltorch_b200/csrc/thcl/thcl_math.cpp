@@ -703,7 +703,9 @@ static void scan_dim(THClState* state, THClTensor* self_, THClTensor* src, long 
   float* dst = THClTensor_data(state, self);
   const float* sp = THClTensor_data(state, in);
   void* scratch = ensure_scratch(ctx, thb200_scan_scratch_bytes(dst, sp, outer, n, inner));
-  int rc = thb200_scan(ctx->stream, op, dst, sp, outer, n, inner, scratch, ctx->scratch_bytes);
+  int rc = thb200_scan(ctx->stream, op, dst, sp, outer, n, inner, scratch, ctx->scratch_bytes,
+                       reinterpret_cast<int*>(ctx->result + 63));
+  ctx->status_pending = true;
   std::string err = rc ? thb200_last_error() : "";
   THClTensor_free(state, in);
   THClTensor_freeCopyTo(state, self, self_);

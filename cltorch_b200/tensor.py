@@ -202,6 +202,10 @@ class ClStorage:
     def data_ptr(self) -> int:
         return C.cast(self._p.contents.wrapper, C.c_void_p).value or 0
 
+    def cdata_ptr(self) -> int:
+        """Address of the THClStorage struct: two wrappers of one storage compare equal here."""
+        return C.cast(self._p, C.c_void_p).value or 0
+
 
 def _is_tensor(x) -> bool:
     return isinstance(x, ClTensor)
@@ -303,6 +307,10 @@ class ClTensor:
 
     def isSameSizeAs(self, other: "ClTensor") -> bool:
         return bool(call("THClTensor_isSameSizeAs", state(), self._p, other._p))
+
+    def cdata_ptr(self) -> int:
+        """Address of the THClTensor struct."""
+        return C.cast(self._p, C.c_void_p).value or 0
 
     def data_ptr(self) -> int:
         """Device address of the first element."""

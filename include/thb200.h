@@ -175,10 +175,13 @@ int thb200_var_all(void* stream, const thb200_tensor* in, int biased, int apply_
  * kept in double and rounded at each store. dst may be src. When the other dimensions are
  * too small to fill the GPU, n is cut into chunks (totals, scan of totals, scan with carry)
  * and `scratch` (8-byte aligned) holds the carries; the pointers matter to the size because
- * 16-byte aligned operands take a different path. */
+ * 16-byte aligned operands take a different path. One of the paths (a TMA pipeline over
+ * 128-column strips) waits on shared-memory barriers: every such wait is bounded, and a wait
+ * that gives up stores a non-zero code into *d_status (a device int the caller keeps at 0 and
+ * may read after synchronising; NULL = do not report) and leaves dst undefined. */
 size_t thb200_scan_scratch_bytes(const float* dst, const float* src, int64_t outer, int64_t n, int64_t inner);
 int thb200_scan(void* stream, int op, float* dst, const float* src, int64_t outer, int64_t n, int64_t inner,
-                void* scratch, size_t scratch_bytes);
+                void* scratch, size_t scratch_bytes, int* d_status);
 
 /* THClTensor_kernel_renorm, src/lib/THClTensorMath2.cl:110-143 (host side
  * src/lib/THClTensorMath2.cpp:414-446, commented out in the reference): every row of the

@@ -89,7 +89,9 @@ def test_varall_point_tensor_form_matches_host_form():
 
 SCAN_SHAPES = [((50, 60), 0), ((50, 60), 1), ((3, 1000, 7), 1), ((3, 1000, 8), 1), ((4, 100000), 1), ((4, 100003), 1),
                ((100000, 8), 0), ((100000, 3), 0), ((1 << 22,), 0), (((1 << 22) + 5,), 0), ((2000, 129), 1),
-               ((2000, 128), 1), ((1, 1), 0), ((5, 1), 1), ((1, 9), 0), ((33000, 40), 0)]
+               ((2000, 128), 1), ((1, 1), 0), ((5, 1), 1), ((1, 9), 0), ((33000, 40), 0),
+               # few thousand columns and many rows: one pass over 128-column strips (ragged last strip, ragged rows)
+               ((2000, 4096), 0), ((1000, 3100), 0), ((3, 500, 1028), 1), ((70, 3072), 0)]
 
 
 def scan_close(got, want_f32, src, dim, is_mul, what):
@@ -134,6 +136,15 @@ def test_scan_in_place_default_dim_and_strided_operands():
     scan_close(out.float(), O.scan(a, 1, True), a, 1, True, "transposed result")
 
 
+def test_strip_scan_in_place_and_status_word():
+    import cltorch_b200 as cl
+    a = rng_uniform(48, (1500, 3200), -0.5, 0.5)
+    r = cl.ClTensor(a)
+    r.cumsum(r, 1)                                                           # in place along the rows: the strip path
+    scan_close(r.float(), O.scan(a, 0, False), a, 0, False, "strips, in place")
+    cl.synchronize()                                                         # reads the kernels' status word: must be 0
+
+
 def test_scan_abi_rejects_bad_arguments():
     import cltorch_b200 as cl
     from cltorch_b200 import _lib
@@ -142,11 +153,11 @@ def test_scan_abi_rejects_bad_arguments():
     ptr = x.data_ptr()
     need = L.thb200_scan_scratch_bytes(ptr, ptr, 4, 100000, 1)
     assert need > 0                                                          # 4 rows: the rows are cut into chunks
-    assert L.thb200_scan(None, 0, ptr, ptr, 4, 100000, 1, None, 0) != 0
+    assert L.thb200_scan(None, 0, ptr, ptr, 4, 100000, 1, None, 0, None) != 0
     assert b"scratch" in L.thb200_last_error()
-    assert L.thb200_scan(None, 3, ptr, ptr, 4, 100000, 1, None, 0) != 0      # RED_MAX is not a scan operator
+    assert L.thb200_scan(None, 3, ptr, ptr, 4, 100000, 1, None, 0, None) != 0      # RED_MAX is not a scan operator
     assert b"neither add nor mul" in L.thb200_last_error()
-    assert L.thb200_scan(None, 0, ptr, ptr, 0, 100000, 1, None, 0) == 0      # empty: nothing to do
+    assert L.thb200_scan(None, 0, ptr, ptr, 0, 100000, 1, None, 0, None) == 0      # empty: nothing to do
 
 
 # ---- renorm ----------------------------------------------------------------------------------
