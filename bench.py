@@ -15,7 +15,8 @@ memory: host->device copy of the shard, the chain, and the 4-byte result read ba
 
 `--impl reference` times the CPU restatement of the reference (oracle/, OpenMP, all host
 cores) on a bounded sample of the same workload; the reference itself (OpenCL + Torch7)
-cannot run on this box. Other workloads (`--workload c1|c2|c3|c4`) report the remaining
+cannot run on this box. Other workloads (`--workload c1|c2|c3|c4|n3`, and the smaller
+`c2small|c3small|c4small|c4batched|n3small` used for profiler captures) report the remaining
 benchmark configurations at N=1; they are not the driver's default line.
 """
 from __future__ import annotations
