@@ -229,6 +229,7 @@ PROTOTYPES = {
     "thb200_reduce_all_scratch_bytes": (C.c_size_t, [C.c_int64]),
     "thb200_reduce_all": (i, [C.c_void_p, i, i, C.POINTER(thb200_tensor), f, f, C.c_void_p, i, f, C.c_void_p,
                               C.c_void_p, C.c_size_t]),
+    "thb200_kernel_status": (i, [C.c_void_p]),
     "thb200_reduce_dim_scratch_bytes": (C.c_size_t, [C.POINTER(thb200_tensor), i]),
     "thb200_reduce_dim": (i, [C.c_void_p, i, i, C.POINTER(thb200_tensor), C.POINTER(thb200_tensor), i, f, f,
                               C.c_void_p, C.c_size_t]),

@@ -34,6 +34,10 @@ int sm_count();  // of the current device, cached per device
 // so that the library does not link libcuda; nullptr if the driver does not offer it.
 void* tensor_map_encoder_ptr();
 
+// Device int of the current device into which kernels with bounded waits store a non-zero
+// code when a wait gives up (read and cleared by thb200_kernel_status); nullptr on failure.
+int* device_status_word();
+
 // Number of chunks to cut a reduced / scanned dimension of `rsize` elements into when only
 // `threads` worker threads (blocks of 256, `blocks_per_sm` resident) exist per chunk: as many
 // as fit one wave of resident blocks, 1 when the threads alone fill half the GPU.

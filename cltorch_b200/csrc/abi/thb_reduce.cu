@@ -3,6 +3,9 @@
 #include "thb_internal.h"
 #include "../kernels/math_policy.cuh"
 #include "../kernels/reduce_kernels.cuh"
+#include "../kernels/reduce_strip_kernels.cuh"
+
+#include <cudaTypedefs.h>
 
 #include <cstring>
 #include <mutex>
@@ -170,6 +173,63 @@ static bool slices_vectorise(const float* data, const Collapsed& in_wo_rdim, int
   return true;
 }
 
+// ---- TMA strip path of max / min with indices (reduce_strip_kernels.cuh) -----------------
+// Sums and variances stay on the one-thread-per-4-columns kernels: their fp64 accumulation
+// needs more warps per SM to hide its latency than a strip pipeline has (measured 0.85 of the
+// HBM rate through strips against 0.87), while the fp32 compare chain of max/min gains
+// (0.87 -> 0.91-0.95).
+struct StripPlan {
+  bool ok = false;
+  int strips_per_outer = 0, total_strips = 0;
+  uint32_t nchunks = 1, chunk_rows = 0;
+};
+
+// Whether max/min over n of a contiguous [outer][n][inner] tensor should go through the strip
+// pipeline, and into how many row chunks: the fewest (up to 16) that fill the SMs to 97 %
+// over whole rounds of work items; without enough items the one-thread-per-column path stays.
+static StripPlan plan_strips(const float* src, int64_t outer, int64_t n, int64_t inner) {
+  StripPlan p;
+  if (((uintptr_t)src & 15) != 0 || (inner & 3) != 0 || inner < 4 || n < 256) return p;
+  if (inner >= (int64_t(1) << 31) || outer >= (int64_t(1) << 31) || n >= (int64_t(1) << 31) ||
+      n * inner * 4 >= (int64_t(1) << 40) || outer * inner >= (int64_t(1) << 32))
+    return p;
+  if (!tensor_map_encoder_ptr()) return p;
+  const int64_t spo = (inner + THB_SS_COLS - 1) / THB_SS_COLS, total = spo * outer;
+  if (total >= (int64_t(1) << 24)) return p;
+  const int sms = sm_count();
+  const int64_t max_c = n / 256 < 16 ? n / 256 : 16;
+  int64_t best_c = 1;
+  double best_eff = 0.0;
+  for (int64_t c = 1; c <= max_c; ++c) {
+    const int64_t items = total * c, rounds = (items + sms - 1) / sms;
+    const double eff = (double)items / (double)(rounds * sms);
+    if (eff > best_eff + 1e-9) { best_eff = eff; best_c = c; }
+    if (eff >= 0.97) break;
+  }
+  if (best_eff < 0.8) return p;
+  int64_t rows = (n + best_c - 1) / best_c;
+  rows = (rows + THB_SS_ROWS - 1) / THB_SS_ROWS * THB_SS_ROWS;
+  p.chunk_rows = (uint32_t)rows;
+  p.nchunks = (uint32_t)((n + rows - 1) / rows);
+  p.strips_per_outer = (int)spo;
+  p.total_strips = (int)total;
+  p.ok = true;
+  return p;
+}
+
+static int make_strip_map(CUtensorMap* map, const float* src, int64_t outer, int64_t n, int64_t inner) {
+  auto enc = (PFN_cuTensorMapEncodeTiled_v12000)tensor_map_encoder_ptr();
+  cuuint64_t dims[3] = {(cuuint64_t)inner, (cuuint64_t)n, (cuuint64_t)outer};
+  cuuint64_t strides[2] = {(cuuint64_t)inner * 4, (cuuint64_t)inner * 4 * (cuuint64_t)n};
+  cuuint32_t box[3] = {THB_SS_COLS, THB_SS_ROWS, 1};
+  cuuint32_t estr[3] = {1, 1, 1};
+  CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, (void*)src, dims, strides, box, estr,
+                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return fail("reduce: cuTensorMapEncodeTiled failed with %d", (int)r);
+  return 0;
+}
+
 struct ReduceDimArgs {
   cudaStream_t st;
   ThbLayout out, in;
@@ -265,6 +325,39 @@ static int argreduce(cudaStream_t st, float* values, float* indices, const float
   }
   const int64_t nslices = outer * inner;
   const bool vec4 = (inner & 3) == 0 && ((uintptr_t)src & 15) == 0;
+  const StripPlan sp = plan_strips(src, outer, n, inner);
+  if (sp.ok) {
+    typedef ThbArgConsumer<IS_MAX> Cons;
+    const size_t need = sp.nchunks > 1 ? (size_t)sp.nchunks * nslices * 8 : 0;
+    if (need && (!scratch || scratch_bytes < need))
+      return fail("max/min: scratch too small (%zu bytes, need %zu)", scratch_bytes, need);
+    CUtensorMap map;
+    if (int rc = make_strip_map(&map, src, outer, n, inner)) return rc;
+    ThbStripGeom g;
+    g.n = (thb_u32)n; g.inner = inner; g.strips_per_outer = sp.strips_per_outer; g.total_strips = sp.total_strips;
+    g.nchunks = sp.nchunks; g.chunk_rows = sp.chunk_rows; g.nslices = (thb_u32)nslices;
+    typename Cons::Params cp;
+    cp.values = values; cp.indices = indices; cp.pval = scratch;
+    cp.pidx = reinterpret_cast<int*>(scratch + (size_t)sp.nchunks * nslices);
+    THB_CUDA(cudaFuncSetAttribute(thb_strip_reduce<Cons>, cudaFuncAttributeMaxDynamicSharedMemorySize, THB_SS_SMEM));
+    const int64_t items = (int64_t)sp.total_strips * sp.nchunks;
+    const unsigned ctas = (unsigned)(items < sms ? items : sms);
+    thb_strip_reduce<Cons><<<ctas, THB_SS_THREADS, THB_SS_SMEM, st>>>(map, g, cp, device_status_word());
+    THB_CUDA(cudaGetLastError());
+    if (sp.nchunks > 1) {
+      if (sp.nchunks >= 8) {
+        int64_t bf = (nslices + 31) / 32;
+        if (bf > 65535 * 16) bf = 65535 * 16;
+        thb_argreduce_fold_chunks<IS_MAX, 8><<<(unsigned)bf, THB_RD_THREADS, 0, st>>>(values, indices, cp.pval, cp.pidx, nslices, sp.nchunks);
+      } else {
+        int64_t bx = (nslices + THB_RD_THREADS - 1) / THB_RD_THREADS;
+        if (bx > 65535 * 16) bx = 65535 * 16;
+        thb_argreduce_fold_chunks<IS_MAX, 1><<<(unsigned)bx, THB_RD_THREADS, 0, st>>>(values, indices, cp.pval, cp.pidx, nslices, sp.nchunks);
+      }
+      THB_CUDA(cudaGetLastError());
+    }
+    return 0;
+  }
   const uint32_t nchunks = vec4 ? pick_chunks(nslices >> 2, n, kOccArgV4) : pick_chunks(nslices, n, kOccScalar);
   const uint32_t chunk_len = (uint32_t)((n + nchunks - 1) / nchunks);
   float* pval = scratch;
@@ -447,9 +540,15 @@ int thb200_var_all(void* stream, const thb200_tensor* in, int biased, int apply_
 
 size_t thb200_reduce_dim_index_scratch_bytes(int64_t outer, int64_t n, int64_t inner) {
   if (inner <= 1 || outer * inner == 0) return 0;
-  // sized for the 128-bit variant (4 slices per thread, hence up to 4 times the chunks)
-  uint32_t chunks = (inner & 3) == 0 ? pick_chunks((outer * inner) >> 2, n, kOccArgV4) : pick_chunks(outer * inner, n, kOccScalar);
-  return chunks > 1 ? (size_t)chunks * outer * inner * (sizeof(float) + sizeof(int)) : 0;
+  {
+    // the strip path is taken when the source is 16-byte aligned, else the one-thread-per-column
+    // kernels (128-bit variant: 4 slices per thread, hence more chunks): size for whichever needs more
+    const StripPlan sp = plan_strips(nullptr, outer, n, inner);
+    const size_t strips = (sp.ok && sp.nchunks > 1) ? (size_t)sp.nchunks * outer * inner * 8 : 0;
+    uint32_t c = (inner & 3) == 0 ? pick_chunks((outer * inner) >> 2, n, kOccArgV4) : pick_chunks(outer * inner, n, kOccScalar);
+    const size_t plain = c > 1 ? (size_t)c * outer * inner * 8 : 0;
+    return strips > plain ? strips : plain;
+  }
 }
 
 int thb200_reduce_dim_index(void* stream, int is_max, float* values, float* indices, const float* src, int64_t outer,
@@ -471,6 +570,39 @@ int thb200_reduce_dim_index(void* stream, int is_max, float* values, float* indi
 // the process exits. In host code the array's name is only a handle for the runtime,
 // not a device address: the address a kernel can use comes from cudaGetSymbolAddress,
 // asked once per device with that device current.
+// Status word of kernels with bounded waits (strip pipelines): lives in the device image like the
+// built-in scratch below; its device address is looked up once per device.
+static __device__ int thb_status_word_storage;
+
+namespace thb {
+int* device_status_word() {
+  static std::mutex mu;
+  static int* addr[64];
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
+  std::lock_guard<std::mutex> lock(mu);
+  if (!addr[dev]) {
+    void* p = nullptr;
+    if (cudaGetSymbolAddress(&p, thb_status_word_storage) != cudaSuccess) return nullptr;
+    addr[dev] = (int*)p;
+  }
+  return addr[dev];
+}
+}  // namespace thb
+
+extern "C" int thb200_kernel_status(void* stream) {
+  int* w = thb::device_status_word();
+  if (!w) { thb::fail("kernel_status: the status word is not available"); return -1; }
+  int h = -1;
+  if (cudaMemcpyAsync(&h, w, sizeof(int), cudaMemcpyDeviceToHost, (cudaStream_t)stream) != cudaSuccess ||
+      cudaStreamSynchronize((cudaStream_t)stream) != cudaSuccess) {
+    thb::fail("kernel_status: could not read the status word");
+    return -1;
+  }
+  if (h != 0) cudaMemsetAsync(w, 0, sizeof(int), (cudaStream_t)stream);
+  return h;
+}
+
 #define THB_NOALLOC_SCRATCH_BYTES (4u << 20)
 static __device__ __align__(256) unsigned char thb_noalloc_scratch[THB_NOALLOC_SCRATCH_BYTES];
 

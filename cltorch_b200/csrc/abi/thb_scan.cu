@@ -72,7 +72,7 @@ static int run_scan_strips(cudaStream_t st, float* dst, const float* src, int64_
   const int sms = sm_count();
   const int ctas = p.total_strips < sms ? p.total_strips : sms;
   thb_scan_strips<Op><<<ctas, THB_SS_THREADS, THB_SS_SMEM, st>>>(map, dst, (thb_u32)n, inner, p.strips_per_outer,
-                                                                  p.total_strips, d_status);
+                                                                  p.total_strips, d_status ? d_status : device_status_word());
   THB_CUDA(cudaGetLastError());
   return 0;
 }

@@ -1,0 +1,148 @@
+// max / min with indices along a non-innermost dimension of a contiguous [outer][n][inner]
+// tensor through the TMA strip pipeline of scan_strip_kernels.cuh: a work item is a strip of
+// 128 columns x a chunk of rows; persistent CTAs stream their items through 8 stages of
+// 32 rows x 512 bytes (128 KB of loads in flight per CTA), one column per consumer thread.
+// Compared with one thread per 4 columns issuing its own loads (thb_argreduce_cols_v4) this
+// keeps HBM busier: 0.87 -> 0.91-0.95 of the measured copy rate on 1 GiB inputs.
+//
+// Same job as THClTensor_kernel_transformReduceOuterDimIndex
+// (reference src/lib/THClTensorMathTransformReduce.cl:17-41).
+//
+// A `Consumer` holds what one thread carries along its column:
+//   begin(geometry, item)   at the start of a work item
+//   row(value, row_index, slot)   for every row of the item, in ascending order; slot =
+//                           row_index % 4, a compile-time constant after unrolling
+//   end()                   result or chunk partial of the column
+// Every wait is bounded as in the scan kernel; a wait that gives up writes *status.
+#pragma once
+#include "scan_strip_kernels.cuh"
+
+struct ThbStripGeom {
+  thb_u32 n;               // length of the reduced dimension
+  thb_i64 inner;           // columns per outer index (row pitch in elements)
+  int strips_per_outer, total_strips;
+  thb_u32 nchunks, chunk_rows;  // chunk_rows is a multiple of THB_SS_ROWS
+  thb_u32 nslices;         // outer * inner
+};
+
+template <class Consumer>
+__global__ void __launch_bounds__(THB_SS_THREADS, 1)
+thb_strip_reduce(const __grid_constant__ CUtensorMap map_src, ThbStripGeom g, typename Consumer::Params cp, int* status) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 127) & ~(uintptr_t)127);
+  uint64_t* bar_full = (uint64_t*)(smem + THB_SS_STAGES * THB_SS_STAGE_BYTES);
+  uint64_t* bar_empty = bar_full + THB_SS_STAGES;
+  volatile int* abort_flag = (volatile int*)(bar_empty + THB_SS_STAGES);
+  volatile int* never_set = abort_flag + 1;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < THB_SS_STAGES; ++s) {
+      thb_mbar_init(thb_smem_u32(&bar_full[s]), 1);
+      thb_mbar_init(thb_smem_u32(&bar_empty[s]), 4);
+    }
+    abort_flag[0] = 0;
+    abort_flag[1] = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  __syncthreads();
+  // item -> (chunk, strip): consecutive CTAs take neighbouring strips of the same rows
+  const int total_items = g.total_strips * (int)g.nchunks;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      long long it = 0;
+      bool ok = true;
+      for (int item = blockIdx.x; item < total_items && ok; item += gridDim.x) {
+        const int chunk = item / g.total_strips, strip = item - chunk * g.total_strips;
+        const int o = strip / g.strips_per_outer;
+        const int c0 = (strip - o * g.strips_per_outer) * THB_SS_COLS;
+        const thb_u32 r0 = (thb_u32)chunk * g.chunk_rows, r1 = min(g.n, r0 + g.chunk_rows);
+        for (thb_u32 r = r0; r < r1; r += THB_SS_ROWS, ++it) {
+          const int s = (int)(it % THB_SS_STAGES);
+          const uint32_t round = (uint32_t)(it / THB_SS_STAGES);
+          if (it >= THB_SS_STAGES && !thb_mbar_wait(thb_smem_u32(&bar_empty[s]), (round - 1) & 1, abort_flag)) {
+            if (!*abort_flag) { *abort_flag = 1; if (status) atomicCAS(status, 0, 1); }
+            ok = false;
+            break;
+          }
+          const uint32_t full = thb_smem_u32(&bar_full[s]);
+          thb_mbar_expect_tx(full, THB_SS_STAGE_BYTES);
+          thb_tma_load_3d(thb_smem_u32(smem + s * THB_SS_STAGE_BYTES), &map_src, full, c0, (int)r, o);
+        }
+      }
+      if (*abort_flag) {
+        for (long long j = (it > THB_SS_STAGES ? it - THB_SS_STAGES : 0); j < it; ++j)
+          thb_mbar_wait(thb_smem_u32(&bar_full[j % THB_SS_STAGES]), (uint32_t)(j / THB_SS_STAGES) & 1, never_set);
+      }
+    }
+  } else {
+    const int tx = threadIdx.x - 32;
+    long long it = 0;
+    bool ok = true;
+    for (int item = blockIdx.x; item < total_items && ok; item += gridDim.x) {
+      const int chunk = item / g.total_strips, strip = item - chunk * g.total_strips;
+      const int o = strip / g.strips_per_outer;
+      const thb_i64 col = (thb_i64)(strip - o * g.strips_per_outer) * THB_SS_COLS + tx;
+      const bool live = col < g.inner;
+      const thb_u32 r0 = (thb_u32)chunk * g.chunk_rows, r1 = min(g.n, r0 + g.chunk_rows);
+      Consumer c;
+      c.begin(cp, g, o, col, live, chunk);
+      for (thb_u32 rb = r0; rb < r1; rb += THB_SS_ROWS, ++it) {
+        const int s = (int)(it % THB_SS_STAGES);
+        const uint32_t round = (uint32_t)(it / THB_SS_STAGES);
+        bool got = thb_mbar_wait(thb_smem_u32(&bar_full[s]), round & 1, abort_flag);
+        if (!got && !*abort_flag) { *abort_flag = 1; if (status) atomicCAS(status, 0, 2); }
+        got = __all_sync(0xffffffffu, got);
+        if (!got) { ok = false; break; }
+        const float* tile = reinterpret_cast<const float*>(smem + s * THB_SS_STAGE_BYTES) + tx;
+        float v[THB_SS_ROWS];
+#pragma unroll
+        for (int r = 0; r < THB_SS_ROWS; ++r) v[r] = tile[r * THB_SS_COLS];
+        __syncwarp();
+        if (lane == 0) thb_mbar_arrive(thb_smem_u32(&bar_empty[s]));
+        if (rb + THB_SS_ROWS <= r1) {
+#pragma unroll
+          for (int r = 0; r < THB_SS_ROWS; ++r) c.row(v[r], rb + r, r & 3);
+        } else {
+#pragma unroll
+          for (int r = 0; r < THB_SS_ROWS; ++r)
+            if (rb + r < r1) c.row(v[r], rb + r, r & 3);
+        }
+      }
+      if (ok && live) c.end(cp, g, o, col, chunk);
+    }
+  }
+  __syncthreads();
+}
+
+// ---- consumers ----------------------------------------------------------------
+
+template <bool IS_MAX>
+struct ThbArgConsumer {
+  struct Params {
+    float* values;   // contiguous [outer][1][inner]
+    float* indices;
+    float* pval;     // [nchunks][nslices] when nchunks > 1
+    int* pidx;
+  };
+  float best;
+  int idx;
+  __device__ __forceinline__ void begin(const Params&, const ThbStripGeom&, int, thb_i64, bool, int) {
+    best = ThbArg<IS_MAX>::start();
+    idx = -1;
+  }
+  __device__ __forceinline__ void row(float v, thb_u32 r, int) {
+    if (ThbArg<IS_MAX>::strictly(v, best)) { best = v; idx = (int)r; }
+  }
+  __device__ __forceinline__ void end(const Params& p, const ThbStripGeom& g, int o, thb_i64 col, int chunk) {
+    const thb_u64 s = (thb_u64)((thb_i64)o * g.inner + col);
+    if (g.nchunks == 1) {
+      p.values[s] = best;
+      p.indices[s] = (float)(idx < 0 ? -1 : idx + 1);
+    } else {
+      p.pval[(thb_u64)chunk * g.nslices + s] = best;
+      p.pidx[(thb_u64)chunk * g.nslices + s] = idx;
+    }
+  }
+};

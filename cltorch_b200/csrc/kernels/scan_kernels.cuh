@@ -239,7 +239,7 @@ thb_scan_rows(float* dst, const float* src, thb_i64 nrows, thb_u32 n, thb_u32 ch
 // when norm = sumpow[r]^(1/p) exceeds maxnorm, and left untouched (not even read)
 // otherwise. One block per piece of THB_RN_PIECE elements of a row.
 #define THB_RN_PIECE 8192
-__global__ void __launch_bounds__(THB_SC_THREADS)
+static __global__ void __launch_bounds__(THB_SC_THREADS)
 thb_renorm_scale(float* data, const float* sumpow, thb_i64 rows, thb_i64 size, float p, float maxnorm,
                  thb_i64 pieces_per_row) {
   const thb_i64 total = rows * pieces_per_row;
@@ -267,7 +267,7 @@ thb_renorm_scale(float* data, const float* sumpow, thb_i64 rows, thb_i64 size, f
 // ---- dist -------------------------------------------------------------------
 // Pass 1 of sum |a - b|^p over two contiguous vectors (any alignment: scalar head/tail
 // handled by block 0 when the vectors are not both 16-byte aligned).
-__global__ void __launch_bounds__(THB_RA_THREADS, THB_RA_BLOCKS_PER_SM)
+static __global__ void __launch_bounds__(THB_RA_THREADS, THB_RA_BLOCKS_PER_SM)
 thb_dist_pass1(const float* a, const float* b, thb_i64 n, float p, int vec_ok, double* partials) {
   __shared__ double smem[32];
   double acc[4] = {0.0, 0.0, 0.0, 0.0};
@@ -308,7 +308,7 @@ thb_dist_pass1(const float* a, const float* b, thb_i64 n, float p, int vec_ok, d
 }
 
 // Pass 2: fold of the partials, then the 1/p power.
-__global__ void __launch_bounds__(1024)
+static __global__ void __launch_bounds__(1024)
 thb_dist_pass2(const double* partials, int count, float p, float* out) {
   __shared__ double smem[32];
   double r = 0.0;

@@ -72,7 +72,7 @@ THClDeviceContext* context(THClState* state, int device) {
     check_cuda(cudaStreamCreateWithFlags(&ctx->stream, cudaStreamNonBlocking), "cudaStreamCreate");
     ctx->owns_stream = true;
     check_cuda(cudaMalloc((void**)&ctx->result, 64 * sizeof(float)), "cudaMalloc(result)");
-    check_cuda(cudaMemset(ctx->result, 0, 64 * sizeof(float)), "cudaMemset(result)");  // slot 63: kernel status word
+    check_cuda(cudaMemset(ctx->result, 0, 64 * sizeof(float)), "cudaMemset(result)");
     check_cuda(cudaMallocHost((void**)&ctx->result_host, 64 * sizeof(float)), "cudaMallocHost(result)");
     ctx->scratch_bytes = 4u << 20;
     check_cuda(cudaMalloc((void**)&ctx->scratch, ctx->scratch_bytes), "cudaMalloc(scratch)");
@@ -125,14 +125,10 @@ void sync_stream(THClDeviceContext* ctx) {
     if (st != 0) raise("GEMM kernel did not complete: a bounded wait gave up (status %d); the result is undefined", st);
   }
   if (ctx->status_pending) {
-    // the status word of kernels with bounded waits other than the GEMM (slot 63 of the result buffer)
+    // kernels with bounded waits other than the GEMM report through the library's status word
     ctx->status_pending = false;
-    int st = 0;
-    check_cuda(cudaMemcpy(&st, ctx->result + 63, sizeof(int), cudaMemcpyDeviceToHost), "cudaMemcpy(status)");
-    if (st != 0) {
-      cudaMemset(ctx->result + 63, 0, sizeof(int));
-      raise("a kernel did not complete: a bounded wait gave up (status %d); its result is undefined", st);
-    }
+    const int st = thb200_kernel_status(ctx->stream);
+    if (st != 0) raise("a kernel did not complete: a bounded wait gave up (status %d); its result is undefined", st);
   }
 }
 

@@ -107,6 +107,13 @@ int thb200_reduce_all(void* stream, int modify, int reduce, const thb200_tensor*
                       float mod_param, const float* mod_point, int fin, float fin_param,
                       float* d_out, float* scratch, size_t scratch_bytes);
 
+/* Reductions and scans over a non-innermost dimension of a contiguous tensor stream through a
+ * TMA pipeline whose waits on shared-memory barriers are bounded (2 s). If such a wait ever
+ * gives up, the kernel stores a non-zero code in a status word inside the library's device
+ * image and leaves its output undefined. This call synchronises `stream`, returns that word
+ * (0 = every kernel since the last call completed) and clears it; < 0 if it cannot be read. */
+int thb200_kernel_status(void* stream);
+
 /* Bytes of scratch thb200_reduce_dim may need for this shape (0 if none). */
 size_t thb200_reduce_dim_scratch_bytes(const thb200_tensor* in, int dim);
 
@@ -178,7 +185,8 @@ int thb200_var_all(void* stream, const thb200_tensor* in, int biased, int apply_
  * 16-byte aligned operands take a different path. One of the paths (a TMA pipeline over
  * 128-column strips) waits on shared-memory barriers: every such wait is bounded, and a wait
  * that gives up stores a non-zero code into *d_status (a device int the caller keeps at 0 and
- * may read after synchronising; NULL = do not report) and leaves dst undefined. */
+ * may read after synchronising; NULL = the library's own word, see thb200_kernel_status) and
+ * leaves dst undefined. */
 size_t thb200_scan_scratch_bytes(const float* dst, const float* src, int64_t outer, int64_t n, int64_t inner);
 int thb200_scan(void* stream, int op, float* dst, const float* src, int64_t outer, int64_t n, int64_t inner,
                 void* scratch, size_t scratch_bytes, int* d_status);

@@ -110,9 +110,12 @@ def test_mean_std_var_point_tensors_and_chain():
 
 
 SHAPES = [(60, 50), (5, 2), (1, 7), (7, 1), (3, 1025), (1025, 3), (4, 5, 6), (2, 300, 7), (33, 2, 2, 9), (2100, 130)]
+# reductions over a non-innermost dimension with enough 128-column strips for the TMA pipeline:
+# several row chunks, a ragged last strip (5000 = 39 * 128 + 8), a ragged last row block, outer > 1
+STRIP_SHAPES = [(4096, 2048), (3000, 5000), (64, 512, 1024), (300, 20000), (2, 1000, 9600)]
 
 
-@pytest.mark.parametrize("shape", SHAPES)
+@pytest.mark.parametrize("shape", SHAPES + STRIP_SHAPES)
 def test_sum_prod_mean_each_dim(shape):
     import cltorch_b200 as cl
     a = rng_uniform(27, shape, 0.9, 1.1)
@@ -154,7 +157,7 @@ def test_norm_along_dim():
     assert np.array_equal(A.norm(0, 1).float(), (a != 0).sum(axis=0, keepdims=True).astype(np.float32))
 
 
-@pytest.mark.parametrize("shape", SHAPES + [(5, 2, 1), (1, 1), (70000, 3), (3, 70000)])
+@pytest.mark.parametrize("shape", SHAPES + STRIP_SHAPES + [(5, 2, 1), (1, 1), (70000, 3), (3, 70000)])
 def test_max_min_with_indices_each_dim(shape):
     import cltorch_b200 as cl
     g = np.random.Generator(np.random.PCG64(30))

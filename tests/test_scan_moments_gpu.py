@@ -30,7 +30,9 @@ def assert_rel(got, want, tol=1e-5, what=""):
 # ---- var / std -------------------------------------------------------------------------------
 
 VAR_SHAPES = [((50, 60), 0), ((50, 60), 1), ((7, 33, 20), 0), ((7, 33, 20), 1), ((7, 33, 20), 2), ((1000, 4096), 0),
-              ((1000, 4096), 1), ((20000, 12), 0), ((3, 100001), 1), ((300, 1003), 0), ((5, 8192 + 4), 1)]
+              ((1000, 4096), 1), ((20000, 12), 0), ((3, 100001), 1), ((300, 1003), 0), ((5, 8192 + 4), 1),
+              # enough 128-column strips for the TMA pipeline (chunked rows, ragged strip, outer > 1)
+              ((4096, 2048), 0), ((3000, 5000), 0), ((64, 512, 1024), 1)]
 
 
 @pytest.mark.parametrize("shape,dim", VAR_SHAPES)
