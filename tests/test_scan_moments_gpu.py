@@ -93,7 +93,7 @@ SCAN_SHAPES = [((50, 60), 0), ((50, 60), 1), ((3, 1000, 7), 1), ((3, 1000, 8), 1
                ((100000, 8), 0), ((100000, 3), 0), ((1 << 22,), 0), (((1 << 22) + 5,), 0), ((2000, 129), 1),
                ((2000, 128), 1), ((1, 1), 0), ((5, 1), 1), ((1, 9), 0), ((33000, 40), 0),
                # few thousand columns and many rows: one pass over 128-column strips (ragged last strip, ragged rows)
-               ((2000, 4096), 0), ((1000, 3100), 0), ((3, 500, 1028), 1), ((70, 3072), 0)]
+               ((2000, 12800), 0), ((1000, 12700), 0), ((12, 500, 1028), 1), ((70, 16384), 0)]
 
 
 def scan_close(got, want_f32, src, dim, is_mul, what):
@@ -140,7 +140,7 @@ def test_scan_in_place_default_dim_and_strided_operands():
 
 def test_strip_scan_in_place_and_status_word():
     import cltorch_b200 as cl
-    a = rng_uniform(48, (1500, 3200), -0.5, 0.5)
+    a = rng_uniform(48, (700, 12804), -0.5, 0.5)
     r = cl.ClTensor(a)
     r.cumsum(r, 1)                                                           # in place along the rows: the strip path
     scan_close(r.float(), O.scan(a, 0, False), a, 0, False, "strips, in place")
