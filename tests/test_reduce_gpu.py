@@ -192,6 +192,26 @@ def test_max_min_index_corner_cases():
     assert np.array_equal(v.float(), wv) and np.array_equal(i.float(), wi)
 
 
+def test_max_min_corner_cases_on_the_strip_path():
+    """The same corners on a shape that streams through the TMA strip pipeline in several row chunks."""
+    import cltorch_b200 as cl
+    g = np.random.Generator(np.random.PCG64(35))
+    a = g.integers(-3, 4, size=(3000, 5000)).astype(np.float32)
+    a[:, 7] = np.nan                     # a column of NaN only: (-FLT_MAX, -1)
+    a[:, 130] = -np.inf                  # nothing above -FLT_MAX: index -1 for max, first row for min
+    a[5:, 4999] = np.nan                 # NaN after real values, in the ragged last strip
+    a[::2, 640] = np.inf
+    a[2999, 1000] = 100.0                # the extreme in the last row of the last chunk
+    a[0, 1001] = -100.0                  # ... and in the very first row
+    A = cl.ClTensor(a)
+    for name, is_max in (("max", True), ("min", False)):
+        v, i = getattr(A, name)(1)
+        wv, wi = O.reduce_dim_index(a, 0, is_max)
+        assert np.array_equal(v.float(), wv) and np.array_equal(i.float(), wi), name
+    v, i = A.max(1)
+    assert i.float()[0, 7] == -1.0 and i.float()[0, 130] == -1.0 and i.float()[0, 1000] == 3000.0
+
+
 def test_errors():
     import cltorch_b200 as cl
     A = cl.ClTensor(np.ones((2, 3), np.float32))
