@@ -7,6 +7,7 @@
 
 #include <cudaTypedefs.h>
 
+#include <cstdlib>
 #include <cstring>
 #include <mutex>
 
@@ -173,18 +174,17 @@ static bool slices_vectorise(const float* data, const Collapsed& in_wo_rdim, int
   return true;
 }
 
-// ---- TMA strip path of max / min with indices (reduce_strip_kernels.cuh) -----------------
-// Sums and variances stay on the one-thread-per-4-columns kernels: their fp64 accumulation
-// needs more warps per SM to hide its latency than a strip pipeline has (measured 0.85 of the
-// HBM rate through strips against 0.87), while the fp32 compare chain of max/min gains
-// (0.87 -> 0.91-0.95).
+// ---- TMA strip path (reduce_strip_kernels.cuh) -----------------------------------------
+// max / min with indices: 4 consumer warps, one thread per column. Sums, products, variances:
+// 8 consumer warps, two threads per column (even / odd rows), because their per-row work is a
+// chain of fp64 conversions and additions that 4 warps per SM cannot hide.
 struct StripPlan {
   bool ok = false;
   int strips_per_outer = 0, total_strips = 0;
   uint32_t nchunks = 1, chunk_rows = 0;
 };
 
-// Whether max/min over n of a contiguous [outer][n][inner] tensor should go through the strip
+// Whether a reduction over n of a contiguous [outer][n][inner] tensor should go through the strip
 // pipeline, and into how many row chunks: the fewest (up to 16) that fill the SMs to 97 %
 // over whole rounds of work items; without enough items the one-thread-per-column path stays.
 static StripPlan plan_strips(const float* src, int64_t outer, int64_t n, int64_t inner) {
@@ -217,6 +217,19 @@ static StripPlan plan_strips(const float* src, int64_t outer, int64_t n, int64_t
   return p;
 }
 
+// `t` as a row-major contiguous tensor split at `dim`: false if it is not one.
+static bool contiguous_split(const thb200_tensor* t, int dim, int64_t* outer, int64_t* inner) {
+  int64_t expect = 1;
+  for (int d = t->ndim - 1; d >= 0; --d) {
+    if (t->size[d] != 1 && t->stride[d] != expect) return false;
+    expect *= t->size[d];
+  }
+  *outer = 1; *inner = 1;
+  for (int d = 0; d < dim; ++d) *outer *= t->size[d];
+  for (int d = dim + 1; d < t->ndim; ++d) *inner *= t->size[d];
+  return true;
+}
+
 static int make_strip_map(CUtensorMap* map, const float* src, int64_t outer, int64_t n, int64_t inner) {
   auto enc = (PFN_cuTensorMapEncodeTiled_v12000)tensor_map_encoder_ptr();
   cuuint64_t dims[3] = {(cuuint64_t)inner, (cuuint64_t)n, (cuuint64_t)outer};
@@ -230,7 +243,15 @@ static int make_strip_map(CUtensorMap* map, const float* src, int64_t outer, int
   return 0;
 }
 
+// Threads per column of the strip reductions with fp64 accumulators (4 measured the same as 2).
+static const int kStripHalves = 2;
+
 struct ReduceDimArgs {
+  // strip path: contiguous [outer][rsize][inner] input, two partials per column and row chunk
+  StripPlan strips;
+  const float* src = nullptr;
+  int64_t outer = 0, inner = 0;
+  int strip_rc = 0;
   cudaStream_t st;
   ThbLayout out, in;
   uint32_t rsize, rstride, nslices;
@@ -257,7 +278,22 @@ struct ReduceDimArgs {
     }
     uint64_t bx = ((uint64_t)nslices + THB_RD_THREADS - 1) / THB_RD_THREADS;
     if (bx > 65535u * 16u) bx = 65535u * 16u;
-    if (vec4) {
+    if (strips.ok) {
+      typedef ThbReduceConsumer<Mod, Red> Cons;
+      CUtensorMap map;
+      strip_rc = make_strip_map(&map, src, outer, rsize, inner);
+      if (strip_rc) return;
+      ThbStripGeom g;
+      g.n = rsize; g.inner = inner; g.strips_per_outer = strips.strips_per_outer; g.total_strips = strips.total_strips;
+      g.nchunks = strips.nchunks; g.chunk_rows = strips.chunk_rows; g.npartials = nchunks; g.nslices = nslices;
+      typename Cons::Params cp;
+      cp.out = out; cp.src = src; cp.partial = (typename Red::acc_t*)scratch; cp.init = init; cp.mparam = mparam;
+      const int64_t items = (int64_t)strips.total_strips * strips.nchunks;
+      const unsigned ctas = (unsigned)(items < sms ? items : sms);
+      err = cudaFuncSetAttribute(thb_strip_reduce<Cons, kStripHalves>, cudaFuncAttributeMaxDynamicSharedMemorySize, THB_SS_SMEM);
+      if (err != cudaSuccess) return;
+      thb_strip_reduce<Cons, kStripHalves><<<ctas, 32 + 128 * kStripHalves, THB_SS_SMEM, st>>>(map, g, cp, device_status_word());
+    } else if (vec4) {
       uint64_t bq = ((uint64_t)(nslices >> 2) + THB_RD_THREADS - 1) / THB_RD_THREADS;
       if (bq > 65535u * 16u) bq = 65535u * 16u;
       thb_reduce_dim_noncontig_v4<Mod, Red><<<dim3((unsigned)bq, nchunks), THB_RD_THREADS, 0, st>>>(
@@ -335,14 +371,14 @@ static int argreduce(cudaStream_t st, float* values, float* indices, const float
     if (int rc = make_strip_map(&map, src, outer, n, inner)) return rc;
     ThbStripGeom g;
     g.n = (thb_u32)n; g.inner = inner; g.strips_per_outer = sp.strips_per_outer; g.total_strips = sp.total_strips;
-    g.nchunks = sp.nchunks; g.chunk_rows = sp.chunk_rows; g.nslices = (thb_u32)nslices;
+    g.nchunks = sp.nchunks; g.chunk_rows = sp.chunk_rows; g.npartials = sp.nchunks; g.nslices = (thb_u32)nslices;
     typename Cons::Params cp;
     cp.values = values; cp.indices = indices; cp.pval = scratch;
     cp.pidx = reinterpret_cast<int*>(scratch + (size_t)sp.nchunks * nslices);
-    THB_CUDA(cudaFuncSetAttribute(thb_strip_reduce<Cons>, cudaFuncAttributeMaxDynamicSharedMemorySize, THB_SS_SMEM));
+    THB_CUDA(cudaFuncSetAttribute(thb_strip_reduce<Cons, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, THB_SS_SMEM));
     const int64_t items = (int64_t)sp.total_strips * sp.nchunks;
     const unsigned ctas = (unsigned)(items < sms ? items : sms);
-    thb_strip_reduce<Cons><<<ctas, THB_SS_THREADS, THB_SS_SMEM, st>>>(map, g, cp, device_status_word());
+    thb_strip_reduce<Cons, 1><<<ctas, THB_SS_THREADS, THB_SS_SMEM, st>>>(map, g, cp, device_status_word());
     THB_CUDA(cudaGetLastError());
     if (sp.nchunks > 1) {
       if (sp.nchunks >= 8) {
@@ -450,6 +486,11 @@ static size_t reduce_dim_scratch(const thb200_tensor* in, int dim, int occ_v4, s
   if (rstride == 1 || nslices == 0) return 0;
   Collapsed ci;
   if (!collapse(in->ndim, in->size, in->stride, dim, &ci)) return 0;
+  int64_t outer, inner;
+  if (contiguous_split(in, dim, &outer, &inner)) {
+    const StripPlan sp = plan_strips(in->data, outer, rsize, inner);
+    if (sp.ok) return (size_t)kStripHalves * sp.nchunks * nslices * acc_bytes;  // one partial per thread of a column and chunk
+  }
   const bool vec4 = slices_vectorise(in->data, ci, rstride);
   uint32_t chunks = vec4 ? pick_chunks(nslices >> 2, rsize, occ_v4) : pick_chunks(nslices, rsize, kOccScalar);
   return chunks > 1 ? (size_t)chunks * nslices * acc_bytes : 0;
@@ -485,11 +526,19 @@ static int reduce_dim_impl(void* stream, int modify, int reduce, const thb200_te
   const int occ_v4 = reduce >= 100 ? kOccMomentsV4 : kOccSumV4;
   a.nchunks = rstride == 1 ? 1 : (a.vec4 ? pick_chunks(nslices >> 2, rsize, occ_v4) : pick_chunks(nslices, rsize, kOccScalar));
   a.chunk_len = (uint32_t)((rsize + a.nchunks - 1) / a.nchunks);
+  if (rstride != 1 && contiguous_split(in, dim, &a.outer, &a.inner)) {
+    a.strips = plan_strips(in->data, a.outer, rsize, a.inner);
+    if (a.strips.ok) {
+      a.src = in->data;
+      a.nchunks = kStripHalves * a.strips.nchunks;  // partials to fold: one per thread of a column and chunk
+    }
+  }
   if (a.nchunks > 1 && (!scratch || scratch_bytes < (size_t)a.nchunks * nslices * acc_bytes))
     return fail("reduceDim: scratch too small (%zu bytes, need %zu)", scratch_bytes,
                 (size_t)a.nchunks * nslices * acc_bytes);
   const bool known = reduce >= 100 ? dispatch_moments(reduce, a) : dispatch_pair(modify, reduce, a);
   if (!known) return fail("reduceDim: unsupported modify/reduce pair (%d, %d)", modify, reduce);
+  if (a.strip_rc) return a.strip_rc;
   if (a.err != cudaSuccess) return fail_cuda(a.err, "reduceDim launch");
   return 0;
 }

@@ -1,9 +1,11 @@
-// max / min with indices along a non-innermost dimension of a contiguous [outer][n][inner]
-// tensor through the TMA strip pipeline of scan_strip_kernels.cuh: a work item is a strip of
+// Reductions (sums, products, variances; max / min with indices) along a non-innermost
+// dimension of a contiguous [outer][n][inner] tensor through the TMA strip pipeline of
+// scan_strip_kernels.cuh: a work item is a strip of
 // 128 columns x a chunk of rows; persistent CTAs stream their items through 8 stages of
 // 32 rows x 512 bytes (128 KB of loads in flight per CTA), one column per consumer thread.
-// Compared with one thread per 4 columns issuing its own loads (thb_argreduce_cols_v4) this
-// keeps HBM busier: 0.87 -> 0.91-0.95 of the measured copy rate on 1 GiB inputs.
+// Compared with one thread per 4 columns issuing its own loads (thb_reduce_dim_noncontig_v4,
+// thb_argreduce_cols_v4) this keeps HBM busier: 0.87 -> 0.90-0.95 of the measured copy rate
+// on 1 GiB inputs.
 //
 // Same job as THClTensor_kernel_transformReduceOuterDimIndex
 // (reference src/lib/THClTensorMathTransformReduce.cl:17-41).
@@ -22,11 +24,16 @@ struct ThbStripGeom {
   thb_i64 inner;           // columns per outer index (row pitch in elements)
   int strips_per_outer, total_strips;
   thb_u32 nchunks, chunk_rows;  // chunk_rows is a multiple of THB_SS_ROWS
+  thb_u32 npartials;       // partial results per column: nchunks x HALVES
   thb_u32 nslices;         // outer * inner
 };
 
-template <class Consumer>
-__global__ void __launch_bounds__(THB_SS_THREADS, 1)
+// HALVES = 1: 4 consumer warps, a thread takes every row of its column. HALVES = 2: 8 consumer
+// warps, two threads per column taking the even and the odd rows of each stage and producing
+// one partial each (for consumers whose per-row work is a chain of fp64 operations: twice the
+// warps hide twice the latency).
+template <class Consumer, int HALVES>
+__global__ void __launch_bounds__(32 + 128 * HALVES, 1)
 thb_strip_reduce(const __grid_constant__ CUtensorMap map_src, ThbStripGeom g, typename Consumer::Params cp, int* status) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 127) & ~(uintptr_t)127);
@@ -39,7 +46,7 @@ thb_strip_reduce(const __grid_constant__ CUtensorMap map_src, ThbStripGeom g, ty
   if (threadIdx.x == 0) {
     for (int s = 0; s < THB_SS_STAGES; ++s) {
       thb_mbar_init(thb_smem_u32(&bar_full[s]), 1);
-      thb_mbar_init(thb_smem_u32(&bar_empty[s]), 4);
+      thb_mbar_init(thb_smem_u32(&bar_empty[s]), 4 * HALVES);  // one arrival per consumer warp
     }
     abort_flag[0] = 0;
     abort_flag[1] = 0;
@@ -77,7 +84,9 @@ thb_strip_reduce(const __grid_constant__ CUtensorMap map_src, ThbStripGeom g, ty
       }
     }
   } else {
-    const int tx = threadIdx.x - 32;
+    const int tx = (threadIdx.x - 32) & (THB_SS_COLS - 1);
+    const int half = (threadIdx.x - 32) / THB_SS_COLS;  // 0 .. HALVES-1: which rows of a stage
+    constexpr int kRows = THB_SS_ROWS / HALVES;
     long long it = 0;
     bool ok = true;
     for (int item = blockIdx.x; item < total_items && ok; item += gridDim.x) {
@@ -95,28 +104,58 @@ thb_strip_reduce(const __grid_constant__ CUtensorMap map_src, ThbStripGeom g, ty
         if (!got && !*abort_flag) { *abort_flag = 1; if (status) atomicCAS(status, 0, 2); }
         got = __all_sync(0xffffffffu, got);
         if (!got) { ok = false; break; }
-        const float* tile = reinterpret_cast<const float*>(smem + s * THB_SS_STAGE_BYTES) + tx;
-        float v[THB_SS_ROWS];
+        const float* tile = reinterpret_cast<const float*>(smem + s * THB_SS_STAGE_BYTES) + tx + half * THB_SS_COLS;
+        float v[kRows];
 #pragma unroll
-        for (int r = 0; r < THB_SS_ROWS; ++r) v[r] = tile[r * THB_SS_COLS];
+        for (int k = 0; k < kRows; ++k) v[k] = tile[k * HALVES * THB_SS_COLS];  // rows half, half + HALVES, ...
         __syncwarp();
         if (lane == 0) thb_mbar_arrive(thb_smem_u32(&bar_empty[s]));
         if (rb + THB_SS_ROWS <= r1) {
 #pragma unroll
-          for (int r = 0; r < THB_SS_ROWS; ++r) c.row(v[r], rb + r, r & 3);
+          for (int k = 0; k < kRows; ++k) c.row(v[k], rb + k * HALVES + half, k & 3);
         } else {
 #pragma unroll
-          for (int r = 0; r < THB_SS_ROWS; ++r)
-            if (rb + r < r1) c.row(v[r], rb + r, r & 3);
+          for (int k = 0; k < kRows; ++k)
+            if (rb + k * HALVES + half < r1) c.row(v[k], rb + k * HALVES + half, k & 3);
         }
       }
-      if (ok && live) c.end(cp, g, o, col, chunk);
+      if (ok && live) c.end(cp, g, o, col, chunk * HALVES + half);
     }
   }
   __syncthreads();
 }
 
 // ---- consumers ----------------------------------------------------------------
+
+// Sums, products, moments ...: four accumulators per thread (rows 4k + j of the thread's rows into
+// accumulator j) because the additions of a column are a chain of dependent fp64 operations.
+template <class Mod, class Red>
+struct ThbReduceConsumer {
+  typedef typename Red::acc_t acc_t;
+  struct Params {
+    ThbLayout out;       // result of slice s at out.data[thb_offset(out, s)]
+    const float* src;    // for operators that want the first element of the slice
+    acc_t* partial;      // [npartials][nslices] when npartials > 1
+    float init, mparam;
+  };
+  acc_t acc[4];
+  float k0, mparam;
+  __device__ __forceinline__ void begin(const Params& p, const ThbStripGeom& g, int o, thb_i64 col, bool live, int) {
+#pragma unroll
+    for (int j = 0; j < 4; ++j) acc[j] = (acc_t)p.init;
+    mparam = p.mparam;
+    k0 = (Mod::kFirst && live) ? p.src[(thb_i64)o * g.n * g.inner + col] : 0.f;
+  }
+  __device__ __forceinline__ void row(float v, thb_u32, int slot) {
+    acc[slot] = Red::apply(acc[slot], Mod::apply(v, mparam, k0));
+  }
+  __device__ __forceinline__ void end(const Params& p, const ThbStripGeom& g, int o, thb_i64 col, int part) {
+    const acc_t a = Red::apply(Red::apply(acc[0], acc[1]), Red::apply(acc[2], acc[3]));
+    const thb_u32 s = (thb_u32)((thb_i64)o * g.inner + col);
+    if (g.npartials == 1) p.out.data[thb_offset(p.out, s)] = Red::result(a, (float)g.n);
+    else p.partial[(thb_u64)part * g.nslices + s] = a;
+  }
+};
 
 template <bool IS_MAX>
 struct ThbArgConsumer {
@@ -137,7 +176,7 @@ struct ThbArgConsumer {
   }
   __device__ __forceinline__ void end(const Params& p, const ThbStripGeom& g, int o, thb_i64 col, int chunk) {
     const thb_u64 s = (thb_u64)((thb_i64)o * g.inner + col);
-    if (g.nchunks == 1) {
+    if (g.npartials == 1) {
       p.values[s] = best;
       p.indices[s] = (float)(idx < 0 ? -1 : idx + 1);
     } else {
