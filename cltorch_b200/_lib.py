@@ -259,6 +259,8 @@ PROTOTYPES = {
     "thb200_user_kernel_rendered": (cp, [C.c_void_p]),
     "thb200_user_kernel_run": (i, [C.c_void_p, C.c_void_p, C.POINTER(thb200_user_arg), i, i, C.c_int64]),
     "thb200_user_kernel_free": (v, [C.c_void_p]),
+    "thb200_ger": (i, [C.c_void_p, C.c_int64, C.c_int64, f, C.c_void_p, C.c_int64, C.c_void_p, C.c_int64, C.c_void_p,
+                       C.c_int64, i]),
     "thb200_dot_scratch_bytes": (C.c_size_t, [C.c_int64]),
     "thb200_dot": (i, [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int64, C.c_void_p, C.c_void_p, C.c_size_t]),
     "thb200_gemv_scratch_bytes": (C.c_size_t, [C.c_char, C.c_int64, C.c_int64]),

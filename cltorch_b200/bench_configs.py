@@ -264,6 +264,24 @@ def n3(T):
            lambda: A.renorm(A, 2, 1, 128.0), 4 * n + 4 * n, setup=lambda: A.copy(A0))
 
 
+def n1(T):
+    """dot, addmv (both orientations of the matrix) and addr on 16384 x 16384 / 2^28 elements."""
+    cl = T.cl
+    g = np.random.Generator(np.random.PCG64(6))
+    n = 16384
+    M = cl.ClTensor(_uniform(g, (n, n), -1, 1))
+    x = cl.ClTensor(_uniform(g, (n,), -1, 1))
+    y = cl.ClTensor(n).zero()
+    T.time("addmv y = y + M x (row-major M)", lambda: y.addmv(1.0, 1.0, M, x), 4 * n * n, setup=lambda: y.zero())
+    Mt = M.t()
+    T.time("addmv y = y + M^T x (transposed view)", lambda: y.addmv(1.0, 1.0, Mt, x), 4 * n * n, setup=lambda: y.zero())
+    R = cl.ClTensor(n, n).zero()
+    T.time("addr R = R + x (x) x [8 B/elt]", lambda: R.addr(1.0, x, x), 8 * n * n)
+    a = cl.ClTensor(_uniform(g, (n * n,), -1, 1))
+    b = cl.ClTensor(_uniform(g, (n * n,), -1, 1))
+    T.time("dot of two 2^28 vectors -> host float [8 B/elt]", lambda: a.dot(b), 8 * n * n)
+
+
 def n3small(T):
     """var, cumsum and dist on 8192 x 8192 (profiler captures of the moments and scan kernels)."""
     cl = T.cl
@@ -280,7 +298,7 @@ def n3small(T):
 
 def run(workload: str, steps: int, warmup: int) -> None:
     T = Timer(steps, warmup)
-    {"c1": c1, "c2": c2, "c3": c3, "c4": c4, "c4small": c4small, "c4batched": c4batched, "c2small": c2small, "c3small": c3small, "n3": n3, "n3small": n3small}[workload](T)
+    {"c1": c1, "c2": c2, "c3": c3, "c4": c4, "c4small": c4small, "c4batched": c4batched, "c2small": c2small, "c3small": c3small, "n1": n1, "n3": n3, "n3small": n3small}[workload](T)
     T.cl.synchronize()
     print(json.dumps({"workload": workload, "n_gpus": 1, "steps": steps, "warmup": warmup, "dtype": "f32",
                       "data": "synthetic", "hbm_peak_gbs_measured": T.peak, "l2_flush": "512 MiB fill between iterations",

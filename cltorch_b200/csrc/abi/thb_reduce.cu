@@ -4,8 +4,7 @@
 #include "../kernels/math_policy.cuh"
 #include "../kernels/reduce_kernels.cuh"
 #include "../kernels/reduce_strip_kernels.cuh"
-
-#include <cudaTypedefs.h>
+#include "thb_strips.h"
 
 #include <cstdlib>
 #include <cstring>
@@ -178,45 +177,6 @@ static bool slices_vectorise(const float* data, const Collapsed& in_wo_rdim, int
 // max / min with indices: 4 consumer warps, one thread per column. Sums, products, variances:
 // 8 consumer warps, two threads per column (even / odd rows), because their per-row work is a
 // chain of fp64 conversions and additions that 4 warps per SM cannot hide.
-struct StripPlan {
-  bool ok = false;
-  int strips_per_outer = 0, total_strips = 0;
-  uint32_t nchunks = 1, chunk_rows = 0;
-};
-
-// Whether a reduction over n of a contiguous [outer][n][inner] tensor should go through the strip
-// pipeline, and into how many row chunks: the fewest (up to 16) that fill the SMs to 97 %
-// over whole rounds of work items; without enough items the one-thread-per-column path stays.
-static StripPlan plan_strips(const float* src, int64_t outer, int64_t n, int64_t inner) {
-  StripPlan p;
-  if (((uintptr_t)src & 15) != 0 || (inner & 3) != 0 || inner < 4 || n < 256) return p;
-  if (inner >= (int64_t(1) << 31) || outer >= (int64_t(1) << 31) || n >= (int64_t(1) << 31) ||
-      n * inner * 4 >= (int64_t(1) << 40) || outer * inner >= (int64_t(1) << 32))
-    return p;
-  if (!tensor_map_encoder_ptr()) return p;
-  const int64_t spo = (inner + THB_SS_COLS - 1) / THB_SS_COLS, total = spo * outer;
-  if (total >= (int64_t(1) << 24)) return p;
-  const int sms = sm_count();
-  const int64_t max_c = n / 256 < 16 ? n / 256 : 16;
-  int64_t best_c = 1;
-  double best_eff = 0.0;
-  for (int64_t c = 1; c <= max_c; ++c) {
-    const int64_t items = total * c, rounds = (items + sms - 1) / sms;
-    const double eff = (double)items / (double)(rounds * sms);
-    if (eff > best_eff + 1e-9) { best_eff = eff; best_c = c; }
-    if (eff >= 0.97) break;
-  }
-  if (best_eff < 0.8) return p;
-  int64_t rows = (n + best_c - 1) / best_c;
-  rows = (rows + THB_SS_ROWS - 1) / THB_SS_ROWS * THB_SS_ROWS;
-  p.chunk_rows = (uint32_t)rows;
-  p.nchunks = (uint32_t)((n + rows - 1) / rows);
-  p.strips_per_outer = (int)spo;
-  p.total_strips = (int)total;
-  p.ok = true;
-  return p;
-}
-
 // `t` as a row-major contiguous tensor split at `dim`: false if it is not one.
 static bool contiguous_split(const thb200_tensor* t, int dim, int64_t* outer, int64_t* inner) {
   int64_t expect = 1;
@@ -228,19 +188,6 @@ static bool contiguous_split(const thb200_tensor* t, int dim, int64_t* outer, in
   for (int d = 0; d < dim; ++d) *outer *= t->size[d];
   for (int d = dim + 1; d < t->ndim; ++d) *inner *= t->size[d];
   return true;
-}
-
-static int make_strip_map(CUtensorMap* map, const float* src, int64_t outer, int64_t n, int64_t inner) {
-  auto enc = (PFN_cuTensorMapEncodeTiled_v12000)tensor_map_encoder_ptr();
-  cuuint64_t dims[3] = {(cuuint64_t)inner, (cuuint64_t)n, (cuuint64_t)outer};
-  cuuint64_t strides[2] = {(cuuint64_t)inner * 4, (cuuint64_t)inner * 4 * (cuuint64_t)n};
-  cuuint32_t box[3] = {THB_SS_COLS, THB_SS_ROWS, 1};
-  cuuint32_t estr[3] = {1, 1, 1};
-  CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, (void*)src, dims, strides, box, estr,
-                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  if (r != CUDA_SUCCESS) return fail("reduce: cuTensorMapEncodeTiled failed with %d", (int)r);
-  return 0;
 }
 
 // Threads per column of the strip reductions with fp64 accumulators (4 measured the same as 2).
@@ -281,7 +228,7 @@ struct ReduceDimArgs {
     if (strips.ok) {
       typedef ThbReduceConsumer<Mod, Red> Cons;
       CUtensorMap map;
-      strip_rc = make_strip_map(&map, src, outer, rsize, inner);
+      strip_rc = make_strip_map(&map, src, outer, rsize, inner, inner);
       if (strip_rc) return;
       ThbStripGeom g;
       g.n = rsize; g.inner = inner; g.strips_per_outer = strips.strips_per_outer; g.total_strips = strips.total_strips;
@@ -368,7 +315,7 @@ static int argreduce(cudaStream_t st, float* values, float* indices, const float
     if (need && (!scratch || scratch_bytes < need))
       return fail("max/min: scratch too small (%zu bytes, need %zu)", scratch_bytes, need);
     CUtensorMap map;
-    if (int rc = make_strip_map(&map, src, outer, n, inner)) return rc;
+    if (int rc = make_strip_map(&map, src, outer, n, inner, inner)) return rc;
     ThbStripGeom g;
     g.n = (thb_u32)n; g.inner = inner; g.strips_per_outer = sp.strips_per_outer; g.total_strips = sp.total_strips;
     g.nchunks = sp.nchunks; g.chunk_rows = sp.chunk_rows; g.npartials = sp.nchunks; g.nslices = (thb_u32)nslices;

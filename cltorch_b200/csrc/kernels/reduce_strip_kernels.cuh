@@ -12,12 +12,16 @@
 //
 // A `Consumer` holds what one thread carries along its column:
 //   begin(geometry, item)   at the start of a work item
-//   row(value, row_index, slot)   for every row of the item, in ascending order; slot =
-//                           row_index % 4, a compile-time constant after unrolling
+//   row(value, row_index, slot, weight)   for every row of the item, in ascending order; slot
+//                           is a compile-time constant after unrolling (0..3); weight is the
+//                           row's weight when Consumer::kRowWeights (then
+//                           Consumer::weight(params, row) says what it is), else unused
 //   end()                   result or chunk partial of the column
 // Every wait is bounded as in the scan kernel; a wait that gives up writes *status.
 #pragma once
 #include "scan_strip_kernels.cuh"
+
+#define THB_SS_WRING 16  // slots of the row-weight ring (32 floats each): 2 KB, twice the stages
 
 struct ThbStripGeom {
   thb_u32 n;               // length of the reduced dimension
@@ -41,6 +45,7 @@ thb_strip_reduce(const __grid_constant__ CUtensorMap map_src, ThbStripGeom g, ty
   uint64_t* bar_empty = bar_full + THB_SS_STAGES;
   volatile int* abort_flag = (volatile int*)(bar_empty + THB_SS_STAGES);
   volatile int* never_set = abort_flag + 1;
+  float* weights = (float*)(smem + THB_SS_STAGES * THB_SS_STAGE_BYTES + 256);  // [stage][row], kRowWeights only
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   if (threadIdx.x == 0) {
@@ -57,31 +62,68 @@ thb_strip_reduce(const __grid_constant__ CUtensorMap map_src, ThbStripGeom g, ty
   const int total_items = g.total_strips * (int)g.nchunks;
 
   if (warp == 0) {
-    if (lane == 0) {
-      long long it = 0;
-      bool ok = true;
-      for (int item = blockIdx.x; item < total_items && ok; item += gridDim.x) {
-        const int chunk = item / g.total_strips, strip = item - chunk * g.total_strips;
-        const int o = strip / g.strips_per_outer;
-        const int c0 = (strip - o * g.strips_per_outer) * THB_SS_COLS;
-        const thb_u32 r0 = (thb_u32)chunk * g.chunk_rows, r1 = min(g.n, r0 + g.chunk_rows);
-        for (thb_u32 r = r0; r < r1; r += THB_SS_ROWS, ++it) {
-          const int s = (int)(it % THB_SS_STAGES);
-          const uint32_t round = (uint32_t)(it / THB_SS_STAGES);
-          if (it >= THB_SS_STAGES && !thb_mbar_wait(thb_smem_u32(&bar_empty[s]), (round - 1) & 1, abort_flag)) {
-            if (!*abort_flag) { *abort_flag = 1; if (status) atomicCAS(status, 0, 1); }
-            ok = false;
-            break;
+    // Producer warp: lane 0 waits for a free stage and issues the TMA load; with row weights
+    // (Consumer::kRowWeights) all 32 lanes first put the stage's 32 weights into shared memory, so
+    // that the consumers do not load them from global memory once per column.
+    long long it = 0;
+    bool ok = true;
+    for (int item = blockIdx.x; item < total_items && ok; item += gridDim.x) {
+      const int chunk = item / g.total_strips, strip = item - chunk * g.total_strips;
+      const int o = strip / g.strips_per_outer;
+      const int c0 = (strip - o * g.strips_per_outer) * THB_SS_COLS;
+      const thb_u32 r0 = (thb_u32)chunk * g.chunk_rows, r1 = min(g.n, r0 + g.chunk_rows);
+      // Row weights travel through a ring of THB_SS_WRING slots of 32 floats, four stages at a
+      // time: the batch written at stage q (q % 4 == 0) was loaded four stages earlier, so the
+      // producer never sits out the latency of its own load (once per item excepted).
+      float batch[4];
+      thb_u32 q = 0;  // stage index within the item
+      if (Consumer::kRowWeights) {
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+          const thb_u32 j = r0 + k * THB_SS_ROWS + lane;
+          weights[((it + k) % THB_SS_WRING) * THB_SS_ROWS + lane] = j < r1 ? Consumer::weight(cp, j) : 0.f;
+        }
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+          const thb_u32 j = r0 + (4 + k) * THB_SS_ROWS + lane;
+          batch[k] = j < r1 ? Consumer::weight(cp, j) : 0.f;
+        }
+        __syncwarp();
+      }
+      for (thb_u32 r = r0; r < r1; r += THB_SS_ROWS, ++it) {
+        const int s = (int)(it % THB_SS_STAGES);
+        const uint32_t round = (uint32_t)(it / THB_SS_STAGES);
+        int free_ok = 1;
+        if (lane == 0 && it >= THB_SS_STAGES && !thb_mbar_wait(thb_smem_u32(&bar_empty[s]), (round - 1) & 1, abort_flag)) {
+          if (!*abort_flag) { *abort_flag = 1; if (status) atomicCAS(status, 0, 1); }
+          free_ok = 0;
+        }
+        free_ok = __shfl_sync(0xffffffffu, free_ok, 0);
+        if (!free_ok) { ok = false; break; }
+        if (Consumer::kRowWeights) {
+          if (q > 0 && (q & 3) == 0) {
+#pragma unroll
+            for (int k = 0; k < 4; ++k) weights[((it + k) % THB_SS_WRING) * THB_SS_ROWS + lane] = batch[k];
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+              const thb_u32 j = r + (4 + k) * THB_SS_ROWS + lane;
+              batch[k] = j < r1 ? Consumer::weight(cp, j) : 0.f;
+            }
+            __syncwarp();
           }
+          ++q;
+        }
+        if (lane == 0) {
           const uint32_t full = thb_smem_u32(&bar_full[s]);
-          thb_mbar_expect_tx(full, THB_SS_STAGE_BYTES);
+          thb_mbar_expect_tx(full, THB_SS_STAGE_BYTES);  // releases the weights written above with it
           thb_tma_load_3d(thb_smem_u32(smem + s * THB_SS_STAGE_BYTES), &map_src, full, c0, (int)r, o);
         }
       }
-      if (*abort_flag) {
-        for (long long j = (it > THB_SS_STAGES ? it - THB_SS_STAGES : 0); j < it; ++j)
-          thb_mbar_wait(thb_smem_u32(&bar_full[j % THB_SS_STAGES]), (uint32_t)(j / THB_SS_STAGES) & 1, never_set);
-      }
+    }
+    if (lane == 0 && *abort_flag) {
+      // do not leave while copies into this CTA's shared memory are in flight
+      for (long long j = (it > THB_SS_STAGES ? it - THB_SS_STAGES : 0); j < it; ++j)
+        thb_mbar_wait(thb_smem_u32(&bar_full[j % THB_SS_STAGES]), (uint32_t)(j / THB_SS_STAGES) & 1, never_set);
     }
   } else {
     const int tx = (threadIdx.x - 32) & (THB_SS_COLS - 1);
@@ -106,17 +148,22 @@ thb_strip_reduce(const __grid_constant__ CUtensorMap map_src, ThbStripGeom g, ty
         if (!got) { ok = false; break; }
         const float* tile = reinterpret_cast<const float*>(smem + s * THB_SS_STAGE_BYTES) + tx + half * THB_SS_COLS;
         float v[kRows];
+        float w[Consumer::kRowWeights ? kRows : 1];
 #pragma unroll
         for (int k = 0; k < kRows; ++k) v[k] = tile[k * HALVES * THB_SS_COLS];  // rows half, half + HALVES, ...
+        if (Consumer::kRowWeights) {
+#pragma unroll
+          for (int k = 0; k < kRows; ++k) w[k] = weights[(it % THB_SS_WRING) * THB_SS_ROWS + k * HALVES + half];
+        }
         __syncwarp();
         if (lane == 0) thb_mbar_arrive(thb_smem_u32(&bar_empty[s]));
         if (rb + THB_SS_ROWS <= r1) {
 #pragma unroll
-          for (int k = 0; k < kRows; ++k) c.row(v[k], rb + k * HALVES + half, k & 3);
+          for (int k = 0; k < kRows; ++k) c.row(v[k], rb + k * HALVES + half, k & 3, w[Consumer::kRowWeights ? k : 0]);
         } else {
 #pragma unroll
           for (int k = 0; k < kRows; ++k)
-            if (rb + k * HALVES + half < r1) c.row(v[k], rb + k * HALVES + half, k & 3);
+            if (rb + k * HALVES + half < r1) c.row(v[k], rb + k * HALVES + half, k & 3, w[Consumer::kRowWeights ? k : 0]);
         }
       }
       if (ok && live) c.end(cp, g, o, col, chunk * HALVES + half);
@@ -131,6 +178,7 @@ thb_strip_reduce(const __grid_constant__ CUtensorMap map_src, ThbStripGeom g, ty
 // accumulator j) because the additions of a column are a chain of dependent fp64 operations.
 template <class Mod, class Red>
 struct ThbReduceConsumer {
+  static constexpr bool kRowWeights = false;
   typedef typename Red::acc_t acc_t;
   struct Params {
     ThbLayout out;       // result of slice s at out.data[thb_offset(out, s)]
@@ -146,7 +194,8 @@ struct ThbReduceConsumer {
     mparam = p.mparam;
     k0 = (Mod::kFirst && live) ? p.src[(thb_i64)o * g.n * g.inner + col] : 0.f;
   }
-  __device__ __forceinline__ void row(float v, thb_u32, int slot) {
+  static __device__ __forceinline__ float weight(const Params&, thb_u32) { return 0.f; }
+  __device__ __forceinline__ void row(float v, thb_u32, int slot, float) {
     acc[slot] = Red::apply(acc[slot], Mod::apply(v, mparam, k0));
   }
   __device__ __forceinline__ void end(const Params& p, const ThbStripGeom& g, int o, thb_i64 col, int part) {
@@ -159,6 +208,7 @@ struct ThbReduceConsumer {
 
 template <bool IS_MAX>
 struct ThbArgConsumer {
+  static constexpr bool kRowWeights = false;
   struct Params {
     float* values;   // contiguous [outer][1][inner]
     float* indices;
@@ -171,7 +221,8 @@ struct ThbArgConsumer {
     best = ThbArg<IS_MAX>::start();
     idx = -1;
   }
-  __device__ __forceinline__ void row(float v, thb_u32 r, int) {
+  static __device__ __forceinline__ float weight(const Params&, thb_u32) { return 0.f; }
+  __device__ __forceinline__ void row(float v, thb_u32 r, int, float) {
     if (ThbArg<IS_MAX>::strictly(v, best)) { best = v; idx = (int)r; }
   }
   __device__ __forceinline__ void end(const Params& p, const ThbStripGeom& g, int o, thb_i64 col, int chunk) {

@@ -20,7 +20,8 @@
 #define THB_SS_STAGES 8
 #define THB_SS_THREADS 160
 #define THB_SS_STAGE_BYTES (THB_SS_ROWS * THB_SS_COLS * 4)
-#define THB_SS_SMEM (THB_SS_STAGES * THB_SS_STAGE_BYTES + 128 /*alignment*/ + 256 /*barriers*/)
+#define THB_SS_SMEM (THB_SS_STAGES * THB_SS_STAGE_BYTES + 128 /*alignment*/ + 256 /*barriers*/ + \
+                     THB_SS_STAGES * THB_SS_ROWS * 8 /*row weights of the matrix-vector consumer*/)
 
 template <class Op>
 __global__ void __launch_bounds__(THB_SS_THREADS, 1)

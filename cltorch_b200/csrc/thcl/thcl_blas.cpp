@@ -190,7 +190,23 @@ void THClTensor_addr(THClState* state, THClTensor* r_, float beta, THClTensor* t
     THClTensor_copy(state, r_, t);
   }
   if (beta != 1) THClTensor_mul(state, r_, r_, beta);
-  // the rank-1 update r += alpha * vec1 (x) vec2 is the pointwise operator
+  // The rank-1 update r += alpha * vec1 (x) vec2. A result with unit-stride rows or columns takes
+  // the 128-bit kernel behind thb200_ger (same rounding order as the operator below) ...
+  if (r_->storage && vec1->storage && vec2->storage && THClTensor_nElement(state, r_) > 0) {
+    THClDeviceContext* ctx = context(state, r_->device);
+    use_device(r_->device);
+    float* rp = THClTensor_data(state, r_);
+    const float* p1 = THClTensor_data(state, vec1);
+    const float* p2 = THClTensor_data(state, vec2);
+    int rc = 1;
+    if (r_->stride[1] == 1 && vec2->stride[0] == 1)        // rows contiguous: the unit-stride index is vec2's
+      rc = thb200_ger(ctx->stream, r_->size[1], r_->size[0], alpha, p2, 1, p1, vec1->stride[0], rp, r_->stride[0], 0);
+    else if (r_->stride[0] == 1 && vec1->stride[0] == 1)   // columns contiguous (a transposed result)
+      rc = thb200_ger(ctx->stream, r_->size[0], r_->size[1], alpha, p1, 1, p2, vec2->stride[0], rp, r_->stride[1], 1);
+    if (rc == 0) { after_launch(state, ctx); return; }
+    if (rc != 1) raise("%s", thb200_last_error());
+  }
+  // ... any other layout the pointwise operator
   // "*out += val1 * *in1 * *in2" over broadcast (stride-0) views of the two vectors
   THClTensor* a = THClTensor_newWithStorage2d(state, vec1->device, vec1->storage, vec1->storageOffset, vec1->size[0],
                                               vec1->stride[0], vec2->size[0], 0);

@@ -231,8 +231,8 @@ int thb200_gemm(void* stream, char transa, char transb, int64_t m, int64_t n, in
 int thb200_gemm_status(void* stream, int64_t m, int64_t n, int64_t k, int64_t batch, void* workspace);
 
 /* clblasSdot as called from THClBlas_dot, src/lib/THClBlas.cpp:149-192: *d_out =
- * sum a[i] * b[i] over two contiguous vectors, exact products accumulated in
- * double. The result stays on the device. */
+ * sum a[i] * b[i] over two contiguous vectors; the products are rounded to fp32, their sum
+ * is kept in double. The result stays on the device. */
 size_t thb200_dot_scratch_bytes(int64_t n);
 int thb200_dot(void* stream, const float* a, const float* b, int64_t n, float* d_out, void* scratch,
                size_t scratch_bytes);
@@ -244,6 +244,16 @@ size_t thb200_gemv_scratch_bytes(char trans, int64_t m, int64_t n);
 int thb200_gemv(void* stream, char trans, int64_t m, int64_t n, float alpha, const float* a, int64_t lda,
                 const float* x, int64_t incx, float beta, float* y, int64_t incy, void* scratch,
                 size_t scratch_bytes);
+
+/* clblasSger as called from THClBlas_ger, src/lib/THClBlas.cpp:264-347: column-major A (m x n,
+ * unit stride along m, leading dimension lda): A[i + j*lda] += (alpha * y[j*incy]) * x[i], or
+ * (alpha * x[i]) * y[j*incy] when alpha_on_x != 0 (the two differ in the last bit; the THCl layer
+ * picks the one that rounds like the reference's operator "*out += val1 * *in1 * *in2").
+ * HBM-bound, 8 bytes per element of A. Only the 128-bit path exists: returns 1 and does nothing
+ * unless A and x are 16-byte aligned, incx == 1 and m, lda are multiples of 4 (the caller then
+ * falls back to the pointwise operator over broadcast views). */
+int thb200_ger(void* stream, int64_t m, int64_t n, float alpha, const float* x, int64_t incx, const float* y,
+               int64_t incy, float* a, int64_t lda, int alpha_on_x);
 
 /* ---- user kernels ---------------------------------------------------------- */
 

@@ -121,7 +121,9 @@ def test_dot_addmv_addr_fixtures_from_reference_tests():
     assert np.array_equal(cl.ClTensor().ger(cl.ClTensor(dd), cl.ClTensor(e)).float(), np.outer(dd, e))
 
 
-@pytest.mark.parametrize("M,K", [(1, 1), (5, 3), (300, 70), (70, 9000), (9000, 70), (20000, 33), (129, 1025)])
+@pytest.mark.parametrize("M,K", [(1, 1), (5, 3), (300, 70), (70, 9000), (9000, 70), (20000, 33), (129, 1025),
+                                 # column-major matrices of these sizes stream through the TMA strip pipeline
+                                 (2048, 4096), (5000, 3000), (20000, 260)])
 def test_addmv_layouts(M, K):
     import cltorch_b200 as cl
     a = rng_uniform(51, (M, K), -1, 1)
@@ -145,6 +147,33 @@ def test_addmv_layouts(M, K):
     assert np.all(np.abs(r.float() - want2) <= 1e-5 * (np.abs(wide.float()[:, ::2].astype(np.float64)) @ np.abs(x2.float()[:, 0].astype(np.float64)) + 1))
     with pytest.raises(cl.ClError, match="size mismatch"):
         cl.ClTensor().addmv(T, A, T if K != M else cl.ClTensor(K + 1))
+
+
+@pytest.mark.parametrize("R,Cc", [(300, 500), (1000, 2048), (4, 4), (333, 12)])
+def test_addr_layouts_round_like_the_pointwise_operator(R, Cc):
+    """r += alpha * v1 (x) v2 is defined by "*out += val1 * *in1 * *in2" (one rounding per operation,
+    alpha * v1 first): the 128-bit rank-1 kernel and the pointwise fallback must agree with it bit for bit."""
+    import cltorch_b200 as cl
+    t = rng_uniform(58, (R, Cc), -1, 1)
+    v1, v2 = rng_uniform(59, (R,), -1, 1), rng_uniform(60, (Cc,), -1, 1)
+    alpha = np.float32(1.7)
+    want = t + ((alpha * v1)[:, None] * v2[None, :]).astype(np.float32)
+    V1, V2 = cl.ClTensor(v1), cl.ClTensor(v2)
+    r = cl.ClTensor(t.copy()).addr(float(alpha), V1, V2)                       # row-major result
+    assert np.array_equal(r.float(), want)
+    rt = cl.ClTensor(np.ascontiguousarray(t.T)).t()                            # column-major (transposed) result
+    rt.addr(float(alpha), V1, V2)
+    assert np.array_equal(rt.float(), want)
+    s2 = cl.ClTensor(np.stack([v2, v2], axis=1)).select(2, 1)                  # strided vector: pointwise fallback
+    r = cl.ClTensor(t.copy()).addr(float(alpha), V1, s2)
+    assert np.array_equal(r.float(), want)
+    if Cc > 8:                                                                 # a window of a wider matrix (pitch > columns)
+        wide = cl.ClTensor(np.zeros((R, Cc + 8), np.float32))
+        w = wide.narrow(2, 5, Cc - 4)                                          # offset 4 elements: 16-byte aligned
+        w.copy(cl.ClTensor(np.ascontiguousarray(t[:, :Cc - 4])))
+        w.addr(float(alpha), V1, cl.ClTensor(np.ascontiguousarray(v2[:Cc - 4])))
+        assert np.array_equal(w.float(), want[:, :Cc - 4])
+        assert np.array_equal(wide.float()[:, :4], np.zeros((R, 4), np.float32))  # nothing written outside the window
 
 
 def test_dot_large_and_strided():
