@@ -54,7 +54,6 @@ int launch_apply(const ApplyKernels& k, cudaStream_t st, int nt, const thb200_te
     all_contig = all_contig && c[i].contiguous();
   }
   ThbScalars s{val1, val2, p1, p2};
-  const int sms = sm_count();
 
   if (all_contig) {
     int head = misalign_elems(t[0].data);
@@ -70,7 +69,7 @@ int launch_apply(const ApplyKernels& k, cudaStream_t st, int nt, const thb200_te
       int64_t nn = n;
       int64_t nvec = (n - head) >> 2;
       int64_t blocks = (nvec + THB_CONTIG_THREADS * THB_CONTIG_UNROLL - 1) / (THB_CONTIG_THREADS * THB_CONTIG_UNROLL);
-      int64_t cap = (int64_t)sms * 32;
+      int64_t cap = kMaxGridBlocks;
       if (blocks > cap) blocks = cap;
       if (blocks < 1) blocks = 1;
       void* args[] = {&a, &b, &cc, &nn, &head, &s};
@@ -117,7 +116,7 @@ int launch_apply(const ApplyKernels& k, cudaStream_t st, int nt, const thb200_te
         Q.nvec = nvec;
         uint64_t per_block = THB_CONTIG_THREADS * THB_CONTIG_UNROLL;
         uint64_t blocks = (nvec + per_block - 1) / per_block;
-        uint64_t cap = (uint64_t)sms * 32;
+        uint64_t cap = (uint64_t)kMaxGridBlocks;
         if (blocks > cap) blocks = cap;
         void* args[] = {&Q, &s};
         THB_CUDA(cudaLaunchKernel(k.rows2d, dim3((unsigned)blocks), dim3(THB_CONTIG_THREADS), args, 0, st));
@@ -156,7 +155,7 @@ int launch_apply(const ApplyKernels& k, cudaStream_t st, int nt, const thb200_te
           uint64_t ntiles = (uint64_t)((R + THB_T4_R - 1) / THB_T4_R) * P.tilesC;
           P.ntiles = (uint32_t)ntiles;
           uint64_t blocks = ntiles;
-          uint64_t cap = (uint64_t)sms * 64;
+          uint64_t cap = (uint64_t)kMaxGridBlocks;
           if (blocks > cap) blocks = cap;
           void* args[] = {&P, &s};
           THB_CUDA(cudaLaunchKernel(k.tile2d_v4, dim3((unsigned)blocks), dim3(256), args, 0, st));
@@ -166,7 +165,7 @@ int launch_apply(const ApplyKernels& k, cudaStream_t st, int nt, const thb200_te
         uint64_t ntiles = (uint64_t)((R + THB_TILE - 1) / THB_TILE) * P.tilesC;
         P.ntiles = (uint32_t)ntiles;
         uint64_t blocks = ntiles;
-        uint64_t cap = (uint64_t)sms * 64;
+        uint64_t cap = (uint64_t)kMaxGridBlocks;
         if (blocks > cap) blocks = cap;
         void* args[] = {&P, &s};
         THB_CUDA(cudaLaunchKernel(k.tile2d, dim3((unsigned)blocks), dim3(THB_TILE, THB_TILE_ROWS), args, 0, st));
@@ -183,7 +182,7 @@ int launch_apply(const ApplyKernels& k, cudaStream_t st, int nt, const thb200_te
   uint64_t nn = (uint64_t)n;
   uint64_t per_block = THB_STRIDED_THREADS * THB_STRIDED_UNROLL;
   uint64_t blocks = (nn + per_block - 1) / per_block;
-  uint64_t cap = (uint64_t)sms * 32;
+  uint64_t cap = (uint64_t)kMaxGridBlocks;
   if (blocks > cap) blocks = cap;
   void* args[] = {&L[0], &L[1], &L[2], &nn, &s};
   THB_CUDA(cudaLaunchKernel(k.strided, dim3((unsigned)blocks), dim3(THB_STRIDED_THREADS), args, 0, st));

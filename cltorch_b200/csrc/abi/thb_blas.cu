@@ -137,7 +137,7 @@ int thb200_ger(void* stream, int64_t m, int64_t n, float alpha, const float* x, 
     return 1;
   const uint64_t nvec = (uint64_t)n * (uint64_t)(m >> 2);
   uint64_t blocks = (nvec + 1023) / 1024;
-  const uint64_t cap = (uint64_t)sm_count() * 32;
+  const uint64_t cap = (uint64_t)kMaxGridBlocks;
   if (blocks > cap) blocks = cap;
   if (alpha_on_x)
     thb_ger_rows<false><<<(unsigned)blocks, 256, 0, (cudaStream_t)stream>>>(a, lda, (thb_u32)n, (thb_u32)(m >> 2), y, incy, x, alpha);

@@ -184,7 +184,7 @@ int thb200_renorm_rows(void* stream, float* data, int64_t rows, int64_t size, fl
   if (int rc = thb200_reduce_dim(stream, THB200_MOD_ABSPOW, THB200_RED_ADD, &tout, &tin, 1, 0.f, p, nullptr, 0)) return rc;
   const int64_t pieces = (size + THB_RN_PIECE - 1) / THB_RN_PIECE;
   int64_t blocks = rows * pieces;
-  const int64_t cap = (int64_t)sm_count() * 64;
+  const int64_t cap = kMaxGridBlocks;
   if (blocks > cap) blocks = cap;
   thb_renorm_scale<<<(unsigned)blocks, THB_SC_THREADS, 0, (cudaStream_t)stream>>>(data, (const float*)scratch, rows, size, p,
                                                                                    maxnorm, pieces);
