@@ -248,7 +248,8 @@ def n3(T):
     pt = cl.ClTensor()
     T.time("std -> point tensor (one pass)", lambda: pt.std(A), 4 * n)
     T.time("norm(2) -> host float", lambda: A.norm(2), 4 * n)
-    T.time("norm(3) -> host float [general power: fp64 pow per element]", lambda: A.norm(3), 4 * n)
+    T.time("norm(3) -> host float", lambda: A.norm(3), 4 * n)
+    T.time("norm(2.5) -> host float [general power: exp2(p*log2|x|) per element]", lambda: A.norm(2.5), 4 * n)
     B = cl.ClTensor(rows, rows)
     for d in (1, 2):
         T.time(f"cumsum(A, {d}) [8 B/elt; the chunked form moves 12]", lambda: B.cumsum(A, d), 8 * n)

@@ -1,8 +1,11 @@
 // Kernel selection and launch for pointwise apply (built-in operators and
 // NVRTC-compiled expressions share this path).
+#include <cudaTypedefs.h>
+
 #include "thb_internal.h"
 #include "../kernels/math_policy.cuh"
 #include "../kernels/apply_kernels.cuh"
+#include "../kernels/apply_tma_kernels.cuh"
 
 #include <cstring>
 
@@ -27,6 +30,48 @@ static void fill_layout(ThbLayout* L, float* data, const Collapsed& c) {
     L->stride[d] = (uint32_t)c.stride[d];
     fastdiv_constants((uint32_t)c.size[d], &L->magic[d], &L->shift[d]);
   }
+}
+
+// Tensor map of one operand of thb_apply_tile_tma: 32 x 32 boxes with the 128-byte swizzle, the
+// unit-stride direction innermost (columns for a row-major operand, rows for a column-major one).
+static bool make_tile_map(CUtensorMap* map, const float* data, int64_t inner, int64_t outer, int64_t pitch) {
+  auto enc = (PFN_cuTensorMapEncodeTiled_v12000)tensor_map_encoder_ptr();
+  if (!enc) return false;
+  cuuint64_t dims[2] = {(cuuint64_t)inner, (cuuint64_t)outer};
+  cuuint64_t strides[1] = {(cuuint64_t)pitch * 4};
+  cuuint32_t box[2] = {THB_AT_BOX, THB_AT_BOX};
+  cuuint32_t estr[2] = {1, 1};
+  return enc(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, (void*)data, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+             CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+// The TMA tile kernel when the operands qualify: 0 launched, -1 not applicable, 1 error.
+static int launch_tile_tma(const ApplyKernels& k, cudaStream_t st, int nt, const ThbTile2d& T, const ThbScalars& s) {
+  if (!k.tile_tma || (nt < 2 && !k.reads_out)) return -1;
+  const int sms = sm_count();
+  const int64_t R = T.R, C = T.C;
+  const int64_t tilesC = (C + THB_AT_TILE - 1) / THB_AT_TILE, ntiles = ((R + THB_AT_TILE - 1) / THB_AT_TILE) * tilesC;
+  if (R < THB_AT_TILE || C < THB_AT_TILE || ntiles < sms || ntiles > INT32_MAX) return -1;
+  CUtensorMap maps[3];
+  for (int i = 0; i < nt; ++i) {
+    const bool col = (T.colmajor >> i) & 1;
+    const int64_t pitch = col ? T.sc[i] : T.sr[i], inner = col ? R : C, outer = col ? C : R;
+    if (((uintptr_t)T.data[i] & 15) || (pitch & 3) || pitch < inner || pitch * 4 >= (int64_t(1) << 40)) return -1;
+    if (!make_tile_map(&maps[i], T.data[i], inner, outer, pitch)) return -1;
+  }
+  for (int i = nt; i < 3; ++i) maps[i] = maps[0];
+  ThbTileTma P;
+  P.R = (uint32_t)R; P.C = (uint32_t)C; P.tilesC = (uint32_t)tilesC; P.ntiles = (uint32_t)ntiles;
+  P.colmajor = T.colmajor; P.status = device_status_word();
+  P.tilesR = (uint32_t)((R + THB_AT_TILE - 1) / THB_AT_TILE);
+  P.band = 8;  // measured on 8192 x 8192: 0.91-0.95 of the copy rate with bands of 4-8 tile rows, 0.84-0.90 row by row
+  const size_t smem = THB_AT_SMEM(nt);
+  THB_CUDA(cudaFuncSetAttribute(k.tile_tma, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+  ThbScalars sc = s;
+  void* args[] = {&maps[0], &maps[1], &maps[2], &P, &sc};
+  THB_CUDA(cudaLaunchKernel(k.tile_tma, dim3((unsigned)(ntiles < sms ? ntiles : sms)), dim3(THB_AT_THREADS), args, smem, st));
+  return 0;
 }
 
 static int misalign_elems(const float* p) {  // elements before the next 16-byte boundary
@@ -143,6 +188,8 @@ int launch_apply(const ApplyKernels& k, cudaStream_t st, int nt, const thb200_te
         if (plan_out) *plan_out = PLAN_TILE2D;
         if (dry_run) return 0;
         P.R = (uint32_t)R; P.C = (uint32_t)C;
+        // large matrices: tiles move through the TMA unit
+        if (const int rc = launch_tile_tma(k, st, nt, P, s); rc >= 0) return rc;
         // 128-bit variant when every access it makes is 16-byte aligned
         bool v4 = k.tile2d_v4 != nullptr;
         for (int i = 0; i < nt && v4; ++i) {

@@ -5,6 +5,7 @@
 #include "thb_internal.h"
 #include "../kernels/math_policy.cuh"
 #include "../kernels/apply_kernels.cuh"
+#include "../kernels/apply_tma_kernels.cuh"
 
 #ifndef THB_NPARTS
 #define THB_NPARTS 1
@@ -44,6 +45,8 @@ static void register_part(ApplyKernels* table) {
     k.tile2d = (const void*)&thb_apply_tile2d<Op_##NAME, NT>;                        \
     k.rows2d = (const void*)&thb_apply_rows2d<Op_##NAME, NT>;                        \
     k.tile2d_v4 = (const void*)&thb_apply_tile2d_v4<Op_##NAME, NT>;                  \
+    if constexpr (NT >= 2 || Op_##NAME::kReadsOut)                                   \
+      k.tile_tma = (const void*)&thb_apply_tile_tma<Op_##NAME, NT>;                  \
     k.nt = NT;                                                                       \
     k.reads_out = Op_##NAME::kReadsOut;                                              \
     k.name = #NAME;                                                                  \

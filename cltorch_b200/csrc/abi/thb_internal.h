@@ -54,6 +54,7 @@ struct ApplyKernels {
   const void* strided = nullptr;
   const void* tile2d = nullptr;
   const void* tile2d_v4 = nullptr;
+  const void* tile_tma = nullptr;  // thb_apply_tile_tma; absent for run-time compiled expressions
   const void* rows2d = nullptr;
   int nt = 0;
   bool reads_out = true;

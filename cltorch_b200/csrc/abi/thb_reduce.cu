@@ -43,7 +43,7 @@ static int64_t reduce_all_blocks(int64_t n) {
 // Calls f.template operator()<Mod, Red>() for the pair the reference's
 // front-ends use; false for a pair nobody asks for.
 template <class F>
-static bool dispatch_pair(int modify, int reduce, F&& f) {
+static bool dispatch_pair(int modify, int reduce, float mod_param, F&& f) {
   switch (modify) {
     case THB200_MOD_COPY:
       switch (reduce) {
@@ -56,8 +56,12 @@ static bool dispatch_pair(int modify, int reduce, F&& f) {
       }
       return false;
     case THB200_MOD_ABSPOW:
-      if (reduce == THB200_RED_ADD) { f.template operator()<ModAbsPow, RedAdd>(); return true; }
-      return false;
+      if (reduce != THB200_RED_ADD) return false;
+      if (mod_param == 2.0f) f.template operator()<ModSquare, RedAdd>();
+      else if (mod_param == 1.0f) f.template operator()<ModAbs, RedAdd>();
+      else if (mod_param == 3.0f) f.template operator()<ModAbsCube, RedAdd>();
+      else f.template operator()<ModAbsPow, RedAdd>();
+      return true;
     case THB200_MOD_NEZERO:
       if (reduce == THB200_RED_ADD) { f.template operator()<ModNeZero, RedAdd>(); return true; }
       return false;
@@ -402,7 +406,7 @@ int thb200_reduce_all(void* stream, int modify, int reduce, const thb200_tensor*
   if (a.head > a.n) a.head = (int)a.n;
   if (!a.contig && !can_use_32bit(in->ndim, in->size, in->stride))
     return fail("reduceAll: non-contiguous tensor needs 64-bit index math: not implemented");
-  if (!dispatch_pair(modify, reduce, a)) return fail("reduceAll: unsupported modify/reduce pair (%d, %d)", modify, reduce);
+  if (!dispatch_pair(modify, reduce, a.mparam, a)) return fail("reduceAll: unsupported modify/reduce pair (%d, %d)", modify, reduce);
   if (a.err != cudaSuccess) return fail_cuda(a.err, "reduceAll launch");
   return 0;
 }
@@ -483,7 +487,7 @@ static int reduce_dim_impl(void* stream, int modify, int reduce, const thb200_te
   if (a.nchunks > 1 && (!scratch || scratch_bytes < (size_t)a.nchunks * nslices * acc_bytes))
     return fail("reduceDim: scratch too small (%zu bytes, need %zu)", scratch_bytes,
                 (size_t)a.nchunks * nslices * acc_bytes);
-  const bool known = reduce >= 100 ? dispatch_moments(reduce, a) : dispatch_pair(modify, reduce, a);
+  const bool known = reduce >= 100 ? dispatch_moments(reduce, a) : dispatch_pair(modify, reduce, mod_param, a);
   if (!known) return fail("reduceDim: unsupported modify/reduce pair (%d, %d)", modify, reduce);
   if (a.strip_rc) return a.strip_rc;
   if (a.err != cudaSuccess) return fail_cuda(a.err, "reduceDim launch");

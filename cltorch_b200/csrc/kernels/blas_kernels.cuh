@@ -67,7 +67,8 @@ thb_gemv_t(const float* A, thb_i64 lda, const float* x, thb_i64 incx, float* y, 
     if (j < n) {
       const float* col = A + j * lda;
       if (incx == 1 && ((((thb_u64)col) | ((thb_u64)x)) & 15) == 0 && (m & 3) == 0) {
-        // 4 vectors of the column and of x in flight per thread, one accumulator per vector lane
+        // 4 vectors of the column and of x in flight per thread, one accumulator per vector lane;
+        // the matrix goes past L1 so that x, which every column needs again, stays there
         const float4* c4 = reinterpret_cast<const float4*>(col);
         const float4* x4 = reinterpret_cast<const float4*>(x);
         const thb_u32 nvec = m >> 2;
@@ -76,7 +77,7 @@ thb_gemv_t(const float* A, thb_i64 lda, const float* x, thb_i64 incx, float* y, 
           float4 a[4], b[4];
 #pragma unroll
           for (int u = 0; u < 4; ++u)
-            if (i + u * nt < nvec) { a[u] = c4[i + u * nt]; b[u] = x4[i + u * nt]; }
+            if (i + u * nt < nvec) { a[u] = __ldcg(c4 + i + u * nt); b[u] = x4[i + u * nt]; }
 #pragma unroll
           for (int u = 0; u < 4; ++u)
             if (i + u * nt < nvec) {

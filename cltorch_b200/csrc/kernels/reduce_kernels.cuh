@@ -26,12 +26,19 @@ __device__ __forceinline__ float thb_abs_pow(float d, float p) {
   if (p == 2.0f) return d * d;
   if (p == 1.0f) return d;
   if (p == 0.0f) return 1.0f;  // pow(x, 0) = 1, also for x = 0
+  if (p == 3.0f) return d * d * d;
+  if (p == 4.0f) return (d * d) * (d * d);
   return __powf(d, p);
 }
 
 // kFirst: the operator wants the first element of the slice as its third argument.
 struct ModCopy { static constexpr bool kFirst = false; static __device__ __forceinline__ float apply(float x, float, float) { return x; } };
 struct ModAbsPow { static constexpr bool kFirst = false; static __device__ __forceinline__ float apply(float x, float p, float) { return thb_abs_pow(x, p); } };
+// |x|^p for the exponents norms are usually taken with: the host picks these when p is 1, 2 or 3,
+// so that the loop carries no comparison of p per element.
+struct ModAbs { static constexpr bool kFirst = false; static __device__ __forceinline__ float apply(float x, float, float) { return fabsf(x); } };
+struct ModSquare { static constexpr bool kFirst = false; static __device__ __forceinline__ float apply(float x, float, float) { return x * x; } };
+struct ModAbsCube { static constexpr bool kFirst = false; static __device__ __forceinline__ float apply(float x, float, float) { x = fabsf(x); return x * x * x; } };
 struct ModNeZero { static constexpr bool kFirst = false; static __device__ __forceinline__ float apply(float x, float, float) { return x != 0.0f; } };
 struct ModSqDev { static constexpr bool kFirst = false; static __device__ __forceinline__ float apply(float x, float, float m) { return (x - m) * (x - m); } };
 // Deviation from the first element of the slice: the single-pass variance accumulates the

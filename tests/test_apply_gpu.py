@@ -238,6 +238,34 @@ def test_transposed_operands_take_the_tile_path(rows, cols):
     a.check(0, "source untouched")
 
 
+@pytest.mark.parametrize("rows,cols,pad", [(832, 768, 0), (1000, 1100, 0), (1028, 644, 8), (2048, 320, 4), (68, 9600, 0)])
+def test_large_transposed_operands_go_through_the_tma_tiles(rows, cols, pad):
+    """At least one 64 x 64 tile per SM: the tiles travel through the TMA unit (ragged edges are
+    clipped by it). `pad` widens the pitch of every view beyond its extent."""
+    prow, pcol = cols + pad, rows + pad
+    a = Pair(rng_uniform(47, (rows * prow,), -1, 1), 0, [rows, cols], [prow, 1])      # row-major
+    b = Pair(rng_uniform(48, (cols * pcol,), -1, 1), 0, [rows, cols], [1, pcol])      # column-major
+    c = Pair(rng_uniform(49, (cols * pcol,), -1, 1), 0, [rows, cols], [1, pcol])
+    d = Pair(rng_uniform(50, (rows * prow,), -1, 1), 0, [rows, cols], [prow, 1])
+    a.cl.addcmul(0.5, b.cl, c.cl); O.apply("ADDCMUL_3", [a.view, b.view, c.view], 0.5)
+    a.check(0, "row-major += 0.5 * transposed * transposed")
+    b.cl.add(a.cl); O.apply("ADD_2", [b.view, a.view])
+    b.check(0, "transposed += row-major")
+    b.cl.addcmul(2.0, c.cl, a.cl); O.apply("ADDCMUL_3", [b.view, c.view, a.view], 2.0)
+    b.check(0, "transposed += 2 * transposed * row-major")
+    d.cl.add(b.cl, c.cl); O.apply("ADD_3", [d.view, b.view, c.view])                  # write-only destination
+    d.check(0, "row-major = transposed + transposed")
+    c.cl.cmul(a.cl, d.cl); O.apply("MUL_3", [c.view, a.view, d.view])
+    c.check(0, "transposed = row-major * row-major")
+    c.cl.copy(a.cl); O.apply("COPY_2", [c.view, a.view])
+    c.check(0, "transposed = copy of row-major")
+    d.cl.copy(b.cl); O.apply("COPY_2", [d.view, b.view])
+    d.check(0, "row-major = copy of transposed")
+    b.cl.tanh(); O.apply("TANH_1", [b.view])
+    b.check(2, "in place on a transposed view")
+    a.check(0, "sources untouched")
+
+
 def test_mixed_alignment_falls_back_to_strided():
     a = Pair(rng_uniform(10, (5000,)), 1, [4000], None)
     b = Pair(rng_uniform(11, (5000,)), 2, [4000], None)

@@ -151,7 +151,7 @@ def test_norm_along_dim():
     import cltorch_b200 as cl
     a = rng_uniform(29, (40, 30), -1, 1)
     A = cl.ClTensor(a)
-    for p in (1.0, 2.0, 3.0):
+    for p in (1.0, 2.0, 3.0, 4.0, 2.5, 0.5):
         want = (np.abs(a.astype(np.float64)) ** p).sum(axis=1, keepdims=True) ** (1 / p)
         assert np.all(np.abs(A.norm(p, 2).float() - want) <= 1e-5 * want)
     assert np.array_equal(A.norm(0, 1).float(), (a != 0).sum(axis=0, keepdims=True).astype(np.float32))

@@ -201,7 +201,7 @@ def test_renorm_argument_checks():
 # ---- dist ------------------------------------------------------------------------------------
 
 @pytest.mark.parametrize("n", [1, 5, 1000, (1 << 20) + 3])
-@pytest.mark.parametrize("p", [1.0, 2.0, 3.0, 0.5])
+@pytest.mark.parametrize("p", [1.0, 2.0, 3.0, 4.0, 0.5])
 def test_dist(n, p):
     import cltorch_b200 as cl
     a, b = normal(61, (n,)), normal(62, (n,))
