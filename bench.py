@@ -95,7 +95,7 @@ class ClockSampler:
 
 # dram__bytes_read.sum + dram__bytes_write.sum of thb_apply_contig for 2^28 elements, per element
 # (profiles/apply_contig_and_reduce_all_2p28.md); DRAM traffic of this kernel grows in proportion.
-NCU_DRAM_BYTES_PER_ELT_APPLY = (1.073753e9 + 1.016120e9) / 268435456
+NCU_DRAM_BYTES_PER_ELT_APPLY = (1.073748e9 + 1.015486e9) / 268435456
 
 
 # ---- CPU leg (oracle port) ---------------------------------------------------------------------
@@ -289,7 +289,7 @@ def run_gpu(args):
                          "frac": achieved / peaks["hbm_gbs"], "peak_source": peaks["source"],
                          "traffic": NCU_DRAM_BYTES_PER_ELT_APPLY * n_local,
                          "traffic_note": "bytes per launch: dram__bytes_read.sum + dram__bytes_write.sum of one ncu "
-                                         "capture at 2^28 elements (2.0899 GB), scaled by the elements of a launch",
+                                         "capture at 2^28 elements (2.0892 GB), scaled by the elements of a launch",
                          "per_kernel_gbs": {"apply_axpb": achieved, "apply_sqrt": 8 * n_local / (k_apply2 * 1e-3) / 1e9,
                                             "reduce_all_sum": 4 * n_local / (k_sum * 1e-3) / 1e9}},
             "e2e": {"value": BYTES_PER_ELT * n_total / (e2e_ms / e2e_steps * 1e-3) / 1e9, "unit": "GB/s",

@@ -39,10 +39,10 @@ CXX_FLAGS = [
 
 
 def _embed_kernel_source() -> Path:
-    """Writes the text NVRTC compiles (math_policy.cuh + apply_kernels.cuh) as a C++ raw string."""
+    """Writes the text NVRTC compiles (math policy, apply kernels, TMA helpers, TMA tile kernel) as a C++ raw string."""
     BUILD.mkdir(parents=True, exist_ok=True)
     out = BUILD / "apply_kernels_src.inc"
-    text = "".join((CSRC / "kernels" / n).read_text() for n in ("math_policy.cuh", "apply_kernels.cuh"))
+    text = "".join((CSRC / "kernels" / n).read_text() for n in ("math_policy.cuh", "apply_kernels.cuh", "tma_pipeline.cuh", "apply_tma_kernels.cuh"))
     text = text.replace("#pragma once", "")
     body = 'R"THBSRC(' + text + ')THBSRC"\n'
     if not out.exists() or out.read_text() != body:

@@ -67,7 +67,10 @@ static int launch_tile_tma(const ApplyKernels& k, cudaStream_t st, int nt, const
   P.tilesR = (uint32_t)((R + THB_AT_TILE - 1) / THB_AT_TILE);
   P.band = 8;  // measured on 8192 x 8192: 0.91-0.95 of the copy rate with bands of 4-8 tile rows, 0.84-0.90 row by row
   const size_t smem = THB_AT_SMEM(nt);
-  THB_CUDA(cudaFuncSetAttribute(k.tile_tma, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+  if (cudaFuncSetAttribute(k.tile_tma, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) {
+    cudaGetLastError();  // not launchable with this much shared memory here: the thread-staged kernel takes over
+    return -1;
+  }
   ThbScalars sc = s;
   void* args[] = {&maps[0], &maps[1], &maps[2], &P, &sc};
   THB_CUDA(cudaLaunchKernel(k.tile_tma, dim3((unsigned)(ntiles < sms ? ntiles : sms)), dim3(THB_AT_THREADS), args, smem, st));

@@ -70,10 +70,10 @@ int thb200_gemv(void* stream, char trans, int64_t m, int64_t n, float alpha, con
     // y (n) = alpha * A^T x + beta * y: one contiguous column of A (length m) per output
     if (m < 8192) {
       int64_t blocks = (n + 7) / 8;
-      if (blocks > (int64_t)sms * 64) blocks = (int64_t)sms * 64;
+      if (blocks > kMaxGridBlocks) blocks = kMaxGridBlocks;
       thb_gemv_t<true><<<(unsigned)blocks, THB_RD_THREADS, 0, st>>>(a, lda, x, incx, y, incy, (thb_u32)m, (thb_u32)n, alpha, beta);
     } else {
-      int64_t blocks = n < (int64_t)sms * 64 ? n : (int64_t)sms * 64;
+      int64_t blocks = n < kMaxGridBlocks ? n : kMaxGridBlocks;
       thb_gemv_t<false><<<(unsigned)blocks, THB_RD_THREADS, 0, st>>>(a, lda, x, incx, y, incy, (thb_u32)m, (thb_u32)n, alpha, beta);
     }
     THB_CUDA(cudaGetLastError());

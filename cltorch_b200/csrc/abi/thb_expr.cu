@@ -76,12 +76,16 @@ int expr_kernels(int nt, const std::string& body, const ApplyKernels** out) {
   nvrtcResult r = nvrtcCreateProgram(&prog, src.c_str(), "thb_user_expr.cu", 0, nullptr, nullptr);
   if (r != NVRTC_SUCCESS) return fail_nvrtc(r, "nvrtcCreateProgram");
   const std::string nts = std::to_string(nt);
-  const int kNumKernels = 5;
-  const std::string names[kNumKernels] = {
+  const bool reads_out = thb_body_reads_out(body.c_str());
+  const bool with_tma = nt >= 2 || reads_out;  // the TMA tile kernel needs at least one operand to load
+  const int kMaxKernels = 6;
+  const int kNumKernels = with_tma ? 6 : 5;
+  const std::string names[kMaxKernels] = {
       "thb_apply_contig<UserOp, " + nts + ">", "thb_apply_strided<UserOp, " + nts + ">",
       "thb_apply_tile2d<UserOp, " + nts + ">", "thb_apply_rows2d<UserOp, " + nts + ">",
-      "thb_apply_tile2d_v4<UserOp, " + nts + ">"};
-  for (const std::string& n : names) {
+      "thb_apply_tile2d_v4<UserOp, " + nts + ">", "thb_apply_tile_tma<UserOp, " + nts + ">"};
+  for (int i = 0; i < kNumKernels; ++i) {
+    const std::string& n = names[i];
     r = nvrtcAddNameExpression(prog, n.c_str());
     if (r != NVRTC_SUCCESS) { nvrtcDestroyProgram(&prog); return fail_nvrtc(r, "nvrtcAddNameExpression"); }
   }
@@ -103,7 +107,7 @@ int expr_kernels(int nt, const std::string& body, const ApplyKernels** out) {
   std::vector<char> cubin(n);
   r = nvrtcGetCUBIN(prog, cubin.data());
   if (r != NVRTC_SUCCESS) { nvrtcDestroyProgram(&prog); return fail_nvrtc(r, "nvrtcGetCUBIN"); }
-  std::string lowered[kNumKernels];
+  std::string lowered[kMaxKernels];
   for (int i = 0; i < kNumKernels; ++i) {
     const char* ln = nullptr;
     r = nvrtcGetLoweredName(prog, names[i].c_str(), &ln);
@@ -116,15 +120,16 @@ int expr_kernels(int nt, const std::string& body, const ApplyKernels** out) {
   e->body = body;
   e->name = "expr";
   THB_CUDA(cudaLibraryLoadData(&e->lib, cubin.data(), nullptr, nullptr, 0, nullptr, nullptr, 0));
-  cudaKernel_t kern[kNumKernels];
+  cudaKernel_t kern[kMaxKernels];
   for (int i = 0; i < kNumKernels; ++i) THB_CUDA(cudaLibraryGetKernel(&kern[i], e->lib, lowered[i].c_str()));
   e->k.contig = (const void*)kern[0];
   e->k.strided = (const void*)kern[1];
   e->k.tile2d = (const void*)kern[2];
   e->k.rows2d = (const void*)kern[3];
   e->k.tile2d_v4 = (const void*)kern[4];
+  if (with_tma) e->k.tile_tma = (const void*)kern[5];
   e->k.nt = nt;
-  e->k.reads_out = thb_body_reads_out(body.c_str());
+  e->k.reads_out = reads_out;
   e->k.name = e->name.c_str();
   e->k.body = e->body.c_str();
   *out = &e->k;

@@ -8,6 +8,7 @@
 
 #include <cstdlib>
 #include <cstring>
+#include <atomic>
 #include <mutex>
 
 namespace thb {
@@ -217,12 +218,20 @@ struct ReduceDimArgs {
     const int sms = sm_count();
     if (rstride == 1) {
       if (rsize >= 8192) {
-        unsigned blocks = nslices < (unsigned)sms * 64u ? nslices : (unsigned)sms * 64u;
+        unsigned blocks = nslices < (unsigned)kMaxGridBlocks ? nslices : (unsigned)kMaxGridBlocks;
         thb_reduce_dim_contig_block<Mod, Red><<<blocks, THB_RD_THREADS, 0, st>>>(out, in, rsize, nslices, init, mparam);
       } else {
-        uint64_t blocks = ((uint64_t)nslices + 7) / 8;
-        if (blocks > (uint64_t)sms * 64) blocks = (uint64_t)sms * 64;
-        thb_reduce_dim_contig_warp<Mod, Red><<<(unsigned)blocks, THB_RD_THREADS, 0, st>>>(out, in, rsize, nslices, init, mparam);
+        // a warp walks several short slices: measured faster than one block per 8 slices (0.86 against 0.81 of
+        // the copy rate on 262144 slices of 1024)
+        if (rsize <= 2048) {
+          uint64_t blocks = ((uint64_t)nslices + 31) / 32;  // 8 lanes per slice
+          if (blocks > (uint64_t)sms * 64) blocks = (uint64_t)sms * 64;
+          thb_reduce_dim_contig_warp<Mod, Red, 8><<<(unsigned)blocks, THB_RD_THREADS, 0, st>>>(out, in, rsize, nslices, init, mparam);
+        } else {
+          uint64_t blocks = ((uint64_t)nslices + 7) / 8;
+          if (blocks > (uint64_t)sms * 64) blocks = (uint64_t)sms * 64;
+          thb_reduce_dim_contig_warp<Mod, Red, 32><<<(unsigned)blocks, THB_RD_THREADS, 0, st>>>(out, in, rsize, nslices, init, mparam);
+        }
       }
       err = cudaGetLastError();
       return;
@@ -301,10 +310,10 @@ static int argreduce(cudaStream_t st, float* values, float* indices, const float
   if (inner == 1) {
     if (n < 8192) {
       int64_t blocks = (outer + 7) / 8;
-      if (blocks > (int64_t)sms * 64) blocks = (int64_t)sms * 64;
+      if (blocks > kMaxGridBlocks) blocks = kMaxGridBlocks;
       thb_argreduce_rows<IS_MAX, true><<<(unsigned)blocks, THB_RD_THREADS, 0, st>>>(values, indices, src, outer, (thb_u32)n);
     } else {
-      int64_t blocks = outer < (int64_t)sms * 64 ? outer : (int64_t)sms * 64;
+      int64_t blocks = outer < kMaxGridBlocks ? outer : kMaxGridBlocks;
       thb_argreduce_rows<IS_MAX, false><<<(unsigned)blocks, THB_RD_THREADS, 0, st>>>(values, indices, src, outer, (thb_u32)n);
     }
     THB_CUDA(cudaGetLastError());
@@ -575,11 +584,16 @@ int thb200_reduce_dim_index(void* stream, int is_max, float* values, float* indi
 static __device__ int thb_status_word_storage;
 
 namespace thb {
+// Set when a launch was given the status word of the device, cleared by thb200_kernel_status: a
+// query with no such launch since the last one answers 0 without touching the GPU.
+static std::atomic<bool> g_status_word_handed_out[64];
+
 int* device_status_word() {
   static std::mutex mu;
   static int* addr[64];
   int dev = 0;
   if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
+  g_status_word_handed_out[dev].store(true, std::memory_order_relaxed);
   std::lock_guard<std::mutex> lock(mu);
   if (!addr[dev]) {
     void* p = nullptr;
@@ -591,8 +605,13 @@ int* device_status_word() {
 }  // namespace thb
 
 extern "C" int thb200_kernel_status(void* stream) {
+  int dev = 0;
+  if (cudaGetDevice(&dev) == cudaSuccess && dev >= 0 && dev < 64 &&
+      !thb::g_status_word_handed_out[dev].exchange(false, std::memory_order_relaxed))
+    return 0;  // no kernel with bounded waits was launched since the last query
   int* w = thb::device_status_word();
   if (!w) { thb::fail("kernel_status: the status word is not available"); return -1; }
+  if (dev >= 0 && dev < 64) thb::g_status_word_handed_out[dev].store(false, std::memory_order_relaxed);
   int h = -1;
   if (cudaMemcpyAsync(&h, w, sizeof(int), cudaMemcpyDeviceToHost, (cudaStream_t)stream) != cudaSuccess ||
       cudaStreamSynchronize((cudaStream_t)stream) != cudaSuccess) {

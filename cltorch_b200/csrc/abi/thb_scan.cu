@@ -90,7 +90,7 @@ static int run_scan(cudaStream_t st, float* dst, const float* src, int64_t outer
   if (p.rows) {
     const int64_t work = outer * p.nchunks;  // warps
     int64_t blocks = (work + THB_SC_THREADS / 32 - 1) / (THB_SC_THREADS / 32);
-    if (blocks > (int64_t)sms * 64) blocks = (int64_t)sms * 64;
+    if (blocks > kMaxGridBlocks) blocks = kMaxGridBlocks;
     if (p.nchunks > 1) {
       if (p.vec == 4) thb_scan_rows<Op, 4, true><<<(unsigned)blocks, THB_SC_THREADS, 0, st>>>(dst, src, outer, (thb_u32)n, p.chunk_len, p.nchunks, carry);
       else thb_scan_rows<Op, 1, true><<<(unsigned)blocks, THB_SC_THREADS, 0, st>>>(dst, src, outer, (thb_u32)n, p.chunk_len, p.nchunks, carry);
@@ -100,7 +100,7 @@ static int run_scan(cudaStream_t st, float* dst, const float* src, int64_t outer
         thb_scan_carries_rows<Op><<<(unsigned)cb, THB_SC_THREADS, 0, st>>>(carry, outer, p.nchunks);
       } else {
         int64_t cb = (outer + 31) / 32;
-        if (cb > (int64_t)sms * 64) cb = (int64_t)sms * 64;
+        if (cb > kMaxGridBlocks) cb = kMaxGridBlocks;
         thb_scan_carries<Op><<<(unsigned)cb, THB_SC_THREADS, 0, st>>>(carry, outer, p.nchunks, 1);
       }
       THB_CUDA(cudaGetLastError());
@@ -112,14 +112,14 @@ static int run_scan(cudaStream_t st, float* dst, const float* src, int64_t outer
   }
   const int64_t threads = outer * inner / p.vec;
   int64_t bx = (threads + THB_SC_THREADS - 1) / THB_SC_THREADS;
-  if (bx > (int64_t)sms * 64) bx = (int64_t)sms * 64;
+  if (bx > kMaxGridBlocks) bx = kMaxGridBlocks;
   const dim3 grid((unsigned)bx, p.nchunks);
   if (p.nchunks > 1) {
     if (p.vec == 4) thb_scan_cols<Op, 4, true><<<grid, THB_SC_THREADS, 0, st>>>(dst, src, outer, (thb_u32)n, inner, p.chunk_len, p.nchunks, carry);
     else thb_scan_cols<Op, 1, true><<<grid, THB_SC_THREADS, 0, st>>>(dst, src, outer, (thb_u32)n, inner, p.chunk_len, p.nchunks, carry);
     THB_CUDA(cudaGetLastError());
     int64_t cb = (outer * inner + 31) / 32;  // 32 positions x 8 lanes per block
-    if (cb > (int64_t)sms * 64) cb = (int64_t)sms * 64;
+    if (cb > kMaxGridBlocks) cb = kMaxGridBlocks;
     thb_scan_carries<Op><<<(unsigned)cb, THB_SC_THREADS, 0, st>>>(carry, outer, p.nchunks, inner);
     THB_CUDA(cudaGetLastError());
   }

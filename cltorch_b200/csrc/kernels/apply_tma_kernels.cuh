@@ -16,9 +16,14 @@
 // wrote their results), empty[s] (the store has read the stage). Every wait is bounded; on expiry the
 // waiter records a code in *status, raises the CTA's abort flag and all roles leave after the
 // copies in flight have landed.
+//
+// Like apply_kernels.cuh this text is also compiled by NVRTC for user expressions: the #include
+// lines are skipped there (the pieces are concatenated instead).
 #pragma once
-#include "gemm_kernels.cuh"  // mbarrier / TMA helpers
+#ifndef __CUDACC_RTC__
+#include "tma_pipeline.cuh"
 #include "apply_kernels.cuh"
+#endif
 
 #define THB_AT_TILE 64
 #define THB_AT_BOX 32
@@ -55,17 +60,6 @@ __device__ __forceinline__ void thb_at_tile_origin(const ThbTileTma& P, thb_u32 
   }
   *r0 = (int)(tr * THB_AT_TILE);
   *c0 = (int)(tc * THB_AT_TILE);
-}
-
-__device__ __forceinline__ void thb_tma_load_2d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int x, int y) {
-  asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
-               ::"r"(dst), "l"(map), "r"(bar), "r"(x), "r"(y)
-               : "memory");
-}
-__device__ __forceinline__ void thb_tma_store_2d(const CUtensorMap* map, uint32_t src, int x, int y) {
-  asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];"
-               ::"l"(map), "r"(src), "r"(x), "r"(y)
-               : "memory");
 }
 
 template <class Op, int NT>

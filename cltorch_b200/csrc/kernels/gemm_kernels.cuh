@@ -31,13 +31,11 @@
 // the common exit, where tensor memory is released.
 #pragma once
 
-#include <cuda.h>
-#include <stdint.h>
+#include "tma_pipeline.cuh"
 
 #define THB_GEMM_BM 128
 // threads of a CTA: warp 0 TMA, warp 1 MMA issuer, then EW (4 or 8) epilogue warps
 #define THB_GEMM_THREADS(EW) (64 + 32 * (EW))
-#define THB_GEMM_WAIT_LIMIT_NS 2000000000ull  // 2 s
 #define THB_GEMM_GROUP_M 16
 
 // Shared-memory budget of one configuration: tile width BN (256, or 128 for problems
@@ -105,49 +103,7 @@ thb_gemm_split(const float* __restrict__ src, long long sr, long long sk, long l
   }
 }
 
-// ---- PTX helpers ------------------------------------------------------------
-__device__ __forceinline__ uint32_t thb_smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
-
-__device__ __forceinline__ void thb_mbar_init(uint32_t bar, uint32_t count) {
-  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
-}
-__device__ __forceinline__ void thb_mbar_expect_tx(uint32_t bar, uint32_t bytes) {
-  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ bool thb_mbar_try_wait(uint32_t bar, uint32_t parity) {
-  uint32_t ok;
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-      "selp.u32 %0, 1, 0, p;\n\t}"
-      : "=r"(ok)
-      : "r"(bar), "r"(parity)
-      : "memory");
-  return ok != 0;
-}
-// Bounded wait; false when the limit ran out or another thread already gave up.
-__device__ __forceinline__ unsigned long long thb_globaltimer_ns() {
-  unsigned long long t;
-  asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
-  return t;
-}
-__device__ __forceinline__ bool thb_mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
-  if (thb_mbar_try_wait(bar, parity)) return true;
-  const unsigned long long t0 = thb_globaltimer_ns();
-  for (uint32_t i = 1;; ++i) {
-    if (thb_mbar_try_wait(bar, parity)) return true;
-    if ((i & 63u) == 0) {
-      if (*abort_flag) return false;
-      if (thb_globaltimer_ns() - t0 > THB_GEMM_WAIT_LIMIT_NS) return false;
-    }
-  }
-}
-__device__ __forceinline__ void thb_tma_load_3d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int x, int y, int z) {
-  asm volatile(
-      "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
-      ::"r"(dst), "l"(map), "r"(bar), "r"(x), "r"(y), "r"(z)
-      : "memory");
-}
+// ---- PTX helpers (mbarrier and TMA ones are in tma_pipeline.cuh) ------------
 // Shared-memory matrix descriptor of a K-major tile whose rows are one swizzle
 // span long: BK = 32 floats -> 128-byte swizzle (8-row groups 1024 bytes apart),
 // BK = 16 floats -> 64-byte swizzle (8-row groups 512 bytes apart).
@@ -178,9 +134,6 @@ __device__ __forceinline__ void thb_umma_tf32(uint32_t d_tmem, uint64_t a_desc, 
 }
 __device__ __forceinline__ void thb_umma_commit(uint32_t bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ void thb_mbar_arrive(uint32_t bar) {
-  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
 }
 
 struct ThbGemmParams {

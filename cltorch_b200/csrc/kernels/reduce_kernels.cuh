@@ -322,45 +322,52 @@ thb_reduce_dim_contig_block(ThbLayout out, ThbLayout in, thb_u32 rsize, thb_u32 
   }
 }
 
-// rstride == 1, one warp per slice (short slices).
-template <class Mod, class Red>
+// rstride == 1, short slices: G adjacent lanes per slice (G = 32: a warp per slice; G = 8: four
+// slices per warp, for slices so short that the shuffle tree of a whole warp would cost as much as
+// the additions). A group reads 16 * G contiguous bytes per load.
+template <class Mod, class Red, int G>
 __global__ void __launch_bounds__(THB_RD_THREADS)
 thb_reduce_dim_contig_warp(ThbLayout out, ThbLayout in, thb_u32 rsize, thb_u32 nslices, float init,
                            float mparam) {
   typedef typename Red::acc_t acc_t;
   const float fin_n = (float)rsize;
   const int lane = threadIdx.x & 31;
-  const thb_u32 warps_per_block = THB_RD_THREADS / 32;
-  for (thb_u64 s64 = (thb_u64)blockIdx.x * warps_per_block + (threadIdx.x >> 5); s64 < nslices;
-       s64 += (thb_u64)gridDim.x * warps_per_block) {
+  const int sub = lane % G;
+  const thb_u32 per_warp = 32 / G, per_block = (THB_RD_THREADS / 32) * per_warp;
+  for (thb_u64 s0 = (thb_u64)blockIdx.x * per_block + (threadIdx.x >> 5) * per_warp; s0 < nslices;
+       s0 += (thb_u64)gridDim.x * per_block) {
+    const thb_u64 s64 = s0 + lane / G;
+    const bool live = s64 < nslices;
     const thb_u32 s = (thb_u32)s64;
-    const float* p = in.data + thb_offset(in, s);
-    const float k0 = Mod::kFirst ? p[0] : 0.f;
     acc_t acc[4] = {(acc_t)init, (acc_t)init, (acc_t)init, (acc_t)init};
-    if ((((thb_u64)p) & 15) == 0 && (rsize & 3) == 0) {
-      const float4* p4 = reinterpret_cast<const float4*>(p);
-      const thb_u32 nvec = rsize >> 2;
-      for (thb_u32 i = lane; i < nvec; i += 32 * 4) {
-        float4 v[4];
+    if (live) {
+      const float* p = in.data + thb_offset(in, s);
+      const float k0 = Mod::kFirst ? p[0] : 0.f;
+      if ((((thb_u64)p) & 15) == 0 && (rsize & 3) == 0) {
+        const float4* p4 = reinterpret_cast<const float4*>(p);
+        const thb_u32 nvec = rsize >> 2;
+        for (thb_u32 i = sub; i < nvec; i += G * 4) {
+          float4 v[4];
 #pragma unroll
-        for (int u = 0; u < 4; ++u)
-          if (i + u * 32 < nvec) v[u] = p4[i + u * 32];
+          for (int u = 0; u < 4; ++u)
+            if (i + u * G < nvec) v[u] = p4[i + u * G];
 #pragma unroll
-        for (int u = 0; u < 4; ++u)
-          if (i + u * 32 < nvec) {
-            acc[0] = Red::apply(acc[0], Mod::apply(v[u].x, mparam, k0));
-            acc[1] = Red::apply(acc[1], Mod::apply(v[u].y, mparam, k0));
-            acc[2] = Red::apply(acc[2], Mod::apply(v[u].z, mparam, k0));
-            acc[3] = Red::apply(acc[3], Mod::apply(v[u].w, mparam, k0));
-          }
+          for (int u = 0; u < 4; ++u)
+            if (i + u * G < nvec) {
+              acc[0] = Red::apply(acc[0], Mod::apply(v[u].x, mparam, k0));
+              acc[1] = Red::apply(acc[1], Mod::apply(v[u].y, mparam, k0));
+              acc[2] = Red::apply(acc[2], Mod::apply(v[u].z, mparam, k0));
+              acc[3] = Red::apply(acc[3], Mod::apply(v[u].w, mparam, k0));
+            }
+        }
+      } else {
+        for (thb_u32 i = sub; i < rsize; i += G) acc[0] = Red::apply(acc[0], Mod::apply(p[i], mparam, k0));
       }
-    } else {
-      for (thb_u32 i = lane; i < rsize; i += 32) acc[0] = Red::apply(acc[0], Mod::apply(p[i], mparam, k0));
     }
     acc_t r = Red::apply(Red::apply(acc[0], acc[1]), Red::apply(acc[2], acc[3]));
 #pragma unroll
-    for (int off = 16; off > 0; off >>= 1) r = Red::apply(r, thb_shfl_down(r, off));
-    if (lane == 0) out.data[thb_offset(out, s)] = Red::result(r, fin_n);
+    for (int off = G / 2; off > 0; off >>= 1) r = Red::apply(r, thb_shfl_down(r, off));  // lane sub < off reads sub + off < G
+    if (sub == 0 && live) out.data[thb_offset(out, s)] = Red::result(r, fin_n);
   }
 }
 

@@ -124,12 +124,11 @@ void sync_stream(THClDeviceContext* ctx) {
                                 ctx->gemm_shape[3], ctx->gemm_ws);
     if (st != 0) raise("GEMM kernel did not complete: a bounded wait gave up (status %d); the result is undefined", st);
   }
-  if (ctx->status_pending) {
-    // kernels with bounded waits other than the GEMM report through the library's status word
-    ctx->status_pending = false;
-    const int st = thb200_kernel_status(ctx->stream);
-    if (st != 0) raise("a kernel did not complete: a bounded wait gave up (status %d); its result is undefined", st);
-  }
+  // kernels with bounded waits other than the GEMM report through the library's status word
+  // (the query costs nothing when no such kernel ran since the last one)
+  ctx->status_pending = false;
+  const int st = thb200_kernel_status(ctx->stream);
+  if (st != 0) raise("a kernel did not complete: a bounded wait gave up (status %d); its result is undefined", st);
 }
 
 void after_launch(THClState* state, THClDeviceContext* ctx) {

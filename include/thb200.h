@@ -107,11 +107,14 @@ int thb200_reduce_all(void* stream, int modify, int reduce, const thb200_tensor*
                       float mod_param, const float* mod_point, int fin, float fin_param,
                       float* d_out, float* scratch, size_t scratch_bytes);
 
-/* Reductions and scans over a non-innermost dimension of a contiguous tensor stream through a
- * TMA pipeline whose waits on shared-memory barriers are bounded (2 s). If such a wait ever
- * gives up, the kernel stores a non-zero code in a status word inside the library's device
- * image and leaves its output undefined. This call synchronises `stream`, returns that word
- * (0 = every kernel since the last call completed) and clears it; < 0 if it cannot be read. */
+/* Reductions and scans over a non-innermost dimension of a contiguous tensor, matrix-vector
+ * products and pointwise operators on large transposed operands stream through TMA pipelines
+ * whose waits on shared-memory barriers are bounded (2 s). If such a wait ever gives up, the
+ * kernel stores a non-zero code in a status word inside the library's device image and leaves
+ * its output undefined. This call synchronises `stream`, returns that word (0 = every kernel
+ * since the last call completed) and clears it; < 0 if it cannot be read. When no such kernel
+ * was launched on the current device since the last call it returns 0 at once, without
+ * synchronising. */
 int thb200_kernel_status(void* stream);
 
 /* Bytes of scratch thb200_reduce_dim may need for this shape (0 if none). */

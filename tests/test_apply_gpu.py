@@ -261,9 +261,18 @@ def test_large_transposed_operands_go_through_the_tma_tiles(rows, cols, pad):
     c.check(0, "transposed = copy of row-major")
     d.cl.copy(b.cl); O.apply("COPY_2", [d.view, b.view])
     d.check(0, "row-major = copy of transposed")
-    b.cl.tanh(); O.apply("TANH_1", [b.view])
-    b.check(2, "in place on a transposed view")
+    # run-time compiled expressions take the same kernel: one that reads its destination, one that does not
+    want = O.eval_expr("x = x * y + z * 0.25", c.view.numpy(), a.view.numpy(), d.view.numpy())
+    c.cl.map2_on_gpu(a.cl, d.cl, "x = x * y + z * 0.25")
+    c.view.numpy()[...] = want
+    c.check(0, "transposed = expression of itself and two row-major operands")
+    want = O.eval_expr("x = y - 2 * z", d.view.numpy(), b.view.numpy(), c.view.numpy())
+    d.cl.map2_on_gpu(b.cl, c.cl, "x = y - 2 * z")
+    d.view.numpy()[...] = want
+    d.check(0, "row-major = expression of two transposed operands")
     a.check(0, "sources untouched")
+    b.cl.tanh(); O.apply("TANH_1", [b.view])                                          # last: 2 ulp of slack from here on
+    b.check(2, "in place on a transposed view")
 
 
 def test_mixed_alignment_falls_back_to_strided():
