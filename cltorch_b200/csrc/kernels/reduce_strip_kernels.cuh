@@ -75,13 +75,16 @@ thb_strip_reduce(const __grid_constant__ CUtensorMap map_src, ThbStripGeom g, ty
       // Row weights travel through a ring of THB_SS_WRING slots of 32 floats, four stages at a
       // time: the batch written at stage q (q % 4 == 0) was loaded four stages earlier, so the
       // producer never sits out the latency of its own load (once per item excepted).
+      // Within a slot the weights of the rows a consumer half takes (half, half + HALVES, ...) are
+      // adjacent, so that a consumer reads them as vectors of four.
+      const int wpos = (lane % HALVES) * (THB_SS_ROWS / HALVES) + lane / HALVES;
       float batch[4];
       thb_u32 q = 0;  // stage index within the item
       if (Consumer::kRowWeights) {
 #pragma unroll
         for (int k = 0; k < 4; ++k) {
           const thb_u32 j = r0 + k * THB_SS_ROWS + lane;
-          weights[((it + k) % THB_SS_WRING) * THB_SS_ROWS + lane] = j < r1 ? Consumer::weight(cp, j) : 0.f;
+          weights[((it + k) % THB_SS_WRING) * THB_SS_ROWS + wpos] = j < r1 ? Consumer::weight(cp, j) : 0.f;
         }
 #pragma unroll
         for (int k = 0; k < 4; ++k) {
@@ -103,7 +106,7 @@ thb_strip_reduce(const __grid_constant__ CUtensorMap map_src, ThbStripGeom g, ty
         if (Consumer::kRowWeights) {
           if (q > 0 && (q & 3) == 0) {
 #pragma unroll
-            for (int k = 0; k < 4; ++k) weights[((it + k) % THB_SS_WRING) * THB_SS_ROWS + lane] = batch[k];
+            for (int k = 0; k < 4; ++k) weights[((it + k) % THB_SS_WRING) * THB_SS_ROWS + wpos] = batch[k];
 #pragma unroll
             for (int k = 0; k < 4; ++k) {
               const thb_u32 j = r + (4 + k) * THB_SS_ROWS + lane;
@@ -151,9 +154,12 @@ thb_strip_reduce(const __grid_constant__ CUtensorMap map_src, ThbStripGeom g, ty
         float w[Consumer::kRowWeights ? kRows : 1];
 #pragma unroll
         for (int k = 0; k < kRows; ++k) v[k] = tile[k * HALVES * THB_SS_COLS];  // rows half, half + HALVES, ...
-        if (Consumer::kRowWeights) {
+        if constexpr (Consumer::kRowWeights) {
 #pragma unroll
-          for (int k = 0; k < kRows; ++k) w[k] = weights[(it % THB_SS_WRING) * THB_SS_ROWS + k * HALVES + half];
+          for (int k4 = 0; k4 < kRows / 4; ++k4) {
+            const float4 t = reinterpret_cast<const float4*>(weights + (it % THB_SS_WRING) * THB_SS_ROWS + half * kRows)[k4];
+            w[4 * k4 + 0] = t.x; w[4 * k4 + 1] = t.y; w[4 * k4 + 2] = t.z; w[4 * k4 + 3] = t.w;
+          }
         }
         __syncwarp();
         if (lane == 0) thb_mbar_arrive(thb_smem_u32(&bar_empty[s]));

@@ -19,7 +19,6 @@ struct THClDeviceContext {
   void* gemm_ws = nullptr;        // split operands of the GEMM
   size_t gemm_ws_bytes = 0;
   bool gemm_pending = false;      // a GEMM was enqueued and its status word not read yet
-  bool status_pending = false;    // a kernel that reports through result[63] was enqueued since the last check
   long gemm_shape[4] = {0, 0, 0, 0};
   THClScratchSpace scratch_space{nullptr, nullptr};
 };

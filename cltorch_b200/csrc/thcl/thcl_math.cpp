@@ -201,7 +201,6 @@ static void reduce_dim(THClState* state, THClTensor* self, THClTensor* src, int 
   size_t need = thb200_reduce_dim_scratch_bytes(&vi.t, (int)dim);
   float* scratch = ensure_scratch(ctx, need);
   check_thb(thb200_reduce_dim(ctx->stream, mod, red, &vo.t, &vi.t, (int)dim, init, mparam, scratch, ctx->scratch_bytes));
-  ctx->status_pending = true;
   after_launch(state, ctx);
 }
 
@@ -228,7 +227,6 @@ static void reduce_dim_index(THClState* state, THClTensor* values_, THClTensor* 
   float* scratch = ensure_scratch(ctx, need);
   int rc = thb200_reduce_dim_index(ctx->stream, is_max, THClTensor_data(state, values), THClTensor_data(state, indices),
                                    THClTensor_data(state, in), outer, n, inner, scratch, ctx->scratch_bytes);
-  ctx->status_pending = true;
   std::string err = rc ? thb200_last_error() : "";
   THClTensor_free(state, in);
   THClTensor_freeCopyTo(state, values, values_);
@@ -686,7 +684,6 @@ static void var_dim(THClState* state, THClTensor* self, THClTensor* src, long di
   vi.set(src);
   float* scratch = ensure_scratch(ctx, thb200_var_dim_scratch_bytes(&vi.t, (int)dim));
   check_thb(thb200_var_dim(ctx->stream, &vo.t, &vi.t, (int)dim, flag, apply_sqrt, scratch, ctx->scratch_bytes));
-  ctx->status_pending = true;
   after_launch(state, ctx);
 }
 
@@ -707,7 +704,6 @@ static void scan_dim(THClState* state, THClTensor* self_, THClTensor* src, long 
   const float* sp = THClTensor_data(state, in);
   void* scratch = ensure_scratch(ctx, thb200_scan_scratch_bytes(dst, sp, outer, n, inner));
   int rc = thb200_scan(ctx->stream, op, dst, sp, outer, n, inner, scratch, ctx->scratch_bytes, nullptr);
-  ctx->status_pending = true;
   std::string err = rc ? thb200_last_error() : "";
   THClTensor_free(state, in);
   THClTensor_freeCopyTo(state, self, self_);

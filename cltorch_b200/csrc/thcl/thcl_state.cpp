@@ -126,7 +126,6 @@ void sync_stream(THClDeviceContext* ctx) {
   }
   // kernels with bounded waits other than the GEMM report through the library's status word
   // (the query costs nothing when no such kernel ran since the last one)
-  ctx->status_pending = false;
   const int st = thb200_kernel_status(ctx->stream);
   if (st != 0) raise("a kernel did not complete: a bounded wait gave up (status %d); its result is undefined", st);
 }
