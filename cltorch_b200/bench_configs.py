@@ -10,6 +10,7 @@ Inputs are seeded synthetic tensors of the configured shapes.
 from __future__ import annotations
 
 import json
+import os
 import statistics
 from pathlib import Path
 
@@ -34,11 +35,25 @@ class Timer:
         cl.setStream(torch.cuda.current_stream().cuda_stream)
         self.steps, self.warmup = steps, warmup
         self.flush = torch.empty(128 << 20, dtype=torch.float32, device="cuda")
+        # THB200_BENCH_CLEAN_FLUSH=1: read 256 MiB after the fill, so that the fill's dirty lines are written
+        # back before the timed call (shows how much of a small call's time is that write-back)
+        self.clean_flush = os.environ.get("THB200_BENCH_CLEAN_FLUSH", "0") == "1"
+        self.flush_read = torch.zeros(64 << 20, dtype=torch.float32, device="cuda") if self.clean_flush else None
         self.peak = _peak()
         self.results = {}
 
     def time(self, name, fn, nbytes=None, flops=None, setup=None):
+        """Median CUDA-event time of fn() over `steps` calls after `warmup` calls.
+
+        L2 state: a call that moves at least 1 GiB works on operands of 512 MiB or more (four times
+        the 126 MB L2) and runs back to back on them: every read is cold because the operands evict
+        themselves, and the dirty lines a call finds in L2 are the previous call's own output, as in
+        steady state. Smaller calls are preceded by a 512 MiB fill that evicts their operands; that
+        fill leaves up to 126 MB of dirty lines whose write-back falls into the timed call (measured:
+        +17 to +30 % on the 64 MiB operands of config 1), so those figures are lower bounds.
+        """
         t = self.torch
+        flush = nbytes is None or nbytes < (1 << 30)
         for _ in range(self.warmup):
             if setup:
                 setup()
@@ -47,7 +62,10 @@ class Timer:
         for _ in range(self.steps):
             if setup:
                 setup()
-            self.flush.fill_(1.0)
+            if flush:
+                self.flush.fill_(1.0)
+                if self.clean_flush:
+                    self.flush_read.sum()
             a, b = t.cuda.Event(enable_timing=True), t.cuda.Event(enable_timing=True)
             a.record()
             fn()
@@ -55,7 +73,8 @@ class Timer:
             b.synchronize()
             ms.append(a.elapsed_time(b))
         med = statistics.median(ms)
-        r = {"ms": med}
+        r = {"ms": med, "l2": ("512 MiB fill" + (" and 256 MiB read" if self.clean_flush else "") + " before each call") if flush
+             else "operands >= 4 x L2, calls back to back"}
         if nbytes is not None:
             r["GB/s"] = nbytes / (med * 1e-3) / 1e9
             r["frac_of_measured_hbm"] = r["GB/s"] / self.peak
@@ -302,5 +321,5 @@ def run(workload: str, steps: int, warmup: int) -> None:
     {"c1": c1, "c2": c2, "c3": c3, "c4": c4, "c4small": c4small, "c4batched": c4batched, "c2small": c2small, "c3small": c3small, "n1": n1, "n3": n3, "n3small": n3small}[workload](T)
     T.cl.synchronize()
     print(json.dumps({"workload": workload, "n_gpus": 1, "steps": steps, "warmup": warmup, "dtype": "f32",
-                      "data": "synthetic", "hbm_peak_gbs_measured": T.peak, "l2_flush": "512 MiB fill between iterations",
+                      "data": "synthetic", "hbm_peak_gbs_measured": T.peak, "l2_flush": "per result: 512 MiB fill before each call, or none when a call moves >= 1 GiB (operands >= 4 x L2)",
                       "results": T.results}))
