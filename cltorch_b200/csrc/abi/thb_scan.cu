@@ -2,8 +2,7 @@
 #include "thb_internal.h"
 #include "../kernels/math_policy.cuh"
 #include "../kernels/scan_strip_kernels.cuh"
-
-#include <cudaTypedefs.h>
+#include "thb_strips.h"
 
 namespace thb {
 
@@ -47,7 +46,7 @@ static ScanPlan plan_scan(const float* dst, const float* src, int64_t outer, int
     // and conversions), so it takes strips on two thirds of the SMs to beat the chunked kernels:
     // measured at 8192 columns (64 strips) 159 us against 143 us, at 16384 (128 strips) 0.35 ms
     // against 0.55 ms.
-    if (p.nchunks > 1 && ((uintptr_t)src & 15) == 0 && (inner & 3) == 0 && total * 3 >= (int64_t)sm_count() * 2 &&
+    if (p.nchunks > 1 && aligned && (inner & 3) == 0 && total * 3 >= (int64_t)sm_count() * 2 &&
         total < (int64_t(1) << 31) &&
         n >= 2 * THB_SS_ROWS && inner < (int64_t(1) << 31) && outer < (int64_t(1) << 31) &&
         n * inner * 4 < (int64_t(1) << 40) && tensor_map_encoder_ptr() != nullptr) {
@@ -63,21 +62,14 @@ static ScanPlan plan_scan(const float* dst, const float* src, int64_t outer, int
 template <class Op>
 static int run_scan_strips(cudaStream_t st, float* dst, const float* src, int64_t outer, int64_t n, int64_t inner,
                            const ScanPlan& p, int* d_status) {
-  auto enc = (PFN_cuTensorMapEncodeTiled_v12000)tensor_map_encoder_ptr();
-  CUtensorMap map;
-  cuuint64_t dims[3] = {(cuuint64_t)inner, (cuuint64_t)n, (cuuint64_t)outer};
-  cuuint64_t strides[2] = {(cuuint64_t)inner * 4, (cuuint64_t)inner * 4 * (cuuint64_t)n};
-  cuuint32_t box[3] = {THB_SS_COLS, THB_SS_ROWS, 1};
-  cuuint32_t estr[3] = {1, 1, 1};
-  CUresult r = enc(&map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, (void*)src, dims, strides, box, estr,
-                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  if (r != CUDA_SUCCESS) return fail("scan: cuTensorMapEncodeTiled failed with %d", (int)r);
+  CUtensorMap map_src, map_dst;
+  if (int rc = make_strip_map(&map_src, src, outer, n, inner, inner)) return rc;
+  if (int rc = make_strip_map(&map_dst, dst, outer, n, inner, inner)) return rc;
   THB_CUDA(cudaFuncSetAttribute(thb_scan_strips<Op>, cudaFuncAttributeMaxDynamicSharedMemorySize, THB_SS_SMEM));
   const int sms = sm_count();
   const int ctas = p.total_strips < sms ? p.total_strips : sms;
-  thb_scan_strips<Op><<<ctas, THB_SS_THREADS, THB_SS_SMEM, st>>>(map, dst, (thb_u32)n, inner, p.strips_per_outer,
-                                                                  p.total_strips, d_status ? d_status : device_status_word());
+  thb_scan_strips<Op><<<ctas, THB_SCAN_STRIP_THREADS, THB_SS_SMEM, st>>>(map_src, map_dst, (thb_u32)n, inner, p.strips_per_outer,
+                                                                          p.total_strips, d_status ? d_status : device_status_word());
   THB_CUDA(cudaGetLastError());
   return 0;
 }

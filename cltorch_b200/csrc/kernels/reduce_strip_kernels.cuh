@@ -45,7 +45,7 @@ thb_strip_reduce(const __grid_constant__ CUtensorMap map_src, ThbStripGeom g, ty
   uint64_t* bar_empty = bar_full + THB_SS_STAGES;
   volatile int* abort_flag = (volatile int*)(bar_empty + THB_SS_STAGES);
   volatile int* never_set = abort_flag + 1;
-  float* weights = (float*)(smem + THB_SS_STAGES * THB_SS_STAGE_BYTES + 256);  // [stage][row], kRowWeights only
+  float* weights = (float*)(smem + THB_SS_STAGES * THB_SS_STAGE_BYTES + 512);  // [stage][row], kRowWeights only
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   if (threadIdx.x == 0) {

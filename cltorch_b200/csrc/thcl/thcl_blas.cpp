@@ -130,15 +130,13 @@ float THClTensor_dot(THClState* state, THClTensor* self, THClTensor* src) {
   use_device(self->device);
   const long n = THClTensor_nElement(state, a);
   float* scratch = ensure_scratch(ctx, thb200_dot_scratch_bytes(n));
-  int rc = thb200_dot(ctx->stream, THClTensor_data(state, a), THClTensor_data(state, b), n, ctx->result, scratch,
+  int rc = thb200_dot(ctx->stream, THClTensor_data(state, a), THClTensor_data(state, b), n, host_result_target(ctx), scratch,
                       ctx->scratch_bytes);
   std::string err = rc ? thb200_last_error() : "";
   THClTensor_free(state, a);
   THClTensor_free(state, b);
   if (rc) raise("%s", err.c_str());
-  check_cuda(cudaMemcpyAsync(ctx->result_host, ctx->result, sizeof(float), cudaMemcpyDeviceToHost, ctx->stream), "cudaMemcpyAsync");
-  sync_stream(ctx);
-  return ctx->result_host[0];
+  return read_host_result(ctx, 0);
   THCL_END(0.f)
 }
 

@@ -14,6 +14,7 @@ struct THClDeviceContext {
   bool owns_stream = false;
   float* result = nullptr;        // 64 device floats: results of host-scalar reductions
   float* result_host = nullptr;   // pinned mirror of `result`
+  float* result_mapped = nullptr; // device address of `result_host` when kernels can write there directly, else null
   float* scratch = nullptr;       // reduction partials
   size_t scratch_bytes = 0;
   void* gemm_ws = nullptr;        // split operands of the GEMM
@@ -87,5 +88,12 @@ struct View {
 // Exactly one of `op` (built-in name) and `expr` (rewritten body) is given.
 void pointwise(THClState* state, int nt, THClTensor** tensors, const bool* read_write, const char* op,
                const char* expr, float val1, float val2, const THClTensor* point1);
+
+// Where a reduction whose result the host wants at once puts it: straight into the pinned host
+// buffer when the device can address it (the read-back is then only a stream synchronisation), else
+// into the device buffer.
+inline float* host_result_target(THClDeviceContext* ctx) { return ctx->result_mapped ? ctx->result_mapped : ctx->result; }
+// Waits for the stream and returns slot `slot` of that target.
+float read_host_result(THClDeviceContext* ctx, int slot);
 
 }  // namespace thcl

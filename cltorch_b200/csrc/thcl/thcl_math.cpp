@@ -147,14 +147,12 @@ static void reduce_all(THClState* state, THClTensor* src, int mod, int red, floa
 // of the host-scalar reductions (scratch->wrapper->copyToHost() in the reference).
 static float read_result(THClState* state, THClDeviceContext* ctx, int slot) {
   if (state->trace) printf("THCl: device -> host 1 float (reduction result)\n");
-  check_cuda(cudaMemcpyAsync(ctx->result_host + slot, ctx->result + slot, sizeof(float), cudaMemcpyDeviceToHost, ctx->stream), "cudaMemcpyAsync");
-  sync_stream(ctx);
-  return ctx->result_host[slot];
+  return read_host_result(ctx, slot);
 }
 
 static float reduce_all_host(THClState* state, THClTensor* self, int mod, int red, float init, float mparam = 0.f) {
   THClDeviceContext* ctx = context(state, self->device);
-  reduce_all(state, self, mod, red, init, mparam, nullptr, THB200_FIN_NONE, 1.f, ctx->result);
+  reduce_all(state, self, mod, red, init, mparam, nullptr, THB200_FIN_NONE, 1.f, host_result_target(ctx));
   return read_result(state, ctx, 0);
 }
 
@@ -547,14 +545,14 @@ float THClTensor_meanall(THClState* state, THClTensor* self) {
 float THClTensor_varall(THClState* state, THClTensor* self) {
   THCL_BEGIN
   THClDeviceContext* ctx = context(state, self->device);
-  moments_point(state, self, 1, ctx->result);
+  moments_point(state, self, 1, host_result_target(ctx));
   return read_result(state, ctx, 0);
   THCL_END(0.f)
 }
 float THClTensor_stdall(THClState* state, THClTensor* self) {
   THCL_BEGIN
   THClDeviceContext* ctx = context(state, self->device);
-  moments_point(state, self, 2, ctx->result);
+  moments_point(state, self, 2, host_result_target(ctx));
   return read_result(state, ctx, 0);
   THCL_END(0.f)
 }
@@ -796,7 +794,7 @@ static void dist_into(THClState* state, THClTensor* self, THClTensor* src, float
 float THClTensor_dist(THClState* state, THClTensor* self, THClTensor* src, float value) {
   THCL_BEGIN
   THClDeviceContext* ctx = context(state, self->device);
-  dist_into(state, self, src, value, ctx->result);
+  dist_into(state, self, src, value, host_result_target(ctx));
   return read_result(state, ctx, 0);
   THCL_END(0.f)
 }

@@ -74,6 +74,10 @@ THClDeviceContext* context(THClState* state, int device) {
     check_cuda(cudaMalloc((void**)&ctx->result, 64 * sizeof(float)), "cudaMalloc(result)");
     check_cuda(cudaMemset(ctx->result, 0, 64 * sizeof(float)), "cudaMemset(result)");
     check_cuda(cudaMallocHost((void**)&ctx->result_host, 64 * sizeof(float)), "cudaMallocHost(result)");
+    memset(ctx->result_host, 0, 64 * sizeof(float));
+    void* mapped = nullptr;
+    if (cudaHostGetDevicePointer(&mapped, ctx->result_host, 0) == cudaSuccess) ctx->result_mapped = (float*)mapped;
+    else cudaGetLastError();
     ctx->scratch_bytes = 4u << 20;
     check_cuda(cudaMalloc((void**)&ctx->scratch, ctx->scratch_bytes), "cudaMalloc(scratch)");
     // keep freed storage memory in the stream-ordered pool instead of returning it at every sync
@@ -128,6 +132,14 @@ void sync_stream(THClDeviceContext* ctx) {
   // (the query costs nothing when no such kernel ran since the last one)
   const int st = thb200_kernel_status(ctx->stream);
   if (st != 0) raise("a kernel did not complete: a bounded wait gave up (status %d); its result is undefined", st);
+}
+
+float read_host_result(THClDeviceContext* ctx, int slot) {
+  if (!ctx->result_mapped)
+    check_cuda(cudaMemcpyAsync(ctx->result_host + slot, ctx->result + slot, sizeof(float), cudaMemcpyDeviceToHost, ctx->stream),
+               "cudaMemcpyAsync");
+  sync_stream(ctx);
+  return ctx->result_host[slot];
 }
 
 void after_launch(THClState* state, THClDeviceContext* ctx) {
