@@ -104,6 +104,12 @@ static bool dispatch_red(int reduce, F&& f) {
 template <class Red> struct IsMoments { static const bool value = false; };
 template <bool B, bool S> struct IsMoments<RedMoments<B, S> > { static const bool value = true; };
 
+// Counters of finished blocks for the single-launch whole-tensor reductions: zero between
+// launches (the last block of a launch resets its counter). Launches take the 64 counters in
+// turn; only a few such grids (592 blocks each) can be resident at a time, so a counter is never
+// shared by two running launches.
+static unsigned int* reduce_ticket();
+
 struct ReduceAllArgs {
   cudaStream_t st;
   const thb200_tensor* in;
@@ -130,17 +136,22 @@ struct ReduceAllArgs {
   template <class Mod, class Red>
   void operator()() {
     const int blocks = (int)reduce_all_blocks(n);
+    // one launch: the block that finishes last folds the partials (a separate pass 2 only if the
+    // library's ticket counters cannot be addressed)
+    ThbFinish F;
+    F.ticket = reduce_ticket();
+    F.fin = fin; F.fparam = fparam; F.out = d_out;
     if (contig) {
       thb_reduce_all_pass1_contig<Mod, Red><<<blocks, THB_RA_THREADS, 0, st>>>(
-          in->data, n, head, init, mparam, mpoint, (typename Red::acc_t*)scratch);
+          in->data, n, head, init, mparam, mpoint, (typename Red::acc_t*)scratch, F);
     } else {
       ThbLayout L;
       fill_layout(&L, in->data, c);
       thb_reduce_all_pass1_strided<Mod, Red><<<blocks, THB_RA_THREADS, 0, st>>>(
-          L, (thb_u64)n, init, mparam, mpoint, (typename Red::acc_t*)scratch);
+          L, (thb_u64)n, init, mparam, mpoint, (typename Red::acc_t*)scratch, F);
     }
     err = cudaGetLastError();
-    if (err != cudaSuccess) return;
+    if (err != cudaSuccess || F.ticket) return;
     launch_pass2<Red>(blocks);
     err = cudaGetLastError();
   }
@@ -582,11 +593,27 @@ int thb200_reduce_dim_index(void* stream, int is_max, float* values, float* indi
 // Status word of kernels with bounded waits (strip pipelines): lives in the device image like the
 // built-in scratch below; its device address is looked up once per device.
 static __device__ int thb_status_word_storage;
+static __device__ unsigned int thb_reduce_ticket_storage[64];
 
 namespace thb {
 // Set when a launch was given the status word of the device, cleared by thb200_kernel_status: a
 // query with no such launch since the last one answers 0 without touching the GPU.
 static std::atomic<bool> g_status_word_handed_out[64];
+
+static unsigned int* reduce_ticket() {
+  static std::mutex mu;
+  static unsigned int* base[64];
+  static unsigned int next[64];
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
+  std::lock_guard<std::mutex> lock(mu);
+  if (!base[dev]) {
+    void* p = nullptr;
+    if (cudaGetSymbolAddress(&p, thb_reduce_ticket_storage) != cudaSuccess) { cudaGetLastError(); return nullptr; }
+    base[dev] = (unsigned int*)p;
+  }
+  return base[dev] + (next[dev]++ & 63u);
+}
 
 int* device_status_word() {
   static std::mutex mu;

@@ -157,11 +157,69 @@ __device__ __forceinline__ typename Red::acc_t thb_block_fold(typename Red::acc_
 #define THB_RA_BLOCKS_PER_SM 4
 #define THB_RA_MAX_BLOCKS 592
 
+#define THB_FIN_NONE 0
+#define THB_FIN_DIV 1
+#define THB_FIN_DIV_SQRT 2
+
+// The block that finishes last folds the partials of all blocks and writes the scalar, so that a
+// whole-tensor reduction is one launch. `ticket` counts the finished blocks (zero before the
+// launch; the last block puts it back to zero); ticket == nullptr: a separate pass 2 does the fold.
+struct ThbFinish {
+  unsigned int* ticket;
+  int fin;       // THB_FIN_*, ignored by the moments reductions
+  float fparam;  // divisor of the finaliser; element count for the moments
+  float* out;
+};
+
+__device__ __forceinline__ float thb_load_partial(const float* p) { return __ldcg(p); }
+__device__ __forceinline__ double thb_load_partial(const double* p) { return __ldcg(p); }
+__device__ __forceinline__ ThbMoments thb_load_partial(const ThbMoments* p) {
+  ThbMoments m;
+  m.s = __ldcg(&p->s);
+  m.q = __ldcg(&p->q);
+  return m;
+}
+template <class Red>
+__device__ __forceinline__ float thb_finish_value(Red*, typename Red::acc_t r, int fin, float fparam) {
+  typedef typename Red::acc_t acc_t;
+  if (fin == THB_FIN_DIV) r = r / (acc_t)fparam;
+  else if (fin == THB_FIN_DIV_SQRT) r = sqrt(r / (acc_t)fparam);
+  return (float)r;
+}
+template <bool B, bool S>
+__device__ __forceinline__ float thb_finish_value(RedMoments<B, S>*, ThbMoments r, int, float n) {
+  return RedMoments<B, S>::result(r, n);
+}
+
+// Called by every thread of every block after the block's partial is in partials[blockIdx.x].
+// The fold order is fixed (thread t takes partials t, t + blockDim.x, ...; then the block fold), so
+// the result does not depend on which block happens to come last.
+template <class Red>
+__device__ __forceinline__ void thb_finish_last_block(const ThbFinish& F, const typename Red::acc_t* partials, float init,
+                                                      typename Red::acc_t* smem) {
+  typedef typename Red::acc_t acc_t;
+  __shared__ int is_last;
+  if (threadIdx.x == 0) {
+    __threadfence();  // this block's partial before its ticket
+    is_last = atomicAdd(F.ticket, 1u) == gridDim.x - 1;
+  }
+  __syncthreads();
+  if (!is_last) return;
+  __threadfence();  // every other block's partial after its ticket
+  acc_t r = (acc_t)init;
+  for (unsigned int i = threadIdx.x; i < gridDim.x; i += blockDim.x) r = Red::apply(r, thb_load_partial(partials + i));
+  r = thb_block_fold<Red>(r, (acc_t)init, smem);
+  if (threadIdx.x == 0) {
+    F.out[0] = thb_finish_value((Red*)nullptr, r, F.fin, F.fparam);
+    *F.ticket = 0;
+  }
+}
+
 // Pass 1 over one contiguous run. `head` as in thb_apply_contig.
 template <class Mod, class Red>
 __global__ void __launch_bounds__(THB_RA_THREADS, THB_RA_BLOCKS_PER_SM)
 thb_reduce_all_pass1_contig(const float* in, thb_i64 n, int head, float init, float mparam,
-                            const float* mpoint, typename Red::acc_t* partials) {
+                            const float* mpoint, typename Red::acc_t* partials, ThbFinish F) {
   typedef typename Red::acc_t acc_t;
   __shared__ acc_t smem[32];
   const float mp = mpoint ? *mpoint : 0.f;
@@ -203,13 +261,14 @@ thb_reduce_all_pass1_contig(const float* in, thb_i64 n, int head, float init, fl
   acc_t r = Red::apply(Red::apply(acc[0], acc[1]), Red::apply(acc[2], acc[3]));
   r = thb_block_fold<Red>(r, (acc_t)init, smem);
   if (threadIdx.x == 0) partials[blockIdx.x] = r;
+  if (F.ticket) thb_finish_last_block<Red>(F, partials, init, smem);
 }
 
 // Pass 1 over any strided layout (32-bit index math).
 template <class Mod, class Red>
 __global__ void __launch_bounds__(THB_RA_THREADS)
 thb_reduce_all_pass1_strided(ThbLayout L, thb_u64 n, float init, float mparam, const float* mpoint,
-                             typename Red::acc_t* partials) {
+                             typename Red::acc_t* partials, ThbFinish F) {
   typedef typename Red::acc_t acc_t;
   __shared__ acc_t smem[32];
   const float mp = mpoint ? *mpoint : 0.f;
@@ -231,11 +290,9 @@ thb_reduce_all_pass1_strided(ThbLayout L, thb_u64 n, float init, float mparam, c
   }
   acc = thb_block_fold<Red>(acc, (acc_t)init, smem);
   if (threadIdx.x == 0) partials[blockIdx.x] = acc;
+  if (F.ticket) thb_finish_last_block<Red>(F, partials, init, smem);
 }
 
-#define THB_FIN_NONE 0
-#define THB_FIN_DIV 1
-#define THB_FIN_DIV_SQRT 2
 
 // Pass 2: one block folds the pass-1 partials and writes the finished scalar.
 template <class Red>

@@ -73,7 +73,7 @@ class GlobalSum:
         self.buf, self.storage = self.ops.new_buffer(self.world + 1)
         self.mine = self.ops.slot(self.storage, self.rank)
         self.result = self.ops.slot(self.storage, self.world)
-        self.launches_per_call = 3  # reduce pass 1, pass 2, fold
+        self.launches_per_call = 2  # whole-shard reduction (one launch: its last block folds the partials), fold of the per-GPU sums
 
     def __call__(self, x):
         self.ops.local_sum_into(self.mine, x)
