@@ -25,10 +25,15 @@ int thb200_dot(void* stream, const float* a, const float* b, int64_t n, float* d
   if (blocks > THB_RA_MAX_BLOCKS) blocks = THB_RA_MAX_BLOCKS;
   if (blocks < 1) blocks = 1;
   const int vec_ok = ((((uintptr_t)a) | ((uintptr_t)b)) & 15) == 0;
-  thb_dot_pass1<<<(unsigned)blocks, THB_RA_THREADS, 0, st>>>(a, b, n, vec_ok, (double*)scratch);
+  ThbFinish F;
+  F.ticket = reduce_ticket();
+  F.fin = THB_FIN_NONE; F.fparam = 1.f; F.out = d_out;
+  thb_dot_pass1<<<(unsigned)blocks, THB_RA_THREADS, 0, st>>>(a, b, n, vec_ok, (double*)scratch, F);
   THB_CUDA(cudaGetLastError());
-  thb_reduce_all_pass2<RedAdd><<<1, 1024, 0, st>>>((const double*)scratch, (int)blocks, 0.f, THB_FIN_NONE, 1.f, d_out);
-  THB_CUDA(cudaGetLastError());
+  if (!F.ticket) {
+    thb_reduce_all_pass2<RedAdd><<<1, 1024, 0, st>>>((const double*)scratch, (int)blocks, 0.f, THB_FIN_NONE, 1.f, d_out);
+    THB_CUDA(cudaGetLastError());
+  }
   return 0;
 }
 

@@ -38,6 +38,12 @@ constexpr int64_t kMaxGridBlocks = 0x7fffffff;
 // so that the library does not link libcuda; nullptr if the driver does not offer it.
 void* tensor_map_encoder_ptr();
 
+// Counter of finished blocks for a single-launch whole-tensor reduction (ThbFinish::ticket): zero
+// between launches (the last block of a launch resets it). Launches take the library's 64 counters
+// per device in turn; only a few such grids (592 blocks each) can be resident at a time, so a
+// counter is never shared by two running launches. nullptr if the counters cannot be addressed.
+unsigned int* reduce_ticket();
+
 // Device int of the current device into which kernels with bounded waits store a non-zero
 // code when a wait gives up (read and cleared by thb200_kernel_status); nullptr on failure.
 int* device_status_word();

@@ -104,12 +104,6 @@ static bool dispatch_red(int reduce, F&& f) {
 template <class Red> struct IsMoments { static const bool value = false; };
 template <bool B, bool S> struct IsMoments<RedMoments<B, S> > { static const bool value = true; };
 
-// Counters of finished blocks for the single-launch whole-tensor reductions: zero between
-// launches (the last block of a launch resets its counter). Launches take the 64 counters in
-// turn; only a few such grids (592 blocks each) can be resident at a time, so a counter is never
-// shared by two running launches.
-static unsigned int* reduce_ticket();
-
 struct ReduceAllArgs {
   cudaStream_t st;
   const thb200_tensor* in;
@@ -600,7 +594,7 @@ namespace thb {
 // query with no such launch since the last one answers 0 without touching the GPU.
 static std::atomic<bool> g_status_word_handed_out[64];
 
-static unsigned int* reduce_ticket() {
+unsigned int* reduce_ticket() {
   static std::mutex mu;
   static unsigned int* base[64];
   static unsigned int next[64];

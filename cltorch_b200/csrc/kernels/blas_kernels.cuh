@@ -8,9 +8,10 @@
 #pragma once
 #include "reduce_strip_kernels.cuh"
 
-// partial[b] = sum over this block's share of a[i] * b[i]; folded by thb_reduce_all_pass2<RedAdd>.
+// partial[b] = sum over this block's share of a[i] * b[i]; the block that finishes last folds the
+// partials (F.ticket), or thb_reduce_all_pass2<RedAdd> does when there is no ticket.
 __global__ void __launch_bounds__(THB_RA_THREADS, THB_RA_BLOCKS_PER_SM)
-thb_dot_pass1(const float* a, const float* b, thb_i64 n, int vec_ok, double* partials) {
+thb_dot_pass1(const float* a, const float* b, thb_i64 n, int vec_ok, double* partials, ThbFinish F) {
   __shared__ double smem[32];
   double acc[4] = {0.0, 0.0, 0.0, 0.0};
   if (vec_ok) {
@@ -47,6 +48,7 @@ thb_dot_pass1(const float* a, const float* b, thb_i64 n, int vec_ok, double* par
   double r = (acc[0] + acc[1]) + (acc[2] + acc[3]);
   r = thb_block_fold<RedAdd>(r, 0.0, smem);
   if (threadIdx.x == 0) partials[blockIdx.x] = r;
+  if (F.ticket) thb_finish_last_block<RedAdd>(F, partials, 0.f, smem);
 }
 
 // y[j] = alpha * sum_i A[i + j*lda] * x[i*incx] + beta * y[j*incy], j < n: every
