@@ -73,6 +73,7 @@ class GlobalSum:
         self.buf, self.storage = self.ops.new_buffer(self.world + 1)
         self.mine = self.ops.slot(self.storage, self.rank)
         self.result = self.ops.slot(self.storage, self.world)
+        self.exchange = "all-gather of one float per rank (torch.distributed), fold in rank order" if self.world > 1 else "none (one GPU)"
         self.launches_per_call = 2  # whole-shard reduction (one launch: its last block folds the partials), fold of the per-GPU sums
 
     def __call__(self, x):

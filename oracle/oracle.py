@@ -66,6 +66,7 @@ def lib() -> C.CDLL:
         L.orc_time_axpb.argtypes = [C.c_void_p, C.c_int64, C.c_float, C.c_float]
         L.orc_time_sqrt.argtypes = [C.c_void_p, C.c_int64]
         L.orc_time_mulc.argtypes = [C.c_void_p, C.c_int64, C.c_float]
+        L.orc_time_touch.argtypes = [C.c_void_p, C.c_int64]
         _lib = L
     return _lib
 

@@ -476,26 +476,72 @@ void orc_addmm(float* r, int64_t r_s0, int64_t r_s1, float beta, const float* t,
 }
 
 /* ---- fp32 variants for timing the CPU path (contiguous data, all cores) --------
- * The same arithmetic as a Torch7 FloatTensor would do it: fp32 accumulate. */
-void orc_time_map2_sqrt(float* x, const float* y, const float* z, int64_t n) {
-#pragma omp parallel for schedule(static)
+ * The arithmetic of a Torch7 FloatTensor: fp32 element operations (two roundings for a*x+b,
+ * -ffp-contract=off), sums accumulated in double (TH's accreal for float). The library is built on
+ * one host and timed on another, so the inner loops are compiled once per instruction set
+ * (target_clones: baseline, AVX2, AVX-512) and the loader picks the widest the running CPU has;
+ * that stands in for -march=native. Each thread works on one contiguous range (the ranges also
+ * decide which NUMA node first touches a page, see orc_time_touch). */
+#if defined(__x86_64__) && defined(__GNUC__) && !defined(__clang__)
+#define ORC_CLONES __attribute__((target_clones("default", "avx2", "avx512f"), noinline))
+#else
+#define ORC_CLONES __attribute__((noinline))
+#endif
+
+ORC_CLONES static void k_map2_sqrt(float* restrict x, const float* restrict y, const float* restrict z, int64_t n) {
   for (int64_t i = 0; i < n; ++i) x[i] = sqrtf(1000 * x[i] + y[i] * 10 + z[i] * z[i]);
 }
-void orc_time_axpb(float* x, int64_t n, float a, float b) {
-#pragma omp parallel for schedule(static)
+ORC_CLONES static void k_axpb(float* restrict x, int64_t n, float a, float b) {
   for (int64_t i = 0; i < n; ++i) x[i] = x[i] * a + b;
 }
-void orc_time_sqrt(float* x, int64_t n) {
-#pragma omp parallel for schedule(static)
+ORC_CLONES static void k_sqrt(float* restrict x, int64_t n) {
   for (int64_t i = 0; i < n; ++i) x[i] = sqrtf(x[i]);
 }
-void orc_time_mulc(float* x, int64_t n, float a) {
-#pragma omp parallel for schedule(static)
+ORC_CLONES static void k_mulc(float* restrict x, int64_t n, float a) {
   for (int64_t i = 0; i < n; ++i) x[i] *= a;
+}
+/* 16 independent double accumulators so that the additions vectorise and pipeline; folded in a fixed order */
+ORC_CLONES static double k_sum(const float* restrict x, int64_t n) {
+  double acc[16] = {0};
+  int64_t i = 0;
+  for (; i + 16 <= n; i += 16)
+    for (int k = 0; k < 16; ++k) acc[k] += (double)x[i + k];
+  double total = 0.0;
+  for (int k = 0; k < 16; ++k) total += acc[k];
+  for (; i < n; ++i) total += (double)x[i];
+  return total;
+}
+
+#define ORC_RANGE(n)                                                     \
+  int64_t t_ = omp_get_thread_num(), T_ = omp_get_num_threads();         \
+  int64_t lo = (n) / T_ * t_ + ((n) % T_ < t_ ? (n) % T_ : t_);          \
+  int64_t len = (n) / T_ + (t_ < (n) % T_ ? 1 : 0)
+
+/* writes zeros with the same thread-to-range mapping as the loops below, so that on a multi-socket
+ * host every page is first touched (and placed) by the thread that will work on it */
+void orc_time_touch(float* x, int64_t n) {
+#pragma omp parallel
+  { ORC_RANGE(n); for (int64_t i = 0; i < len; ++i) x[lo + i] = 0.0f; }
+}
+void orc_time_map2_sqrt(float* x, const float* y, const float* z, int64_t n) {
+#pragma omp parallel
+  { ORC_RANGE(n); k_map2_sqrt(x + lo, y + lo, z + lo, len); }
+}
+void orc_time_axpb(float* x, int64_t n, float a, float b) {
+#pragma omp parallel
+  { ORC_RANGE(n); k_axpb(x + lo, len, a, b); }
+}
+void orc_time_sqrt(float* x, int64_t n) {
+#pragma omp parallel
+  { ORC_RANGE(n); k_sqrt(x + lo, len); }
+}
+void orc_time_mulc(float* x, int64_t n, float a) {
+#pragma omp parallel
+  { ORC_RANGE(n); k_mulc(x + lo, len, a); }
 }
 double orc_time_sum(const float* x, int64_t n) {
   double total = 0.0;
-#pragma omp parallel for schedule(static) reduction(+ : total)
-  for (int64_t i = 0; i < n; ++i) total += x[i];
+#pragma omp parallel reduction(+ : total)
+  { ORC_RANGE(n); total += k_sum(x + lo, len); }
   return total;
 }
