@@ -417,24 +417,34 @@ thb_apply_tile2d_v4(ThbTile2d P, ThbScalars s) {
 }
 
 // ---------------------------------------------------------------------------
-// Whether an operator body reads *out before overwriting it: it does unless
-// "*out" occurs exactly once and is directly followed by a plain '='.
+// Whether a kernel must load *out before running an operator body. It need not
+// only when the body is ONE unconditional assignment to *out: the text begins
+// with "*out" or "(*out)" followed by a plain '=', "*out" occurs nowhere else,
+// and there is no second statement and no block (no ';' before the end, no
+// '{'). Anything else - "if (...) *out = ...", a loop, "*out += ..." - may
+// leave an element as it was or read it, so the old value has to be there.
 // ---------------------------------------------------------------------------
+__host__ __device__ constexpr bool thb_is_ident_char(char c) {
+  return (c >= 'a' && c <= 'z') || (c >= 'A' && c <= 'Z') || (c >= '0' && c <= '9') || c == '_';
+}
 __host__ __device__ constexpr bool thb_body_reads_out(const char* s) {
   int count = 0;
-  bool plainAssign = false;
   for (int i = 0; s[i]; ++i) {
-    if (s[i] == '*' && s[i + 1] == 'o' && s[i + 2] == 'u' && s[i + 3] == 't') {
-      char nx = s[i + 4];
-      if ((nx >= 'a' && nx <= 'z') || (nx >= 'A' && nx <= 'Z') || (nx >= '0' && nx <= '9') || nx == '_')
-        continue;  // a longer identifier
-      ++count;
-      int j = i + 4;
-      while (s[j] == ' ' || s[j] == ')') ++j;
-      plainAssign = (s[j] == '=' && s[j + 1] != '=');
+    if (s[i] == '*' && s[i + 1] == 'o' && s[i + 2] == 'u' && s[i + 3] == 't' && !thb_is_ident_char(s[i + 4])) ++count;
+    if (s[i] == '{') return true;
+    if (s[i] == ';') {  // only white space may follow the one statement
+      int j = i + 1;
+      while (s[j] == ' ' || s[j] == '\t' || s[j] == '\n' || s[j] == ';') ++j;
+      if (s[j]) return true;
     }
   }
-  return !(count == 1 && plainAssign);
+  if (count != 1) return true;
+  int i = 0;
+  while (s[i] == ' ' || s[i] == '\t' || s[i] == '\n' || s[i] == '(') ++i;
+  if (!(s[i] == '*' && s[i + 1] == 'o' && s[i + 2] == 'u' && s[i + 3] == 't' && !thb_is_ident_char(s[i + 4]))) return true;
+  i += 4;
+  while (s[i] == ' ' || s[i] == ')') ++i;
+  return !(s[i] == '=' && s[i + 1] != '=');
 }
 
 // OpenCL spellings that the reference's operator strings use and CUDA lacks.

@@ -378,6 +378,44 @@ def test_expression_on_strided_operands_and_identifiers():
     assert O.ulp_diff(out.float(), want).max() <= 2
 
 
+@pytest.mark.parametrize("expr", ["if (y > 0) x = y", "if (y > 0) { x = y; }", "for (int i = 0; i < 2; ++i) if (y > i) x = y + i"])
+def test_expression_with_conditional_store_keeps_other_elements(expr):
+    """A body that stores only under a condition must leave every other element as it was (the reference
+    hands the operator a pointer into the tensor). Contiguous, stride-2, small transposed (tile kernel) and
+    large transposed (TMA tile kernel) layouts."""
+    import cltorch_b200 as cl
+
+    def want(x, y):
+        if expr.startswith("for"):
+            out = np.where(y > 0, y, x)
+            return np.where(y > 1, y + np.float32(1), out).astype(np.float32)
+        return np.where(y > 0, y, x).astype(np.float32)
+
+    g = np.random.Generator(np.random.PCG64(77))
+    # contiguous, with a ragged length so that the scalar head / tail run too
+    x, y = (g.uniform(-2, 2, 100003).astype(np.float32) for _ in range(2))
+    got = cl.ClTensor(x).map_on_gpu(cl.ClTensor(y), expr).float()
+    assert np.array_equal(got, want(x, y)), "contiguous"
+    # every second element of the destination; the elements in between must not change either
+    base = g.uniform(-2, 2, 20000).astype(np.float32)
+    full = cl.ClTensor(base)
+    view = cl.ClTensor(full.storage(), 1, [10000], [2])
+    yy = g.uniform(-2, 2, 10000).astype(np.float32)
+    view.map_on_gpu(cl.ClTensor(yy), expr)
+    expect = base.copy()
+    expect[::2] = want(base[::2], yy)
+    assert np.array_equal(full.float(), expect), "stride 2"
+    # transposed source: a small matrix and one large enough for a tile per SM
+    for rows, cols in ((96, 80), (1024, 1536)):
+        xs = g.uniform(-2, 2, (rows, cols)).astype(np.float32)
+        ys = g.uniform(-2, 2, (cols, rows)).astype(np.float32)
+        got = cl.ClTensor(xs).map_on_gpu(cl.ClTensor(ys).t(), expr).float()
+        assert np.array_equal(got, want(xs, ys.T)), f"transposed {rows}x{cols}"
+        out = cl.ClTensor(ys.copy())
+        out.t().map_on_gpu(cl.ClTensor(xs), expr)                # transposed destination
+        assert np.array_equal(out.float(), want(ys.T, xs).T), f"transposed destination {rows}x{cols}"
+
+
 def test_expression_errors_are_reported():
     import cltorch_b200 as cl
     a = cl.ClTensor(np.ones(4, np.float32))
