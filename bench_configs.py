@@ -201,6 +201,8 @@ def c1(T):
     n = 4096 * 4096
     X, Y, Z = (cl.ClTensor(_uniform(g, (4096, 4096), 0, 1)) for _ in range(3))
     S = cl.ClTensor()
+    one = cl.ClTensor(1)
+    T.time("timing floor: fill of a 1-element tensor (launch + the two event records)", lambda: one.fill(0.0))
     T.time("map2 x = sqrt(1000*x + y*10 + z*z)", lambda: X.map2_on_gpu(Y, Z, "x = sqrt(1000*x + y*10 + z*z)"), 16 * n,
            also_dirty=True)
     T.time("sum -> point tensor", lambda: S.sum(X), 4 * n, also_dirty=True)
@@ -213,6 +215,29 @@ def c1(T):
         S.sum(X)
         X.div(S)
     T.time("sequence map2 + sum + div (point tensor)", chain, 28 * n, also_dirty=True)
+
+    def chain_host():
+        X.map2_on_gpu(Y, Z, "x = sqrt(1000*x + y*10 + z*z)")
+        X.div(X.sum())
+    T.time("sequence map2 + s = sum (host float) + div(s), as the configuration is worded", chain_host, 28 * n)
+
+    # The same operations in steady state: eight sets of tensors (1.5 GiB, twelve times L2) taken in
+    # turn and launched back to back, so every operand comes from HBM and the launch and event
+    # overheads of the single calls above (the timing floor) are spread over eight calls.
+    sets = [(X, Y, Z)] + [tuple(cl.ClTensor(_uniform(g, (4096, 4096), 0, 1)) for _ in range(3)) for _ in range(7)]
+    pts = [cl.ClTensor() for _ in range(8)]
+    T.time("8 x map2 on eight tensor sets, back to back", lambda: [x.map2_on_gpu(y, z, "x = sqrt(1000*x + y*10 + z*z)") for x, y, z in sets],
+           8 * 16 * n)
+    T.time("8 x sum -> point tensor on eight tensors, back to back", lambda: [p.sum(s[0]) for p, s in zip(pts, sets)], 8 * 4 * n)
+    T.time("8 x div by point tensor on eight tensors, back to back", lambda: [s[0].div(p) for p, s in zip(pts, sets)], 8 * 8 * n,
+           setup=lambda: [s[0].fill(1.0) and p.sum(s[0]) for p, s in zip(pts, sets)])
+
+    def chains():
+        for p, (x, y, z) in zip(pts, sets):
+            x.map2_on_gpu(y, z, "x = sqrt(1000*x + y*10 + z*z)")
+            p.sum(x)
+            x.div(p)
+    T.time("8 x sequence map2 + sum + div (point tensor), back to back", chains, 8 * 28 * n)
 
 
 def c2(T):

@@ -111,6 +111,8 @@ PROTOTYPES = {
     "THClState_setDevice": (v, [S, i]), "THClState_getDevice": (i, [S]),
     "THClState_getDeviceScratchSpace": (C.POINTER(THClScratchSpace), [S, i, i]),
     "THClState_getDeviceScratchSpaceSize": (C.c_size_t, [S, i]),
+    "THClState_getCurrentDeviceScratchSpace": (C.POINTER(THClScratchSpace), [S]),
+    "THClState_getCurrentDeviceScratchSpaceSize": (C.c_size_t, [S]),
     "THClSynchronize": (v, [S]), "THClState_getStream": (C.c_void_p, [S, i]),
     "THClState_setStream": (v, [S, i, C.c_void_p]),
     "THClSetErrorHandler": (v, [ERROR_HANDLER, C.c_void_p]), "THClLastError": (cp, []), "THClClearError": (v, []),
@@ -134,6 +136,7 @@ PROTOTYPES = {
     "THClTensor_size": (l, [S, T, i]), "THClTensor_stride": (l, [S, T, i]),
     "THClTensor_newSizeOf": (LS, [S, T]), "THClTensor_newStrideOf": (LS, [S, T]),
     "THClTensor_data": (c_float_p, [S, T]),
+    "THClTensor_wrapper": (c_float_p, [S, T]),
     "THClTensor_setFlag": (v, [S, T, C.c_char]), "THClTensor_clearFlag": (v, [S, T, C.c_char]),
     "THClTensor_new": (T, [S]), "THClTensor_newv2": (T, [S, i]), "THClTensor_newWithTensor": (T, [S, T]),
     "THClTensor_newWithStorage": (T, [S, i, ST, l, LS, LS]),
@@ -230,6 +233,7 @@ PROTOTYPES = {
     "thb200_reduce_all": (i, [C.c_void_p, i, i, C.POINTER(thb200_tensor), f, f, C.c_void_p, i, f, C.c_void_p,
                               C.c_void_p, C.c_size_t]),
     "thb200_kernel_status": (i, [C.c_void_p]),
+    "thb200_selftest_wait_expiry": (i, [C.c_void_p, C.c_uint64, i]),
     "thb200_reduce_dim_scratch_bytes": (C.c_size_t, [C.POINTER(thb200_tensor), i]),
     "thb200_reduce_dim": (i, [C.c_void_p, i, i, C.POINTER(thb200_tensor), C.POINTER(thb200_tensor), i, f, f,
                               C.c_void_p, C.c_size_t]),

@@ -3,6 +3,7 @@
 #include <cudaTypedefs.h>
 
 #include "thb_internal.h"
+#include <unordered_map>
 #include "../kernels/math_policy.cuh"
 #include "../kernels/apply_kernels.cuh"
 #include "../kernels/apply_tma_kernels.cuh"
@@ -63,7 +64,7 @@ static int launch_tile_tma(const ApplyKernels& k, cudaStream_t st, int nt, const
   for (int i = nt; i < 3; ++i) maps[i] = maps[0];
   ThbTileTma P;
   P.R = (uint32_t)R; P.C = (uint32_t)C; P.tilesC = (uint32_t)tilesC; P.ntiles = (uint32_t)ntiles;
-  P.colmajor = T.colmajor; P.status = device_status_word();
+  P.colmajor = T.colmajor; P.status = device_status_word(STATUS_TILE_APPLY);
   P.tilesR = (uint32_t)((R + THB_AT_TILE - 1) / THB_AT_TILE);
   P.band = 8;  // measured on 8192 x 8192: 0.91-0.95 of the copy rate with bands of 4-8 tile rows, 0.84-0.90 row by row
   const size_t smem = THB_AT_SMEM(nt);
@@ -245,9 +246,14 @@ extern "C" {
 
 int thb200_op_code(const char* name) {
   if (!name) return -1;
-  for (int i = 0; i < thb::builtin_op_count(); ++i)
-    if (strcmp(thb::builtin_op(i)->name, name) == 0) return i;
-  return -1;
+  // name -> code, built on the first call (the operator table is constant)
+  static const std::unordered_map<std::string, int>* table = [] {
+    auto* m = new std::unordered_map<std::string, int>();
+    for (int i = 0; i < thb::builtin_op_count(); ++i) m->emplace(thb::builtin_op(i)->name, i);
+    return m;
+  }();
+  auto it = table->find(name);
+  return it == table->end() ? -1 : it->second;
 }
 
 int thb200_op_arity(int op) {

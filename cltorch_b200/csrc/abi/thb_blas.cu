@@ -104,7 +104,7 @@ int thb200_gemv(void* stream, char trans, int64_t m, int64_t n, float alpha, con
     const int64_t items = (int64_t)sp.total_strips * sp.nchunks;
     const unsigned ctas = (unsigned)(items < sms ? items : sms);
     thb_strip_reduce<ThbGemvConsumer, kGemvHalves><<<ctas, 32 + 128 * kGemvHalves, THB_SS_SMEM, st>>>(map, g, cp,
-                                                                                                      device_status_word());
+                                                                                                      device_status_word(STATUS_STRIP_GEMV));
     THB_CUDA(cudaGetLastError());
     thb_gemv_n_fold<<<(unsigned)bxf, THB_RD_THREADS, 0, st>>>((const double*)scratch, y, incy, (thb_u32)m, nparts, alpha, beta);
     THB_CUDA(cudaGetLastError());

@@ -44,9 +44,20 @@ void* tensor_map_encoder_ptr();
 // counter is never shared by two running launches. nullptr if the counters cannot be addressed.
 unsigned int* reduce_ticket();
 
-// Device int of the current device into which kernels with bounded waits store a non-zero
-// code when a wait gives up (read and cleared by thb200_kernel_status); nullptr on failure.
-int* device_status_word();
+// Device int of the current device into which the kernels of one family with bounded waits store
+// a non-zero code when a wait gives up (read and cleared by thb200_kernel_status, which reports
+// family and code); nullptr on failure. One word per family, so that a report names the kind of
+// launch that gave up.
+enum StatusFamily {
+  STATUS_STRIP_REDUCE = 1,   // sum / prod / moments over a strided dimension (TMA strips)
+  STATUS_STRIP_ARGREDUCE = 2,  // max / min with indices over a strided dimension
+  STATUS_STRIP_SCAN = 3,     // cumsum / cumprod over a strided dimension
+  STATUS_STRIP_GEMV = 4,     // matrix-vector product over the columns of a row-major matrix
+  STATUS_TILE_APPLY = 5,     // pointwise operators on large transposed operands (TMA tiles)
+  STATUS_SELFTEST = 6,       // thb200_selftest_wait_expiry
+  STATUS_FAMILIES = 8
+};
+int* device_status_word(int family);
 
 // Number of chunks to cut a reduced / scanned dimension of `rsize` elements into when only
 // `threads` worker threads (blocks of 256, `blocks_per_sm` resident) exist per chunk: as many

@@ -35,10 +35,13 @@ static void fill_layout(ThbLayout* L, float* data, const Collapsed& c) {
 
 static int64_t reduce_all_blocks(int64_t n) {
   int64_t per_block = (int64_t)THB_RA_THREADS * THB_RA_UNROLL * 4;
-  int64_t blocks = (n + per_block - 1) / per_block;
-  if (blocks > THB_RA_MAX_BLOCKS) blocks = THB_RA_MAX_BLOCKS;
-  if (blocks < 1) blocks = 1;
-  return blocks;
+  int64_t pieces = (n + per_block - 1) / per_block;
+  if (pieces < 1) pieces = 1;
+  // every block takes the same number of pieces (a function of n alone, so the summation order
+  // stays independent of the device): 2048 pieces run as 512 blocks x 4 rather than 592 blocks of
+  // which three quarters take 3 and the rest 4
+  const int64_t sweeps = (pieces + THB_RA_MAX_BLOCKS - 1) / THB_RA_MAX_BLOCKS;
+  return (pieces + sweeps - 1) / sweeps;
 }
 
 // Calls f.template operator()<Mod, Red>() for the pair the reference's
@@ -257,7 +260,7 @@ struct ReduceDimArgs {
       const unsigned ctas = (unsigned)(items < sms ? items : sms);
       err = cudaFuncSetAttribute(thb_strip_reduce<Cons, kStripHalves>, cudaFuncAttributeMaxDynamicSharedMemorySize, THB_SS_SMEM);
       if (err != cudaSuccess) return;
-      thb_strip_reduce<Cons, kStripHalves><<<ctas, 32 + 128 * kStripHalves, THB_SS_SMEM, st>>>(map, g, cp, device_status_word());
+      thb_strip_reduce<Cons, kStripHalves><<<ctas, 32 + 128 * kStripHalves, THB_SS_SMEM, st>>>(map, g, cp, device_status_word(STATUS_STRIP_REDUCE));
     } else if (vec4) {
       uint64_t bq = ((uint64_t)(nslices >> 2) + THB_RD_THREADS - 1) / THB_RD_THREADS;
       if (bq > 65535u * 16u) bq = 65535u * 16u;
@@ -343,7 +346,7 @@ static int argreduce(cudaStream_t st, float* values, float* indices, const float
     THB_CUDA(cudaFuncSetAttribute(thb_strip_reduce<Cons, 1>, cudaFuncAttributeMaxDynamicSharedMemorySize, THB_SS_SMEM));
     const int64_t items = (int64_t)sp.total_strips * sp.nchunks;
     const unsigned ctas = (unsigned)(items < sms ? items : sms);
-    thb_strip_reduce<Cons, 1><<<ctas, THB_SS_THREADS, THB_SS_SMEM, st>>>(map, g, cp, device_status_word());
+    thb_strip_reduce<Cons, 1><<<ctas, THB_SS_THREADS, THB_SS_SMEM, st>>>(map, g, cp, device_status_word(STATUS_STRIP_ARGREDUCE));
     THB_CUDA(cudaGetLastError());
     if (sp.nchunks > 1) {
       if (sp.nchunks >= 8) {
@@ -586,7 +589,7 @@ int thb200_reduce_dim_index(void* stream, int is_max, float* values, float* indi
 // asked once per device with that device current.
 // Status word of kernels with bounded waits (strip pipelines): lives in the device image like the
 // built-in scratch below; its device address is looked up once per device.
-static __device__ int thb_status_word_storage;
+static __device__ int thb_status_word_storage[thb::STATUS_FAMILIES];
 static __device__ unsigned int thb_reduce_ticket_storage[64];
 
 namespace thb {
@@ -609,10 +612,11 @@ unsigned int* reduce_ticket() {
   return base[dev] + (next[dev]++ & 63u);
 }
 
-int* device_status_word() {
+int* device_status_word(int family) {
   static std::mutex mu;
   static int* addr[64];
   int dev = 0;
+  if (family <= 0 || family >= STATUS_FAMILIES) return nullptr;
   if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
   g_status_word_handed_out[dev].store(true, std::memory_order_relaxed);
   std::lock_guard<std::mutex> lock(mu);
@@ -621,26 +625,73 @@ int* device_status_word() {
     if (cudaGetSymbolAddress(&p, thb_status_word_storage) != cudaSuccess) return nullptr;
     addr[dev] = (int*)p;
   }
-  return addr[dev];
+  return addr[dev] + family;
+}
+
+// Puts the 64 ticket counters of the current device back to zero (after a launch that may not
+// have run to its end, a counter could otherwise stay non-zero and the next reduction that draws
+// it would never write its result).
+void reset_reduce_tickets(cudaStream_t st) {
+  void* p = nullptr;
+  if (cudaGetSymbolAddress(&p, thb_reduce_ticket_storage) == cudaSuccess) cudaMemsetAsync(p, 0, sizeof(unsigned int) * 64, st);
+  else cudaGetLastError();
 }
 }  // namespace thb
+
+// One warp waits on a shared-memory barrier that nothing ever arrives on, with the given limit;
+// when the wait gives up it stores `code` in the self-test status word, exactly as the pipelines do.
+static __global__ void thb_selftest_wait_kernel(unsigned long long limit_ns, int code, int* status) {
+  __shared__ uint64_t bar;
+  __shared__ int abort_flag;
+  if (threadIdx.x == 0) {
+    thb_mbar_init(thb_smem_u32(&bar), 1);
+    abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    if (!thb_mbar_wait_ns(thb_smem_u32(&bar), 0, &abort_flag, limit_ns)) {
+      abort_flag = 1;
+      atomicCAS(status, 0, code);
+    }
+  }
+  __syncthreads();
+}
+
+extern "C" int thb200_selftest_wait_expiry(void* stream, uint64_t limit_ns, int code) {
+  if (limit_ns == 0 || limit_ns > 1000000000ull) return thb::fail("selftest: the limit must be between 1 ns and 1 s");
+  if (code <= 0 || code > 255) return thb::fail("selftest: the code must be between 1 and 255");
+  int* w = thb::device_status_word(thb::STATUS_SELFTEST);
+  if (!w) return thb::fail("selftest: the status word is not available");
+  thb_selftest_wait_kernel<<<1, 32, 0, (cudaStream_t)stream>>>((unsigned long long)limit_ns, code, w);
+  THB_CUDA(cudaGetLastError());
+  return 0;
+}
 
 extern "C" int thb200_kernel_status(void* stream) {
   int dev = 0;
   if (cudaGetDevice(&dev) == cudaSuccess && dev >= 0 && dev < 64 &&
       !thb::g_status_word_handed_out[dev].exchange(false, std::memory_order_relaxed))
     return 0;  // no kernel with bounded waits was launched since the last query
-  int* w = thb::device_status_word();
+  int* w = thb::device_status_word(1);
   if (!w) { thb::fail("kernel_status: the status word is not available"); return -1; }
+  w -= 1;  // the whole array
   if (dev >= 0 && dev < 64) thb::g_status_word_handed_out[dev].store(false, std::memory_order_relaxed);
-  int h = -1;
-  if (cudaMemcpyAsync(&h, w, sizeof(int), cudaMemcpyDeviceToHost, (cudaStream_t)stream) != cudaSuccess ||
+  int h[thb::STATUS_FAMILIES];
+  if (cudaMemcpyAsync(h, w, sizeof h, cudaMemcpyDeviceToHost, (cudaStream_t)stream) != cudaSuccess ||
       cudaStreamSynchronize((cudaStream_t)stream) != cudaSuccess) {
-    thb::fail("kernel_status: could not read the status word");
+    thb::fail("kernel_status: could not read the status words");
     return -1;
   }
-  if (h != 0) cudaMemsetAsync(w, 0, sizeof(int), (cudaStream_t)stream);
-  return h;
+  int first = 0;
+  for (int f = 1; f < thb::STATUS_FAMILIES; ++f)
+    if (h[f] != 0 && first == 0) first = f * 256 + (h[f] & 255);
+  if (first != 0) {
+    cudaMemsetAsync(w, 0, sizeof h, (cudaStream_t)stream);
+    // a kernel that gave up may have left its reduction ticket counter non-zero
+    thb::reset_reduce_tickets((cudaStream_t)stream);
+  }
+  return first;
 }
 
 #define THB_NOALLOC_SCRATCH_BYTES (4u << 20)

@@ -69,7 +69,7 @@ static int run_scan_strips(cudaStream_t st, float* dst, const float* src, int64_
   const int sms = sm_count();
   const int ctas = p.total_strips < sms ? p.total_strips : sms;
   thb_scan_strips<Op><<<ctas, THB_SCAN_STRIP_THREADS, THB_SS_SMEM, st>>>(map_src, map_dst, (thb_u32)n, inner, p.strips_per_outer,
-                                                                          p.total_strips, d_status ? d_status : device_status_word());
+                                                                          p.total_strips, d_status ? d_status : device_status_word(STATUS_STRIP_SCAN));
   THB_CUDA(cudaGetLastError());
   return 0;
 }

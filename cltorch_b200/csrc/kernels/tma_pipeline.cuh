@@ -44,16 +44,20 @@ __device__ __forceinline__ unsigned long long thb_globaltimer_ns() {
   asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
   return t;
 }
-__device__ __forceinline__ bool thb_mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+__device__ __forceinline__ bool thb_mbar_wait_ns(uint32_t bar, uint32_t parity, volatile int* abort_flag,
+                                                 unsigned long long limit_ns) {
   if (thb_mbar_try_wait(bar, parity)) return true;
   const unsigned long long t0 = thb_globaltimer_ns();
   for (uint32_t i = 1;; ++i) {
     if (thb_mbar_try_wait(bar, parity)) return true;
     if ((i & 63u) == 0) {
       if (*abort_flag) return false;
-      if (thb_globaltimer_ns() - t0 > THB_GEMM_WAIT_LIMIT_NS) return false;
+      if (thb_globaltimer_ns() - t0 > limit_ns) return false;
     }
   }
+}
+__device__ __forceinline__ bool thb_mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+  return thb_mbar_wait_ns(bar, parity, abort_flag, THB_GEMM_WAIT_LIMIT_NS);
 }
 __device__ __forceinline__ void thb_tma_load_3d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int x, int y, int z) {
   asm volatile(

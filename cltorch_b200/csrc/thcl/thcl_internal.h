@@ -90,10 +90,11 @@ void pointwise(THClState* state, int nt, THClTensor** tensors, const bool* read_
                const char* expr, float val1, float val2, const THClTensor* point1);
 
 // Where a reduction whose result the host wants at once puts it: straight into the pinned host
-// buffer when the device can address it (the read-back is then only a stream synchronisation), else
-// into the device buffer.
-inline float* host_result_target(THClDeviceContext* ctx) { return ctx->result_mapped ? ctx->result_mapped : ctx->result; }
-// Waits for the stream and returns slot `slot` of that target.
+// buffer when the device can address it, else into the device buffer. Call it right before the
+// launch that writes the result: it marks the pinned word as "not arrived yet".
+float* host_result_target(THClDeviceContext* ctx);
+// Returns slot `slot` of that target once the result has arrived: by watching the pinned word
+// (slot 0, mapped buffer), else by synchronising the stream.
 float read_host_result(THClDeviceContext* ctx, int slot);
 
 }  // namespace thcl

@@ -1,5 +1,6 @@
 // State, per-device contexts and the error convention of include/THCl.h.
 #include "thcl_internal.h"
+#include <atomic>
 
 #include <cstdarg>
 #include <cstdio>
@@ -131,15 +132,46 @@ void sync_stream(THClDeviceContext* ctx) {
   // kernels with bounded waits other than the GEMM report through the library's status word
   // (the query costs nothing when no such kernel ran since the last one)
   const int st = thb200_kernel_status(ctx->stream);
-  if (st != 0) raise("a kernel did not complete: a bounded wait gave up (status %d); its result is undefined", st);
+  if (st != 0) {
+    static const char* const kFamily[] = {"?", "sum over a strided dimension", "max/min over a strided dimension", "scan",
+                                          "matrix-vector product", "pointwise operator on transposed operands", "self-test", "?"};
+    raise("a kernel did not complete: a bounded wait gave up (%s, code %d); its result is undefined",
+          st > 0 ? kFamily[(st >> 8) & 7] : "status unreadable", st > 0 ? (st & 255) : st);
+  }
+}
+
+// A quiet NaN with a payload that no kernel of this library produces: "the result has not arrived".
+static const uint32_t kResultPending = 0x7FC5A5A5u;
+
+float* host_result_target(THClDeviceContext* ctx) {
+  if (!ctx->result_mapped) return ctx->result;
+  *reinterpret_cast<volatile uint32_t*>(ctx->result_host) = kResultPending;
+  return ctx->result_mapped;
 }
 
 float read_host_result(THClDeviceContext* ctx, int slot) {
-  if (!ctx->result_mapped)
-    check_cuda(cudaMemcpyAsync(ctx->result_host + slot, ctx->result + slot, sizeof(float), cudaMemcpyDeviceToHost, ctx->stream),
-               "cudaMemcpyAsync");
-  sync_stream(ctx);
-  return ctx->result_host[slot];
+  if (!ctx->result_mapped || slot != 0 || ctx->gemm_pending) {
+    if (!ctx->result_mapped)
+      check_cuda(cudaMemcpyAsync(ctx->result_host + slot, ctx->result + slot, sizeof(float), cudaMemcpyDeviceToHost, ctx->stream),
+                 "cudaMemcpyAsync");
+    sync_stream(ctx);
+    return ctx->result_host[slot];
+  }
+  // The kernel stores its one result straight into this pinned word. Watching the word costs a few
+  // microseconds less than a stream synchronisation, which returns only after the kernel has been
+  // retired. Every so often the stream is asked whether it is done, so that a result that happens
+  // to equal the marker, or a launch that failed, cannot keep the host here.
+  volatile uint32_t* word = reinterpret_cast<volatile uint32_t*>(ctx->result_host);
+  for (unsigned spin = 1; *word == kResultPending; ++spin) {
+    if ((spin & 2047u) == 0) {
+      cudaError_t q = cudaStreamQuery(ctx->stream);
+      if (q == cudaSuccess) break;
+      if (q != cudaErrorNotReady) check_cuda(q, "cudaStreamQuery");
+    }
+  }
+  std::atomic_thread_fence(std::memory_order_acquire);
+  // bounded-wait status words are read at the next full synchronisation
+  return ctx->result_host[0];
 }
 
 void after_launch(THClState* state, THClDeviceContext* ctx) {
@@ -226,6 +258,14 @@ struct THClScratchSpace* THClState_getDeviceScratchSpace(THClState* state, int d
 }
 
 size_t THClState_getDeviceScratchSpaceSize(THClState*, int) { return 64 * sizeof(float); }
+
+struct THClScratchSpace* THClState_getCurrentDeviceScratchSpace(THClState* state) {
+  return THClState_getDeviceScratchSpace(state, state->currentDevice, 0);
+}
+
+size_t THClState_getCurrentDeviceScratchSpaceSize(THClState* state) {
+  return THClState_getDeviceScratchSpaceSize(state, state->currentDevice);
+}
 
 void THClSynchronize(THClState* state) {
   THCL_BEGIN

@@ -131,6 +131,8 @@ float* THClTensor_data(THClState*, const THClTensor* self) {
   return (self->storage && self->storage->wrapper) ? self->storage->wrapper + self->storageOffset : nullptr;
 }
 
+float* THClTensor_wrapper(THClState*, const THClTensor* self) { return self->storage ? self->storage->wrapper : nullptr; }
+
 void THClTensor_setFlag(THClState*, THClTensor* self, const char flag) { self->flag |= flag; }
 void THClTensor_clearFlag(THClState*, THClTensor* self, const char flag) { self->flag &= ~flag; }
 

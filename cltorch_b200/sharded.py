@@ -49,7 +49,7 @@ class CudaShardOps:
         return self.T.ClTensor(storage, index + 1, [], [])
 
     def local_sum_into(self, slot, x) -> None:
-        slot.sum(x)          # THClTensor_sumall_gpu: two launches, result written into the buffer
+        slot.sum(x)          # THClTensor_sumall_gpu: one launch, result written into the buffer
 
     def fold(self, storage, count: int, out_slot) -> None:
         L, T = self.T.lib(), self.T

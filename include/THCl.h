@@ -94,6 +94,9 @@ THCL_API void THClState_setDevice(THClState* state, int device);
 THCL_API int THClState_getDevice(THClState* state);
 THCL_API struct THClScratchSpace* THClState_getDeviceScratchSpace(THClState* state, int device, int stream);
 THCL_API size_t THClState_getDeviceScratchSpaceSize(THClState* state, int device);
+/* the deprecated current-device forms, src/lib/THClGeneral.h:128-130 */
+THCL_API struct THClScratchSpace* THClState_getCurrentDeviceScratchSpace(THClState* state);
+THCL_API size_t THClState_getCurrentDeviceScratchSpaceSize(THClState* state);
 /* cltorch.synchronize / cltorch.finish, src/init.cpp:72-78 */
 THCL_API void THClSynchronize(THClState* state);
 /* The CUDA stream (cudaStream_t as void*) that carries device `device`'s work.
@@ -174,6 +177,9 @@ THCL_API long THClTensor_stride(THClState* state, const THClTensor* self, int di
 THCL_API THLongStorage* THClTensor_newSizeOf(THClState* state, THClTensor* self);
 THCL_API THLongStorage* THClTensor_newStrideOf(THClState* state, THClTensor* self);
 THCL_API float* THClTensor_data(THClState* state, const THClTensor* self); /* device address of element 0 */
+/* src/lib/THClTensor.h:40 (returns the storage's CLWrapper there): the device address of the
+ * storage's first float, NOT offset by storageOffset; NULL without storage. */
+THCL_API float* THClTensor_wrapper(THClState* state, const THClTensor* self);
 THCL_API void THClTensor_setFlag(THClState* state, THClTensor* self, const char flag);
 THCL_API void THClTensor_clearFlag(THClState* state, THClTensor* self, const char flag);
 

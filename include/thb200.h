@@ -97,9 +97,17 @@ size_t thb200_reduce_all_scratch_bytes(int64_t n);
 
 /* THClTensor_reduceAll, src/lib/THClReduceAll.cpp:276-316 with kernels
  * src/lib/THClReduceAll.cl:24-100: r = init; r = reduce(r, modify(e)) over all
- * elements; *d_out = finalise(r). Two launches in a fixed order (no atomics):
- * pass 1 writes one partial per block into `scratch`, pass 2 folds them. Sums
- * and products accumulate in double and round to fp32 once at the end.
+ * elements; *d_out = finalise(r). One launch: every block writes one partial into
+ * `scratch`, then draws a ticket (the only atomic; data never goes through atomics);
+ * the block that draws the last ticket folds all partials in a fixed order, so the
+ * result does not depend on which block that is. The ticket is one of 64 counters per
+ * device inside the library's device image, used in turn; a counter is zero between
+ * launches (the last block resets it). Consequences: at most 64 whole-tensor
+ * reductions may be in flight on a device at a time, replays of a captured graph that
+ * contains one must not overlap each other, and after a launch that did not run to its
+ * end (a sticky error) the counters are put back to zero by the next
+ * thb200_kernel_status call that reports a failure. Sums and products accumulate in
+ * double and round to fp32 once at the end.
  * `mod_param` is the exponent of ABSPOW; `mod_point` the device-resident mean of
  * SQDEV; `fin_param` the divisor of FIN_DIV / FIN_DIV_SQRT. d_out is a device
  * pointer: the result never visits the host (point tensors, README.md:88-138). */
@@ -110,12 +118,23 @@ int thb200_reduce_all(void* stream, int modify, int reduce, const thb200_tensor*
 /* Reductions and scans over a non-innermost dimension of a contiguous tensor, matrix-vector
  * products and pointwise operators on large transposed operands stream through TMA pipelines
  * whose waits on shared-memory barriers are bounded (2 s). If such a wait ever gives up, the
- * kernel stores a non-zero code in a status word inside the library's device image and leaves
- * its output undefined. This call synchronises `stream`, returns that word (0 = every kernel
- * since the last call completed) and clears it; < 0 if it cannot be read. When no such kernel
- * was launched on the current device since the last call it returns 0 at once, without
- * synchronising. */
+ * kernel stores a non-zero code in the status word of its kernel family (inside the library's
+ * device image) and leaves its output undefined. This call synchronises `stream`, returns
+ * 256 * family + code of the first family whose word is set (0 = every kernel since the last call
+ * completed) and clears all of them; < 0 if they cannot be read. Families: 1 sum / product /
+ * moments over a strided dimension, 2 max / min with indices over a strided dimension, 3 scans,
+ * 4 matrix-vector products, 5 pointwise operators on transposed operands, 6 the self-test below.
+ * Codes: 1 = the producer's wait for a free stage, 2 = a consumer's wait for a full stage, other
+ * values as the kernel documents. When no such kernel was launched on the current device since
+ * the last call it returns 0 at once, without synchronising. */
 int thb200_kernel_status(void* stream);
+
+/* Runs the give-up path of those bounded waits on purpose, harmlessly: a one-warp kernel waits on
+ * a shared-memory barrier that nothing arrives on (no copy is in flight), for at most `limit_ns`
+ * nanoseconds (1 .. 1e9), then stores `code` (1 .. 255) in the status word of family 6 and returns.
+ * thb200_kernel_status then reports 256 * 6 + code and the stream stays usable. For tests of a
+ * host's error handling; no counterpart in the reference. */
+int thb200_selftest_wait_expiry(void* stream, uint64_t limit_ns, int code);
 
 /* Bytes of scratch thb200_reduce_dim may need for this shape (0 if none). */
 size_t thb200_reduce_dim_scratch_bytes(const thb200_tensor* in, int dim);
@@ -141,6 +160,10 @@ int thb200_reduce_dim(void* stream, int modify, int reduce, const thb200_tensor*
  *  - The first call on each device looks up the array's device address (a one-time
  *    host-side query, done with that device current). Make that first call before
  *    starting any stream capture.
+ *  - The array used is the one of the device that is CURRENT when the call is made,
+ *    not the device `stream` belongs to: make the stream's device current first, or
+ *    the kernel is handed another GPU's array. The cached address does not survive
+ *    cudaDeviceReset.
  *  - All calls on a device share the one array and it keeps the previous call's bytes.
  *    Nothing in it has to start at zero (every partial is written before it is read),
  *    but two calls that overlap on the GPU — different streams, or different host

@@ -70,6 +70,31 @@ def test_no_alloc_matches_the_allocating_entry_point_twice_in_a_row():
     assert np.array_equal(new2, ref2) and np.array_equal(new2, _reduce_both_ways(cl, L, a, 0, RED_ADD, 0.0)[1])
 
 
+def test_no_alloc_call_leaves_free_device_memory_unchanged():
+    """The point of the entry point: once its set-up call is over, a call neither takes nor returns device
+    memory (the free bytes the driver reports stay the same across it)."""
+    import torch
+    import cltorch_b200 as cl
+    L = cl.lib()
+    cl.setDevice(1)
+    keep = []
+    a = rng_uniform(73, (4096, 1000), -1, 1)
+    A = cl.ClTensor(a)
+    out = cl.ClTensor(1, 1000)
+    vin, vout = _view(A, keep), _view(out, keep)
+    stream = C.c_void_p(cl.getStream())
+    assert L.thb200_reduce_dim_noalloc(stream, MOD_COPY, RED_ADD, C.byref(vout), C.byref(vin), 0, 0.0, 0.0) == 0   # set-up call
+    cl.synchronize()
+    free_before, _ = torch.cuda.mem_get_info(0)
+    for _ in range(3):
+        assert L.thb200_reduce_dim_noalloc(stream, MOD_COPY, RED_ADD, C.byref(vout), C.byref(vin), 0, 0.0, 0.0) == 0
+    cl.synchronize()
+    free_after, _ = torch.cuda.mem_get_info(0)
+    assert free_after == free_before
+    want = a.sum(axis=0, dtype=np.float64, keepdims=True)
+    assert np.all(np.abs(out.float() - want) <= 1e-5 * np.maximum(np.abs(want), 1.0))
+
+
 def test_no_alloc_refuses_shapes_beyond_its_scratch():
     import cltorch_b200 as cl
     L = cl.lib()
