@@ -27,6 +27,10 @@ def shard_bounds(n: int, world: int, rank: int) -> Tuple[int, int]:
     return begin, begin + base + (1 if rank < extra else 0)
 
 
+class ExchangeError(RuntimeError):
+    """The exchange of the per-rank partials did not complete (a rank is absent or the transport failed)."""
+
+
 class CudaShardOps:
     """Device side on a GPU: per-rank partial straight into the gather buffer, fold with a kernel."""
 
@@ -81,9 +85,14 @@ class GlobalSum:
         if self.world > 1:
             partials = self.buf[: self.world]
             mine = self.buf[self.rank: self.rank + 1]
-            if self.dist.get_backend(self.group) == "nccl":
-                self.dist.all_gather_into_tensor(partials, mine, group=self.group)   # in place: mine is partials[rank]
-            else:
-                self.dist.all_gather([partials[r: r + 1] for r in range(self.world)], mine.clone(), group=self.group)
+            try:
+                if self.dist.get_backend(self.group) == "nccl":
+                    self.dist.all_gather_into_tensor(partials, mine, group=self.group)   # in place: mine is partials[rank]
+                else:
+                    self.dist.all_gather([partials[r: r + 1] for r in range(self.world)], mine.clone(), group=self.group)
+            except RuntimeError as e:
+                # a rank that never joins ends the collective after the process group's time limit
+                raise ExchangeError(f"rank {self.rank} of {self.world}: the exchange of the partial sums did not "
+                                    f"complete ({str(e).splitlines()[0][:200]})") from e
         self.ops.fold(self.storage, self.world, self.result)
         return self.result

@@ -94,3 +94,46 @@ def test_global_sum_over_gloo_ranks(world):
         want_r = float(np.sum(full[b:e] * np.float32(2), dtype=np.float64))
         assert abs(out[0][2][r] - want_r) <= 1e-6 * want_r
         assert out[r][2] == out[0][2]
+
+
+def _worker_with_absent_rank(rank, world, port, out):
+    """Rank `world - 1` takes part in the first global sum and then stays away from the second."""
+    import datetime
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world, timeout=datetime.timedelta(seconds=3))
+    from cltorch_b200.sharded import ExchangeError
+    import time
+    x = np.full(1000, rank + 1, dtype=np.float32)
+    gsum = GlobalSum(ops=NumpyShardOps())
+    first = float(gsum(x)[0])
+    if rank == world - 1:
+        out[rank] = ("absent", first)
+        time.sleep(8)                      # alive, but never joins the second exchange
+        os._exit(0)                        # no orderly shutdown: its peers have given up on it
+    t0 = time.perf_counter()
+    try:
+        gsum(x)
+        out[rank] = ("no error", first)
+    except ExchangeError as e:
+        out[rank] = ("error", first, time.perf_counter() - t0, str(e))
+    os._exit(0)
+
+
+def test_absent_rank_surfaces_as_a_timeout_error_not_a_hang():
+    world = 3
+    ctx = mp.get_context("spawn")
+    out = ctx.Manager().dict()
+    port = _free_port()
+    procs = [ctx.Process(target=_worker_with_absent_rank, args=(r, world, port, out)) for r in range(world)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(timeout=60)
+        assert p.exitcode == 0
+    want_first = 1000.0 * (1 + 2 + 3)
+    assert out[world - 1] == ("absent", want_first)
+    for r in range(world - 1):
+        kind, first, waited, msg = out[r]
+        assert kind == "error" and first == want_first
+        assert waited < 6.0                                   # the 3 s limit of the group, not forever
+        assert f"rank {r}" in msg and "exchange" in msg
