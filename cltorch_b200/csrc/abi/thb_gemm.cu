@@ -1,6 +1,6 @@
 // Host side of thb200_gemm: operand split, TMA descriptors, launch.
 #include "thb_internal.h"
-#include "../kernels/gemm_kernels.cuh"
+#include "../kernels/gemm_fused_kernels.cuh"
 
 #include <cudaTypedefs.h>
 #include <cstdlib>
@@ -43,6 +43,37 @@ static int make_operand_map(CUtensorMap* map, const float* base, int64_t rows, i
                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) return fail("gemm: cuTensorMapEncodeTiled failed with %d", (int)r);
   return 0;
+}
+
+// The caller's own matrix as a TMA tensor: element (row r, k) at base[r * sr + k * sk] with one of the
+// two strides equal to 1. K-major (sk == 1): dimensions (k, rows, batch), box bk x box_rows x 1 with the
+// swizzle span of one box row; MN-major (sr == 1): dimensions (rows, k, batch), box 32 x bk x 1 with the
+// 128-byte swizzle in 32-byte atoms (the only layout the tensor core transposes 32-bit operands from). Out-of-range parts of a box read as zero, which is what pads K and the edge tiles.
+static int make_raw_operand_map(CUtensorMap* map, const float* base, bool mn_major, int64_t rows, int64_t k, int64_t ld,
+                                int64_t batch, int64_t batch_stride, int box_rows, int bk) {
+  auto enc = tensor_map_encoder();
+  if (!enc) return fail("gemm: cuTensorMapEncodeTiled is not available from this driver");
+  const int64_t inner = mn_major ? rows : k, outer = mn_major ? k : rows;
+  const int64_t bstride = batch > 1 ? batch_stride : ld * outer;
+  cuuint64_t dims[3] = {(cuuint64_t)inner, (cuuint64_t)outer, (cuuint64_t)batch};
+  cuuint64_t strides[2] = {(cuuint64_t)ld * 4, (cuuint64_t)bstride * 4};
+  cuuint32_t box[3] = {(cuuint32_t)(mn_major ? 32 : bk), (cuuint32_t)(mn_major ? bk : box_rows), 1};
+  cuuint32_t estr[3] = {1, 1, 1};
+  const CUtensorMapSwizzle sw = mn_major ? CU_TENSOR_MAP_SWIZZLE_128B_ATOM_32B
+                                         : (bk == 32 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B);
+  CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, (void*)base, dims, strides, box, estr,
+                   CU_TENSOR_MAP_INTERLEAVE_NONE, sw, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return fail("gemm: cuTensorMapEncodeTiled failed with %d on a caller matrix", (int)r);
+  return 0;
+}
+
+// Whether TMA can read this operand in place: 16-byte aligned base, leading dimension and batch
+// stride multiples of 4 floats, extents within the tensor-map limits.
+static bool raw_operand_ok(const float* base, int64_t ld, int64_t batch, int64_t batch_stride) {
+  if (((uintptr_t)base & 15) != 0 || (ld & 3) != 0 || ld <= 0) return false;
+  if (batch > 1 && ((batch_stride & 3) != 0 || batch_stride <= 0)) return false;
+  if ((uint64_t)ld * 4 >= (1ull << 40) || (batch > 1 && (uint64_t)batch_stride * 4 >= (1ull << 40))) return false;
+  return true;
 }
 
 struct Workspace {
@@ -107,15 +138,31 @@ int thb200_gemm(void* stream, char transa, char transb, int64_t m, int64_t n, in
     return fail("gemm: workspace too small (%zu bytes, need %zu)", workspace_bytes, w.bytes);
 
   const int64_t Kp = round_up(k > 0 ? k : 1, kKPad);
+  // Split inside the kernel (operands cross HBM once) or in a pre-pass (one operand layout, and
+  // the tensor pipe is not slowed by the conversion traffic in shared memory)? The pre-pass moves
+  // 12 bytes per operand element; the in-kernel split costs the main loop about a third of its
+  // speed. THB200_GEMM_FUSED=0|1 pins the choice (tests, experiments).
+  static const int forced_fused = [] {
+    const char* e = getenv("THB200_GEMM_FUSED");
+    return e ? (atoi(e) != 0 ? 1 : 0) : -1;
+  }();
+  bool fused = k > 0 && raw_operand_ok(a, lda, batch, stride_a) && raw_operand_ok(b, ldb, batch, stride_b);
+  if (fused && forced_fused < 0) {
+    const double t_pre = 12.0 * (double)batch * ((double)m * k + (double)n * k) / 6.0e12;
+    const double t_mma = 2.0 * (double)batch * (double)m * n * k / 250.0e12;
+    fused = t_pre > 0.3 * t_mma;
+  } else if (forced_fused == 0) {
+    fused = false;
+  }
   // op(A)(i, kk): column-major A, 'n': a[i + kk*lda] (unit stride along i), 't': a[kk + i*lda]
-  {
+  if (!fused) {
     dim3 grid((unsigned)(Kp / 32), (unsigned)((m + 31) / 32), (unsigned)batch);
     if (!ta) thb_gemm_split<true><<<grid, 256, 0, st>>>(a, 1, lda, stride_a, w.a, (int)m, (int)k, (int)Kp);
     else thb_gemm_split<false><<<grid, 256, 0, st>>>(a, lda, 1, stride_a, w.a, (int)m, (int)k, (int)Kp);
     THB_CUDA(cudaGetLastError());
   }
   // B' row j, column kk = op(B)(kk, j): 'n': b[kk + j*ldb] (unit stride along kk), 't': b[j + kk*ldb]
-  {
+  if (!fused) {
     dim3 grid((unsigned)(Kp / 32), (unsigned)((n + 31) / 32), (unsigned)batch);
     if (!tb) thb_gemm_split<false><<<grid, 256, 0, st>>>(b, ldb, 1, stride_b, w.b, (int)n, (int)k, (int)Kp);
     else thb_gemm_split<true><<<grid, 256, 0, st>>>(b, 1, ldb, stride_b, w.b, (int)n, (int)k, (int)Kp);
@@ -125,10 +172,11 @@ int thb200_gemm(void* stream, char transa, char transb, int64_t m, int64_t n, in
 
   // k-block depth: 32 floats (128-byte swizzle, 2-stage ring) or 16 floats (64-byte swizzle,
   // 4-stage ring: more loads in flight). THB200_GEMM_BK overrides the default for experiments.
-  static const int bk = [] {
+  static const int bk_default = [] {
     const char* e = getenv("THB200_GEMM_BK");
     return (e && atoi(e) == 32) ? 32 : 16;
   }();
+  int bk = bk_default;
   // 128 x 128 tiles only when they finish sooner: a CTA works through ceil(tiles / SMs) tiles one
   // after the other, and a 128-wide tile takes about 0.8 of the time of a 256-wide one (half the
   // MMA columns, but the same A traffic and a lower tensor-pipe duty: measured 52% against 84%).
@@ -149,7 +197,8 @@ int thb200_gemm(void* stream, char transa, char transb, int64_t m, int64_t n, in
     return (v >= 1 && v <= kMaxSplits) ? v : 0;
   }();
   int splits = 1;
-  const int64_t kblocks_all = Kp / bk;
+  if (fused) bk = 16;
+  const int64_t kblocks_all = fused ? (k + bk - 1) / bk : Kp / bk;
   if (tiles256 <= kSplitTileLimit && Kp >= 1024 && !forced_bn) {
     int64_t want = forced_splits ? forced_splits : sms / tiles256;
     if (want > kMaxSplits) want = kMaxSplits;
@@ -161,8 +210,15 @@ int thb200_gemm(void* stream, char transa, char transb, int64_t m, int64_t n, in
   splits = (int)((kblocks_all + kb_per_split - 1) / kb_per_split);  // no empty split
   const int bn = forced_bn ? forced_bn : (splits > 1 ? 256 : (cost128 < cost256 ? 128 : 256));
   CUtensorMap map_a, map_b;
-  if (int rc = make_operand_map(&map_a, w.a, m, Kp, 2 * batch, THB_GEMM_BM, bk)) return rc;
-  if (int rc = make_operand_map(&map_b, w.b, n, Kp, 2 * batch, bn, bk)) return rc;
+  // in memory, op(A) has unit stride along its rows for 'n' and along k for 't'; B' the other way round
+  const bool a_mn = !ta, b_mn = tb;
+  if (fused) {
+    if (int rc = make_raw_operand_map(&map_a, a, a_mn, m, k, lda, batch, stride_a, THB_GEMM_BM, bk)) return rc;
+    if (int rc = make_raw_operand_map(&map_b, b, b_mn, n, k, ldb, batch, stride_b, bn, bk)) return rc;
+  } else {
+    if (int rc = make_operand_map(&map_a, w.a, m, Kp, 2 * batch, THB_GEMM_BM, bk)) return rc;
+    if (int rc = make_operand_map(&map_b, w.b, n, Kp, 2 * batch, bn, bk)) return rc;
+  }
 
   ThbGemmParams p;
   p.c = c;
@@ -170,7 +226,7 @@ int thb200_gemm(void* stream, char transa, char transb, int64_t m, int64_t n, in
   p.batch_stride_c = stride_c;
   p.m = (int)m;
   p.n = (int)n;
-  p.kblocks = (int)(Kp / bk);  // k == 0: the split wrote zeros, so C = beta * C
+  p.kblocks = (int)kblocks_all;  // k == 0 (never fused): the split wrote zeros, so C = beta * C
   p.alpha = alpha;
   p.beta = beta;
   p.tiles_m = (int)tm;
@@ -181,6 +237,7 @@ int thb200_gemm(void* stream, char transa, char transb, int64_t m, int64_t n, in
   p.kb_per_split = (int)kb_per_split;
   p.partial = w.partial;
   p.partial_split_stride = batch * m * n;
+  p.debug = (fused && getenv("THB200_GEMM_DEBUG_DUMP")) ? w.a : nullptr;
   const int64_t total_tiles = (int64_t)p.tiles_m * p.tiles_n * batch * splits;
   if (total_tiles > INT32_MAX) return fail("gemm: too many tiles");
   const unsigned ctas = (unsigned)(total_tiles < sms ? total_tiles : sms);
@@ -193,11 +250,30 @@ int thb200_gemm(void* stream, char transa, char transb, int64_t m, int64_t n, in
     thb_gemm_3xtf32<BN_, BK_, ST_, 8, true><<<ctas, THB_GEMM_THREADS(8), ThbGemmCfg<BN_, BK_, ST_>::kSmem, st>>>(        \
         map_a, map_b, p);                                                                                                \
   } while (0)
-  if (bn == 256 && bk == 32) THB_LAUNCH_GEMM(256, 32, 2);
+#define THB_LAUNCH_FUSED(BN_, ST_, AMN_, BMN_)                                                                             \
+  do {                                                                                                                   \
+    THB_CUDA(cudaFuncSetAttribute(thb_gemm_3xtf32_fused<BN_, 16, ST_, AMN_, BMN_>,                                        \
+                                  cudaFuncAttributeMaxDynamicSharedMemorySize, ThbGemmFusedCfg<BN_, 16, ST_>::kSmem));   \
+    thb_gemm_3xtf32_fused<BN_, 16, ST_, AMN_, BMN_>                                                                       \
+        <<<ctas, THB_GEMM_FUSED_THREADS, ThbGemmFusedCfg<BN_, 16, ST_>::kSmem, st>>>(map_a, map_b, p);                    \
+  } while (0)
+#define THB_LAUNCH_FUSED_BN(AMN_, BMN_)                    \
+  do {                                                     \
+    if (bn == 256) THB_LAUNCH_FUSED(256, 4, AMN_, BMN_);   \
+    else THB_LAUNCH_FUSED(128, 6, AMN_, BMN_);             \
+  } while (0)
+  if (fused) {
+    if (a_mn && b_mn) THB_LAUNCH_FUSED_BN(true, true);
+    else if (a_mn) THB_LAUNCH_FUSED_BN(true, false);
+    else if (b_mn) THB_LAUNCH_FUSED_BN(false, true);
+    else THB_LAUNCH_FUSED_BN(false, false);
+  } else if (bn == 256 && bk == 32) THB_LAUNCH_GEMM(256, 32, 2);
   else if (bn == 256) THB_LAUNCH_GEMM(256, 16, 4);
   else if (bk == 32) THB_LAUNCH_GEMM(128, 32, 3);
   else THB_LAUNCH_GEMM(128, 16, 6);
 #undef THB_LAUNCH_GEMM
+#undef THB_LAUNCH_FUSED_BN
+#undef THB_LAUNCH_FUSED
   THB_CUDA(cudaGetLastError());
   if (splits > 1) {
     int64_t blocks = (batch * m * n + 255) / 256;

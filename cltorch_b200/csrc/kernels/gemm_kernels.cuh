@@ -149,7 +149,136 @@ struct ThbGemmParams {
   int splits, kb_per_split;
   float* partial;
   long long partial_split_stride;
+  float* debug;  // diagnostics: when set, the first converted stage of CTA 0 is copied here (one stage of floats)
 };
+
+// tile index -> (batch, tile_m, tile_n): within a batch, THB_GEMM_GROUP_M row tiles
+// share their B tiles in L2
+#define THB_GEMM_TILE_COORDS(work)                                          \
+const int split = (work) % p.splits;                                      \
+const int tile_ = (work) / p.splits;                                      \
+const int kb_begin = split * p.kb_per_split;                              \
+const int kb_end = min(p.kblocks, kb_begin + p.kb_per_split);             \
+const int batch = tile_ / tiles_per_batch;                                \
+const int rem_ = tile_ % tiles_per_batch;                                 \
+const int first_m_ = (rem_ / group_sz) * THB_GEMM_GROUP_M;                \
+const int gm_ = min(THB_GEMM_GROUP_M, p.tiles_m - first_m_);              \
+const int tile_m = first_m_ + (rem_ % group_sz) % gm_;                    \
+const int tile_n = (rem_ % group_sz) / gm_;
+
+
+// ---- epilogue, shared by the GEMM kernels: run by warps 2 .. 2+EW-1 of the CTA. Warp w reads
+// TMEM lanes 32*(w%4) .. +31 (the lanes a warp may touch); with 8 warps, warps 2-5 take the first
+// half of the tile's columns and warps 6-9 the second half.
+template <int BN, int EW, bool PREFETCH_C>
+__device__ __forceinline__ void thb_gemm_epilogue_loop(const ThbGemmParams& p, const uint32_t tmem_base,
+                                                       uint64_t* bar_acc_full, uint64_t* bar_acc_empty,
+                                                       volatile int* abort_flag) {
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int tiles_per_batch = p.tiles_m * p.tiles_n;
+  const int total_tiles = tiles_per_batch * p.batch * p.splits;
+  const int group_sz = THB_GEMM_GROUP_M * p.tiles_n;
+  // ---- epilogue: warps 2..9; warp w reads TMEM lanes 32*(w%4) .. +31 (the lanes a warp may
+  // touch), warps 2-5 the first half of the tile's columns, warps 6-9 the second half ----
+  const int lane_group = warp & 3;
+  constexpr int kColsPerWarp = BN / (EW / 4);
+  const int col_begin = ((warp - 2) >> 2) * kColsPerWarp, col_end = col_begin + kColsPerWarp;
+  // with split-K the raw accumulators go to the partial buffer (leading dimension m)
+  const bool to_partial = p.splits > 1;
+  const bool use_c = !to_partial && p.beta != 0.f;
+  const float alpha = to_partial ? 1.0f : p.alpha;
+  const long long ldc = to_partial ? (long long)p.m : p.ldc;
+  int t = 0;
+  for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, ++t) {
+    THB_GEMM_TILE_COORDS(tile)
+    const int acc = t & 1;
+    const int row = tile_m * THB_GEMM_BM + lane_group * 32 + lane;
+    float* cb = (to_partial ? p.partial + (long long)split * p.partial_split_stride + (long long)batch * p.m * p.n
+                            : p.c + (long long)batch * p.batch_stride_c) + row;
+    const bool row_ok = row < p.m;
+    // a tile that lies wholly inside C needs no per-element bounds checks
+    const bool full = (tile_m + 1) * THB_GEMM_BM <= p.m && (tile_n + 1) * BN <= p.n;
+    // Old values of C, 32 columns of this thread's row. They are read past L1 (ld.global.cg):
+    // the 32 lines of one such block are ldc * 4 bytes apart and would fight for a few L1 sets.
+    auto load_c = [&](float* dst, int col) {
+      if (!use_c) return;
+      const float* q = cb + (long long)col * ldc;
+      if (full) {
+#pragma unroll
+        for (int j = 0; j < 32; ++j) { dst[j] = __ldcg(q); q += ldc; }
+      } else {
+#pragma unroll
+        for (int j = 0; j < 32; ++j) { dst[j] = (row_ok && col + j < p.n) ? __ldcg(q) : 0.f; q += ldc; }
+      }
+    };
+    // C does not depend on the MMAs: with PREFETCH_C the first block of it is requested before
+    // the wait, and each further block while the previous one is being combined and stored
+    float cv[32], cn[32];
+    if (PREFETCH_C) load_c(cv, tile_n * BN + col_begin);
+    bool ok = thb_mbar_wait(thb_smem_u32(&bar_acc_full[acc]), (uint32_t)(t >> 1) & 1, abort_flag);
+    if (!ok && !*abort_flag) { *abort_flag = 1; atomicCAS(p.status, 0, 3); }
+    ok = __all_sync(0xffffffffu, ok);
+    if (!ok) break;
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+#pragma unroll 1
+    for (int c0 = col_begin; c0 < col_end; c0 += 32) {
+      uint32_t r[32];
+      const uint32_t taddr = tmem_base + ((uint32_t)(lane_group * 32) << 16) + (uint32_t)(acc * BN + c0);
+      asm volatile(
+          "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+          "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+          "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+          : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+            "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+            "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+            "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+          : "r"(taddr));
+      const int col0 = tile_n * BN + c0;
+      if (PREFETCH_C) {
+        if (c0 + 32 < col_end) load_c(cn, col0 + 32);
+      } else {
+        load_c(cv, col0);
+      }
+      // the accumulator registers are named as operands so that no use of them can be
+      // scheduled before the wait
+      asm volatile("tcgen05.wait::ld.sync.aligned;"
+                   : "+r"(r[0]), "+r"(r[1]), "+r"(r[2]), "+r"(r[3]), "+r"(r[4]), "+r"(r[5]), "+r"(r[6]), "+r"(r[7]),
+                     "+r"(r[8]), "+r"(r[9]), "+r"(r[10]), "+r"(r[11]), "+r"(r[12]), "+r"(r[13]), "+r"(r[14]), "+r"(r[15]),
+                     "+r"(r[16]), "+r"(r[17]), "+r"(r[18]), "+r"(r[19]), "+r"(r[20]), "+r"(r[21]), "+r"(r[22]), "+r"(r[23]),
+                     "+r"(r[24]), "+r"(r[25]), "+r"(r[26]), "+r"(r[27]), "+r"(r[28]), "+r"(r[29]), "+r"(r[30]), "+r"(r[31])
+                   :
+                   : "memory");
+      float* q = cb + (long long)col0 * ldc;
+      if (full) {
+        if (use_c) {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) { *q = alpha * __uint_as_float(r[j]) + p.beta * cv[j]; q += ldc; }
+        } else {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) { *q = alpha * __uint_as_float(r[j]); q += ldc; }
+        }
+      } else if (row_ok && col0 < p.n) {
+#pragma unroll
+        for (int j = 0; j < 32; ++j) {
+          if (col0 + j < p.n) {
+            float v = alpha * __uint_as_float(r[j]);
+            if (use_c) v += p.beta * cv[j];
+            *q = v;
+          }
+          q += ldc;
+        }
+      }
+      if (PREFETCH_C) {
+#pragma unroll
+        for (int j = 0; j < 32; ++j) cv[j] = cn[j];
+      }
+    }
+    // this warp is done reading the accumulator: hand it back to the MMA issuer
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncwarp();
+    if (lane == 0) thb_mbar_arrive(thb_smem_u32(&bar_acc_empty[acc]));
+  }
+}
 
 // Persistent: CTA i works on tiles i, i + gridDim.x, ... The k loop of tile t+1
 // overlaps the epilogue of tile t through two TMEM accumulators.
@@ -197,20 +326,6 @@ thb_gemm_3xtf32(const __grid_constant__ CUtensorMap map_a, const __grid_constant
   __syncthreads();
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
   const uint32_t tmem_base = *tmem_slot;
-
-  // tile index -> (batch, tile_m, tile_n): within a batch, THB_GEMM_GROUP_M row tiles
-  // share their B tiles in L2
-#define THB_GEMM_TILE_COORDS(work)                                          \
-  const int split = (work) % p.splits;                                      \
-  const int tile_ = (work) / p.splits;                                      \
-  const int kb_begin = split * p.kb_per_split;                              \
-  const int kb_end = min(p.kblocks, kb_begin + p.kb_per_split);             \
-  const int batch = tile_ / tiles_per_batch;                                \
-  const int rem_ = tile_ % tiles_per_batch;                                 \
-  const int first_m_ = (rem_ / group_sz) * THB_GEMM_GROUP_M;                \
-  const int gm_ = min(THB_GEMM_GROUP_M, p.tiles_m - first_m_);              \
-  const int tile_m = first_m_ + (rem_ % group_sz) % gm_;                    \
-  const int tile_n = (rem_ % group_sz) / gm_;
 
   if (warp == 0) {
     if (lane == 0) {
@@ -297,108 +412,8 @@ thb_gemm_3xtf32(const __grid_constant__ CUtensorMap map_a, const __grid_constant
       }
     }
   } else {
-    // ---- epilogue: warps 2..9; warp w reads TMEM lanes 32*(w%4) .. +31 (the lanes a warp may
-    // touch), warps 2-5 the first half of the tile's columns, warps 6-9 the second half ----
-    const int lane_group = warp & 3;
-    constexpr int kColsPerWarp = BN / (EW / 4);
-    const int col_begin = ((warp - 2) >> 2) * kColsPerWarp, col_end = col_begin + kColsPerWarp;
-    // with split-K the raw accumulators go to the partial buffer (leading dimension m)
-    const bool to_partial = p.splits > 1;
-    const bool use_c = !to_partial && p.beta != 0.f;
-    const float alpha = to_partial ? 1.0f : p.alpha;
-    const long long ldc = to_partial ? (long long)p.m : p.ldc;
-    int t = 0;
-    for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, ++t) {
-      THB_GEMM_TILE_COORDS(tile)
-      const int acc = t & 1;
-      const int row = tile_m * THB_GEMM_BM + lane_group * 32 + lane;
-      float* cb = (to_partial ? p.partial + (long long)split * p.partial_split_stride + (long long)batch * p.m * p.n
-                              : p.c + (long long)batch * p.batch_stride_c) + row;
-      const bool row_ok = row < p.m;
-      // a tile that lies wholly inside C needs no per-element bounds checks
-      const bool full = (tile_m + 1) * THB_GEMM_BM <= p.m && (tile_n + 1) * BN <= p.n;
-      // Old values of C, 32 columns of this thread's row. They are read past L1 (ld.global.cg):
-      // the 32 lines of one such block are ldc * 4 bytes apart and would fight for a few L1 sets.
-      auto load_c = [&](float* dst, int col) {
-        if (!use_c) return;
-        const float* q = cb + (long long)col * ldc;
-        if (full) {
-#pragma unroll
-          for (int j = 0; j < 32; ++j) { dst[j] = __ldcg(q); q += ldc; }
-        } else {
-#pragma unroll
-          for (int j = 0; j < 32; ++j) { dst[j] = (row_ok && col + j < p.n) ? __ldcg(q) : 0.f; q += ldc; }
-        }
-      };
-      // C does not depend on the MMAs: with PREFETCH_C the first block of it is requested before
-      // the wait, and each further block while the previous one is being combined and stored
-      float cv[32], cn[32];
-      if (PREFETCH_C) load_c(cv, tile_n * BN + col_begin);
-      bool ok = thb_mbar_wait(thb_smem_u32(&bar_acc_full[acc]), (uint32_t)(t >> 1) & 1, abort_flag);
-      if (!ok && !*abort_flag) { *abort_flag = 1; atomicCAS(p.status, 0, 3); }
-      ok = __all_sync(0xffffffffu, ok);
-      if (!ok) break;
-      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-#pragma unroll 1
-      for (int c0 = col_begin; c0 < col_end; c0 += 32) {
-        uint32_t r[32];
-        const uint32_t taddr = tmem_base + ((uint32_t)(lane_group * 32) << 16) + (uint32_t)(acc * BN + c0);
-        asm volatile(
-            "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-            "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
-            "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
-            : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
-              "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
-              "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
-              "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
-            : "r"(taddr));
-        const int col0 = tile_n * BN + c0;
-        if (PREFETCH_C) {
-          if (c0 + 32 < col_end) load_c(cn, col0 + 32);
-        } else {
-          load_c(cv, col0);
-        }
-        // the accumulator registers are named as operands so that no use of them can be
-        // scheduled before the wait
-        asm volatile("tcgen05.wait::ld.sync.aligned;"
-                     : "+r"(r[0]), "+r"(r[1]), "+r"(r[2]), "+r"(r[3]), "+r"(r[4]), "+r"(r[5]), "+r"(r[6]), "+r"(r[7]),
-                       "+r"(r[8]), "+r"(r[9]), "+r"(r[10]), "+r"(r[11]), "+r"(r[12]), "+r"(r[13]), "+r"(r[14]), "+r"(r[15]),
-                       "+r"(r[16]), "+r"(r[17]), "+r"(r[18]), "+r"(r[19]), "+r"(r[20]), "+r"(r[21]), "+r"(r[22]), "+r"(r[23]),
-                       "+r"(r[24]), "+r"(r[25]), "+r"(r[26]), "+r"(r[27]), "+r"(r[28]), "+r"(r[29]), "+r"(r[30]), "+r"(r[31])
-                     :
-                     : "memory");
-        float* q = cb + (long long)col0 * ldc;
-        if (full) {
-          if (use_c) {
-#pragma unroll
-            for (int j = 0; j < 32; ++j) { *q = alpha * __uint_as_float(r[j]) + p.beta * cv[j]; q += ldc; }
-          } else {
-#pragma unroll
-            for (int j = 0; j < 32; ++j) { *q = alpha * __uint_as_float(r[j]); q += ldc; }
-          }
-        } else if (row_ok && col0 < p.n) {
-#pragma unroll
-          for (int j = 0; j < 32; ++j) {
-            if (col0 + j < p.n) {
-              float v = alpha * __uint_as_float(r[j]);
-              if (use_c) v += p.beta * cv[j];
-              *q = v;
-            }
-            q += ldc;
-          }
-        }
-        if (PREFETCH_C) {
-#pragma unroll
-          for (int j = 0; j < 32; ++j) cv[j] = cn[j];
-        }
-      }
-      // this warp is done reading the accumulator: hand it back to the MMA issuer
-      asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-      __syncwarp();
-      if (lane == 0) thb_mbar_arrive(thb_smem_u32(&bar_acc_empty[acc]));
-    }
+    thb_gemm_epilogue_loop<BN, EW, PREFETCH_C>(p, tmem_base, bar_acc_full, bar_acc_empty, abort_flag);
   }
-#undef THB_GEMM_TILE_COORDS
 
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
   __syncthreads();
