@@ -1,9 +1,10 @@
 // Host side of thb200_gemm: operand split, TMA descriptors, launch.
 #include "thb_internal.h"
-#include "../kernels/gemm_fused_kernels.cuh"
+#include "../kernels/gemm_ts_kernels.cuh"
 
 #include <cudaTypedefs.h>
 #include <cstdlib>
+#include <cstring>
 #include <mutex>
 
 namespace thb {
@@ -63,6 +64,24 @@ static int make_raw_operand_map(CUtensorMap* map, const float* base, bool mn_maj
                                          : (bk == 32 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B);
   CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, (void*)base, dims, strides, box, estr,
                    CU_TENSOR_MAP_INTERLEAVE_NONE, sw, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return fail("gemm: cuTensorMapEncodeTiled failed with %d on a caller matrix", (int)r);
+  return 0;
+}
+
+// A' for the tensor-memory kernel: MN-major caller matrix as (rows, k, batch), box 128 x bk x 1, no swizzle
+// (the converter warps read it with one thread per row).
+static int make_raw_rows_map(CUtensorMap* map, const float* base, int64_t rows, int64_t k, int64_t ld, int64_t batch,
+                             int64_t batch_stride, int bk) {
+  auto enc = tensor_map_encoder();
+  if (!enc) return fail("gemm: cuTensorMapEncodeTiled is not available from this driver");
+  const int64_t bstride = batch > 1 ? batch_stride : ld * k;
+  cuuint64_t dims[3] = {(cuuint64_t)rows, (cuuint64_t)k, (cuuint64_t)batch};
+  cuuint64_t strides[2] = {(cuuint64_t)ld * 4, (cuuint64_t)bstride * 4};
+  cuuint32_t box[3] = {THB_GEMM_BM, (cuuint32_t)bk, 1};
+  cuuint32_t estr[3] = {1, 1, 1};
+  CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, (void*)base, dims, strides, box, estr,
+                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) return fail("gemm: cuTensorMapEncodeTiled failed with %d on a caller matrix", (int)r);
   return 0;
 }
@@ -138,24 +157,37 @@ int thb200_gemm(void* stream, char transa, char transb, int64_t m, int64_t n, in
     return fail("gemm: workspace too small (%zu bytes, need %zu)", workspace_bytes, w.bytes);
 
   const int64_t Kp = round_up(k > 0 ? k : 1, kKPad);
-  // Split inside the kernel (operands cross HBM once) or in a pre-pass (one operand layout, and
-  // the tensor pipe is not slowed by the conversion traffic in shared memory)? The pre-pass moves
-  // 12 bytes per operand element; the in-kernel split costs the main loop about a third of its
-  // speed. THB200_GEMM_FUSED=0|1 pins the choice (tests, experiments).
-  static const int forced_fused = [] {
-    const char* e = getenv("THB200_GEMM_FUSED");
-    return e ? (atoi(e) != 0 ? 1 : 0) : -1;
+  // Three ways to get hi/lo operands to the tensor core:
+  //  pre-pass  both operands are split in HBM first (12 bytes moved per operand element); the main
+  //            loop then runs at ~0.9 of the tensor pipe. Any layout.
+  //  fused     both operands are read in place and split in shared memory: nothing extra crosses HBM,
+  //            but the conversion traffic costs the main loop about 40 % of its speed. For problems
+  //            where the pre-pass would cost as much as the product (short K, few rows).
+  //  ts        A' (MN-major in memory) is read in place and split into TENSOR memory, only B' is
+  //            pre-split: the main loop is faster than with pre-split operands and the big operand of
+  //            "few rows x large weight matrix" is not pre-processed. Needs a long K (one accumulator).
+  // THB200_GEMM_MODE=prepass|fused|ts pins the choice where it is eligible (tests, experiments).
+  enum { MODE_PREPASS = 0, MODE_FUSED = 1, MODE_TS = 2 };
+  static const int forced_mode = [] {
+    const char* e = getenv("THB200_GEMM_MODE");
+    if (!e) return -1;
+    return !strcmp(e, "fused") ? (int)MODE_FUSED : !strcmp(e, "ts") ? (int)MODE_TS : !strcmp(e, "prepass") ? (int)MODE_PREPASS : -1;
   }();
-  bool fused = k > 0 && raw_operand_ok(a, lda, batch, stride_a) && raw_operand_ok(b, ldb, batch, stride_b);
-  if (fused && forced_fused < 0) {
+  const bool a_raw_ok = k > 0 && raw_operand_ok(a, lda, batch, stride_a);
+  const bool fused_ok = a_raw_ok && raw_operand_ok(b, ldb, batch, stride_b);
+  const bool ts_ok = a_raw_ok && !ta;   // op(A) = A: unit stride along the rows
+  int mode = MODE_PREPASS;
+  if (forced_mode == MODE_FUSED) mode = fused_ok ? MODE_FUSED : MODE_PREPASS;
+  else if (forced_mode == MODE_TS) mode = ts_ok ? MODE_TS : MODE_PREPASS;
+  else if (forced_mode < 0) {
     const double t_pre = 12.0 * (double)batch * ((double)m * k + (double)n * k) / 6.0e12;
     const double t_mma = 2.0 * (double)batch * (double)m * n * k / 250.0e12;
-    fused = t_pre > 0.3 * t_mma;
-  } else if (forced_fused == 0) {
-    fused = false;
+    if (ts_ok && k >= 1024) mode = MODE_TS;
+    else if (fused_ok && t_pre > 0.3 * t_mma) mode = MODE_FUSED;
   }
+  const bool fused = mode == MODE_FUSED, ts = mode == MODE_TS;
   // op(A)(i, kk): column-major A, 'n': a[i + kk*lda] (unit stride along i), 't': a[kk + i*lda]
-  if (!fused) {
+  if (mode == MODE_PREPASS) {
     dim3 grid((unsigned)(Kp / 32), (unsigned)((m + 31) / 32), (unsigned)batch);
     if (!ta) thb_gemm_split<true><<<grid, 256, 0, st>>>(a, 1, lda, stride_a, w.a, (int)m, (int)k, (int)Kp);
     else thb_gemm_split<false><<<grid, 256, 0, st>>>(a, lda, 1, stride_a, w.a, (int)m, (int)k, (int)Kp);
@@ -197,8 +229,8 @@ int thb200_gemm(void* stream, char transa, char transb, int64_t m, int64_t n, in
     return (v >= 1 && v <= kMaxSplits) ? v : 0;
   }();
   int splits = 1;
-  if (fused) bk = 16;
-  const int64_t kblocks_all = fused ? (k + bk - 1) / bk : Kp / bk;
+  if (fused || ts) bk = 16;
+  const int64_t kblocks_all = (fused || ts) ? (k + bk - 1) / bk : Kp / bk;
   if (tiles256 <= kSplitTileLimit && Kp >= 1024 && !forced_bn) {
     int64_t want = forced_splits ? forced_splits : sms / tiles256;
     if (want > kMaxSplits) want = kMaxSplits;
@@ -215,6 +247,9 @@ int thb200_gemm(void* stream, char transa, char transb, int64_t m, int64_t n, in
   if (fused) {
     if (int rc = make_raw_operand_map(&map_a, a, a_mn, m, k, lda, batch, stride_a, THB_GEMM_BM, bk)) return rc;
     if (int rc = make_raw_operand_map(&map_b, b, b_mn, n, k, ldb, batch, stride_b, bn, bk)) return rc;
+  } else if (ts) {
+    if (int rc = make_raw_rows_map(&map_a, a, m, k, lda, batch, stride_a, bk)) return rc;
+    if (int rc = make_operand_map(&map_b, w.b, n, Kp, 2 * batch, bn, bk)) return rc;
   } else {
     if (int rc = make_operand_map(&map_a, w.a, m, Kp, 2 * batch, THB_GEMM_BM, bk)) return rc;
     if (int rc = make_operand_map(&map_b, w.b, n, Kp, 2 * batch, bn, bk)) return rc;
@@ -262,7 +297,17 @@ int thb200_gemm(void* stream, char transa, char transb, int64_t m, int64_t n, in
     if (bn == 256) THB_LAUNCH_FUSED(256, 4, AMN_, BMN_);   \
     else THB_LAUNCH_FUSED(128, 6, AMN_, BMN_);             \
   } while (0)
-  if (fused) {
+  if (ts) {
+    if (bn == 256) {
+      THB_CUDA(cudaFuncSetAttribute(thb_gemm_3xtf32_ts<256, 16, 5>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                    ThbGemmTsCfg<256, 16, 5>::kSmem));
+      thb_gemm_3xtf32_ts<256, 16, 5><<<ctas, THB_GEMM_FUSED_THREADS, ThbGemmTsCfg<256, 16, 5>::kSmem, st>>>(map_a, map_b, p);
+    } else {
+      THB_CUDA(cudaFuncSetAttribute(thb_gemm_3xtf32_ts<128, 16, 8>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                    ThbGemmTsCfg<128, 16, 8>::kSmem));
+      thb_gemm_3xtf32_ts<128, 16, 8><<<ctas, THB_GEMM_FUSED_THREADS, ThbGemmTsCfg<128, 16, 8>::kSmem, st>>>(map_a, map_b, p);
+    }
+  } else if (fused) {
     if (a_mn && b_mn) THB_LAUNCH_FUSED_BN(true, true);
     else if (a_mn) THB_LAUNCH_FUSED_BN(true, false);
     else if (b_mn) THB_LAUNCH_FUSED_BN(false, true);

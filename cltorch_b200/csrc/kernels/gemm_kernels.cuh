@@ -170,7 +170,8 @@ const int tile_n = (rem_ % group_sz) / gm_;
 // ---- epilogue, shared by the GEMM kernels: run by warps 2 .. 2+EW-1 of the CTA. Warp w reads
 // TMEM lanes 32*(w%4) .. +31 (the lanes a warp may touch); with 8 warps, warps 2-5 take the first
 // half of the tile's columns and warps 6-9 the second half.
-template <int BN, int EW, bool PREFETCH_C>
+// NACC = number of TMEM accumulators the kernel alternates between (tile t uses accumulator t % NACC).
+template <int BN, int EW, bool PREFETCH_C, int NACC = 2>
 __device__ __forceinline__ void thb_gemm_epilogue_loop(const ThbGemmParams& p, const uint32_t tmem_base,
                                                        uint64_t* bar_acc_full, uint64_t* bar_acc_empty,
                                                        volatile int* abort_flag) {
@@ -191,7 +192,7 @@ __device__ __forceinline__ void thb_gemm_epilogue_loop(const ThbGemmParams& p, c
   int t = 0;
   for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, ++t) {
     THB_GEMM_TILE_COORDS(tile)
-    const int acc = t & 1;
+    const int acc = t % NACC;
     const int row = tile_m * THB_GEMM_BM + lane_group * 32 + lane;
     float* cb = (to_partial ? p.partial + (long long)split * p.partial_split_stride + (long long)batch * p.m * p.n
                             : p.c + (long long)batch * p.batch_stride_c) + row;
@@ -215,7 +216,7 @@ __device__ __forceinline__ void thb_gemm_epilogue_loop(const ThbGemmParams& p, c
     // the wait, and each further block while the previous one is being combined and stored
     float cv[32], cn[32];
     if (PREFETCH_C) load_c(cv, tile_n * BN + col_begin);
-    bool ok = thb_mbar_wait(thb_smem_u32(&bar_acc_full[acc]), (uint32_t)(t >> 1) & 1, abort_flag);
+    bool ok = thb_mbar_wait(thb_smem_u32(&bar_acc_full[acc]), (uint32_t)(t / NACC) & 1, abort_flag);
     if (!ok && !*abort_flag) { *abort_flag = 1; atomicCAS(p.status, 0, 3); }
     ok = __all_sync(0xffffffffu, ok);
     if (!ok) break;

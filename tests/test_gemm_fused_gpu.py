@@ -1,7 +1,7 @@
-"""thb200_gemm with the hi/lo split inside the kernel (operands read in place by TMA, K-major or
-MN-major as they lie in memory) against the same call with the split pre-pass and against an
-fp64-accumulated CPU GEMM: every transposition pair, ragged edges, K not a multiple of the k block,
-batches, split-K, alpha/beta. The library reads THB200_GEMM_FUSED once per process, so each
+"""thb200_gemm with the hi/lo split inside the kernel - both operands split in shared memory ("fused"),
+or A' split into tensor memory with only B' pre-split ("ts") - against the same call with the split
+pre-pass and against an fp64-accumulated CPU GEMM: every transposition pair, ragged edges, K not a multiple of the k block,
+batches, split-K, alpha/beta. The library reads THB200_GEMM_MODE once per process, so each
 path runs in a child process of its own (this file is also that child's program).
 
 Tolerance: 1e-4 relative (Frobenius norm and worst element against the largest entry), as for
@@ -78,7 +78,7 @@ def _child(mode):
 
 
 def _run(mode):
-    env = dict(os.environ, THB200_GEMM_FUSED="1" if mode == "fused" else "0")
+    env = dict(os.environ, THB200_GEMM_MODE=mode)
     r = subprocess.run([sys.executable, __file__, mode], env=env, capture_output=True, text=True, timeout=600)
     assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-4000:]
     line = [l for l in r.stdout.splitlines() if l.startswith("RESULT ")][-1]
@@ -86,19 +86,21 @@ def _run(mode):
 
 
 @pytest.mark.gpu
-def test_split_inside_the_kernel_matches_prepass_and_fp64():
-    fused, prepass = _run("fused"), _run("prepass")
+def test_split_inside_the_kernels_matches_prepass_and_fp64():
+    prepass = _run("prepass")
     bad = []
-    for idx, case in enumerate(CASES):
-        f, p = fused[str(idx)], prepass[str(idx)]
-        if not (f["err"] <= 1e-4 and f["worst"] <= 1e-4):
-            bad.append(("in-kernel split", case, f))
-        if not (p["err"] <= 1e-4 and p["worst"] <= 1e-4):
-            bad.append(("pre-pass", case, p))
-        if not (f["pad_untouched"] and p["pad_untouched"]):                  # nothing written between m and ldc
-            bad.append(("padding written", case, f, p))
-        if abs(f["digest"] - p["digest"]) > 1e-4 * (abs(p["digest"]) + 1.0):
-            bad.append(("paths disagree", case, f["digest"], p["digest"]))
+    for mode in ("fused", "ts"):
+        res = _run(mode)
+        for idx, case in enumerate(CASES):
+            f, p = res[str(idx)], prepass[str(idx)]
+            if not (f["err"] <= 1e-4 and f["worst"] <= 1e-4):
+                bad.append((mode, case, f))
+            if mode == "fused" and not (p["err"] <= 1e-4 and p["worst"] <= 1e-4):
+                bad.append(("prepass", case, p))
+            if not (f["pad_untouched"] and p["pad_untouched"]):                  # nothing written between m and ldc
+                bad.append((mode, "padding written", case, f, p))
+            if abs(f["digest"] - p["digest"]) > 1e-4 * (abs(p["digest"]) + 1.0):
+                bad.append((mode, "paths disagree", case, f["digest"], p["digest"]))
     assert not bad, "\n".join(str(b) for b in bad)
 
 
