@@ -272,7 +272,6 @@ int thb200_gemm(void* stream, char transa, char transb, int64_t m, int64_t n, in
   p.kb_per_split = (int)kb_per_split;
   p.partial = w.partial;
   p.partial_split_stride = batch * m * n;
-  p.debug = (fused && getenv("THB200_GEMM_DEBUG_DUMP")) ? w.a : nullptr;
   const int64_t total_tiles = (int64_t)p.tiles_m * p.tiles_n * batch * splits;
   if (total_tiles > INT32_MAX) return fail("gemm: too many tiles");
   const unsigned ctas = (unsigned)(total_tiles < sms ? total_tiles : sms);
@@ -301,11 +300,11 @@ int thb200_gemm(void* stream, char transa, char transb, int64_t m, int64_t n, in
     if (bn == 256) {
       THB_CUDA(cudaFuncSetAttribute(thb_gemm_3xtf32_ts<256, 16, 5>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                     ThbGemmTsCfg<256, 16, 5>::kSmem));
-      thb_gemm_3xtf32_ts<256, 16, 5><<<ctas, THB_GEMM_FUSED_THREADS, ThbGemmTsCfg<256, 16, 5>::kSmem, st>>>(map_a, map_b, p);
+      thb_gemm_3xtf32_ts<256, 16, 5><<<ctas, THB_GEMM_TS_THREADS, ThbGemmTsCfg<256, 16, 5>::kSmem, st>>>(map_a, map_b, p);
     } else {
       THB_CUDA(cudaFuncSetAttribute(thb_gemm_3xtf32_ts<128, 16, 8>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                     ThbGemmTsCfg<128, 16, 8>::kSmem));
-      thb_gemm_3xtf32_ts<128, 16, 8><<<ctas, THB_GEMM_FUSED_THREADS, ThbGemmTsCfg<128, 16, 8>::kSmem, st>>>(map_a, map_b, p);
+      thb_gemm_3xtf32_ts<128, 16, 8><<<ctas, THB_GEMM_TS_THREADS, ThbGemmTsCfg<128, 16, 8>::kSmem, st>>>(map_a, map_b, p);
     }
   } else if (fused) {
     if (a_mn && b_mn) THB_LAUNCH_FUSED_BN(true, true);
@@ -321,10 +320,10 @@ int thb200_gemm(void* stream, char transa, char transb, int64_t m, int64_t n, in
 #undef THB_LAUNCH_FUSED
   THB_CUDA(cudaGetLastError());
   if (splits > 1) {
-    int64_t blocks = (batch * m * n + 255) / 256;
-    if (blocks > (int64_t)sms * 32) blocks = (int64_t)sms * 32;
-    thb_gemm_splitk_fixup<<<(unsigned)blocks, 256, 0, st>>>(c, ldc, stride_c, w.partial, p.partial_split_stride, splits,
-                                                            (int)m, (int)n, (int)batch, alpha, beta);
+    const bool vec = (m & 3) == 0 && (ldc & 3) == 0 && (stride_c & 3) == 0 && ((uintptr_t)c & 15) == 0;
+    dim3 grid((unsigned)((m / (vec ? 4 : 1) + 255) / 256), (unsigned)((n + 3) / 4), (unsigned)batch);
+    if (vec) thb_gemm_splitk_fixup<true><<<grid, 256, 0, st>>>(c, ldc, stride_c, w.partial, p.partial_split_stride, splits, (int)m, (int)n, alpha, beta);
+    else thb_gemm_splitk_fixup<false><<<grid, 256, 0, st>>>(c, ldc, stride_c, w.partial, p.partial_split_stride, splits, (int)m, (int)n, alpha, beta);
     THB_CUDA(cudaGetLastError());
   }
   return 0;

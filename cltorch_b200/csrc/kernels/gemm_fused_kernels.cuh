@@ -9,14 +9,14 @@
 //    orientation it has in memory: K-major (unit stride along k: one box of BK x rows) or
 //    MN-major (unit stride along the rows: one box of 32 rows x BK per 32 rows, in the 128-byte
 //    swizzle with 32-byte atoms that the tensor core's MN-major descriptors expect for fp32). No transposition anywhere.
-//  * four converter warps turn a landed stage into hi (written back in place) and lo (written
+//  * two converter warps turn a landed stage into hi (written back in place) and lo (written
 //    to a second buffer at the same offset). The conversion is position-preserving, so it is
 //    independent of the swizzle pattern TMA applied.
 //  * the MMA issuer then runs the same three tcgen05.mma.kind::tf32 per k step as
 //    thb_gemm_3xtf32, with the A/B "major" bits of the instruction descriptor set per operand.
 //
 // Roles: warp 0 TMA producer, warp 1 MMA issuer, warps 2-9 epilogue (shared with
-// thb_gemm_3xtf32), warps 10-13 converters. Barriers per stage: raw (TMA -> converters),
+// thb_gemm_3xtf32), warps 10-11 converters. Barriers per stage: raw (TMA -> converters),
 // conv (converters -> MMA), empty (MMA -> TMA). Every wait is bounded as in gemm_kernels.cuh;
 // status codes 1-4 as there, 5 = a converter's wait for a landed stage, 6 = the MMA issuer's
 // wait for a converted stage.
@@ -24,7 +24,10 @@
 
 #include "gemm_kernels.cuh"
 
-#define THB_GEMM_CONV_WARPS 4
+// Two converter warps: with TMA, the MMA issuer and eight epilogue warps that makes 384 threads, which
+// leaves the epilogue the 168 registers per thread it needs to keep two 32-column blocks of C in
+// flight (this kernel serves memory-bound problems, where the epilogue sets the pace).
+#define THB_GEMM_CONV_WARPS 2
 #define THB_GEMM_FUSED_THREADS (64 + 32 * 8 + 32 * THB_GEMM_CONV_WARPS)
 
 template <int BN, int BK, int STAGES>
@@ -61,7 +64,7 @@ __device__ __forceinline__ void thb_split_tf32(float x, float& hi, float& lo) {
   lo = x - hi;
 }
 
-// One converter thread's share of a tile of BYTES bytes: 16-byte chunks t, t + 128, ...
+// One converter thread's share of a tile of BYTES bytes: 16-byte chunks t, t + (converter threads), ...
 template <int BYTES>
 __device__ __forceinline__ void thb_split_tile_in_place(uint8_t* raw_hi, uint8_t* lo, int t) {
   constexpr int kPer = BYTES / 16 / (32 * THB_GEMM_CONV_WARPS);
@@ -250,10 +253,6 @@ thb_gemm_3xtf32_fused(const __grid_constant__ CUtensorMap map_a, const __grid_co
         thb_split_tile_in_place<Cfg::kTileB>(st + 2 * Cfg::kTileA, st + 2 * Cfg::kTileA + Cfg::kTileB, ct);
         // the tensor core reads shared memory through the async proxy
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-        if (p.debug && blockIdx.x == 0 && it == 0) {
-          asm volatile("bar.sync 1, 128;" ::: "memory");  // the four converter warps
-          for (int i = ct; i < Cfg::kStage / 4; i += 32 * THB_GEMM_CONV_WARPS) p.debug[i] = reinterpret_cast<const float*>(st)[i];
-        }
         __syncwarp();
         if (lane == 0) thb_mbar_arrive(thb_smem_u32(&bar_conv[s]));
       }

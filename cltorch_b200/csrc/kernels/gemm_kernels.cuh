@@ -149,7 +149,6 @@ struct ThbGemmParams {
   int splits, kb_per_split;
   float* partial;
   long long partial_split_stride;
-  float* debug;  // diagnostics: when set, the first converted stage of CTA 0 is copied here (one stage of floats)
 };
 
 // tile index -> (batch, tile_m, tile_n): within a batch, THB_GEMM_GROUP_M row tiles
@@ -424,21 +423,62 @@ thb_gemm_3xtf32(const __grid_constant__ CUtensorMap map_a, const __grid_constant
   }
 }
 
-// Split-K fix-up: C = alpha * (P_0 + P_1 + ... in split order) + beta * C, one thread per
-// element, adjacent threads on adjacent rows (C and the partials are column-major).
+// Split-K fix-up: C = alpha * (P_0 + P_1 + ... in split order) + beta * C. C and the partials are
+// column-major: a thread takes 4 consecutive rows (one 128-bit access; VEC = false: one row) of 4
+// columns, all loads of which are issued before the first use. grid = (row groups, column groups, batch).
+template <bool VEC>
 static __global__ void __launch_bounds__(256)
 thb_gemm_splitk_fixup(float* c, long long ldc, long long batch_stride_c, const float* partial,
-                      long long partial_split_stride, int splits, int m, int n, int batch, float alpha, float beta) {
-  const long long per_batch = (long long)m * n;
-  const long long total = per_batch * batch;
-  for (long long e = (long long)blockIdx.x * 256 + threadIdx.x; e < total; e += (long long)gridDim.x * 256) {
-    const long long b = e / per_batch, r = e - b * per_batch;
-    const long long col = r / m, row = r - col * m;
-    float acc = partial[e];
-    for (int s = 1; s < splits; ++s) acc += partial[(long long)s * partial_split_stride + e];
-    float* dst = c + b * batch_stride_c + col * ldc + row;
-    float v = alpha * acc;
-    if (beta != 0.f) v += beta * *dst;
-    *dst = v;
+                      long long partial_split_stride, int splits, int m, int n, float alpha, float beta) {
+  constexpr int W = VEC ? 4 : 1;
+  const int row = (blockIdx.x * 256 + threadIdx.x) * W;
+  if (row >= m) return;
+  const int col0 = blockIdx.y * 4;
+  const float* part = partial + (long long)blockIdx.z * m * n + row;
+  float* dst = c + (long long)blockIdx.z * batch_stride_c + row;
+  float sum[4][W], old[4][W];
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    const bool ok = col0 + j < n;
+    if (VEC) {
+      const float4 v = ok ? __ldcg(reinterpret_cast<const float4*>(part + (long long)(col0 + j) * m)) : make_float4(0, 0, 0, 0);
+      sum[j][0] = v.x; sum[j][1 % W] = v.y; sum[j][2 % W] = v.z; sum[j][3 % W] = v.w;
+      const float4 o = (ok && beta != 0.f) ? *reinterpret_cast<const float4*>(dst + (long long)(col0 + j) * ldc) : make_float4(0, 0, 0, 0);
+      old[j][0] = o.x; old[j][1 % W] = o.y; old[j][2 % W] = o.z; old[j][3 % W] = o.w;
+    } else {
+      sum[j][0] = ok ? __ldcg(part + (long long)(col0 + j) * m) : 0.f;
+      old[j][0] = (ok && beta != 0.f) ? dst[(long long)(col0 + j) * ldc] : 0.f;
+    }
+  }
+  for (int s = 1; s < splits; ++s) {
+    float nxt[4][W];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const bool ok = col0 + j < n;
+      const float* q = part + (long long)s * partial_split_stride + (long long)(col0 + j) * m;
+      if (VEC) {
+        const float4 v = ok ? __ldcg(reinterpret_cast<const float4*>(q)) : make_float4(0, 0, 0, 0);
+        nxt[j][0] = v.x; nxt[j][1 % W] = v.y; nxt[j][2 % W] = v.z; nxt[j][3 % W] = v.w;
+      } else {
+        nxt[j][0] = ok ? __ldcg(q) : 0.f;
+      }
+    }
+#pragma unroll
+    for (int j = 0; j < 4; ++j)
+#pragma unroll
+      for (int w = 0; w < W; ++w) sum[j][w] += nxt[j][w];
+  }
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    if (col0 + j >= n) break;
+    float v[W];
+#pragma unroll
+    for (int w = 0; w < W; ++w) {
+      v[w] = alpha * sum[j][w];
+      if (beta != 0.f) v[w] += beta * old[j][w];
+    }
+    float* q = dst + (long long)(col0 + j) * ldc;
+    if (VEC) *reinterpret_cast<float4*>(q) = make_float4(v[0], v[1 % W], v[2 % W], v[3 % W]);
+    else *q = v[0];
   }
 }

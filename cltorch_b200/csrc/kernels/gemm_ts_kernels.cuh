@@ -26,6 +26,9 @@
 
 #include "gemm_fused_kernels.cuh"
 
+#define THB_GEMM_TS_CONV_WARPS 4   // one per quarter of the TMEM lanes
+#define THB_GEMM_TS_THREADS (64 + 32 * 8 + 32 * THB_GEMM_TS_CONV_WARPS)
+
 template <int BN, int BK, int STAGES>
 struct ThbGemmTsCfg {
   static constexpr int kTileA = THB_GEMM_BM * BK * 4;   // raw A', [BK][128] floats
@@ -61,7 +64,7 @@ __device__ __forceinline__ void thb_tmem_store16(uint32_t taddr, const uint32_t 
 // map_a: the caller's A' as (rows, k, batch), box 128 x BK x 1, no swizzle.
 // map_b: the pre-split B' as in thb_gemm_3xtf32 ([2 * batch][n][Kp], box BK x BN x 1, 64-byte swizzle).
 template <int BN, int BK, int STAGES>
-__global__ void __launch_bounds__(THB_GEMM_FUSED_THREADS, 1)
+__global__ void __launch_bounds__(THB_GEMM_TS_THREADS, 1)
 thb_gemm_3xtf32_ts(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, ThbGemmParams p) {
   typedef ThbGemmTsCfg<BN, BK, STAGES> Cfg;
   static_assert(BK == 16, "one tcgen05.st of 16 columns per half");
@@ -86,7 +89,7 @@ thb_gemm_3xtf32_ts(const __grid_constant__ CUtensorMap map_a, const __grid_const
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
       thb_mbar_init(thb_smem_u32(&bar_raw[s]), 1);
-      thb_mbar_init(thb_smem_u32(&bar_conv[s]), THB_GEMM_CONV_WARPS);
+      thb_mbar_init(thb_smem_u32(&bar_conv[s]), THB_GEMM_TS_CONV_WARPS);
       thb_mbar_init(thb_smem_u32(&bar_empty[s]), 1);
     }
     for (int a = 0; a < 2; ++a) {
