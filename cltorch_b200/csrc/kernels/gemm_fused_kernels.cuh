@@ -9,8 +9,9 @@
 //    orientation it has in memory: K-major (unit stride along k: one box of BK x rows) or
 //    MN-major (unit stride along the rows: one box of 32 rows x BK per 32 rows, in the 128-byte
 //    swizzle with 32-byte atoms that the tensor core's MN-major descriptors expect for fp32). No transposition anywhere.
-//  * two converter warps turn a landed stage into hi (written back in place) and lo (written
-//    to a second buffer at the same offset). The conversion is position-preserving, so it is
+//  * two converter warps compute lo = x - (x with its 13 low mantissa bits cleared) for a landed
+//    stage and write it to a second buffer at the same offset; the raw tile itself serves as hi
+//    (the tensor core ignores those 13 bits). The conversion is position-preserving, so it is
 //    independent of the swizzle pattern TMA applied.
 //  * the MMA issuer then runs the same three tcgen05.mma.kind::tf32 per k step as
 //    thb_gemm_3xtf32, with the A/B "major" bits of the instruction descriptor set per operand.
@@ -35,7 +36,7 @@ struct ThbGemmFusedCfg {
   static constexpr int kTileA = THB_GEMM_BM * BK * 4;
   static constexpr int kTileB = BN * BK * 4;
   static constexpr int kTmemCols = 2 * BN;
-  static constexpr int kStage = 2 * kTileA + 2 * kTileB;  // A raw -> hi, A lo, B raw -> hi, B lo
+  static constexpr int kStage = 2 * kTileA + 2 * kTileB;  // A raw (= hi), A lo, B raw (= hi), B lo
   static constexpr int kRawBytes = kTileA + kTileB;       // what TMA delivers per stage
   static constexpr int kSmem = STAGES * kStage + 1024 /*alignment slack*/ + 512 /*barriers*/;
 };
@@ -65,21 +66,26 @@ __device__ __forceinline__ void thb_split_tf32(float x, float& hi, float& lo) {
 }
 
 // One converter thread's share of a tile of BYTES bytes: 16-byte chunks t, t + (converter threads), ...
+// The tensor core reads a TF32 operand as the upper 19 bits of the fp32 word and ignores the 13 low
+// mantissa bits. The raw tile therefore already IS a valid hi operand, hi = x with its low bits cut
+// off, and only lo = x - hi has to be computed and written (exact in fp32; |lo| < 2^-10 |x|). That
+// halves what the converters write to shared memory, which is what bounds this kernel. Against the
+// rounded split of the other kernels the dropped terms are about twice as large (lo*lo ~ 2^-20,
+// truncation of lo by the tensor core ~ 2^-21 relative): still two orders below the 1e-4 bar.
 template <int BYTES>
-__device__ __forceinline__ void thb_split_tile_in_place(uint8_t* raw_hi, uint8_t* lo, int t) {
+__device__ __forceinline__ void thb_split_tile_lo(const uint8_t* raw, uint8_t* lo, int t) {
   constexpr int kPer = BYTES / 16 / (32 * THB_GEMM_CONV_WARPS);
-  static_assert(kPer * 16 * 32 * THB_GEMM_CONV_WARPS == BYTES, "tile size must be a multiple of 2 KB");
+  static_assert(kPer * 16 * 32 * THB_GEMM_CONV_WARPS == BYTES, "tile size must be a multiple of the converters' stride");
   float4 v[kPer];
 #pragma unroll
-  for (int j = 0; j < kPer; ++j) v[j] = *reinterpret_cast<const float4*>(raw_hi + (t + j * 32 * THB_GEMM_CONV_WARPS) * 16);
+  for (int j = 0; j < kPer; ++j) v[j] = *reinterpret_cast<const float4*>(raw + (t + j * 32 * THB_GEMM_CONV_WARPS) * 16);
 #pragma unroll
   for (int j = 0; j < kPer; ++j) {
-    float4 h, l;
-    thb_split_tf32(v[j].x, h.x, l.x);
-    thb_split_tf32(v[j].y, h.y, l.y);
-    thb_split_tf32(v[j].z, h.z, l.z);
-    thb_split_tf32(v[j].w, h.w, l.w);
-    *reinterpret_cast<float4*>(raw_hi + (t + j * 32 * THB_GEMM_CONV_WARPS) * 16) = h;
+    float4 l;
+    l.x = v[j].x - __uint_as_float(__float_as_uint(v[j].x) & 0xFFFFE000u);
+    l.y = v[j].y - __uint_as_float(__float_as_uint(v[j].y) & 0xFFFFE000u);
+    l.z = v[j].z - __uint_as_float(__float_as_uint(v[j].z) & 0xFFFFE000u);
+    l.w = v[j].w - __uint_as_float(__float_as_uint(v[j].w) & 0xFFFFE000u);
     *reinterpret_cast<float4*>(lo + (t + j * 32 * THB_GEMM_CONV_WARPS) * 16) = l;
   }
 }
@@ -233,7 +239,7 @@ thb_gemm_3xtf32_fused(const __grid_constant__ CUtensorMap map_a, const __grid_co
   } else if (warp < 2 + EW) {
     thb_gemm_epilogue_loop<BN, EW, true>(p, tmem_base, bar_acc_full, bar_acc_empty, abort_flag);
   } else {
-    // ---- converters: hi in place, lo beside it ----
+    // ---- converters: lo beside the raw tile ----
     const int ct = threadIdx.x - 32 * (2 + EW);
     long long it = 0;
     bool ok = true;
@@ -249,8 +255,8 @@ thb_gemm_3xtf32_fused(const __grid_constant__ CUtensorMap map_a, const __grid_co
         got = __all_sync(0xffffffffu, got);
         if (!got) { ok = false; break; }
         uint8_t* st = smem + s * Cfg::kStage;
-        thb_split_tile_in_place<Cfg::kTileA>(st, st + Cfg::kTileA, ct);
-        thb_split_tile_in_place<Cfg::kTileB>(st + 2 * Cfg::kTileA, st + 2 * Cfg::kTileA + Cfg::kTileB, ct);
+        thb_split_tile_lo<Cfg::kTileA>(st, st + Cfg::kTileA, ct);
+        thb_split_tile_lo<Cfg::kTileB>(st + 2 * Cfg::kTileA, st + 2 * Cfg::kTileA + Cfg::kTileB, ct);
         // the tensor core reads shared memory through the async proxy
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
         __syncwarp();
