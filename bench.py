@@ -211,7 +211,8 @@ def run_gpu(args):
     import cltorch_b200 as cl
     from cltorch_b200.sharded import GlobalSum, shard_bounds
 
-    gsum = GlobalSum()                      # binds the library to this GPU and to torch's current stream
+    # binds the library to this GPU and to torch's current stream
+    gsum = GlobalSum(exchange=None if args.exchange == "auto" else args.exchange)
     n_total = args.elements
     begin, end = shard_bounds(n_total, world, rank)
     n_local = end - begin
@@ -230,7 +231,8 @@ def run_gpu(args):
 
     ev = lambda: torch.cuda.Event(enable_timing=True)
 
-    def step(events=None):
+    def step(events=None, gs=None):
+        gs = gs or gsum
         if events is not None:
             events[0].record()
         x.apply_on_gpu(EXPR1)
@@ -239,7 +241,7 @@ def run_gpu(args):
         x.apply_on_gpu(EXPR2)
         if events is not None:
             events[2].record()
-        r = gsum(x)
+        r = gs(x)
         if events is not None:
             events[3].record()
         return r
@@ -268,6 +270,21 @@ def run_gpu(args):
     elapsed_ms = start.elapsed_time(stop)
     resident_sum = float(result.s())
 
+    # the same timed region with the other exchange (N > 1): the all-gather through torch.distributed
+    alt_ms = None
+    if world > 1 and gsum.x is not None:
+        other = GlobalSum(exchange="nccl")
+        for _ in range(max(args.warmup, 3)):
+            step(gs=other)
+        a0, a1 = ev(), ev()
+        barrier()
+        a0.record()
+        for _ in range(args.steps):
+            step(gs=other)
+        a1.record()
+        barrier()
+        alt_ms = a0.elapsed_time(a1)
+
     # e2e: host buffer -> device, chain, result back to the host; every step
     e2e_steps = args.steps
     for _ in range(2):
@@ -280,10 +297,10 @@ def run_gpu(args):
     torch.cuda.synchronize()
     e2e_s = time.perf_counter() - t0
 
-    times = torch.tensor([elapsed_ms, e2e_s * 1e3], dtype=torch.float64, device="cuda")
+    times = torch.tensor([elapsed_ms, e2e_s * 1e3, alt_ms or 0.0], dtype=torch.float64, device="cuda")
     if world > 1:
         dist.all_reduce(times, op=dist.ReduceOp.MAX)
-    elapsed_ms, e2e_ms = times.tolist()
+    elapsed_ms, e2e_ms, alt_ms = times.tolist()
 
     # parity of the sharded sum: double-precision host sums of the same pinned shards, block by block
     block_sums = host_oracle_block_sums(host, begin, n_total, host_threads() // world).cuda()
@@ -308,6 +325,12 @@ def run_gpu(args):
     config = shared_config(n_total, world)
     config.update({"elements_per_gpu": n_local, "extra_untimed_warmup_steps": args.clock_warmup * world,
                    "exchange": gsum.exchange})
+    if gsum.why_not_p2p:
+        config["p2p_exchange_unavailable"] = gsum.why_not_p2p
+    if alt_ms:
+        config["exchange_alternative"] = {"exchange": "all-gather of one float per rank (torch.distributed), fold in rank order",
+                                          "ms_per_step": alt_ms / args.steps,
+                                          "value": BYTES_PER_ELT * n_total / (alt_ms / args.steps * 1e-3) / 1e9}
     line = {
         "metric": "achieved_hbm_gbs_sharded_apply_reduceall", "value": value, "unit": "GB/s", "n_gpus": world,
         "steps": args.steps, "warmup": max(args.warmup, 3), "ms_per_step": ms_per_step, "higher_is_better": True,
@@ -366,6 +389,8 @@ def main():
     ap.add_argument("--workload", default="c5")
     ap.add_argument("--configs", default="c1,c2,c3,c4",
                     help="groups of per-operation timings added to the N=1 line (comma separated; empty: none)")
+    ap.add_argument("--exchange", default="auto", choices=["auto", "p2p", "nccl"],
+                    help="how the per-GPU sums are combined at N > 1 (auto: the library's peer-store exchange where it can be set up)")
     ap.add_argument("--elements", type=int, default=N_TOTAL,
                     help="length of the sharded vector (default 2^31; smaller values are for profiler captures)")
     ap.add_argument("--clock-warmup", type=int, default=64,

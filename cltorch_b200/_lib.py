@@ -243,6 +243,13 @@ PROTOTYPES = {
                                     C.c_int64, C.c_void_p, C.c_size_t]),
     "thb200_reduce_dim_index_scratch_bytes": (C.c_size_t, [C.c_int64, C.c_int64, C.c_int64]),
     "thb200_fold_partials": (i, [C.c_void_p, i, C.c_void_p, i, C.c_void_p]),
+    "thb200_exchange_create": (i, [i, i, C.POINTER(C.c_void_p), C.c_void_p]),
+    "thb200_exchange_connect": (i, [C.c_void_p, C.c_void_p]),
+    "thb200_exchange_push": (i, [C.c_void_p, C.c_void_p, i, C.POINTER(thb200_tensor), C.c_void_p, C.c_size_t]),
+    "thb200_exchange_fold": (i, [C.c_void_p, C.c_void_p, i, C.c_void_p, C.c_uint64]),
+    "thb200_exchange_reduce": (i, [C.c_void_p, C.c_void_p, i, C.POINTER(thb200_tensor), C.c_void_p, C.c_void_p, C.c_size_t,
+                                   C.c_uint64]),
+    "thb200_exchange_destroy": (i, [C.c_void_p]),
     "thb200_gemm_workspace_bytes": (C.c_size_t, [C.c_int64] * 4),
     "thb200_gemm": (i, [C.c_void_p, C.c_char, C.c_char, C.c_int64, C.c_int64, C.c_int64, f, C.c_void_p, C.c_int64,
                         C.c_void_p, C.c_int64, f, C.c_void_p, C.c_int64, C.c_int64, C.c_int64, C.c_int64, C.c_int64,

@@ -55,9 +55,19 @@ enum StatusFamily {
   STATUS_STRIP_GEMV = 4,     // matrix-vector product over the columns of a row-major matrix
   STATUS_TILE_APPLY = 5,     // pointwise operators on large transposed operands (TMA tiles)
   STATUS_SELFTEST = 6,       // thb200_selftest_wait_expiry
+  STATUS_EXCHANGE = 7,       // the wait for the other GPUs' partial results (thb200_exchange_fold)
   STATUS_FAMILIES = 8
 };
 int* device_status_word(int family);
+
+// thb200_reduce_all with the cross-GPU push (push_cells == nullptr: plain reduction), and the launch of
+// the bounded wait + fold over this GPU's cells; both live with the reduction kernels.
+int reduce_all_impl(void* stream, int modify, int reduce, const thb200_tensor* in, float init, float mod_param,
+                    const float* mod_point, int fin, float fin_param, float* d_out, float* scratch, size_t scratch_bytes,
+                    unsigned long long* const* push_cells, int push_count, unsigned int push_epoch);
+int exchange_fold_launch(void* stream, int reduce, const unsigned long long* cells, int count, unsigned int epoch,
+                         float* d_out, unsigned long long limit_ns);
+float exchange_identity(int reduce);
 
 // Number of chunks to cut a reduced / scanned dimension of `rsize` elements into when only
 // `threads` worker threads (blocks of 256, `blocks_per_sm` resident) exist per chunk: as many

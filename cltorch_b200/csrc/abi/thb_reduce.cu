@@ -121,6 +121,11 @@ struct ReduceAllArgs {
   int head;
   Collapsed c;
   cudaError_t err = cudaSuccess;
+  // cross-GPU exchange (thb200_exchange_push): cells the finishing block also stores the result to
+  unsigned long long* const* push_cells = nullptr;
+  int push_count = 0;
+  unsigned int push_epoch = 0;
+  bool pushed = false;
 
   template <class Red>
   void launch_pass2(int blocks) {
@@ -138,6 +143,8 @@ struct ReduceAllArgs {
     ThbFinish F;
     F.ticket = reduce_ticket();
     F.fin = fin; F.fparam = fparam; F.out = d_out;
+    F.push_cells = F.ticket ? push_cells : nullptr; F.push_count = push_count; F.push_epoch = push_epoch;
+    pushed = F.push_cells != nullptr;
     if (contig) {
       thb_reduce_all_pass1_contig<Mod, Red><<<blocks, THB_RA_THREADS, 0, st>>>(
           in->data, n, head, init, mparam, mpoint, (typename Red::acc_t*)scratch, F);
@@ -402,9 +409,12 @@ extern "C" {
 // one partial per pass-1 block; sums keep theirs in double
 size_t thb200_reduce_all_scratch_bytes(int64_t n) { return (size_t)reduce_all_blocks(n) * sizeof(double); }
 
-int thb200_reduce_all(void* stream, int modify, int reduce, const thb200_tensor* in, float init, float mod_param,
-                      const float* mod_point, int fin, float fin_param, float* d_out, float* scratch,
-                      size_t scratch_bytes) {
+}  // extern "C"
+
+namespace thb {
+int reduce_all_impl(void* stream, int modify, int reduce, const thb200_tensor* in, float init, float mod_param,
+                    const float* mod_point, int fin, float fin_param, float* d_out, float* scratch, size_t scratch_bytes,
+                    unsigned long long* const* push_cells, int push_count, unsigned int push_epoch) {
   if (!in || !d_out) return fail("reduceAll: null argument");
   if (in->ndim > THB200_MAX_DIMS) return fail("reduceAll: too many dimensions");
   ReduceAllArgs a;
@@ -414,6 +424,7 @@ int thb200_reduce_all(void* stream, int modify, int reduce, const thb200_tensor*
   a.init = init; a.mparam = mod_param; a.mpoint = mod_point;
   a.fin = fin; a.fparam = fin_param;
   a.d_out = d_out; a.scratch = scratch;
+  a.push_cells = push_cells; a.push_count = push_count; a.push_epoch = push_epoch;
   if (a.n > 0 && !in->data) return fail("reduceAll: input has no device memory");
   if (!scratch || scratch_bytes < thb200_reduce_all_scratch_bytes(a.n))
     return fail("reduceAll: scratch too small (%zu bytes, need %zu)", scratch_bytes, thb200_reduce_all_scratch_bytes(a.n));
@@ -425,7 +436,18 @@ int thb200_reduce_all(void* stream, int modify, int reduce, const thb200_tensor*
     return fail("reduceAll: non-contiguous tensor needs 64-bit index math: not implemented");
   if (!dispatch_pair(modify, reduce, a.mparam, a)) return fail("reduceAll: unsupported modify/reduce pair (%d, %d)", modify, reduce);
   if (a.err != cudaSuccess) return fail_cuda(a.err, "reduceAll launch");
+  if (push_cells && !a.pushed) return fail("exchange: the library's ticket counters are not available on this device");
   return 0;
+}
+}  // namespace thb
+
+extern "C" {
+
+int thb200_reduce_all(void* stream, int modify, int reduce, const thb200_tensor* in, float init, float mod_param,
+                      const float* mod_point, int fin, float fin_param, float* d_out, float* scratch,
+                      size_t scratch_bytes) {
+  return reduce_all_impl(stream, modify, reduce, in, init, mod_param, mod_point, fin, fin_param, d_out, scratch, scratch_bytes,
+                         nullptr, 0, 0);
 }
 
 int thb200_fold_partials(void* stream, int reduce, const float* d_partials, int count, float* d_out) {
@@ -437,6 +459,41 @@ int thb200_fold_partials(void* stream, int reduce, const float* d_partials, int 
   if (a.err != cudaSuccess) return fail_cuda(a.err, "fold_partials launch");
   return 0;
 }
+
+}  // extern "C"
+
+namespace thb {
+struct ExchangeFoldArgs {
+  cudaStream_t st;
+  const unsigned long long* cells;
+  int count;
+  unsigned int epoch;
+  float init;
+  float* d_out;
+  unsigned long long limit_ns;
+  int* status;
+  cudaError_t err = cudaSuccess;
+  template <class Red>
+  void operator()() {
+    thb_exchange_wait_fold<Red><<<1, 1024, 0, st>>>(cells, count, epoch, init, d_out, limit_ns, status);
+    err = cudaGetLastError();
+  }
+};
+int exchange_fold_launch(void* stream, int reduce, const unsigned long long* cells, int count, unsigned int epoch,
+                         float* d_out, unsigned long long limit_ns) {
+  ExchangeFoldArgs a;
+  a.st = (cudaStream_t)stream;
+  a.cells = cells; a.count = count; a.epoch = epoch; a.init = identity_of(reduce); a.d_out = d_out;
+  a.limit_ns = limit_ns; a.status = device_status_word(STATUS_EXCHANGE);
+  if (!a.status) return fail("exchange: the status word is not available");
+  if (!dispatch_red(reduce, a)) return fail("exchange: unknown reduce op %d", reduce);
+  if (a.err != cudaSuccess) return fail_cuda(a.err, "exchange fold launch");
+  return 0;
+}
+float exchange_identity(int reduce) { return identity_of(reduce); }
+}  // namespace thb
+
+extern "C" {
 
 static int reduce_dim_geometry(const thb200_tensor* in, int dim, int64_t* nslices, int64_t* rsize, int64_t* rstride) {
   if (!in || in->ndim < 1 || in->ndim > THB200_MAX_DIMS) return fail("reduceDim: bad input tensor");

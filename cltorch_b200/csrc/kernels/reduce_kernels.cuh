@@ -169,7 +169,23 @@ struct ThbFinish {
   int fin;       // THB_FIN_*, ignored by the moments reductions
   float fparam;  // divisor of the finaliser; element count for the moments
   float* out;
+  // Cross-GPU exchange (null otherwise): the block that writes the scalar also stores
+  // (epoch << 32 | bits of the scalar) into push_cells[0 .. push_count), one 8-byte cell in the
+  // memory of every GPU of the group (this GPU's own cell included), with plain stores.
+  unsigned long long* const* push_cells;
+  int push_count;
+  unsigned int push_epoch;
 };
+
+// One 8-byte store / load at system scope: whole or not at all, also across NVLink.
+__device__ __forceinline__ void thb_store_cell(unsigned long long* cell, unsigned long long v) {
+  asm volatile("st.relaxed.sys.global.u64 [%0], %1;" ::"l"(cell), "l"(v) : "memory");
+}
+__device__ __forceinline__ unsigned long long thb_load_cell(const unsigned long long* cell) {
+  unsigned long long v;
+  asm volatile("ld.relaxed.sys.global.u64 %0, [%1];" : "=l"(v) : "l"(cell) : "memory");
+  return v;
+}
 
 __device__ __forceinline__ float thb_load_partial(const float* p) { return __ldcg(p); }
 __device__ __forceinline__ double thb_load_partial(const double* p) { return __ldcg(p); }
@@ -210,8 +226,13 @@ __device__ __forceinline__ void thb_finish_last_block(const ThbFinish& F, const 
   for (unsigned int i = threadIdx.x; i < gridDim.x; i += blockDim.x) r = Red::apply(r, thb_load_partial(partials + i));
   r = thb_block_fold<Red>(r, (acc_t)init, smem);
   if (threadIdx.x == 0) {
-    F.out[0] = thb_finish_value((Red*)nullptr, r, F.fin, F.fparam);
+    const float value = thb_finish_value((Red*)nullptr, r, F.fin, F.fparam);
+    F.out[0] = value;
     *F.ticket = 0;
+    if (F.push_cells) {
+      const unsigned long long cell = ((unsigned long long)F.push_epoch << 32) | (unsigned long long)__float_as_uint(value);
+      for (int j = 0; j < F.push_count; ++j) thb_store_cell(F.push_cells[j], cell);
+    }
   }
 }
 
@@ -345,6 +366,45 @@ thb_fold_floats(const float* values, int count, float init, float* out) {
   for (int i = threadIdx.x; i < count; i += blockDim.x) r = Red::apply(r, (acc_t)values[i]);
   r = thb_block_fold<Red>(r, (acc_t)init, smem);
   if (threadIdx.x == 0) out[0] = (float)r;
+}
+
+// Consumer side of the cross-GPU exchange: thread i waits until cell i of THIS GPU's buffer carries
+// the expected epoch (its peer's store has arrived), then the values are folded exactly as
+// thb_fold_floats folds an array. The wait is bounded: when a cell does not arrive within limit_ns
+// the kernel stores 1 + (index of the first missing rank, at most 254) in *status, writes NaN and ends.
+template <class Red>
+__global__ void __launch_bounds__(1024)
+thb_exchange_wait_fold(const unsigned long long* cells, int count, unsigned int epoch, float init, float* out,
+                       unsigned long long limit_ns, int* status) {
+  typedef typename Red::acc_t acc_t;
+  __shared__ acc_t smem[32];
+  __shared__ int missing;
+  if (threadIdx.x == 0) missing = 0x7fffffff;
+  __syncthreads();
+  acc_t r = (acc_t)init;
+  for (int i = threadIdx.x; i < count; i += blockDim.x) {
+    unsigned long long t0 = 0, v = thb_load_cell(cells + i);
+    for (unsigned int spin = 1; (unsigned int)(v >> 32) != epoch; ++spin) {
+      if (spin == 1) asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t0));
+      if ((spin & 31u) == 0) {
+        unsigned long long now;
+        asm volatile("mov.u64 %0, %globaltimer;" : "=l"(now));
+        if (now - t0 > limit_ns) { atomicMin(&missing, i); break; }
+      }
+      v = thb_load_cell(cells + i);
+    }
+    r = Red::apply(r, (acc_t)__uint_as_float((unsigned int)v));
+  }
+  __syncthreads();
+  r = thb_block_fold<Red>(r, (acc_t)init, smem);
+  if (threadIdx.x == 0) {
+    if (missing != 0x7fffffff) {
+      if (status) atomicCAS(status, 0, 1 + (missing < 254 ? missing : 254));
+      out[0] = __int_as_float(0x7fc00000);
+    } else {
+      out[0] = (float)r;
+    }
+  }
 }
 
 // ---- reduce along one dimension --------------------------------------------

@@ -134,7 +134,8 @@ void sync_stream(THClDeviceContext* ctx) {
   const int st = thb200_kernel_status(ctx->stream);
   if (st != 0) {
     static const char* const kFamily[] = {"?", "sum over a strided dimension", "max/min over a strided dimension", "scan",
-                                          "matrix-vector product", "pointwise operator on transposed operands", "self-test", "?"};
+                                          "matrix-vector product", "pointwise operator on transposed operands", "self-test",
+                                          "exchange between GPUs (a rank is absent or late)"};
     raise("a kernel did not complete: a bounded wait gave up (%s, code %d); its result is undefined",
           st > 0 ? kFamily[(st >> 8) & 7] : "status unreadable", st > 0 ? (st & 255) : st);
   }

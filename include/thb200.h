@@ -123,7 +123,8 @@ int thb200_reduce_all(void* stream, int modify, int reduce, const thb200_tensor*
  * 256 * family + code of the first family whose word is set (0 = every kernel since the last call
  * completed) and clears all of them; < 0 if they cannot be read. Families: 1 sum / product /
  * moments over a strided dimension, 2 max / min with indices over a strided dimension, 3 scans,
- * 4 matrix-vector products, 5 pointwise operators on transposed operands, 6 the self-test below.
+ * 4 matrix-vector products, 5 pointwise operators on transposed operands, 6 the self-test below,
+ * 7 the cross-GPU exchange (thb200_exchange_fold; code = 1 + first missing rank).
  * Codes: 1 = the producer's wait for a free stage, 2 = a consumer's wait for a full stage, other
  * values as the kernel documents. When no such kernel was launched on the current device since
  * the last call it returns 0 at once, without synchronising. */
@@ -135,6 +136,39 @@ int thb200_kernel_status(void* stream);
  * thb200_kernel_status then reports 256 * 6 + code and the stream stays usable. For tests of a
  * host's error handling; no counterpart in the reference. */
 int thb200_selftest_wait_expiry(void* stream, uint64_t limit_ns, int code);
+
+/* ---- whole-tensor reduction over the GPUs of one box ------------------------
+ * No counterpart in the reference (one OpenCL context per device, cross-device copy "Not
+ * implemented", src/lib/THClTensorCopy.cpp:185-220). A tensor sharded over `world` GPUs, one
+ * process (or thread) per GPU: every rank reduces its shard and all ranks end up with the same
+ * total, device-resident, bit-identical (folded in rank order), without a collective library and
+ * without a host synchronisation.
+ *
+ *   create   on each rank, with its GPU current: allocates this GPU's cells and fills a
+ *            THB200_EXCHANGE_HANDLE_BYTES-byte handle.
+ *   (the host passes every rank all handles, in rank order: MPI, torch.distributed, a file ...)
+ *   connect  maps the other ranks' cells (CUDA IPC between processes, peer access within one).
+ *   push     thb200_reduce_all of this rank's shard (modify = copy) in ONE launch whose finishing
+ *            block also stores the result, tagged with the step number, into this rank's cell on
+ *            every GPU: plain 8-byte stores over NVLink. It waits for nobody.
+ *   fold     one block waits until this GPU's cells of all ranks carry the current step number and
+ *            folds them in rank order into *d_out. The wait is bounded by wait_limit_ns (a rank
+ *            that is absent or late): on expiry *d_out is NaN, the status word of family 7 gets
+ *            1 + the first missing rank (see thb200_kernel_status) and the stream stays usable.
+ *   reduce   push followed by fold.
+ * push and fold of one step must be issued in that order on every rank, steps in the same order
+ * on all ranks; `scratch` as for thb200_reduce_all. All ranks of one box must be able to store
+ * to each other (NVLink / PCIe peer access). */
+#define THB200_EXCHANGE_HANDLE_BYTES 128
+typedef struct thb200_exchange thb200_exchange;
+int thb200_exchange_create(int rank, int world, thb200_exchange** out, void* handle_out);
+int thb200_exchange_connect(thb200_exchange* x, const void* all_handles);
+int thb200_exchange_push(void* stream, thb200_exchange* x, int reduce, const thb200_tensor* in, float* scratch,
+                         size_t scratch_bytes);
+int thb200_exchange_fold(void* stream, thb200_exchange* x, int reduce, float* d_out, uint64_t wait_limit_ns);
+int thb200_exchange_reduce(void* stream, thb200_exchange* x, int reduce, const thb200_tensor* in, float* d_out,
+                           float* scratch, size_t scratch_bytes, uint64_t wait_limit_ns);
+int thb200_exchange_destroy(thb200_exchange* x);
 
 /* Bytes of scratch thb200_reduce_dim may need for this shape (0 if none). */
 size_t thb200_reduce_dim_scratch_bytes(const thb200_tensor* in, int dim);
