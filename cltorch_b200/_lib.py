@@ -221,6 +221,8 @@ PROTOTYPES = {
     "THClTensor_dot": (f, [S, T, T]),
     # thin ABI
     "thb200_last_error": (cp, []),
+    "thb200_timing_enable": (v, [i]), "thb200_timing_reset": (v, []),
+    "thb200_timing_report": (C.c_size_t, [C.c_char_p, C.c_size_t]),
     "thb200_collapse_dims": (i, [i, c_int64_p, c_int64_p, i, c_int64_p, c_int64_p]),
     "thb200_can_use_32bit_index": (i, [i, c_int64_p, c_int64_p]),
     "thb200_overlapping_indices": (i, [i, c_int64_p, c_int64_p]),

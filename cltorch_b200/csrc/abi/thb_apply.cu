@@ -273,6 +273,7 @@ int thb200_apply_plan(int ntensors, const thb200_tensor* t) {
 
 int thb200_apply_op(void* stream, int op, int ntensors, const thb200_tensor* t, float val1, float val2,
                     const float* point1, const float* point2) {
+  THB_TIMED(stream, "thb200_apply_op");
   const thb::ApplyKernels* k = thb::builtin_op(op);
   if (!k) return thb::fail("apply: unknown operator code %d", op);
   return thb::launch_apply(*k, (cudaStream_t)stream, ntensors, t, val1, val2, point1, point2, false, nullptr);
@@ -280,6 +281,7 @@ int thb200_apply_op(void* stream, int op, int ntensors, const thb200_tensor* t, 
 
 int thb200_apply_expr(void* stream, const char* body, int ntensors, const thb200_tensor* t, float val1,
                       float val2, const float* point1, const float* point2) {
+  THB_TIMED(stream, "thb200_apply_expr");
   if (!body) return thb::fail("apply: null expression");
   const thb::ApplyKernels* k = nullptr;
   if (int rc = thb::expr_kernels(ntensors, body, &k)) return rc;

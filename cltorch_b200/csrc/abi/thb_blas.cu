@@ -15,6 +15,7 @@ size_t thb200_dot_scratch_bytes(int64_t n) {
 
 int thb200_dot(void* stream, const float* a, const float* b, int64_t n, float* d_out, void* scratch,
                size_t scratch_bytes) {
+  THB_TIMED(stream, "thb200_dot");
   if (n < 0) return fail("dot: negative length");
   if (!d_out) return fail("dot: null output");
   if (n > 0 && (!a || !b)) return fail("dot: null operand");
@@ -61,6 +62,7 @@ size_t thb200_gemv_scratch_bytes(char trans, int64_t m, int64_t n) {
 
 int thb200_gemv(void* stream, char trans, int64_t m, int64_t n, float alpha, const float* a, int64_t lda, const float* x,
                 int64_t incx, float beta, float* y, int64_t incy, void* scratch, size_t scratch_bytes) {
+  THB_TIMED(stream, "thb200_gemv");
   const bool t = (trans == 't' || trans == 'T');
   if (!t && trans != 'n' && trans != 'N') return fail("gemv: trans must be 'n' or 't'");
   if (m < 0 || n < 0) return fail("gemv: negative extent");
@@ -134,6 +136,7 @@ int thb200_gemv(void* stream, char trans, int64_t m, int64_t n, float alpha, con
  * qualify, so that the caller can fall back to the pointwise operator. */
 int thb200_ger(void* stream, int64_t m, int64_t n, float alpha, const float* x, int64_t incx, const float* y, int64_t incy,
                float* a, int64_t lda, int alpha_on_x) {
+  THB_TIMED(stream, "thb200_ger");
   if (m < 0 || n < 0) return fail("ger: negative extent");
   if (m == 0 || n == 0) return 0;
   if (!x || !y || !a) return fail("ger: null operand");

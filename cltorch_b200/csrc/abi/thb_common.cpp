@@ -5,7 +5,12 @@
 #include <climits>
 #include <cstdarg>
 #include <cstdio>
+#include <atomic>
+#include <cstring>
+#include <map>
 #include <mutex>
+#include <string>
+#include <vector>
 
 namespace thb {
 
@@ -131,6 +136,94 @@ int thb200_overlapping_indices(int ndim, const int64_t* size, const int64_t* str
   for (int i = 1; i < k; ++i)
     if (d[i].first < d[i - 1].first * d[i - 1].second) return 1;
   return 0;
+}
+
+}  // extern "C"
+
+// ---- per-call device timing ---------------------------------------------------
+// The thin equivalent of cltorch.setProfiling / dumpProfiling and setEnableTiming / dumpTimings
+// (reference src/init.cpp:130-178): device time per entry point, from CUDA events on the call's stream.
+namespace thb {
+namespace {
+struct Pending { const char* name; cudaEvent_t start, stop; };
+struct Bucket { long calls = 0; double ms = 0.0; };
+std::mutex g_timing_mu;
+std::atomic<bool> g_timing_on{false};
+std::vector<Pending> g_pending;
+std::vector<cudaEvent_t> g_free_events;
+std::map<std::string, Bucket> g_buckets;
+
+cudaEvent_t take_event() {
+  if (!g_free_events.empty()) { cudaEvent_t e = g_free_events.back(); g_free_events.pop_back(); return e; }
+  cudaEvent_t e = nullptr;
+  if (cudaEventCreate(&e) != cudaSuccess) { cudaGetLastError(); return nullptr; }
+  return e;
+}
+// resolves every finished pair; with `wait`, waits for the unfinished ones too
+void drain(bool wait) {
+  std::vector<Pending> keep;
+  for (const Pending& p : g_pending) {
+    cudaError_t q = wait ? cudaEventSynchronize(p.stop) : cudaEventQuery(p.stop);
+    if (q == cudaErrorNotReady) { keep.push_back(p); continue; }
+    float ms = 0.f;
+    if (q == cudaSuccess && cudaEventElapsedTime(&ms, p.start, p.stop) == cudaSuccess) {
+      Bucket& b = g_buckets[p.name];
+      b.calls += 1;
+      b.ms += ms;
+    } else {
+      cudaGetLastError();
+    }
+    g_free_events.push_back(p.start);
+    g_free_events.push_back(p.stop);
+  }
+  g_pending.swap(keep);
+}
+}  // namespace
+
+CallTimer::CallTimer(void* stream, const char* name) {
+  if (!g_timing_on.load(std::memory_order_relaxed)) return;
+  std::lock_guard<std::mutex> lock(g_timing_mu);
+  start_ = take_event();
+  stop_ = take_event();
+  if (!start_ || !stop_) { start_ = stop_ = nullptr; return; }
+  stream_ = (cudaStream_t)stream;
+  name_ = name;
+  cudaEventRecord(start_, stream_);
+}
+CallTimer::~CallTimer() {
+  if (!start_) return;
+  cudaEventRecord(stop_, stream_);
+  std::lock_guard<std::mutex> lock(g_timing_mu);
+  g_pending.push_back(Pending{name_, start_, stop_});
+  if (g_pending.size() > 4096) drain(false);
+}
+}  // namespace thb
+
+extern "C" {
+
+void thb200_timing_enable(int on) { thb::g_timing_on.store(on != 0, std::memory_order_relaxed); }
+
+void thb200_timing_reset(void) {
+  std::lock_guard<std::mutex> lock(thb::g_timing_mu);
+  thb::drain(true);
+  thb::g_buckets.clear();
+}
+
+size_t thb200_timing_report(char* buf, size_t capacity) {
+  std::lock_guard<std::mutex> lock(thb::g_timing_mu);
+  thb::drain(true);
+  std::string out;
+  char line[256];
+  for (const auto& kv : thb::g_buckets) {
+    snprintf(line, sizeof line, "%s %ld %.6f\n", kv.first.c_str(), kv.second.calls, kv.second.ms);
+    out += line;
+  }
+  if (buf && capacity > 0) {
+    size_t n = out.size() < capacity - 1 ? out.size() : capacity - 1;
+    memcpy(buf, out.data(), n);
+    buf[n] = 0;
+  }
+  return out.size() + 1;
 }
 
 }  // extern "C"

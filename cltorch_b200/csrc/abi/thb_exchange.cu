@@ -117,6 +117,7 @@ int thb200_exchange_connect(thb200_exchange* x, const void* all_handles) {
 }
 
 int thb200_exchange_push(void* stream, thb200_exchange* x, int reduce, const thb200_tensor* in, float* scratch, size_t scratch_bytes) {
+  THB_TIMED(stream, "thb200_exchange_push");
   if (!x || !x->connected) return fail("exchange: not connected");
   const unsigned int epoch = x->epoch + 1;
   const int parity = (int)(epoch & 1u);
@@ -127,6 +128,7 @@ int thb200_exchange_push(void* stream, thb200_exchange* x, int reduce, const thb
 }
 
 int thb200_exchange_fold(void* stream, thb200_exchange* x, int reduce, float* d_out, uint64_t wait_limit_ns) {
+  THB_TIMED(stream, "thb200_exchange_fold");
   if (!x || !x->connected) return fail("exchange: not connected");
   if (!d_out) return fail("exchange: null result pointer");
   if (x->epoch == 0) return fail("exchange: fold before the first push");

@@ -142,6 +142,7 @@ size_t thb200_gemm_workspace_bytes(int64_t m, int64_t n, int64_t k, int64_t batc
 int thb200_gemm(void* stream, char transa, char transb, int64_t m, int64_t n, int64_t k, float alpha, const float* a,
                 int64_t lda, const float* b, int64_t ldb, float beta, float* c, int64_t ldc, int64_t batch,
                 int64_t stride_a, int64_t stride_b, int64_t stride_c, void* workspace, size_t workspace_bytes) {
+  THB_TIMED(stream, "thb200_gemm");
   cudaStream_t st = (cudaStream_t)stream;
   const bool ta = (transa == 't' || transa == 'T'), tb = (transb == 't' || transb == 'T');
   if (!ta && transa != 'n' && transa != 'N') return fail("gemm: transa must be 'n' or 't'");

@@ -18,6 +18,18 @@ int fail_cuda(cudaError_t e, const char* what);
     if (thb_e_ != cudaSuccess) return ::thb::fail_cuda(thb_e_, #expr); \
   } while (0)
 
+// Per-call device timing (thb200_timing_*): when switched on, an entry point brackets what it
+// enqueues with two CUDA events on its stream; thb200_timing_report resolves them. Off by default:
+// the object then does nothing (no event is created, nothing is recorded).
+struct CallTimer {
+  CallTimer(void* stream, const char* name);
+  ~CallTimer();
+  cudaEvent_t start_ = nullptr, stop_ = nullptr;
+  cudaStream_t stream_ = nullptr;
+  const char* name_ = nullptr;
+};
+#define THB_TIMED(stream, name) ::thb::CallTimer thb_call_timer_((stream), (name))
+
 struct Collapsed {
   int dims = 0;
   int64_t size[THB200_MAX_DIMS];

@@ -446,11 +446,13 @@ extern "C" {
 int thb200_reduce_all(void* stream, int modify, int reduce, const thb200_tensor* in, float init, float mod_param,
                       const float* mod_point, int fin, float fin_param, float* d_out, float* scratch,
                       size_t scratch_bytes) {
+  THB_TIMED(stream, "thb200_reduce_all");
   return reduce_all_impl(stream, modify, reduce, in, init, mod_param, mod_point, fin, fin_param, d_out, scratch, scratch_bytes,
                          nullptr, 0, 0);
 }
 
 int thb200_fold_partials(void* stream, int reduce, const float* d_partials, int count, float* d_out) {
+  THB_TIMED(stream, "thb200_fold_partials");
   if (!d_partials || !d_out || count < 1 || count > 1024) return fail("fold_partials: bad arguments");
   FoldArgs a;
   a.st = (cudaStream_t)stream;
@@ -570,6 +572,7 @@ static int reduce_dim_impl(void* stream, int modify, int reduce, const thb200_te
 
 int thb200_reduce_dim(void* stream, int modify, int reduce, const thb200_tensor* out, const thb200_tensor* in, int dim,
                       float init, float mod_param, float* scratch, size_t scratch_bytes) {
+  THB_TIMED(stream, "thb200_reduce_dim");
   if (reduce >= 100) return fail("reduceDim: unknown reduce op %d", reduce);
   return reduce_dim_impl(stream, modify, reduce, out, in, dim, init, mod_param, scratch, scratch_bytes, sizeof(double));
 }
@@ -580,6 +583,7 @@ size_t thb200_var_dim_scratch_bytes(const thb200_tensor* in, int dim) {
 
 int thb200_var_dim(void* stream, const thb200_tensor* out, const thb200_tensor* in, int dim, int biased, int apply_sqrt,
                    float* scratch, size_t scratch_bytes) {
+  THB_TIMED(stream, "thb200_var_dim");
   return reduce_dim_impl(stream, THB200_MOD_COPY, moments_code(biased, apply_sqrt), out, in, dim, 0.f, 0.f, scratch,
                          scratch_bytes, sizeof(ThbMoments));
 }
@@ -588,6 +592,7 @@ size_t thb200_var_all_scratch_bytes(int64_t n) { return (size_t)reduce_all_block
 
 int thb200_var_all(void* stream, const thb200_tensor* in, int biased, int apply_sqrt, float* d_out, float* scratch,
                    size_t scratch_bytes) {
+  THB_TIMED(stream, "thb200_var_all");
   if (!in || !d_out) return fail("varall: null argument");
   if (in->ndim > THB200_MAX_DIMS) return fail("varall: too many dimensions");
   ReduceAllArgs a;
@@ -627,6 +632,7 @@ size_t thb200_reduce_dim_index_scratch_bytes(int64_t outer, int64_t n, int64_t i
 
 int thb200_reduce_dim_index(void* stream, int is_max, float* values, float* indices, const float* src, int64_t outer,
                             int64_t n, int64_t inner, float* scratch, size_t scratch_bytes) {
+  THB_TIMED(stream, "thb200_reduce_dim_index");
   if (outer < 0 || n < 0 || inner < 0) return fail("max/min: negative extent");
   if (outer * inner == 0 || n == 0) return 0;
   if (!values || !indices || !src) return fail("max/min: null pointer");

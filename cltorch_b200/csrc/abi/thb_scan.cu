@@ -142,6 +142,7 @@ size_t thb200_scan_scratch_bytes(const float* dst, const float* src, int64_t out
 
 int thb200_scan(void* stream, int op, float* dst, const float* src, int64_t outer, int64_t n, int64_t inner,
                 void* scratch, size_t scratch_bytes, int* d_status) {
+  THB_TIMED(stream, "thb200_scan");
   if (outer < 0 || n < 0 || inner < 0) return fail("scan: negative extent");
   if (outer == 0 || n == 0 || inner == 0) return 0;
   if (!dst || !src) return fail("scan: null pointer");
@@ -163,6 +164,7 @@ size_t thb200_renorm_rows_scratch_bytes(int64_t rows, int64_t size) {
 
 int thb200_renorm_rows(void* stream, float* data, int64_t rows, int64_t size, float p, float maxnorm, void* scratch,
                        size_t scratch_bytes) {
+  THB_TIMED(stream, "thb200_renorm_rows");
   if (rows < 0 || size < 0) return fail("renorm: negative extent");
   if (rows == 0 || size == 0) return 0;
   if (!data) return fail("renorm: null pointer");
@@ -188,6 +190,7 @@ size_t thb200_dist_scratch_bytes(int64_t n) { return (size_t)dist_blocks(n) * si
 
 int thb200_dist(void* stream, const float* a, const float* b, int64_t n, float p, float* d_out, void* scratch,
                 size_t scratch_bytes) {
+  THB_TIMED(stream, "thb200_dist");
   if (n < 0) return fail("dist: negative length");
   if (!d_out) return fail("dist: null output");
   if (n > 0 && (!a || !b)) return fail("dist: null pointer");

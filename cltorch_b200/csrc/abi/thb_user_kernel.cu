@@ -49,6 +49,7 @@ static const char* kOpenClPrelude =
     "#define CLK_LOCAL_MEM_FENCE 1\n"
     "#define CLK_GLOBAL_MEM_FENCE 2\n"
     "#define barrier(flags) __syncthreads()\n"
+    "#define thb_mem_fence(flags) __threadfence_block()\n"
     "#define mad(a, b, c) ((a) * (b) + (c))\n";
 
 // The OpenCL address-space words cannot be macros (CUDA's own __global__ / __shared__ expand
@@ -80,9 +81,22 @@ static std::string translate_opencl_words(const std::string& in) {
       size_t e = i;
       while (e < n && (isalnum((unsigned char)in[e]) || in[e] == '_')) ++e;
       const std::string id = in.substr(i, e - i);
-      if (id == "global" || id == "__global") out += "";
-      else if (id == "local" || id == "__local") out += "__shared__";
-      else out += id;
+      if (id == "global" || id == "__global" || id == "kernel" || id == "__kernel") {
+        out += "";
+      } else if (id == "constant" || id == "__constant" || id == "local" || id == "__local") {
+        // A declared object ("local float buf[64];", "constant float w[2] = {...};") becomes a
+        // __shared__ / __constant__ object. Where the word qualifies a pointer ("float f(local float*
+        // buf)", a '*' follows before the declaration ends) CUDA spells the pointer without it.
+        size_t q = e;
+        while (q < n && in[q] != '*' && in[q] != ';' && in[q] != ',' && in[q] != ')' && in[q] != '[' && in[q] != '=' && in[q] != '{') ++q;
+        const bool pointer = q < n && in[q] == '*';
+        if (id == "local" || id == "__local") out += pointer ? "" : "__shared__";
+        else out += pointer ? "const" : "__constant__";
+      } else if (id == "mem_fence" || id == "read_mem_fence" || id == "write_mem_fence") {
+        out += "thb_mem_fence";
+      } else {
+        out += id;
+      }
       i = e;
     } else if (isdigit((unsigned char)c)) {  // a number may contain letters (1e5f, 0x1F): copy it whole
       size_t e = i;
@@ -184,6 +198,7 @@ const char* thb200_user_kernel_rendered(const thb200_user_kernel* k) { return k 
 
 int thb200_user_kernel_run(void* stream, thb200_user_kernel* k, const thb200_user_arg* args, int nargs,
                            int workgroup_size, int64_t num_workgroups) {
+  THB_TIMED(stream, "thb200_user_kernel_run");
   if (!k) return fail("user kernel: null kernel");
   if (nargs != (int)k->kinds.size()) return fail("user kernel: %d arguments given, %d declared", nargs, (int)k->kinds.size());
   if (nargs > 0 && !args) return fail("user kernel: null argument array");

@@ -211,14 +211,28 @@ static void reduce_dim_index(THClState* state, THClTensor* values_, THClTensor* 
   THClTensor_resize(state, values_, sizes, nullptr);
   THClTensor_resize(state, indices_, sizes, nullptr);
   THLongStorage_free(sizes);
-  // as the reference: contiguous copies of all three (src/lib/THClTensorMathTransformReduce.cpp:172-174)
+  // The reference makes contiguous copies of all three (src/lib/THClTensorMathTransformReduce.cpp:172-174).
+  // The copy of the source is skipped for the transposed view of a contiguous matrix: reducing it
+  // along one dimension is reducing the matrix underneath along the other, positions along the
+  // reduced dimension and the order of the results are the same, so the kernels run on the
+  // storage as it lies (a transposed 1 GiB input would otherwise pay 8 bytes per element for the
+  // copy before a 4-byte-per-element reduction).
   THClTensor* values = THClTensor_newContiguous(state, values_);
   THClTensor* indices = THClTensor_newContiguous(state, indices_);
-  THClTensor* in = THClTensor_newContiguous(state, src);
-  int64_t outer = 1, inner = 1;
-  for (int d = 0; d < dim; ++d) outer *= in->size[d];
-  for (int d = (int)dim + 1; d < in->nDimension; ++d) inner *= in->size[d];
-  const int64_t n = in->size[dim];
+  const bool transposed2d = src->nDimension == 2 && src->size[0] > 1 && src->size[1] > 1 && src->stride[0] == 1 &&
+                            src->stride[1] == src->size[0];
+  THClTensor* in = transposed2d ? src : THClTensor_newContiguous(state, src);
+  int64_t outer = 1, inner = 1, n = 0;
+  if (transposed2d) {
+    // underneath: a contiguous size[1] x size[0] matrix; dimension `dim` of the view is dimension 1 - dim there
+    n = src->size[dim];
+    if (dim == 0) outer = src->size[1];   // innermost dimension of the matrix underneath
+    else inner = src->size[0];            // its outer dimension
+  } else {
+    for (int d = 0; d < dim; ++d) outer *= in->size[d];
+    for (int d = (int)dim + 1; d < in->nDimension; ++d) inner *= in->size[d];
+    n = in->size[dim];
+  }
   THClDeviceContext* ctx = context(state, src->device);
   use_device(src->device);
   size_t need = thb200_reduce_dim_index_scratch_bytes(outer, n, inner);
@@ -226,7 +240,7 @@ static void reduce_dim_index(THClState* state, THClTensor* values_, THClTensor* 
   int rc = thb200_reduce_dim_index(ctx->stream, is_max, THClTensor_data(state, values), THClTensor_data(state, indices),
                                    THClTensor_data(state, in), outer, n, inner, scratch, ctx->scratch_bytes);
   std::string err = rc ? thb200_last_error() : "";
-  THClTensor_free(state, in);
+  if (!transposed2d) THClTensor_free(state, in);
   THClTensor_freeCopyTo(state, values, values_);
   THClTensor_freeCopyTo(state, indices, indices_);
   if (rc) raise("%s", err.c_str());
@@ -772,21 +786,46 @@ void THClTensor_renorm(THClState* state, THClTensor* self, THClTensor* src, floa
   THCL_END_VOID
 }
 
+// Both tensors have the same sizes and strides, and those strides are a permutation of a contiguous
+// layout: the elements fill [data, data + nElement) without gaps, in the same order in both.
+static bool same_dense_layout(const THClTensor* a, const THClTensor* b) {
+  if (a->nDimension != b->nDimension || a->nDimension < 1 || a->nDimension > 8) return false;
+  int order[8], nd = 0;
+  for (int d = 0; d < a->nDimension; ++d) {
+    if (a->size[d] != b->size[d] || a->stride[d] != b->stride[d]) return false;
+    if (a->size[d] == 0) return false;
+    if (a->size[d] > 1) order[nd++] = d;
+  }
+  for (int i = 1; i < nd; ++i)           // by ascending stride
+    for (int j = i; j > 0 && a->stride[order[j]] < a->stride[order[j - 1]]; --j) { int t = order[j]; order[j] = order[j - 1]; order[j - 1] = t; }
+  long expect = 1;
+  for (int i = 0; i < nd; ++i) {
+    if (a->stride[order[i]] != expect) return false;
+    expect *= a->size[order[i]];
+  }
+  return true;
+}
+
 static void dist_into(THClState* state, THClTensor* self, THClTensor* src, float value, float* d_out) {
   if (self->device != src->device) raise("tensors are on different devices");
   arg_check(THClTensor_nElement(state, self) == THClTensor_nElement(state, src), 2, "sizes do not match");
   THClDeviceContext* ctx = context(state, self->device);
   use_device(self->device);
-  // contiguous copies of both, as src/lib/THClTensorMath2.cpp:463-465
-  THClTensor* a = THClTensor_newContiguous(state, self);
-  THClTensor* b = THClTensor_newContiguous(state, src);
-  const long n = THClTensor_nElement(state, a);
+  // contiguous copies of both, as src/lib/THClTensorMath2.cpp:463-465 - unless the two tensors lie in
+  // memory in the same way and without gaps (e.g. both transposed): the distance is a sum over pairs of
+  // elements, and walking both storages front to back pairs the same elements
+  const bool same_dense = same_dense_layout(self, src);
+  THClTensor* a = same_dense ? self : THClTensor_newContiguous(state, self);
+  THClTensor* b = same_dense ? src : THClTensor_newContiguous(state, src);
+  const long n = THClTensor_nElement(state, self);
   void* scratch = ensure_scratch(ctx, thb200_dist_scratch_bytes(n));
   int rc = thb200_dist(ctx->stream, THClTensor_data(state, a), THClTensor_data(state, b), n, value, d_out, scratch,
                        ctx->scratch_bytes);
   std::string err = rc ? thb200_last_error() : "";
-  THClTensor_free(state, a);
-  THClTensor_free(state, b);
+  if (!same_dense) {
+    THClTensor_free(state, a);
+    THClTensor_free(state, b);
+  }
   if (rc) raise("%s", err.c_str());
   after_launch(state, ctx);
 }

@@ -96,6 +96,32 @@ def setAddFinish(on: int) -> None:
     _STATE.addFinish = int(on)
 
 
+def setProfiling(on: int) -> None:
+    """cltorch.setProfiling / setEnableTiming (reference src/init.cpp:130-178): device time per library call."""
+    lib().thb200_timing_enable(int(on))
+
+
+setEnableTiming = setProfiling
+
+
+def dumpProfiling(reset: bool = True) -> dict:
+    """cltorch.dumpProfiling / dumpTimings: {entry point: (calls, total milliseconds)} since the last dump."""
+    L = lib()
+    need = L.thb200_timing_report(None, 0)
+    buf = C.create_string_buffer(need + 4096)
+    L.thb200_timing_report(buf, len(buf))
+    out = {}
+    for line in buf.value.decode().splitlines():
+        name, calls, ms = line.split()
+        out[name] = (int(calls), float(ms))
+    if reset:
+        L.thb200_timing_reset()
+    return out
+
+
+dumpTimings = dumpProfiling
+
+
 def getStream(device: Optional[int] = None) -> int:
     dev = _STATE.currentDevice if (device is None and _STATE is not None) else ((device or 1) - 1)
     return call("THClState_getStream", state(), dev) or 0

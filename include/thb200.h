@@ -83,6 +83,18 @@ int thb200_apply_expr(void* stream, const char* body, int ntensors, const thb200
  * -1 if `cap` is too small. */
 int thb200_rewrite_expr(const char* expr, int ntensors, char* out, size_t cap);
 
+/* ---- per-call device timing -------------------------------------------------
+ * The thin equivalent of cltorch.setProfiling / dumpProfiling and setEnableTiming / dumpTimings
+ * (src/init.cpp:130-178, EasyCL event profiling and StatefulTimer buckets): while switched on,
+ * every entry point of this header that takes a stream brackets what it enqueues with two CUDA
+ * events. thb200_timing_report waits for the outstanding events and writes one line per entry
+ * point, "<name> <calls> <total milliseconds>", into buf (NUL-terminated, truncated to capacity);
+ * it returns the size the whole report needs. Off by default; thb200_reduce_dim_noalloc is never
+ * timed (events are driver allocations). */
+void thb200_timing_enable(int on);
+void thb200_timing_reset(void);
+size_t thb200_timing_report(char* buf, size_t capacity);
+
 /* ---- reductions ----------------------------------------------------------- */
 
 enum thb200_modify { THB200_MOD_COPY = 0, THB200_MOD_ABSPOW = 1, THB200_MOD_NEZERO = 2, THB200_MOD_SQDEV = 3 };

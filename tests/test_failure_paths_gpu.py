@@ -59,3 +59,29 @@ def test_selftest_rejects_unbounded_limits():
     assert L.thb200_selftest_wait_expiry(stream, 5_000_000_000, 1) != 0
     assert L.thb200_selftest_wait_expiry(stream, 1000, 0) != 0
     assert L.thb200_kernel_status(stream) == 0
+
+
+def test_per_call_device_timing_counts_calls_and_time():
+    """cltorch.setProfiling(1) ... cltorch.dumpProfiling(): one bucket per entry point with its call count and
+    the device time between the events that bracket its launches."""
+    import cltorch_b200 as cl
+    cl.setDevice(1)
+    a = cl.ClTensor(np.ones((2048, 2048), np.float32))
+    b = cl.ClTensor(np.full((2048, 2048), 2.0, np.float32))
+    assert cl.dumpProfiling() == {}                       # off: nothing is recorded
+    a.add(b)
+    assert cl.dumpProfiling() == {}
+    cl.setProfiling(1)
+    for _ in range(5):
+        a.add(b)
+    s = cl.ClTensor().sum(a)
+    m, i = a.max(1)
+    cl.setProfiling(0)
+    a.add(b)                                               # not recorded any more
+    prof = cl.dumpProfiling()
+    assert prof["thb200_apply_op"][0] == 5
+    assert prof["thb200_reduce_all"][0] == 1 and prof["thb200_reduce_dim_index"][0] == 1
+    # 5 x 48 MiB of traffic cannot take less than 30 us of device time, nor as long as a second
+    assert 0.03 < prof["thb200_apply_op"][1] < 1000.0
+    assert cl.dumpProfiling() == {}                       # dumped and reset
+    assert s.s() == float(2048 * 2048 * 11)

@@ -174,6 +174,26 @@ def test_max_min_with_indices_each_dim(shape):
             assert np.array_equal(i.long().squeeze(d), first)
 
 
+@pytest.mark.parametrize("shape", [(5, 7), (300, 257), (3000, 5000), (4096, 2048), (70000, 3), (3, 70000)])
+def test_max_min_of_a_transposed_view_runs_on_the_storage_as_it_lies(shape):
+    """max / min of A:t() along either dimension: same values and 1-based positions as for a contiguous copy of the
+    transposed matrix (the front-end reduces the matrix underneath along the other dimension instead of copying)."""
+    import cltorch_b200 as cl
+    g = np.random.Generator(np.random.PCG64(36))
+    a = g.integers(-9, 10, size=shape).astype(np.float32)
+    a[0, 0] = np.nan
+    At = cl.ClTensor(a).t()
+    at = np.ascontiguousarray(a.T)
+    for d in (0, 1):
+        for name, is_max in (("max", True), ("min", False)):
+            v, i = getattr(At, name)(d + 1)
+            wv, wi = O.reduce_dim_index(at, d, is_max)
+            assert v.size() == list(wv.shape) and v.isContiguous()
+            assert np.array_equal(v.float(), wv), (name, d)
+            assert np.array_equal(i.float(), wi), (name, d)
+    assert np.array_equal(At.float()[1:], at[1:])                        # the source is untouched
+
+
 def test_max_min_index_corner_cases():
     import cltorch_b200 as cl
     a = np.array([[np.nan, 1, 3, 3], [-np.inf, -np.inf, -np.inf, -np.inf], [2, np.nan, 2, 1]], np.float32)

@@ -109,6 +109,34 @@ def test_helper_functions_float_arguments_inout_and_local_memory():
 
 
 @pytest.mark.gpu
+def test_opencl_qualifiers_in_helper_functions():
+    """OpenCL spellings that helper functions of existing ClKernel sources use: a `local` pointer parameter,
+    a `constant` table, the `kernel` word and mem_fence."""
+    import cltorch_b200 as cl
+    n = 64 * 5
+    a = rng_uniform(74, (n,), -1, 1)
+    t = cl.ClTensor(a)
+    k = cl.ClKernel({
+        "inout": {"data": "torch.ClTensor"}, "input": {"n": "int"},
+        "funcs": """
+          constant float weights[2] = {2.0f, 0.5f};
+          float pick(local float* buf, int i) { return buf[i] * weights[i & 1]; }
+        """,
+        "src": """
+          local float buf[64];
+          int lid = get_local_id(0), gid = get_global_id(0);
+          buf[lid] = gid < n ? data_data[gid] : 0.0f;
+          mem_fence(CLK_LOCAL_MEM_FENCE);
+          barrier(CLK_LOCAL_MEM_FENCE);
+          if (gid < n) data_data[gid] = pick(buf, lid ^ 1);
+        """})
+    k.run({"data": t, "n": n})
+    src = a.reshape(-1, 2)[:, ::-1].reshape(-1)               # neighbour within each pair
+    w = np.where(np.arange(n) % 2 == 0, np.float32(0.5), np.float32(2.0))   # weight of the neighbour's slot
+    assert np.array_equal(t.float(), (src * w).astype(np.float32))
+
+
+@pytest.mark.gpu
 def test_run_and_compile_errors():
     import cltorch_b200 as cl
     x = cl.ClTensor(np.zeros(4, np.float32))
