@@ -190,14 +190,22 @@ int thb200_gemm(void* stream, char transa, char transb, int64_t m, int64_t n, in
   // op(A)(i, kk): column-major A, 'n': a[i + kk*lda] (unit stride along i), 't': a[kk + i*lda]
   if (mode == MODE_PREPASS) {
     dim3 grid((unsigned)(Kp / 32), (unsigned)((m + 31) / 32), (unsigned)batch);
-    if (!ta) thb_gemm_split<true><<<grid, 256, 0, st>>>(a, 1, lda, stride_a, w.a, (int)m, (int)k, (int)Kp);
+    const bool rows_v4 = ta && ((uintptr_t)a & 15) == 0 && (lda & 3) == 0 && (batch == 1 || (stride_a & 3) == 0);
+    if (rows_v4) {
+      dim3 g4((unsigned)((Kp + 127) / 128), (unsigned)((m + 7) / 8), (unsigned)batch);
+      thb_gemm_split_rows_v4<<<g4, 256, 0, st>>>(a, lda, stride_a, w.a, (int)m, (int)k, (int)Kp);
+    } else if (!ta) thb_gemm_split<true><<<grid, 256, 0, st>>>(a, 1, lda, stride_a, w.a, (int)m, (int)k, (int)Kp);
     else thb_gemm_split<false><<<grid, 256, 0, st>>>(a, lda, 1, stride_a, w.a, (int)m, (int)k, (int)Kp);
     THB_CUDA(cudaGetLastError());
   }
   // B' row j, column kk = op(B)(kk, j): 'n': b[kk + j*ldb] (unit stride along kk), 't': b[j + kk*ldb]
   if (!fused) {
     dim3 grid((unsigned)(Kp / 32), (unsigned)((n + 31) / 32), (unsigned)batch);
-    if (!tb) thb_gemm_split<false><<<grid, 256, 0, st>>>(b, ldb, 1, stride_b, w.b, (int)n, (int)k, (int)Kp);
+    const bool rows_v4 = !tb && ((uintptr_t)b & 15) == 0 && (ldb & 3) == 0 && (batch == 1 || (stride_b & 3) == 0);
+    if (rows_v4) {
+      dim3 g4((unsigned)((Kp + 127) / 128), (unsigned)((n + 7) / 8), (unsigned)batch);
+      thb_gemm_split_rows_v4<<<g4, 256, 0, st>>>(b, ldb, stride_b, w.b, (int)n, (int)k, (int)Kp);
+    } else if (!tb) thb_gemm_split<false><<<grid, 256, 0, st>>>(b, ldb, 1, stride_b, w.b, (int)n, (int)k, (int)Kp);
     else thb_gemm_split<true><<<grid, 256, 0, st>>>(b, 1, ldb, stride_b, w.b, (int)n, (int)k, (int)Kp);
     THB_CUDA(cudaGetLastError());
   }

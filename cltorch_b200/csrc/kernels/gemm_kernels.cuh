@@ -103,6 +103,32 @@ thb_gemm_split(const float* __restrict__ src, long long sr, long long sk, long l
   }
 }
 
+// The same split for a K-major source (unit stride along k) whose rows start on 16-byte boundaries:
+// one thread takes 4 consecutive k of one row with 128-bit accesses. Block = 32 x 8 threads = 128 k x 8 rows.
+static __global__ void __launch_bounds__(256)
+thb_gemm_split_rows_v4(const float* __restrict__ src, long long sr, long long batch_stride_src, float* __restrict__ dst,
+                       int rows, int K, int Kp) {
+  const int b = blockIdx.z;
+  const int k = (blockIdx.x * 32 + (threadIdx.x & 31)) * 4;
+  const int r = blockIdx.y * 8 + (threadIdx.x >> 5);
+  if (r >= rows || k >= Kp) return;
+  const float* s = src + (long long)b * batch_stride_src + (long long)r * sr + k;
+  float4 x = make_float4(0.f, 0.f, 0.f, 0.f);
+  if (k + 3 < K) {
+    x = *reinterpret_cast<const float4*>(s);
+  } else {
+    if (k < K) x.x = s[0];
+    if (k + 1 < K) x.y = s[1];
+    if (k + 2 < K) x.z = s[2];
+  }
+  float4 h;
+  h.x = thb_round_tf32(x.x); h.y = thb_round_tf32(x.y); h.z = thb_round_tf32(x.z); h.w = thb_round_tf32(x.w);
+  float* hi = dst + ((long long)b * 2 + 0) * rows * (long long)Kp + (long long)r * Kp + k;
+  float* lo = dst + ((long long)b * 2 + 1) * rows * (long long)Kp + (long long)r * Kp + k;
+  *reinterpret_cast<float4*>(hi) = h;
+  *reinterpret_cast<float4*>(lo) = make_float4(x.x - h.x, x.y - h.y, x.z - h.z, x.w - h.w);
+}
+
 // ---- PTX helpers (mbarrier and TMA ones are in tma_pipeline.cuh) ------------
 // Shared-memory matrix descriptor of a K-major tile whose rows are one swizzle
 // span long: BK = 32 floats -> 128-byte swizzle (8-row groups 1024 bytes apart),

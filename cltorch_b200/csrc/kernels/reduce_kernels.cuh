@@ -33,7 +33,14 @@ __device__ __forceinline__ float thb_abs_pow(float d, float p) {
 
 // kFirst: the operator wants the first element of the slice as its third argument.
 struct ModCopy { static constexpr bool kFirst = false; static __device__ __forceinline__ float apply(float x, float, float) { return x; } };
-struct ModAbsPow { static constexpr bool kFirst = false; static __device__ __forceinline__ float apply(float x, float p, float) { return thb_abs_pow(x, p); } };
+// General exponent (the host routes p = 1, 2, 3 to the operators below, so no comparison of p is left in
+// the loop): |x|^p = 2^(p log2|x|) on the special-function unit. p == 0 gives 1 for every x, also for 0.
+__device__ __forceinline__ float thb_abs_pow_general(float x, float p) {
+  float r;
+  asm("ex2.approx.f32 %0, %1;" : "=f"(r) : "f"(p * __log2f(fabsf(x))));
+  return p == 0.0f ? 1.0f : r;
+}
+struct ModAbsPow { static constexpr bool kFirst = false; static __device__ __forceinline__ float apply(float x, float p, float) { return thb_abs_pow_general(x, p); } };
 // |x|^p for the exponents norms are usually taken with: the host picks these when p is 1, 2 or 3,
 // so that the loop carries no comparison of p per element.
 struct ModAbs { static constexpr bool kFirst = false; static __device__ __forceinline__ float apply(float x, float, float) { return fabsf(x); } };

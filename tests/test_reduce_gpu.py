@@ -188,7 +188,7 @@ def test_max_min_of_a_transposed_view_runs_on_the_storage_as_it_lies(shape):
         for name, is_max in (("max", True), ("min", False)):
             v, i = getattr(At, name)(d + 1)
             wv, wi = O.reduce_dim_index(at, d, is_max)
-            assert v.size() == list(wv.shape) and v.isContiguous()
+            assert tuple(v.size()) == tuple(wv.shape) and v.isContiguous()
             assert np.array_equal(v.float(), wv), (name, d)
             assert np.array_equal(i.float(), wi), (name, d)
     assert np.array_equal(At.float()[1:], at[1:])                        # the source is untouched
