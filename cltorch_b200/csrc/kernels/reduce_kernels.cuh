@@ -172,16 +172,16 @@ __device__ __forceinline__ typename Red::acc_t thb_block_fold(typename Red::acc_
 // whole-tensor reduction is one launch. `ticket` counts the finished blocks (zero before the
 // launch; the last block puts it back to zero); ticket == nullptr: a separate pass 2 does the fold.
 struct ThbFinish {
-  unsigned int* ticket;
-  int fin;       // THB_FIN_*, ignored by the moments reductions
-  float fparam;  // divisor of the finaliser; element count for the moments
-  float* out;
+  unsigned int* ticket = nullptr;
+  int fin = 0;         // THB_FIN_*, ignored by the moments reductions
+  float fparam = 1.f;  // divisor of the finaliser; element count for the moments
+  float* out = nullptr;
   // Cross-GPU exchange (null otherwise): the block that writes the scalar also stores
   // (epoch << 32 | bits of the scalar) into push_cells[0 .. push_count), one 8-byte cell in the
   // memory of every GPU of the group (this GPU's own cell included), with plain stores.
-  unsigned long long* const* push_cells;
-  int push_count;
-  unsigned int push_epoch;
+  unsigned long long* const* push_cells = nullptr;
+  int push_count = 0;
+  unsigned int push_epoch = 0;
 };
 
 // One 8-byte store / load at system scope: whole or not at all, also across NVLink.
