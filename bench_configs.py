@@ -370,6 +370,17 @@ def c4small(T):
     T.time(f"addmm {M}x{N}x{K}", lambda: C.addmm(1.0, C, 1.0, A, B), flops=2.0 * M * N * K, setup=lambda: C.zero())
 
 
+def c4mlp(T):
+    """The 512 x 4096 x 4096 addmm alone (profiler captures of the tensor-memory GEMM and the split-K fix-up)."""
+    cl = T.cl
+    g = np.random.Generator(np.random.PCG64(3))
+    M, N, K = 512, 4096, 4096
+    lim = 1.0 / np.sqrt(K)
+    A, B = cl.ClTensor(_uniform(g, (M, K), -lim, lim)), cl.ClTensor(_uniform(g, (K, N), -lim, lim))
+    C = cl.ClTensor(M, N).zero()
+    T.time(f"addmm {M}x{N}x{K}", lambda: C.addmm(1.0, C, 1.0, A, B), flops=2.0 * M * N * K, setup=lambda: C.zero())
+
+
 def c2small(T):
     """Transpose and column-narrowed adds on 4096 x 4096 (profiler captures of the strided kernels)."""
     cl = T.cl
@@ -460,7 +471,7 @@ def n3small(T):
     T.time("dist(A, B, 2) -> point tensor", lambda: pt.dist_gpu(A, B, 2), 8 * n * n)
 
 
-GROUPS = {"c1": c1, "c2": c2, "c3": c3, "c4": c4, "c4small": c4small, "c4batched": c4batched, "c2small": c2small,
+GROUPS = {"c1": c1, "c2": c2, "c3": c3, "c4": c4, "c4small": c4small, "c4batched": c4batched, "c4mlp": c4mlp, "c2small": c2small,
           "c3small": c3small, "n1": n1, "n3": n3, "n3small": n3small}
 
 
