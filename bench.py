@@ -301,6 +301,15 @@ def run_gpu(args):
     if world > 1:
         dist.all_reduce(times, op=dist.ReduceOp.MAX)
     elapsed_ms, e2e_ms, alt_ms = times.tolist()
+    # every rank's own kernel windows: the step waits for the slowest GPU at the exchange
+    mine = torch.tensor([statistics.mean(e[i].elapsed_time(e[i + 1]) for e in step_events) for i in range(3)],
+                        dtype=torch.float64, device="cuda")
+    per_rank = [torch.zeros_like(mine) for _ in range(world)]
+    if world > 1:
+        dist.all_gather(per_rank, mine)
+    else:
+        per_rank = [mine]
+    per_rank = [[round(v, 4) for v in t.tolist()] for t in per_rank]
 
     # parity of the sharded sum: double-precision host sums of the same pinned shards, block by block
     block_sums = host_oracle_block_sums(host, begin, n_total, host_threads() // world).cuda()
@@ -345,7 +354,10 @@ def run_gpu(args):
                                      "scaled by the elements of a launch",
                      "per_kernel_gbs": {"apply_axpb": achieved, "apply_sqrt": 8 * n_local / (k_apply2 * 1e-3) / 1e9,
                                         "reduce_all_sum": 4 * n_local / (k_sum * 1e-3) / 1e9},
-                     "per_kernel_ms": {"apply_axpb": k_apply, "apply_sqrt": k_apply2, "sum_and_exchange": k_sum}},
+                     "per_kernel_ms": {"apply_axpb": k_apply, "apply_sqrt": k_apply2, "sum_and_exchange": k_sum},
+                     "per_rank_kernel_ms": {"columns": ["apply_axpb", "apply_sqrt", "sum_and_exchange"], "ranks": per_rank,
+                                            "note": "mean CUDA-event windows on each rank; the third window ends when the "
+                                                    "slowest rank's partial has arrived"}},
         "e2e": {"value": BYTES_PER_ELT * n_total / (e2e_ms / e2e_steps * 1e-3) / 1e9, "unit": "GB/s",
                 "h2d_bytes_per_step": 4 * n_local, "d2h_bytes_per_step": 4, "steps": e2e_steps},
         "gpu_launches": launches_c5,

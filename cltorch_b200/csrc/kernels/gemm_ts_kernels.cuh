@@ -1,9 +1,8 @@
 // fp32 GEMM for long-K problems with the A' operand fed to the tensor core from TENSOR MEMORY.
 //
-// With both operands in shared memory, every tcgen05.mma of the 3xTF32 scheme reads 4 KB of A and
-// 8 KB of B (128 x 256 x 8 tile step): 36 KB per k step of 8, on top of what TMA writes, and the
-// shared-memory port - not the tensor pipe - sets the pace (measured: 91 % tensor-pipe duty with
-// pre-split operands, 54 % when the hi/lo conversion also goes through shared memory). Here
+// The pre-pass of thb_gemm_3xtf32 reads every operand once and writes it twice before the product
+// starts; for "few rows x large weight matrix" that costs a quarter of the call. Here the large
+// operand is never pre-processed:
 //
 //  * A' (the operand whose rows run along C's unit stride) is loaded RAW by TMA (MN-major in
 //    memory: a box of 128 rows x BK, no swizzle), and four converter warps - one per quarter of
@@ -11,7 +10,9 @@
 //    lo = x - hi in registers and store both with tcgen05.st into a ring of TMEM slots
 //    (2 x BK columns per stage). It never goes back to shared memory and is not pre-processed in HBM.
 //  * B' comes pre-split (hi, lo; K-major; 64-byte swizzle) from the small pre-pass, as in
-//    thb_gemm_3xtf32, and is the only operand the MMAs read from shared memory: 24 KB per k step.
+//    thb_gemm_3xtf32, and is the only operand the MMAs read from shared memory (24 KB per k step
+//    instead of 36 KB). Measured: the tensor pipe is ~90-92 % busy, the same as with both operands
+//    in shared memory, so those reads were not what keeps it from 100 %.
 //  * the MMA issuer runs  a_lo*b_hi + a_hi*b_lo + a_hi*b_hi  per k step with A addressed in TMEM.
 //
 // One 128 x BN accumulator (TMEM: BN columns + STAGES slots of 2*BK columns <= 512): the

@@ -260,22 +260,8 @@ thb_reduce_all_pass1_contig(const float* in, thb_i64 n, int head, float init, fl
   // with the 8 vectors of a thread spread 2.4 MB apart and 5.7 TB/s with one contiguous
   // share per block.
   const thb_i64 step = (thb_i64)gridDim.x * (THB_RA_THREADS * THB_RA_UNROLL);
-  // whole pieces need no bounds checks; the one ragged piece at the end is taken with them
-  const thb_i64 nfull = nvec / (THB_RA_THREADS * THB_RA_UNROLL) * (THB_RA_THREADS * THB_RA_UNROLL);
-  thb_i64 base = (thb_i64)blockIdx.x * (THB_RA_THREADS * THB_RA_UNROLL) + threadIdx.x;
-  for (; base < nfull; base += step) {
-    float4 v[THB_RA_UNROLL];
-#pragma unroll
-    for (int u = 0; u < THB_RA_UNROLL; ++u) v[u] = __ldcs(in4 + base + u * THB_RA_THREADS);
-#pragma unroll
-    for (int u = 0; u < THB_RA_UNROLL; ++u) {
-      acc[0] = Red::apply(acc[0], Mod::apply(v[u].x, mparam, mp));
-      acc[1] = Red::apply(acc[1], Mod::apply(v[u].y, mparam, mp));
-      acc[2] = Red::apply(acc[2], Mod::apply(v[u].z, mparam, mp));
-      acc[3] = Red::apply(acc[3], Mod::apply(v[u].w, mparam, mp));
-    }
-  }
-  if (base < nvec) {
+  for (thb_i64 base = (thb_i64)blockIdx.x * (THB_RA_THREADS * THB_RA_UNROLL) + threadIdx.x; base < nvec;
+       base += step) {
     float4 v[THB_RA_UNROLL];
 #pragma unroll
     for (int u = 0; u < THB_RA_UNROLL; ++u) {
