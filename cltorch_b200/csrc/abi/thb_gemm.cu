@@ -1,6 +1,7 @@
 // Host side of thb200_gemm: operand split, TMA descriptors, launch.
 #include "thb_internal.h"
 #include "../kernels/gemm_ts_kernels.cuh"
+#include "../kernels/gemm_pair_kernels.cuh"
 
 #include <cudaTypedefs.h>
 #include <cstdlib>
@@ -164,29 +165,35 @@ int thb200_gemm(void* stream, char transa, char transb, int64_t m, int64_t n, in
   //  fused     both operands are read in place and split in shared memory: nothing extra crosses HBM,
   //            but the conversion traffic costs the main loop about 40 % of its speed. For problems
   //            where the pre-pass would cost as much as the product (short K, few rows).
+  //  pair      the same on clusters of two CTAs (tcgen05 cta_group::2, 256 x 256 tiles): each CTA holds
+  //            half of the B' tile, a third less shared-memory traffic per CTA. Chosen instead of
+  //            "fused" whenever the problem has at least two row tiles.
   //  ts        A' (MN-major in memory) is read in place and split into TENSOR memory, only B' is
   //            pre-split: the main loop is faster than with pre-split operands and the big operand of
   //            "few rows x large weight matrix" is not pre-processed. Needs a long K (one accumulator).
-  // THB200_GEMM_MODE=prepass|fused|ts pins the choice where it is eligible (tests, experiments).
-  enum { MODE_PREPASS = 0, MODE_FUSED = 1, MODE_TS = 2 };
+  // THB200_GEMM_MODE=prepass|fused|pair|ts pins the choice where it is eligible (tests, experiments).
+  enum { MODE_PREPASS = 0, MODE_FUSED = 1, MODE_TS = 2, MODE_PAIR = 3 };
   static const int forced_mode = [] {
     const char* e = getenv("THB200_GEMM_MODE");
     if (!e) return -1;
-    return !strcmp(e, "fused") ? (int)MODE_FUSED : !strcmp(e, "ts") ? (int)MODE_TS : !strcmp(e, "prepass") ? (int)MODE_PREPASS : -1;
+    return !strcmp(e, "fused") ? (int)MODE_FUSED : !strcmp(e, "ts") ? (int)MODE_TS : !strcmp(e, "prepass") ? (int)MODE_PREPASS
+           : !strcmp(e, "pair") ? (int)MODE_PAIR : -1;
   }();
   const bool a_raw_ok = k > 0 && raw_operand_ok(a, lda, batch, stride_a);
   const bool fused_ok = a_raw_ok && raw_operand_ok(b, ldb, batch, stride_b);
   const bool ts_ok = a_raw_ok && !ta;   // op(A) = A: unit stride along the rows
   int mode = MODE_PREPASS;
   if (forced_mode == MODE_FUSED) mode = fused_ok ? MODE_FUSED : MODE_PREPASS;
+  else if (forced_mode == MODE_PAIR) mode = fused_ok ? MODE_PAIR : MODE_PREPASS;
   else if (forced_mode == MODE_TS) mode = ts_ok ? MODE_TS : MODE_PREPASS;
   else if (forced_mode < 0) {
     const double t_pre = 12.0 * (double)batch * ((double)m * k + (double)n * k) / 6.0e12;
     const double t_mma = 2.0 * (double)batch * (double)m * n * k / 250.0e12;
     if (ts_ok && k >= 1024) mode = MODE_TS;
-    else if (fused_ok && t_pre > 0.3 * t_mma) mode = MODE_FUSED;
+    else if (fused_ok && t_pre > 0.3 * t_mma) mode = m > THB_GEMM_BM ? MODE_PAIR : MODE_FUSED;   // pairs need two row tiles
   }
-  const bool fused = mode == MODE_FUSED, ts = mode == MODE_TS;
+  const bool pair = mode == MODE_PAIR;
+  const bool fused = mode == MODE_FUSED || pair, ts = mode == MODE_TS;
   // op(A)(i, kk): column-major A, 'n': a[i + kk*lda] (unit stride along i), 't': a[kk + i*lda]
   if (mode == MODE_PREPASS) {
     dim3 grid((unsigned)(Kp / 32), (unsigned)((m + 31) / 32), (unsigned)batch);
@@ -249,13 +256,14 @@ int thb200_gemm(void* stream, char transa, char transb, int64_t m, int64_t n, in
   }
   int64_t kb_per_split = (kblocks_all + splits - 1) / splits;
   splits = (int)((kblocks_all + kb_per_split - 1) / kb_per_split);  // no empty split
-  const int bn = forced_bn ? forced_bn : (splits > 1 ? 256 : (cost128 < cost256 ? 128 : 256));
+  const int bn = pair ? 256 : (forced_bn ? forced_bn : (splits > 1 ? 256 : (cost128 < cost256 ? 128 : 256)));
   CUtensorMap map_a, map_b;
   // in memory, op(A) has unit stride along its rows for 'n' and along k for 't'; B' the other way round
   const bool a_mn = !ta, b_mn = tb;
   if (fused) {
     if (int rc = make_raw_operand_map(&map_a, a, a_mn, m, k, lda, batch, stride_a, THB_GEMM_BM, bk)) return rc;
-    if (int rc = make_raw_operand_map(&map_b, b, b_mn, n, k, ldb, batch, stride_b, bn, bk)) return rc;
+    // a CTA of a pair loads only its half (128 rows) of a 256-row B' tile
+    if (int rc = make_raw_operand_map(&map_b, b, b_mn, n, k, ldb, batch, stride_b, pair ? 128 : bn, bk)) return rc;
   } else if (ts) {
     if (int rc = make_raw_rows_map(&map_a, a, m, k, lda, batch, stride_a, bk)) return rc;
     if (int rc = make_operand_map(&map_b, w.b, n, Kp, 2 * batch, bn, bk)) return rc;
@@ -273,7 +281,7 @@ int thb200_gemm(void* stream, char transa, char transb, int64_t m, int64_t n, in
   p.kblocks = (int)kblocks_all;  // k == 0 (never fused): the split wrote zeros, so C = beta * C
   p.alpha = alpha;
   p.beta = beta;
-  p.tiles_m = (int)tm;
+  p.tiles_m = pair ? (int)((tm + 1) / 2) : (int)tm;   // pairs of CTAs take 256-row double tiles
   p.tiles_n = (int)((n + bn - 1) / bn);
   p.batch = (int)batch;
   p.status = w.status;
@@ -283,7 +291,8 @@ int thb200_gemm(void* stream, char transa, char transb, int64_t m, int64_t n, in
   p.partial_split_stride = batch * m * n;
   const int64_t total_tiles = (int64_t)p.tiles_m * p.tiles_n * batch * splits;
   if (total_tiles > INT32_MAX) return fail("gemm: too many tiles");
-  const unsigned ctas = (unsigned)(total_tiles < sms ? total_tiles : sms);
+  const unsigned ctas = pair ? 2u * (unsigned)(total_tiles < sms / 2 ? total_tiles : sms / 2)
+                             : (unsigned)(total_tiles < sms ? total_tiles : sms);
   // 8 epilogue warps with the old C prefetched one block ahead: measured 0.181 ms against 0.230 ms
   // with 4 warps and no prefetch on the batched K = 128 shape, and no slower anywhere else
 #define THB_LAUNCH_GEMM(BN_, BK_, ST_)                                                                                   \
@@ -315,6 +324,18 @@ int thb200_gemm(void* stream, char transa, char transb, int64_t m, int64_t n, in
                                     ThbGemmTsCfg<128, 16, 8>::kSmem));
       thb_gemm_3xtf32_ts<128, 16, 8><<<ctas, THB_GEMM_TS_THREADS, ThbGemmTsCfg<128, 16, 8>::kSmem, st>>>(map_a, map_b, p);
     }
+  } else if (pair) {
+#define THB_LAUNCH_PAIR(AMN_, BMN_)                                                                                       \
+  do {                                                                                                                   \
+    THB_CUDA(cudaFuncSetAttribute(thb_gemm_3xtf32_pair<16, 6, AMN_, BMN_>, cudaFuncAttributeMaxDynamicSharedMemorySize,    \
+                                  ThbGemmPairCfg<16, 6>::kSmem));                                                          \
+    thb_gemm_3xtf32_pair<16, 6, AMN_, BMN_><<<ctas, THB_GEMM_FUSED_THREADS, ThbGemmPairCfg<16, 6>::kSmem, st>>>(map_a, map_b, p); \
+  } while (0)
+    if (a_mn && b_mn) THB_LAUNCH_PAIR(true, true);
+    else if (a_mn) THB_LAUNCH_PAIR(true, false);
+    else if (b_mn) THB_LAUNCH_PAIR(false, true);
+    else THB_LAUNCH_PAIR(false, false);
+#undef THB_LAUNCH_PAIR
   } else if (fused) {
     if (a_mn && b_mn) THB_LAUNCH_FUSED_BN(true, true);
     else if (a_mn) THB_LAUNCH_FUSED_BN(true, false);

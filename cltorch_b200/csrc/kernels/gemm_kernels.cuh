@@ -196,7 +196,10 @@ const int tile_n = (rem_ % group_sz) / gm_;
 // TMEM lanes 32*(w%4) .. +31 (the lanes a warp may touch); with 8 warps, warps 2-5 take the first
 // half of the tile's columns and warps 6-9 the second half.
 // NACC = number of TMEM accumulators the kernel alternates between (tile t uses accumulator t % NACC).
-template <int BN, int EW, bool PREFETCH_C, int NACC = 2>
+// PAIR: the CTA is one of a cluster of two that work on one 256-row tile together (p.tiles_m counts
+// those double tiles): work items are taken per cluster, this CTA owns the rows of its rank's half, and
+// "accumulator free" is signalled to the barrier of the cluster's first CTA, whose thread issues the MMAs.
+template <int BN, int EW, bool PREFETCH_C, int NACC = 2, bool PAIR = false>
 __device__ __forceinline__ void thb_gemm_epilogue_loop(const ThbGemmParams& p, const uint32_t tmem_base,
                                                        uint64_t* bar_acc_full, uint64_t* bar_acc_empty,
                                                        volatile int* abort_flag) {
@@ -204,6 +207,9 @@ __device__ __forceinline__ void thb_gemm_epilogue_loop(const ThbGemmParams& p, c
   const int tiles_per_batch = p.tiles_m * p.tiles_n;
   const int total_tiles = tiles_per_batch * p.batch * p.splits;
   const int group_sz = THB_GEMM_GROUP_M * p.tiles_n;
+  const int work_first = PAIR ? (int)(blockIdx.x >> 1) : (int)blockIdx.x;
+  const int work_stride = PAIR ? (int)(gridDim.x >> 1) : (int)gridDim.x;
+  const int pair_rank = PAIR ? (int)(blockIdx.x & 1) : 0;
   // ---- epilogue: warps 2..9; warp w reads TMEM lanes 32*(w%4) .. +31 (the lanes a warp may
   // touch), warps 2-5 the first half of the tile's columns, warps 6-9 the second half ----
   const int lane_group = warp & 3;
@@ -215,15 +221,16 @@ __device__ __forceinline__ void thb_gemm_epilogue_loop(const ThbGemmParams& p, c
   const float alpha = to_partial ? 1.0f : p.alpha;
   const long long ldc = to_partial ? (long long)p.m : p.ldc;
   int t = 0;
-  for (int tile = blockIdx.x; tile < total_tiles; tile += gridDim.x, ++t) {
+  for (int tile = work_first; tile < total_tiles; tile += work_stride, ++t) {
     THB_GEMM_TILE_COORDS(tile)
     const int acc = t % NACC;
-    const int row = tile_m * THB_GEMM_BM + lane_group * 32 + lane;
+    const int tile_m_own = PAIR ? 2 * tile_m + pair_rank : tile_m;   // this CTA's 128-row tile
+    const int row = tile_m_own * THB_GEMM_BM + lane_group * 32 + lane;
     float* cb = (to_partial ? p.partial + (long long)split * p.partial_split_stride + (long long)batch * p.m * p.n
                             : p.c + (long long)batch * p.batch_stride_c) + row;
     const bool row_ok = row < p.m;
     // a tile that lies wholly inside C needs no per-element bounds checks
-    const bool full = (tile_m + 1) * THB_GEMM_BM <= p.m && (tile_n + 1) * BN <= p.n;
+    const bool full = (tile_m_own + 1) * THB_GEMM_BM <= p.m && (tile_n + 1) * BN <= p.n;
     // Old values of C, 32 columns of this thread's row. They are read past L1 (ld.global.cg):
     // the 32 lines of one such block are ldc * 4 bytes apart and would fight for a few L1 sets.
     auto load_c = [&](float* dst, int col) {
@@ -302,7 +309,10 @@ __device__ __forceinline__ void thb_gemm_epilogue_loop(const ThbGemmParams& p, c
     // this warp is done reading the accumulator: hand it back to the MMA issuer
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncwarp();
-    if (lane == 0) thb_mbar_arrive(thb_smem_u32(&bar_acc_empty[acc]));
+    if (lane == 0) {
+      if (PAIR) thb_mbar_arrive_cluster_relaxed(thb_smem_u32(&bar_acc_empty[acc]), 0);
+      else thb_mbar_arrive(thb_smem_u32(&bar_acc_empty[acc]));
+    }
   }
 }
 

@@ -68,6 +68,28 @@ __device__ __forceinline__ void thb_tma_load_3d(uint32_t dst, const CUtensorMap*
 __device__ __forceinline__ void thb_mbar_arrive(uint32_t bar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
 }
+// Arrival on the barrier at the same shared-memory offset in CTA `cta_rank` of this thread-block cluster.
+__device__ __forceinline__ void thb_mbar_arrive_cluster(uint32_t bar, uint32_t cta_rank) {
+  asm volatile(
+      "{\n\t.reg .b32 remote;\n\t"
+      "mapa.shared::cluster.u32 remote, %0, %1;\n\t"
+      "mbarrier.arrive.release.cluster.shared::cluster.b64 _, [remote];\n\t}"
+      ::"r"(bar), "r"(cta_rank)
+      : "memory");
+}
+// The same without release semantics: for hand-overs whose ordering comes from tcgen05 fences (tensor
+// memory), so that the arrival does not wait for the thread's earlier global stores.
+__device__ __forceinline__ void thb_mbar_arrive_cluster_relaxed(uint32_t bar, uint32_t cta_rank) {
+  asm volatile(
+      "{\n\t.reg .b32 remote;\n\t"
+      "mapa.shared::cluster.u32 remote, %0, %1;\n\t"
+      "mbarrier.arrive.relaxed.cluster.shared::cluster.b64 _, [remote];\n\t}"
+      ::"r"(bar), "r"(cta_rank)
+      : "memory");
+}
+__device__ __forceinline__ void thb_cluster_sync() {
+  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
 __device__ __forceinline__ void thb_tma_load_2d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int x, int y) {
   asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
                ::"r"(dst), "l"(map), "r"(bar), "r"(x), "r"(y)

@@ -1,5 +1,6 @@
-"""thb200_gemm with the hi/lo split inside the kernel - both operands split in shared memory ("fused"),
-or A' split into tensor memory with only B' pre-split ("ts") - against the same call with the split
+"""thb200_gemm with the hi/lo split inside the kernel - both operands split in shared memory by one CTA per
+tile ("fused") or by pairs of CTAs on 256-row tiles ("pair"), or A' split into tensor memory with only B'
+pre-split ("ts") - against the same call with the split
 pre-pass and against an fp64-accumulated CPU GEMM: every transposition pair, ragged edges, K not a multiple of the k block,
 batches, split-K, alpha/beta. The library reads THB200_GEMM_MODE once per process, so each
 path runs in a child process of its own (this file is also that child's program).
@@ -89,7 +90,7 @@ def _run(mode):
 def test_split_inside_the_kernels_matches_prepass_and_fp64():
     prepass = _run("prepass")
     bad = []
-    for mode in ("fused", "ts"):
+    for mode in ("fused", "ts", "pair"):
         res = _run(mode)
         for idx, case in enumerate(CASES):
             f, p = res[str(idx)], prepass[str(idx)]
