@@ -2,7 +2,6 @@
 #include "thb_internal.h"
 #include "../kernels/math_policy.cuh"
 #include "../kernels/scan_strip_kernels.cuh"
-#include "../kernels/scan_onepass_kernels.cuh"
 #include "thb_strips.h"
 
 namespace thb {
@@ -13,20 +12,12 @@ struct ScanPlan {
   uint32_t nchunks, chunk_len;
   bool strips;      // single pass over 128-column strips through a TMA pipeline
   int strips_per_outer, total_strips;
-  bool onepass;     // few very long rows: one pass with a fixed tree of tile aggregates (scan_onepass_kernels.cuh)
-  int levels;
-  unsigned int count[THB_SO_MAX_LEVELS], offset[THB_SO_MAX_LEVELS], nodes_per_row;
-  size_t onepass_bytes;
 };
 
 static ScanPlan plan_scan(const float* dst, const float* src, int64_t outer, int64_t n, int64_t inner) {
   ScanPlan p;
   p.strips = false;
   p.strips_per_outer = p.total_strips = 0;
-  p.onepass = false;
-  p.levels = 0;
-  p.nodes_per_row = 0;
-  p.onepass_bytes = 0;
   p.rows = inner == 1;
   const bool aligned = (((uintptr_t)dst | (uintptr_t)src) & 15) == 0;
   if (p.rows) {
@@ -42,27 +33,6 @@ static ScanPlan plan_scan(const float* dst, const float* src, int64_t outer, int
     len = (len + piece - 1) / piece * piece;
     p.chunk_len = (uint32_t)len;
     p.nchunks = (uint32_t)((n + len - 1) / len);
-    // Rows so long that they have to be cut into chunks would be read twice by the three-phase form;
-    // the one-pass kernel reads them once. It wants 128-bit accesses and enough tiles to fill the GPU.
-    const int64_t tiles = (n + THB_SO_TILE - 1) / THB_SO_TILE;
-    if (p.nchunks > 1 && p.vec == 4 && outer <= 4096 && tiles * outer >= (int64_t)sm_count() * 16) {
-      p.onepass = true;
-      int64_t c = tiles;
-      unsigned int off = 0;
-      int l = 0;
-      for (;; ++l) {
-        p.count[l] = (unsigned int)c;
-        p.offset[l] = off;
-        off += (unsigned int)c;
-        if (c <= 32 || l + 1 >= THB_SO_MAX_LEVELS) break;
-        c = (c + 31) / 32;
-      }
-      p.levels = l + 1;
-      p.nodes_per_row = off;
-      if (p.count[p.levels - 1] > 32) p.onepass = false;   // cannot happen below 2^36 elements per row
-      // values (8 bytes), flags and counters (4 bytes each) per node and row, then the work counter
-      p.onepass_bytes = (size_t)outer * off * 16 + 256;
-    }
   } else {
     p.vec = (aligned && (inner & 3) == 0) ? 4 : 1;
     p.nchunks = pick_chunks(outer * inner / p.vec, n, THB_SC_COLS_BLOCKS);
@@ -109,22 +79,6 @@ static int run_scan(cudaStream_t st, float* dst, const float* src, int64_t outer
                     const ScanPlan& p, int* d_status) {
   if (p.strips) return run_scan_strips<Op>(st, dst, src, outer, n, inner, p, d_status);
   const int sms = sm_count();
-  if (p.onepass) {
-    ThbScanOnePass P;
-    P.src = src; P.dst = dst; P.n = n; P.rows = (int)outer; P.levels = p.levels;
-    for (int l = 0; l < THB_SO_MAX_LEVELS; ++l) { P.count[l] = l < p.levels ? p.count[l] : 0; P.offset[l] = l < p.levels ? p.offset[l] : 0; }
-    P.nodes_per_row = p.nodes_per_row;
-    const size_t nodes = (size_t)outer * p.nodes_per_row;
-    P.value = carry;                                             // the scratch, 8-byte aligned
-    P.flag = (unsigned int*)(carry + nodes);
-    P.counter = P.flag + nodes;
-    P.next_tile = P.counter + nodes;
-    P.status = d_status ? d_status : device_status_word(STATUS_STRIP_SCAN);
-    THB_CUDA(cudaMemsetAsync(carry, 0, p.onepass_bytes, st));
-    thb_scan_rows_onepass<Op><<<(unsigned)(sms * 2), THB_SC_THREADS, 0, st>>>(P);
-    THB_CUDA(cudaGetLastError());
-    return 0;
-  }
   if (p.rows) {
     const int64_t work = outer * p.nchunks;  // warps
     int64_t blocks = (work + THB_SC_THREADS / 32 - 1) / (THB_SC_THREADS / 32);
@@ -183,7 +137,6 @@ extern "C" {
 size_t thb200_scan_scratch_bytes(const float* dst, const float* src, int64_t outer, int64_t n, int64_t inner) {
   if (outer <= 0 || n <= 0 || inner <= 0) return 0;
   const ScanPlan p = plan_scan(dst, src, outer, n, inner);
-  if (p.onepass) return p.onepass_bytes;
   return p.nchunks > 1 ? (size_t)outer * p.nchunks * inner * sizeof(double) : 0;
 }
 
@@ -196,7 +149,7 @@ int thb200_scan(void* stream, int op, float* dst, const float* src, int64_t oute
   if (n >= (int64_t(1) << 31)) return fail("scan: dimension of %lld elements is too long", (long long)n);
   if (op != THB200_RED_ADD && op != THB200_RED_MUL) return fail("scan: operator %d is neither add nor mul", op);
   const ScanPlan p = plan_scan(dst, src, outer, n, inner);
-  const size_t need = p.onepass ? p.onepass_bytes : (p.nchunks > 1 ? (size_t)outer * p.nchunks * inner * sizeof(double) : 0);
+  const size_t need = p.nchunks > 1 ? (size_t)outer * p.nchunks * inner * sizeof(double) : 0;
   if (need && (!scratch || scratch_bytes < need || ((uintptr_t)scratch & 7)))
     return fail("scan: scratch too small or misaligned (%zu bytes, need %zu)", scratch_bytes, need);
   return op == THB200_RED_ADD
