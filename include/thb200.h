@@ -290,15 +290,24 @@ int thb200_fold_partials(void* stream, int reduce, const float* d_partials, int 
  * 't', fp32 in and out. Computed with tcgen05 TF32 tensor-core MMAs on a
  * three-term split of each operand (hi*hi + hi*lo + lo*hi) accumulated in fp32.
  * `batch` independent problems at the given element strides (batch = 1 for addmm).
- * `workspace` holds the split operands; size from thb200_gemm_workspace_bytes. */
+ * `workspace` holds split operands, split-K partial sums and the status word; size from
+ * thb200_gemm_workspace_bytes. How the hi/lo parts reach the tensor core is chosen per problem:
+ * long K with op(A) = A: A is read in place and split into tensor memory, only B is pre-split;
+ * short K / few rows: both operands are read in place and split in shared memory (by pairs of
+ * CTAs when there are at least two row tiles); otherwise, and whenever an operand is not 16-byte
+ * aligned with a leading dimension that is a multiple of 4, both are pre-split in the workspace.
+ * The environment variable THB200_GEMM_MODE = prepass | fused | pair | ts pins the choice where it is
+ * eligible (read once per process; for tests and experiments). */
 size_t thb200_gemm_workspace_bytes(int64_t m, int64_t n, int64_t k, int64_t batch);
 int thb200_gemm(void* stream, char transa, char transb, int64_t m, int64_t n, int64_t k, float alpha,
                 const float* a, int64_t lda, const float* b, int64_t ldb, float beta, float* c, int64_t ldc,
                 int64_t batch, int64_t stride_a, int64_t stride_b, int64_t stride_c,
                 void* workspace, size_t workspace_bytes);
 /* Every wait inside the GEMM kernel is bounded. Status word of the last
- * thb200_gemm that used this workspace: 0 = completed, 1/2/3 = a wait of the
- * load / MMA / store stage gave up (C is then undefined). Synchronises `stream`.
+ * thb200_gemm that used this workspace: 0 = completed; 1 = the TMA producer's wait for a free
+ * stage, 2 / 6 = the MMA issuer's wait for a loaded / converted stage, 3 = the epilogue's wait for
+ * an accumulator, 4 = the MMA issuer's wait for a free accumulator, 5 = a converter's wait for a
+ * loaded stage gave up (C is then undefined). Synchronises `stream`.
  * < 0: the status could not be read. */
 int thb200_gemm_status(void* stream, int64_t m, int64_t n, int64_t k, int64_t batch, void* workspace);
 
