@@ -168,7 +168,7 @@ int thb200_gemm(void* stream, char transa, char transb, int64_t m, int64_t n, in
   //  pair      the same on clusters of two CTAs (tcgen05 cta_group::2, 256 x 256 tiles): each CTA holds
   //            half of the B' tile, a third less shared-memory traffic per CTA. Chosen instead of
   //            "fused" whenever the problem has at least two row tiles.
-  //  ts        A' (MN-major in memory) is read in place and split into TENSOR memory, only B' is
+  //  ts        A' is read in place (either orientation) and split into TENSOR memory, only B' is
   //            pre-split: the main loop is faster than with pre-split operands and the big operand of
   //            "few rows x large weight matrix" is not pre-processed. Needs a long K (one accumulator).
   // THB200_GEMM_MODE=prepass|fused|pair|ts pins the choice where it is eligible (tests, experiments).
@@ -181,7 +181,7 @@ int thb200_gemm(void* stream, char transa, char transb, int64_t m, int64_t n, in
   }();
   const bool a_raw_ok = k > 0 && raw_operand_ok(a, lda, batch, stride_a);
   const bool fused_ok = a_raw_ok && raw_operand_ok(b, ldb, batch, stride_b);
-  const bool ts_ok = a_raw_ok && !ta;   // op(A) = A: unit stride along the rows
+  const bool ts_ok = a_raw_ok;
   int mode = MODE_PREPASS;
   if (forced_mode == MODE_FUSED) mode = fused_ok ? MODE_FUSED : MODE_PREPASS;
   else if (forced_mode == MODE_PAIR) mode = fused_ok ? MODE_PAIR : MODE_PREPASS;
@@ -265,7 +265,8 @@ int thb200_gemm(void* stream, char transa, char transb, int64_t m, int64_t n, in
     // a CTA of a pair loads only its half (128 rows) of a 256-row B' tile
     if (int rc = make_raw_operand_map(&map_b, b, b_mn, n, k, ldb, batch, stride_b, pair ? 128 : bn, bk)) return rc;
   } else if (ts) {
-    if (int rc = make_raw_rows_map(&map_a, a, m, k, lda, batch, stride_a, bk)) return rc;
+    if (a_mn) { if (int rc = make_raw_rows_map(&map_a, a, m, k, lda, batch, stride_a, bk)) return rc; }
+    else if (int rc = make_raw_operand_map(&map_a, a, false, m, k, lda, batch, stride_a, THB_GEMM_BM, bk)) return rc;
     if (int rc = make_operand_map(&map_b, w.b, n, Kp, 2 * batch, bn, bk)) return rc;
   } else {
     if (int rc = make_operand_map(&map_a, w.a, m, Kp, 2 * batch, THB_GEMM_BM, bk)) return rc;
@@ -315,15 +316,15 @@ int thb200_gemm(void* stream, char transa, char transb, int64_t m, int64_t n, in
     else THB_LAUNCH_FUSED(128, 6, AMN_, BMN_);             \
   } while (0)
   if (ts) {
-    if (bn == 256) {
-      THB_CUDA(cudaFuncSetAttribute(thb_gemm_3xtf32_ts<256, 16, 5>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                    ThbGemmTsCfg<256, 16, 5>::kSmem));
-      thb_gemm_3xtf32_ts<256, 16, 5><<<ctas, THB_GEMM_TS_THREADS, ThbGemmTsCfg<256, 16, 5>::kSmem, st>>>(map_a, map_b, p);
-    } else {
-      THB_CUDA(cudaFuncSetAttribute(thb_gemm_3xtf32_ts<128, 16, 8>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                    ThbGemmTsCfg<128, 16, 8>::kSmem));
-      thb_gemm_3xtf32_ts<128, 16, 8><<<ctas, THB_GEMM_TS_THREADS, ThbGemmTsCfg<128, 16, 8>::kSmem, st>>>(map_a, map_b, p);
-    }
+#define THB_LAUNCH_TS(BN_, ST_, AK_)                                                                                      \
+  do {                                                                                                                   \
+    THB_CUDA(cudaFuncSetAttribute(thb_gemm_3xtf32_ts<BN_, 16, ST_, AK_>, cudaFuncAttributeMaxDynamicSharedMemorySize,     \
+                                  ThbGemmTsCfg<BN_, 16, ST_>::kSmem));                                                    \
+    thb_gemm_3xtf32_ts<BN_, 16, ST_, AK_><<<ctas, THB_GEMM_TS_THREADS, ThbGemmTsCfg<BN_, 16, ST_>::kSmem, st>>>(map_a, map_b, p); \
+  } while (0)
+    if (bn == 256) { if (a_mn) THB_LAUNCH_TS(256, 5, false); else THB_LAUNCH_TS(256, 5, true); }
+    else { if (a_mn) THB_LAUNCH_TS(128, 8, false); else THB_LAUNCH_TS(128, 8, true); }
+#undef THB_LAUNCH_TS
   } else if (pair) {
 #define THB_LAUNCH_PAIR(AMN_, BMN_)                                                                                       \
   do {                                                                                                                   \

@@ -4,8 +4,9 @@
 // starts; for "few rows x large weight matrix" that costs a quarter of the call. Here the large
 // operand is never pre-processed:
 //
-//  * A' (the operand whose rows run along C's unit stride) is loaded RAW by TMA (MN-major in
-//    memory: a box of 128 rows x BK, no swizzle), and four converter warps - one per quarter of
+//  * A' (the operand whose rows run along C's unit stride) is loaded RAW by TMA in the orientation it
+//    has in memory (MN-major: a box of 128 rows x BK, no swizzle; K-major: BK x 128 rows with the
+//    64-byte swizzle), and four converter warps - one per quarter of
 //    the 128 TMEM lanes - read it (thread = row, conflict-free), split it into hi = tf32(x) and
 //    lo = x - hi in registers and store both with tcgen05.st into a ring of TMEM slots
 //    (2 x BK columns per stage). It never goes back to shared memory and is not pre-processed in HBM.
@@ -62,9 +63,13 @@ __device__ __forceinline__ void thb_tmem_store16(uint32_t taddr, const uint32_t 
       : "memory");
 }
 
-// map_a: the caller's A' as (rows, k, batch), box 128 x BK x 1, no swizzle.
+// map_a: the caller's A'. A_KMAJOR = false (unit stride along the rows): (rows, k, batch), box 128 x BK x 1,
+//        no swizzle; a converter thread reads its row's k-th element from k-row k (a warp reads 128
+//        consecutive bytes). A_KMAJOR = true (unit stride along k): (k, rows, batch), box BK x 128 x 1
+//        with the 64-byte swizzle; a thread reads the four 16-byte pieces of its own 64-byte row, whose
+//        positions the swizzle spreads over all banks (piece j of row r sits at j ^ ((r >> 1) & 3)).
 // map_b: the pre-split B' as in thb_gemm_3xtf32 ([2 * batch][n][Kp], box BK x BN x 1, 64-byte swizzle).
-template <int BN, int BK, int STAGES>
+template <int BN, int BK, int STAGES, bool A_KMAJOR>
 __global__ void __launch_bounds__(THB_GEMM_TS_THREADS, 1)
 thb_gemm_3xtf32_ts(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, ThbGemmParams p) {
   typedef ThbGemmTsCfg<BN, BK, STAGES> Cfg;
@@ -131,7 +136,8 @@ thb_gemm_3xtf32_ts(const __grid_constant__ CUtensorMap map_a, const __grid_const
           const uint32_t st = thb_smem_u32(smem + s * Cfg::kStage);
           thb_mbar_expect_tx(full, Cfg::kStage);
           const int k0 = kb * BK;
-          thb_tma_load_3d(st, &map_a, full, tile_m * THB_GEMM_BM, k0, batch);
+          if (A_KMAJOR) thb_tma_load_3d(st, &map_a, full, k0, tile_m * THB_GEMM_BM, batch);
+          else thb_tma_load_3d(st, &map_a, full, tile_m * THB_GEMM_BM, k0, batch);
           thb_tma_load_3d(st + Cfg::kTileA, &map_b, full, k0, tile_n * BN, batch * 2 + 0);
           thb_tma_load_3d(st + Cfg::kTileA + Cfg::kTileB, &map_b, full, k0, tile_n * BN, batch * 2 + 1);
         }
@@ -209,14 +215,30 @@ thb_gemm_3xtf32_ts(const __grid_constant__ CUtensorMap map_a, const __grid_const
         if (!got && !*abort_flag) { *abort_flag = 1; atomicCAS(p.status, 0, 5); }
         got = __all_sync(0xffffffffu, got);
         if (!got) { ok = false; break; }
-        const float* raw = reinterpret_cast<const float*>(smem + s * Cfg::kStage) + row;  // [k][128]
         uint32_t hi[BK], lo[BK];
+        if (A_KMAJOR) {
+          const uint8_t* raw = smem + s * Cfg::kStage + row * (BK * 4);  // [128][BK], 16-byte pieces swizzled
 #pragma unroll
-        for (int k = 0; k < BK; ++k) {
-          float h, l;
-          thb_split_tf32(raw[k * THB_GEMM_BM], h, l);
-          hi[k] = __float_as_uint(h);
-          lo[k] = __float_as_uint(l);
+          for (int j = 0; j < BK / 4; ++j) {
+            const float4 x = *reinterpret_cast<const float4*>(raw + ((j ^ ((row >> 1) & 3)) << 4));
+            const float xs[4] = {x.x, x.y, x.z, x.w};
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+              float h, l;
+              thb_split_tf32(xs[e], h, l);
+              hi[4 * j + e] = __float_as_uint(h);
+              lo[4 * j + e] = __float_as_uint(l);
+            }
+          }
+        } else {
+          const float* raw = reinterpret_cast<const float*>(smem + s * Cfg::kStage) + row;  // [k][128]
+#pragma unroll
+          for (int k = 0; k < BK; ++k) {
+            float h, l;
+            thb_split_tf32(raw[k * THB_GEMM_BM], h, l);
+            hi[k] = __float_as_uint(h);
+            lo[k] = __float_as_uint(l);
+          }
         }
         // the MMAs that read this slot one round ago have completed: the producer waited for their
         // commit before it refilled the stage whose arrival was just observed

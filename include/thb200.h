@@ -292,7 +292,7 @@ int thb200_fold_partials(void* stream, int reduce, const float* d_partials, int 
  * `batch` independent problems at the given element strides (batch = 1 for addmm).
  * `workspace` holds split operands, split-K partial sums and the status word; size from
  * thb200_gemm_workspace_bytes. How the hi/lo parts reach the tensor core is chosen per problem:
- * long K with op(A) = A: A is read in place and split into tensor memory, only B is pre-split;
+ * long K: A is read in place (either orientation) and split into tensor memory, only B is pre-split;
  * short K / few rows: both operands are read in place and split in shared memory (by pairs of
  * CTAs when there are at least two row tiles); otherwise, and whenever an operand is not 16-byte
  * aligned with a leading dimension that is a multiple of 4, both are pre-split in the workspace.
