@@ -99,3 +99,47 @@ def test_absent_rank_makes_the_bounded_wait_give_up_and_report():
     assert L.thb200_exchange_fold(stream, xs[0], RED_ADD, C.c_void_p(out.data_ptr()), 0) != 0
     for x in xs:
         L.thb200_exchange_destroy(x)
+
+
+def _two_gpu_child():
+    """One rank of the two-process group below (run through torch.distributed.run)."""
+    import os
+    import sys
+    import torch
+    import torch.distributed as dist
+    sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+    rank, local = int(os.environ["RANK"]), int(os.environ["LOCAL_RANK"])
+    torch.cuda.set_device(local)
+    dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    import cltorch_b200 as cl
+    from cltorch_b200.sharded import GlobalSum, shard_bounds
+    g = GlobalSum(exchange="p2p", wait_limit_s=5.0)
+    n = 3_000_001
+    full = np.random.Generator(np.random.PCG64(90)).random(n, dtype=np.float32)
+    b, e = shard_bounds(n, 2, rank)
+    x = cl.ClTensor(full[b:e])
+    got = [float(g(x).s()) for _ in range(3)]               # three steps: both parities of the cells
+    ref = float(np.sum(full, dtype=np.float64))
+    assert got[0] == got[1] == got[2] and abs(got[0] - ref) <= 1e-5 * ref, (got, ref)
+    vals = [None, None]
+    dist.all_gather_object(vals, got[0])
+    assert vals[0] == vals[1]                                # the same bits on both GPUs
+    dist.destroy_process_group()
+    print("TWO_GPU_OK")
+
+
+def test_two_processes_on_two_gpus_over_cuda_ipc():
+    """The exchange between processes (CUDA IPC, stores over NVLink). Needs two GPUs; skipped on one."""
+    import subprocess
+    import sys
+    import torch
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    r = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2",
+                        "--master-addr", "127.0.0.1", "--master-port", "29541", __file__], capture_output=True, text=True,
+                       timeout=300)
+    assert r.returncode == 0 and r.stdout.count("TWO_GPU_OK") == 2, r.stdout[-2000:] + r.stderr[-3000:]
+
+
+if __name__ == "__main__":
+    _two_gpu_child()
