@@ -2,6 +2,10 @@
 #include "thb_internal.h"
 #include "../kernels/math_policy.cuh"
 #include "../kernels/scan_strip_kernels.cuh"
+#include "../kernels/scan_chain_kernels.cuh"
+#include <stdlib.h>
+
+#define THB_SCH_TILE 8192  // elements per tile of the chained scan
 #include "thb_strips.h"
 
 namespace thb {
@@ -12,12 +16,27 @@ struct ScanPlan {
   uint32_t nchunks, chunk_len;
   bool strips;      // single pass over 128-column strips through a TMA pipeline
   int strips_per_outer, total_strips;
+  bool chain;       // inner == 1, few long rows: single pass over tiles that wait for their carries
 };
+
+// Whether kernels can be launched with all their CTAs guaranteed resident (the chained scan's
+// CTAs wait for one another's totals).
+static bool cooperative_launch_ok() {
+  static int cached[64];  // 0 unknown, 1 yes, 2 no
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return false;
+  if (!cached[dev]) {
+    int v = 0;
+    cached[dev] = (cudaDeviceGetAttribute(&v, cudaDevAttrCooperativeLaunch, dev) == cudaSuccess && v) ? 1 : 2;
+  }
+  return cached[dev] == 1;
+}
 
 static ScanPlan plan_scan(const float* dst, const float* src, int64_t outer, int64_t n, int64_t inner) {
   ScanPlan p;
   p.strips = false;
   p.strips_per_outer = p.total_strips = 0;
+  p.chain = false;
   p.rows = inner == 1;
   const bool aligned = (((uintptr_t)dst | (uintptr_t)src) & 15) == 0;
   if (p.rows) {
@@ -33,6 +52,14 @@ static ScanPlan plan_scan(const float* dst, const float* src, int64_t outer, int
     len = (len + piece - 1) / piece * piece;
     p.chunk_len = (uint32_t)len;
     p.nchunks = (uint32_t)((n + len - 1) / len);
+    // Rows that have to be cut (three phases, 12 bytes per element) go through the chained
+    // single-pass kernel instead when the layout suits bulk copies.
+    if (p.nchunks > 1 && aligned && (n & 31) == 0 && n >= 2 * THB_SCH_TILE && outer < (int64_t(1) << 31) &&
+        cooperative_launch_ok() && tensor_map_encoder_ptr() != nullptr) {
+      p.chain = true;
+      p.chunk_len = THB_SCH_TILE;
+      p.nchunks = (uint32_t)((n + THB_SCH_TILE - 1) / THB_SCH_TILE);
+    }
   } else {
     p.vec = (aligned && (inner & 3) == 0) ? 4 : 1;
     p.nchunks = pick_chunks(outer * inner / p.vec, n, THB_SC_COLS_BLOCKS);
@@ -74,10 +101,61 @@ static int run_scan_strips(cudaStream_t st, float* dst, const float* src, int64_
   return 0;
 }
 
+// Tensor map over [outer][n / 32][32] floats with the 128-byte swizzle: a box is one tile of the chained scan.
+static int make_chain_map(CUtensorMap* map, const float* p, int64_t outer, int64_t n) {
+  auto enc = (PFN_cuTensorMapEncodeTiled_v12000)tensor_map_encoder_ptr();
+  cuuint64_t dims[3] = {32, (cuuint64_t)(n / 32), (cuuint64_t)outer};
+  cuuint64_t strides[2] = {128, (cuuint64_t)n * 4};
+  cuuint32_t box[3] = {32, THB_SCH_TILE / 32, 1};
+  cuuint32_t estr[3] = {1, 1, 1};
+  CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 3, (void*)p, dims, strides, box, estr,
+                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return fail("scan: cuTensorMapEncodeTiled failed with %d", (int)r);
+  return 0;
+}
+
+template <class Op>
+static int run_scan_chain(cudaStream_t st, float* dst, const float* src, int64_t outer, int64_t n, double* scratch,
+                          const ScanPlan& p, int* d_status) {
+  thb_i64 nwork = outer * (int64_t)p.nchunks;
+  unsigned long long* totals = (unsigned long long*)scratch;
+  THB_CUDA(cudaMemsetAsync(totals, 0xFF, (size_t)nwork * sizeof(unsigned long long), st));  // "not written yet"
+  int ctas = sm_count() < THB_SCH_MAX_CTAS ? sm_count() : THB_SCH_MAX_CTAS;
+  if (nwork < ctas) ctas = (int)nwork;
+  thb_u32 n32 = (thb_u32)n, nchunks = p.nchunks;
+  int* status = d_status ? d_status : device_status_word(STATUS_STRIP_SCAN);
+  CUtensorMap map_src, map_dst;
+  if (int rc = make_chain_map(&map_src, src, outer, n)) return rc;
+  if (int rc = make_chain_map(&map_dst, dst, outer, n)) return rc;
+  void* args[] = {&map_src, &map_dst, &n32, &nchunks, &nwork, &totals, &status};
+  static int variant = -1;
+  if (variant < 0) { const char* e = getenv("THB200_SCAN_CHAIN_VARIANT"); variant = e ? atoi(e) : 0; }
+#define THB_SCH_LAUNCH(TILE, STAGES, LAG)                                                                             \
+  do {                                                                                                                \
+    auto kern = thb_scan_chain<Op, TILE, STAGES, LAG>;                                                                \
+    THB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, THB_SCH_SMEM_BYTES(TILE, STAGES))); \
+    THB_CUDA(cudaLaunchCooperativeKernel((const void*)kern, dim3(ctas), dim3(THB_SCH_THREADS), args,                  \
+                                         THB_SCH_SMEM_BYTES(TILE, STAGES), st));                                      \
+  } while (0)
+  switch (variant) {
+    case 1: THB_SCH_LAUNCH(THB_SCH_TILE, 6, 2); break;
+    case 2: THB_SCH_LAUNCH(THB_SCH_TILE, 6, 1); break;
+    case 3: THB_SCH_LAUNCH(THB_SCH_TILE, 7, 2); break;
+    case 4: THB_SCH_LAUNCH(THB_SCH_TILE, 7, 3); break;
+    case 5: THB_SCH_LAUNCH(THB_SCH_TILE, 7, 4); break;
+    case 6: THB_SCH_LAUNCH(THB_SCH_TILE, 7, 5); break;
+    default: THB_SCH_LAUNCH(THB_SCH_TILE, 7, 4); break;
+  }
+#undef THB_SCH_LAUNCH
+  return 0;
+}
+
 template <class Op>
 static int run_scan(cudaStream_t st, float* dst, const float* src, int64_t outer, int64_t n, int64_t inner, double* carry,
                     const ScanPlan& p, int* d_status) {
   if (p.strips) return run_scan_strips<Op>(st, dst, src, outer, n, inner, p, d_status);
+  if (p.chain) return run_scan_chain<Op>(st, dst, src, outer, n, carry, p, d_status);
   const int sms = sm_count();
   if (p.rows) {
     const int64_t work = outer * p.nchunks;  // warps

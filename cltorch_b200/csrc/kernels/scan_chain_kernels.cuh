@@ -1,0 +1,329 @@
+// Single-pass scan along the innermost dimension when there are too few rows for one warp per
+// row to keep HBM busy (one long vector is the extreme case). The rows are cut into tiles of
+// THB_SCH_TILE elements; tile w (row-major over (row, piece)) is taken by CTA w mod G of a
+// grid of G co-resident CTAs (cooperative launch, one per SM). A tile stays in shared
+// memory from its load to its store, so every element crosses HBM once in each direction:
+// 8 bytes per element, against 12 for the three-phase form (totals, scan of totals, scan).
+//
+// Same job as THClTensor_kernel_scanInnermostDim (reference src/lib/THClTensorMathScan.cl:52-139).
+//
+// The rows are seen as [row][n / 32][32 floats] through a tensor map with the 128-byte swizzle, so
+// that a lane can own 16 consecutive elements (one inclusive scan over the lane totals per 512
+// elements instead of one per 128) and still read and write shared memory without bank conflicts.
+//
+// Per CTA: warp 0 loads tiles with cp.async.bulk.tensor (no multicast) into a ring of
+// STAGES stages, warp 1 collects the carry of each tile, warp 2 returns finished
+// stages with cp.async.bulk.tensor stores, warps 3.. do the arithmetic in two passes over a stage:
+//   pass A  as soon as the tile has landed: its total in double, published as one 8-byte word
+//           totals[w] (the word itself says whether it has been written: the scratch is preset
+//           to all-ones, a pattern no published total has);
+//   pass B  LAG tiles later: carry + inclusive scan, written back into the stage.
+// carry(w) = carry(w - G) (+) totals[w-G] (+) ... (+) totals[w-1], restricted to the tiles of w's own
+// row: the additions are done in a fixed order (lane k folds entries k, k+32, ..., then a shuffle
+// tree), so the result does not depend on which CTA was early. Totals never depend on carries,
+// so no CTA waits for another's scan, only for its loads.
+//
+// Every wait is bounded (THB_GEMM_WAIT_LIMIT_NS). On expiry the waiter writes *status and sets
+// the CTA's abort flag; waits in other CTAs notice *status and leave as well.
+#pragma once
+#include "gemm_kernels.cuh"  // mbarrier / TMA helpers
+#include "scan_kernels.cuh"
+#include "scan_strip_kernels.cuh"  // thb_tma_store_3d
+
+#define THB_SCH_CWARPS 16
+#define THB_SCH_THREADS ((3 + THB_SCH_CWARPS) * 32)
+#define THB_SCH_MAX_CTAS 256  // the carry warp reads at most 8 totals per lane
+#define THB_SCH_SMEM_BYTES(TILE, STAGES)                                                              \
+  ((STAGES) * (TILE) * 4 + 1024 /*alignment of the swizzled stages*/ + (STAGES) * (THB_SCH_CWARPS + 1) * 8 /*warp totals and carry per stage*/ + \
+   5 * (STAGES) * 8 /*barriers*/ + 16 /*flags*/)
+#define THB_SCH_UNSET 0xFFFFFFFFFFFFFFFFull
+
+__device__ __forceinline__ unsigned long long thb_ld_relaxed_u64(const unsigned long long* p) {
+  unsigned long long v;
+  asm volatile("ld.relaxed.gpu.global.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ void thb_st_relaxed_u64(unsigned long long* p, unsigned long long v) {
+  asm volatile("st.relaxed.gpu.global.u64 [%0], %1;" ::"l"(p), "l"(v) : "memory");
+}
+
+// Status codes (family "strip scan"): 4 a carry never arrived, 5 load, 6 warp totals, 7 carry hand-over,
+// 8 store, 9 a stage never came free.
+template <class Op, int THB_SCH_TILE, int THB_SCH_STAGES, int THB_SCH_LAG>
+__global__ void __launch_bounds__(THB_SCH_THREADS, 1)
+thb_scan_chain(const __grid_constant__ CUtensorMap map_src, const __grid_constant__ CUtensorMap map_dst, thb_u32 n,
+               thb_u32 nchunks, thb_i64 nwork, unsigned long long* totals, int* status) {
+  constexpr int THB_SCH_STAGE_BYTES = THB_SCH_TILE * 4;
+  constexpr int THB_SCH_WARP_ELEMS = THB_SCH_TILE / THB_SCH_CWARPS;
+  constexpr int THB_SCH_LANE_ELEMS = THB_SCH_WARP_ELEMS / 32;  // consecutive elements of a lane
+  constexpr int THB_SCH_PIECES = THB_SCH_LANE_ELEMS / 4;       // float4 per lane and tile
+  static_assert(THB_SCH_STAGES >= THB_SCH_LAG + 2, "a stage's warp totals are rewritten LAG+2 tiles later at the earliest");
+  static_assert(THB_SCH_LANE_ELEMS == 16, "a lane owns half a 128-byte row of the swizzled stage");
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  double* wtot = (double*)(smem + THB_SCH_STAGES * THB_SCH_STAGE_BYTES);  // [stage][warp]
+  double* carry_s = wtot + THB_SCH_STAGES * THB_SCH_CWARPS;               // [stage]
+  uint64_t* bar_full = (uint64_t*)(carry_s + THB_SCH_STAGES);
+  uint64_t* bar_empty = bar_full + THB_SCH_STAGES;
+  uint64_t* bar_tot = bar_empty + THB_SCH_STAGES;
+  uint64_t* bar_pre = bar_tot + THB_SCH_STAGES;
+  uint64_t* bar_done = bar_pre + THB_SCH_STAGES;
+  volatile int* abort_flag = (volatile int*)(bar_done + THB_SCH_STAGES);
+  volatile int* never_set = abort_flag + 1;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < THB_SCH_STAGES; ++s) {
+      thb_mbar_init(thb_smem_u32(&bar_full[s]), 1);
+      thb_mbar_init(thb_smem_u32(&bar_empty[s]), 1);
+      thb_mbar_init(thb_smem_u32(&bar_tot[s]), THB_SCH_CWARPS);
+      thb_mbar_init(thb_smem_u32(&bar_pre[s]), 2);
+      thb_mbar_init(thb_smem_u32(&bar_done[s]), THB_SCH_CWARPS);
+    }
+    abort_flag[0] = 0;
+    abort_flag[1] = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  __syncthreads();
+  const thb_i64 G = gridDim.x;
+  const thb_i64 w_first = blockIdx.x;
+  const int iters = w_first < nwork ? (int)((nwork - w_first + G - 1) / G) : 0;
+  volatile int* gstatus = status;
+
+#define THB_SCH_GIVE_UP(code)                                   \
+  do {                                                          \
+    if (!*abort_flag) { *abort_flag = 1; atomicCAS(status, 0, (code)); } \
+  } while (0)
+
+  if (warp == 0) {
+    if (lane == 0) {
+      int i = 0;
+      for (; i < iters; ++i) {
+        const int s = i % THB_SCH_STAGES;
+        const uint32_t round = (uint32_t)(i / THB_SCH_STAGES);
+        if (i >= THB_SCH_STAGES && !thb_mbar_wait(thb_smem_u32(&bar_empty[s]), (round - 1) & 1, abort_flag)) {
+          THB_SCH_GIVE_UP(9);
+          break;
+        }
+        const thb_i64 w = w_first + (thb_i64)i * G;
+        const thb_i64 row = w / nchunks;
+        const thb_u32 c0 = (thb_u32)(w - row * nchunks) * THB_SCH_TILE;
+        const uint32_t full = thb_smem_u32(&bar_full[s]);
+        thb_mbar_expect_tx(full, THB_SCH_STAGE_BYTES);  // 128-byte rows past the end of the row arrive as zeros
+        thb_tma_load_3d(thb_smem_u32(smem + s * THB_SCH_STAGE_BYTES), &map_src, full, 0, (int)(c0 >> 5), (int)row);
+      }
+      if (*abort_flag) {
+        // do not leave while copies into this CTA's shared memory are in flight
+        for (int j = (i > THB_SCH_STAGES ? i - THB_SCH_STAGES : 0); j < i; ++j)
+          thb_mbar_wait(thb_smem_u32(&bar_full[j % THB_SCH_STAGES]), (uint32_t)(j / THB_SCH_STAGES) & 1, never_set);
+      }
+    }
+  } else if (warp == 1) {
+    // The totals of the next tile's predecessors are requested before this tile's are folded, so that
+    // the trip to L2 is off the path from one carry to the next.
+    constexpr int M = THB_SCH_MAX_CTAS / 32;
+    double prev = Op::identity();
+    unsigned long long nxt[M];
+    thb_i64 w_n = w_first, row0_n = (w_n / nchunks) * nchunks, lo_n = (w_n - G > row0_n) ? w_n - G : row0_n;
+    if (iters > 0) {
+#pragma unroll
+      for (int m = 0; m < M; ++m) nxt[m] = lo_n + lane + 32 * m < w_n ? thb_ld_relaxed_u64(totals + lo_n + lane + 32 * m) : 0ull;
+    }
+    for (int i = 0; i < iters; ++i) {
+      const int s = i % THB_SCH_STAGES;
+      const uint32_t round = (uint32_t)(i / THB_SCH_STAGES);
+      const thb_i64 w = w_n, row0 = row0_n, lo = lo_n;
+      unsigned long long bits[M];
+#pragma unroll
+      for (int m = 0; m < M; ++m) bits[m] = nxt[m];
+      if (i + 1 < iters) {
+        w_n = w + G;
+        row0_n = (w_n / nchunks) * nchunks;
+        lo_n = (w_n - G > row0_n) ? w_n - G : row0_n;
+#pragma unroll
+        for (int m = 0; m < M; ++m) nxt[m] = lo_n + lane + 32 * m < w_n ? thb_ld_relaxed_u64(totals + lo_n + lane + 32 * m) : 0ull;
+      }
+      bool ok = true;
+      bool missing = false;
+#pragma unroll
+      for (int m = 0; m < M; ++m) missing |= bits[m] == THB_SCH_UNSET;
+      if (missing) {
+        const unsigned long long t0 = thb_globaltimer_ns();
+        for (uint32_t spin = 1; missing; ++spin) {
+          missing = false;
+#pragma unroll
+          for (int m = 0; m < M; ++m) {
+            if (bits[m] == THB_SCH_UNSET) {
+              bits[m] = thb_ld_relaxed_u64(totals + lo + lane + 32 * m);
+              missing |= bits[m] == THB_SCH_UNSET;
+            }
+          }
+          if (missing && (spin & 31u) == 0 &&
+              (*abort_flag || *gstatus != 0 || thb_globaltimer_ns() - t0 > THB_GEMM_WAIT_LIMIT_NS)) {
+            ok = false;
+            break;
+          }
+        }
+      }
+      if (!__all_sync(0xffffffffu, ok)) {
+        if (lane == 0) THB_SCH_GIVE_UP(4);
+        break;
+      }
+      double acc = Op::identity();
+#pragma unroll
+      for (int m = 0; m < M; ++m)
+        if (lo + lane + 32 * m < w) acc = Op::apply(acc, __longlong_as_double((long long)bits[m]));
+#pragma unroll
+      for (int off = 1; off < 32; off <<= 1) acc = Op::apply(acc, __shfl_xor_sync(0xffffffffu, acc, off));
+      prev = (w - G >= row0) ? Op::apply(prev, acc) : acc;
+      // the carry slot of this stage is free once the tile that used it before has been stored
+      if (i >= THB_SCH_STAGES) ok = thb_mbar_wait(thb_smem_u32(&bar_empty[s]), (round - 1) & 1, abort_flag);
+      if (!__all_sync(0xffffffffu, ok)) {
+        if (lane == 0) THB_SCH_GIVE_UP(9);
+        break;
+      }
+      if (lane == 0) {
+        carry_s[s] = prev;
+        thb_mbar_arrive(thb_smem_u32(&bar_pre[s]));
+      }
+    }
+  } else if (warp == 2) {
+    if (lane == 0) {
+      for (int i = 0; i < iters; ++i) {
+        const int s = i % THB_SCH_STAGES;
+        const uint32_t round = (uint32_t)(i / THB_SCH_STAGES);
+        if (!thb_mbar_wait(thb_smem_u32(&bar_done[s]), round & 1, abort_flag)) {
+          THB_SCH_GIVE_UP(8);
+          break;
+        }
+        const thb_i64 w = w_first + (thb_i64)i * G;
+        const thb_i64 row = w / nchunks;
+        const thb_u32 c0 = (thb_u32)(w - row * nchunks) * THB_SCH_TILE;
+        // 128-byte rows past the end of the row are clipped by the TMA unit
+        thb_tma_store_3d(&map_dst, thb_smem_u32(smem + s * THB_SCH_STAGE_BYTES), 0, (int)(c0 >> 5), (int)row);
+        asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+        asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+        thb_mbar_arrive(thb_smem_u32(&bar_empty[s]));
+      }
+      asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
+    }
+  } else {
+    const int cw = warp - 3;
+    // This lane's 16 consecutive elements: half of row `srow` of the stage ([TILE / 32] rows of 128 bytes whose
+    // 16-byte pieces sit at (piece ^ (row & 7)): the 128-byte swizzle of the tensor map).
+    const thb_u32 e_lane = cw * THB_SCH_WARP_ELEMS + lane * THB_SCH_LANE_ELEMS;
+    const int srow = cw * (THB_SCH_WARP_ELEMS / 32) + (lane >> 1);
+    uint32_t piece_off[THB_SCH_PIECES];
+#pragma unroll
+    for (int j = 0; j < THB_SCH_PIECES; ++j) piece_off[j] = srow * 128 + ((((lane & 1) * 4 + j) ^ (srow & 7)) << 4);
+    for (int i = 0; i < iters + THB_SCH_LAG; ++i) {
+      if (i < iters) {  // pass A: the tile's total
+        const int s = i % THB_SCH_STAGES;
+        const uint32_t par = (uint32_t)(i / THB_SCH_STAGES) & 1;
+        bool ok = thb_mbar_wait(thb_smem_u32(&bar_full[s]), par, abort_flag);
+        if (!__all_sync(0xffffffffu, ok)) {
+          if (lane == 0) THB_SCH_GIVE_UP(5);
+          break;
+        }
+        const thb_i64 w = w_first + (thb_i64)i * G;
+        const thb_u32 c0 = (thb_u32)(w % nchunks) * THB_SCH_TILE;
+        const thb_u32 len = min((thb_u32)THB_SCH_TILE, n - c0);
+        const uint8_t* tile = smem + s * THB_SCH_STAGE_BYTES;
+        double tot = Op::identity();
+        if (e_lane < len) {  // n is a multiple of 32: a lane's elements are all inside or all outside
+          double a[THB_SCH_PIECES];
+#pragma unroll
+          for (int j = 0; j < THB_SCH_PIECES; ++j) {
+            const float4 t = *reinterpret_cast<const float4*>(tile + piece_off[j]);
+            a[j] = Op::apply(Op::apply((double)t.x, (double)t.y), Op::apply((double)t.z, (double)t.w));
+          }
+          tot = Op::apply(Op::apply(a[0], a[1]), Op::apply(a[2], a[3]));
+        }
+#pragma unroll
+        for (int off = 1; off < 32; off <<= 1) tot = Op::apply(tot, __shfl_xor_sync(0xffffffffu, tot, off));
+        if (lane == 0) {
+          wtot[s * THB_SCH_CWARPS + cw] = tot;
+          thb_mbar_arrive(thb_smem_u32(&bar_tot[s]));
+        }
+        if (cw == 0) {
+          ok = thb_mbar_wait(thb_smem_u32(&bar_tot[s]), par, abort_flag);
+          if (!__all_sync(0xffffffffu, ok)) {
+            if (lane == 0) THB_SCH_GIVE_UP(6);
+            break;
+          }
+          if (lane == 0) {
+            // the warp totals become what precedes each warp inside the tile (read in pass B)
+            double t = Op::identity();
+#pragma unroll
+            for (int k = 0; k < THB_SCH_CWARPS; ++k) {
+              const double x = wtot[s * THB_SCH_CWARPS + k];
+              wtot[s * THB_SCH_CWARPS + k] = t;
+              t = Op::apply(t, x);
+            }
+            thb_mbar_arrive(thb_smem_u32(&bar_pre[s]));
+            unsigned long long bits = (unsigned long long)__double_as_longlong(t);
+            if (bits == THB_SCH_UNSET) bits ^= 1ull;  // still a NaN; never the "not written" pattern
+            thb_st_relaxed_u64(totals + w, bits);
+          }
+        }
+      }
+      const int j = i - THB_SCH_LAG;
+      if (j >= 0 && j < iters) {  // pass B: carry + scan of the tile, in place
+        const int s = j % THB_SCH_STAGES;
+        const uint32_t par = (uint32_t)(j / THB_SCH_STAGES) & 1;
+        // two arrivals: the carry (warp 1) and the offsets of the warps inside the tile (pass A)
+        bool ok = thb_mbar_wait(thb_smem_u32(&bar_pre[s]), par, abort_flag);
+        if (!__all_sync(0xffffffffu, ok)) {
+          if (lane == 0) THB_SCH_GIVE_UP(7);
+          break;
+        }
+        const thb_i64 w = w_first + (thb_i64)j * G;
+        const thb_u32 c0 = (thb_u32)(w % nchunks) * THB_SCH_TILE;
+        const thb_u32 len = min((thb_u32)THB_SCH_TILE, n - c0);
+        uint8_t* tile = smem + s * THB_SCH_STAGE_BYTES;
+        const bool live = e_lane < len;
+        const double run = Op::apply(carry_s[s], wtot[s * THB_SCH_CWARPS + cw]);  // everything before this warp's elements
+        // inclusive scans inside each float4, in double
+        double q[THB_SCH_PIECES][4];
+        const float idf = (float)Op::identity();
+#pragma unroll
+        for (int u = 0; u < THB_SCH_PIECES; ++u) {
+          float4 t = make_float4(idf, idf, idf, idf);
+          if (live) t = *reinterpret_cast<const float4*>(tile + piece_off[u]);
+          q[u][0] = (double)t.x;
+          q[u][1] = Op::apply(q[u][0], (double)t.y);
+          q[u][2] = Op::apply(q[u][1], (double)t.z);
+          q[u][3] = Op::apply(q[u][2], (double)t.w);
+        }
+        // what precedes each float4 inside the lane, and the lane's total
+        double o[THB_SCH_PIECES];
+        o[0] = Op::identity();
+#pragma unroll
+        for (int u = 1; u < THB_SCH_PIECES; ++u) o[u] = Op::apply(o[u - 1], q[u - 1][3]);
+        double incl = Op::apply(o[THB_SCH_PIECES - 1], q[THB_SCH_PIECES - 1][3]);
+#pragma unroll
+        for (int off = 1; off < 32; off <<= 1) {
+          const double t = __shfl_up_sync(0xffffffffu, incl, off);
+          if (lane >= off) incl = Op::apply(t, incl);
+        }
+        double excl = __shfl_up_sync(0xffffffffu, incl, 1);
+        if (lane == 0) excl = Op::identity();
+        const double before = Op::apply(run, excl);
+        if (live) {
+#pragma unroll
+          for (int u = 0; u < THB_SCH_PIECES; ++u) {
+            const double b = Op::apply(before, o[u]);
+            *reinterpret_cast<float4*>(tile + piece_off[u]) =
+                make_float4((float)Op::apply(b, q[u][0]), (float)Op::apply(b, q[u][1]), (float)Op::apply(b, q[u][2]),
+                            (float)Op::apply(b, q[u][3]));
+          }
+        }
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // results visible to the TMA store
+        __syncwarp();
+        if (lane == 0) thb_mbar_arrive(thb_smem_u32(&bar_done[s]));
+      }
+    }
+  }
+#undef THB_SCH_GIVE_UP
+  __syncthreads();
+}

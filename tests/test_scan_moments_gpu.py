@@ -93,7 +93,10 @@ SCAN_SHAPES = [((50, 60), 0), ((50, 60), 1), ((3, 1000, 7), 1), ((3, 1000, 8), 1
                ((100000, 8), 0), ((100000, 3), 0), ((1 << 22,), 0), (((1 << 22) + 5,), 0), ((2000, 129), 1),
                ((2000, 128), 1), ((1, 1), 0), ((5, 1), 1), ((1, 9), 0), ((33000, 40), 0),
                # few thousand columns and many rows: one pass over 128-column strips (ragged last strip, ragged rows)
-               ((2000, 12800), 0), ((1000, 12700), 0), ((12, 500, 1028), 1), ((70, 16384), 0)]
+               ((2000, 12800), 0), ((1000, 12700), 0), ((12, 500, 1028), 1), ((70, 16384), 0),
+               # few long rows: single pass over 8192-element tiles that wait for their carries (rows that end
+               # inside a round of tiles, ragged last tiles, fewer tiles than SMs, more than one round)
+               ((3, (1 << 20) + 32), 1), ((3, (1 << 20) + 4), 1), ((1 << 24,), 0), ((7, 81920), 1), ((2, 16384), 1), ((150, 40000), 1)]
 
 
 def scan_close(got, want_f32, src, dim, is_mul, what):
@@ -144,6 +147,19 @@ def test_strip_scan_in_place_and_status_word():
     r = cl.ClTensor(a)
     r.cumsum(r, 1)                                                           # in place along the rows: the strip path
     scan_close(r.float(), O.scan(a, 0, False), a, 0, False, "strips, in place")
+    cl.synchronize()                                                         # reads the kernels' status word: must be 0
+
+
+def test_chained_scan_in_place_repeatable_and_status_word():
+    import cltorch_b200 as cl
+    a = rng_uniform(49, (2, (1 << 21) + 96), -0.5, 0.5)
+    want = O.scan(a, 1, False)
+    r = cl.ClTensor(a)
+    r.cumsum(r, 2)                                                           # in place: a tile is loaded before it is stored
+    first = r.float()
+    scan_close(first, want, a, 1, False, "chained, in place")
+    for _ in range(3):                                                       # the order of the additions is fixed
+        assert np.array_equal(cl.ClTensor(a).cumsum(2).float(), first)
     cl.synchronize()                                                         # reads the kernels' status word: must be 0
 
 
