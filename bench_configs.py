@@ -430,7 +430,7 @@ def n3(T):
     T.time("cumprod(A, 2)", lambda: B.cumprod(A, 2), 8 * n)
     V = cl.ClTensor(g.standard_normal((n,), dtype=np.float32))
     W = cl.ClTensor(n)
-    T.time("cumsum of a 2^28 vector [8 B/elt; chunked: 12 moved]", lambda: W.cumsum(V, 1), 8 * n)
+    T.time("cumsum of a 2^28 vector [8 B/elt; single pass, tiles wait for their carries in L2]", lambda: W.cumsum(V, 1), 8 * n)
     T.time("dist(A, B, 2) -> point tensor", lambda: pt.dist_gpu(A, B, 2), 8 * n)
     # renorm in place along dimension 1 (rows of 16384 normal values have 2-norms close to 128:
     # about half of them exceed the limit and are rescaled); A is restored before every call
@@ -458,7 +458,7 @@ def n1(T):
 
 
 def n3small(T):
-    """var, cumsum and dist on 8192 x 8192 (profiler captures of the moments and scan kernels)."""
+    """var, cumsum and dist on 8192 x 8192 and cumsum of a 2^26 vector (profiler captures of the moments and scan kernels)."""
     cl = T.cl
     g = np.random.Generator(np.random.PCG64(5))
     n = 8192
@@ -469,6 +469,9 @@ def n3small(T):
         T.time(f"var(A, {d})", lambda: out.var(A, d), 4 * n * n)
         T.time(f"cumsum(A, {d})", lambda: B.cumsum(A, d), 8 * n * n)
     T.time("dist(A, B, 2) -> point tensor", lambda: pt.dist_gpu(A, B, 2), 8 * n * n)
+    V = cl.ClTensor(g.standard_normal((1 << 26,), dtype=np.float32))
+    W = cl.ClTensor(1 << 26)
+    T.time("cumsum of a 2^26 vector", lambda: W.cumsum(V, 1), 8 << 26)
 
 
 GROUPS = {"c1": c1, "c2": c2, "c3": c3, "c4": c4, "c4small": c4small, "c4batched": c4batched, "c4mlp": c4mlp, "c2small": c2small,

@@ -3,7 +3,6 @@
 #include "../kernels/math_policy.cuh"
 #include "../kernels/scan_strip_kernels.cuh"
 #include "../kernels/scan_chain_kernels.cuh"
-#include <stdlib.h>
 
 #define THB_SCH_TILE 8192  // elements per tile of the chained scan
 #include "thb_strips.h"
@@ -129,25 +128,13 @@ static int run_scan_chain(cudaStream_t st, float* dst, const float* src, int64_t
   if (int rc = make_chain_map(&map_src, src, outer, n)) return rc;
   if (int rc = make_chain_map(&map_dst, dst, outer, n)) return rc;
   void* args[] = {&map_src, &map_dst, &n32, &nchunks, &nwork, &totals, &status};
-  static int variant = -1;
-  if (variant < 0) { const char* e = getenv("THB200_SCAN_CHAIN_VARIANT"); variant = e ? atoi(e) : 0; }
-#define THB_SCH_LAUNCH(TILE, STAGES, LAG)                                                                             \
-  do {                                                                                                                \
-    auto kern = thb_scan_chain<Op, TILE, STAGES, LAG>;                                                                \
-    THB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, THB_SCH_SMEM_BYTES(TILE, STAGES))); \
-    THB_CUDA(cudaLaunchCooperativeKernel((const void*)kern, dim3(ctas), dim3(THB_SCH_THREADS), args,                  \
-                                         THB_SCH_SMEM_BYTES(TILE, STAGES), st));                                      \
-  } while (0)
-  switch (variant) {
-    case 1: THB_SCH_LAUNCH(THB_SCH_TILE, 6, 2); break;
-    case 2: THB_SCH_LAUNCH(THB_SCH_TILE, 6, 1); break;
-    case 3: THB_SCH_LAUNCH(THB_SCH_TILE, 7, 2); break;
-    case 4: THB_SCH_LAUNCH(THB_SCH_TILE, 7, 3); break;
-    case 5: THB_SCH_LAUNCH(THB_SCH_TILE, 7, 4); break;
-    case 6: THB_SCH_LAUNCH(THB_SCH_TILE, 7, 5); break;
-    default: THB_SCH_LAUNCH(THB_SCH_TILE, 7, 4); break;
-  }
-#undef THB_SCH_LAUNCH
+  // 3 stages of first visits, 4 of second visits, at most 4 tiles between the two: measured 349-352 us on 2^28
+  // elements; 3/3/4 363 us, 2/4/4 385 us, 3/3/3 414 us, 3/3/5 and 4/3/4 423 us (a longer lead of the first
+  // visits pushes tiles out of L2 before their second visit).
+  auto kern = thb_scan_chain<Op, THB_SCH_TILE, 3, 4, 4>;
+  const int smem = THB_SCH_SMEM_BYTES(THB_SCH_TILE, 3, 4, 4);
+  THB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+  THB_CUDA(cudaLaunchCooperativeKernel((const void*)kern, dim3(ctas), dim3(THB_SCH_THREADS), args, smem, st));
   return 0;
 }
 

@@ -252,13 +252,15 @@ int thb200_var_all(void* stream, const thb200_tensor* in, int biased, int apply_
  * (src/lib/THClTensorMathScan.cpp:29-142, src/lib/THClTensorMathScan.cl:27-139); op is
  * THB200_RED_ADD (cumsum, start 0) or THB200_RED_MUL (cumprod, start 1). Running values are
  * kept in double and rounded at each store. dst may be src. When the other dimensions are
- * too small to fill the GPU, n is cut into chunks (totals, scan of totals, scan with carry)
- * and `scratch` (8-byte aligned) holds the carries; the pointers matter to the size because
- * 16-byte aligned operands take a different path. One of the paths (a TMA pipeline over
- * 128-column strips) waits on shared-memory barriers: every such wait is bounded, and a wait
- * that gives up stores a non-zero code into *d_status (a device int the caller keeps at 0 and
- * may read after synchronising; NULL = the library's own word, see thb200_kernel_status) and
- * leaves dst undefined. */
+ * too small to fill the GPU, n is cut into chunks and `scratch` (8-byte aligned) holds the
+ * chunk totals / carries; the pointers matter to the size because 16-byte aligned operands
+ * take a different path. Few long rows (inner == 1, n a multiple of 32, 16-byte aligned) are
+ * scanned in a single pass by co-resident CTAs (a cooperative launch) that hand each other
+ * their tile totals through `scratch`, in a fixed order of additions: results do not vary from
+ * run to run. That path and the TMA pipeline over 128-column strips wait on barriers and on
+ * words of `scratch`: every such wait is bounded, and a wait that gives up stores a non-zero
+ * code into *d_status (a device int the caller keeps at 0 and may read after synchronising;
+ * NULL = the library's own word, see thb200_kernel_status) and leaves dst undefined. */
 size_t thb200_scan_scratch_bytes(const float* dst, const float* src, int64_t outer, int64_t n, int64_t inner);
 int thb200_scan(void* stream, int op, float* dst, const float* src, int64_t outer, int64_t n, int64_t inner,
                 void* scratch, size_t scratch_bytes, int* d_status);
