@@ -16,7 +16,13 @@ struct ScanPlan {
   bool strips;      // single pass over 128-column strips through a TMA pipeline
   int strips_per_outer, total_strips;
   bool chain;       // inner == 1, few long rows: single pass over tiles that wait for their carries
+  uint32_t tail;    // chain, one vector: elements after the last multiple of 32, scanned by a follow-up kernel
 };
+
+static size_t scan_scratch_need(const ScanPlan& p, int64_t outer, int64_t inner) {
+  if (p.nchunks <= 1) return 0;
+  return ((size_t)outer * p.nchunks * inner + (p.chain ? (size_t)outer : 0)) * sizeof(double);
+}
 
 // Whether kernels can be launched with all their CTAs guaranteed resident (the chained scan's
 // CTAs wait for one another's totals).
@@ -36,6 +42,7 @@ static ScanPlan plan_scan(const float* dst, const float* src, int64_t outer, int
   p.strips = false;
   p.strips_per_outer = p.total_strips = 0;
   p.chain = false;
+  p.tail = 0;
   p.rows = inner == 1;
   const bool aligned = (((uintptr_t)dst | (uintptr_t)src) & 15) == 0;
   if (p.rows) {
@@ -53,11 +60,12 @@ static ScanPlan plan_scan(const float* dst, const float* src, int64_t outer, int
     p.nchunks = (uint32_t)((n + len - 1) / len);
     // Rows that have to be cut (three phases, 12 bytes per element) go through the chained
     // single-pass kernel instead when the layout suits bulk copies.
-    if (p.nchunks > 1 && aligned && (n & 31) == 0 && n >= 2 * THB_SCH_TILE && outer < (int64_t(1) << 31) &&
-        cooperative_launch_ok() && tensor_map_encoder_ptr() != nullptr) {
+    if (p.nchunks > 1 && aligned && ((n & 31) == 0 || outer == 1) && n >= 2 * THB_SCH_TILE &&
+        outer < (int64_t(1) << 31) && cooperative_launch_ok() && tensor_map_encoder_ptr() != nullptr) {
       p.chain = true;
+      p.tail = (uint32_t)(n & 31);
       p.chunk_len = THB_SCH_TILE;
-      p.nchunks = (uint32_t)((n + THB_SCH_TILE - 1) / THB_SCH_TILE);
+      p.nchunks = (uint32_t)((n - p.tail + THB_SCH_TILE - 1) / THB_SCH_TILE);
     }
   } else {
     p.vec = (aligned && (inner & 3) == 0) ? 4 : 1;
@@ -119,6 +127,9 @@ static int run_scan_chain(cudaStream_t st, float* dst, const float* src, int64_t
                           const ScanPlan& p, int* d_status) {
   thb_i64 nwork = outer * (int64_t)p.nchunks;
   unsigned long long* totals = (unsigned long long*)scratch;
+  double* row_carry = scratch + nwork;  // [outer]
+  const int64_t n_all = n;
+  n -= p.tail;  // the part the tiles cover
   THB_CUDA(cudaMemsetAsync(totals, 0xFF, (size_t)nwork * sizeof(unsigned long long), st));  // "not written yet"
   int ctas = sm_count() < THB_SCH_MAX_CTAS ? sm_count() : THB_SCH_MAX_CTAS;
   if (nwork < ctas) ctas = (int)nwork;
@@ -127,7 +138,7 @@ static int run_scan_chain(cudaStream_t st, float* dst, const float* src, int64_t
   CUtensorMap map_src, map_dst;
   if (int rc = make_chain_map(&map_src, src, outer, n)) return rc;
   if (int rc = make_chain_map(&map_dst, dst, outer, n)) return rc;
-  void* args[] = {&map_src, &map_dst, &n32, &nchunks, &nwork, &totals, &status};
+  void* args[] = {&map_src, &map_dst, &n32, &nchunks, &nwork, &totals, &row_carry, &status};
   // 3 stages of first visits, 4 of second visits, at most 4 tiles between the two: measured 349-352 us on 2^28
   // elements; 3/3/4 363 us, 2/4/4 385 us, 3/3/3 414 us, 3/3/5 and 4/3/4 423 us (a longer lead of the first
   // visits pushes tiles out of L2 before their second visit).
@@ -135,6 +146,10 @@ static int run_scan_chain(cudaStream_t st, float* dst, const float* src, int64_t
   const int smem = THB_SCH_SMEM_BYTES(THB_SCH_TILE, 3, 4, 4);
   THB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
   THB_CUDA(cudaLaunchCooperativeKernel((const void*)kern, dim3(ctas), dim3(THB_SCH_THREADS), args, smem, st));
+  if (p.tail) {
+    thb_scan_chain_tail<Op><<<1, 32, 0, st>>>(dst, src, n32, (thb_u32)n_all, nchunks, totals, row_carry);
+    THB_CUDA(cudaGetLastError());
+  }
   return 0;
 }
 
@@ -202,7 +217,7 @@ extern "C" {
 size_t thb200_scan_scratch_bytes(const float* dst, const float* src, int64_t outer, int64_t n, int64_t inner) {
   if (outer <= 0 || n <= 0 || inner <= 0) return 0;
   const ScanPlan p = plan_scan(dst, src, outer, n, inner);
-  return p.nchunks > 1 ? (size_t)outer * p.nchunks * inner * sizeof(double) : 0;
+  return scan_scratch_need(p, outer, inner);
 }
 
 int thb200_scan(void* stream, int op, float* dst, const float* src, int64_t outer, int64_t n, int64_t inner,
@@ -214,7 +229,7 @@ int thb200_scan(void* stream, int op, float* dst, const float* src, int64_t oute
   if (n >= (int64_t(1) << 31)) return fail("scan: dimension of %lld elements is too long", (long long)n);
   if (op != THB200_RED_ADD && op != THB200_RED_MUL) return fail("scan: operator %d is neither add nor mul", op);
   const ScanPlan p = plan_scan(dst, src, outer, n, inner);
-  const size_t need = p.nchunks > 1 ? (size_t)outer * p.nchunks * inner * sizeof(double) : 0;
+  const size_t need = scan_scratch_need(p, outer, inner);
   if (need && (!scratch || scratch_bytes < need || ((uintptr_t)scratch & 7)))
     return fail("scan: scratch too small or misaligned (%zu bytes, need %zu)", scratch_bytes, need);
   return op == THB200_RED_ADD

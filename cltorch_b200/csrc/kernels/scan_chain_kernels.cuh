@@ -27,6 +27,9 @@
 // tree), so the result does not depend on which CTA was early. Totals never depend on carries,
 // so no CTA waits for another's scan, only for its loads.
 //
+// A single vector whose length is not a multiple of 32 is scanned up to the last multiple; thb_scan_chain_tail
+// continues over the remaining elements from the carry and the total of the last tile.
+//
 // Every wait is bounded (THB_GEMM_WAIT_LIMIT_NS). On expiry the waiter writes *status and sets
 // the CTA's abort flag; waits in other CTAs notice *status and leave as well.
 #pragma once
@@ -59,7 +62,7 @@ __device__ __forceinline__ void thb_st_relaxed_u64(unsigned long long* p, unsign
 template <class Op, int TILE, int SA, int SB, int NSLOT>
 __global__ void __launch_bounds__(THB_SCH_THREADS, 1)
 thb_scan_chain(const __grid_constant__ CUtensorMap map_src, const __grid_constant__ CUtensorMap map_dst, thb_u32 n,
-               thb_u32 nchunks, thb_i64 nwork, unsigned long long* totals, int* status) {
+               thb_u32 nchunks, thb_i64 nwork, unsigned long long* totals, double* row_carry, int* status) {
   constexpr int STAGE_BYTES = TILE * 4;
   constexpr int WARP_ELEMS = TILE / THB_SCH_CWARPS;
   constexpr int LANE_ELEMS = WARP_ELEMS / 32;  // consecutive elements of a lane
@@ -213,6 +216,7 @@ thb_scan_chain(const __grid_constant__ CUtensorMap map_src, const __grid_constan
       if (lane == 0) {
         carry_s[slot] = prev;
         thb_mbar_arrive(thb_smem_u32(&bar_pre[slot]));
+        if (row_carry && w - row0 == (thb_i64)nchunks - 1) row_carry[row0 / nchunks] = prev;  // what precedes the row's last tile
       }
     }
   } else if (warp == 2) {
@@ -374,4 +378,17 @@ thb_scan_chain(const __grid_constant__ CUtensorMap map_src, const __grid_constan
   }
 #undef THB_SCH_GIVE_UP
   __syncthreads();
+}
+
+// The up to 31 elements of a single vector that follow the part scanned by thb_scan_chain (n_main elements,
+// nchunks tiles): running value = carry of the last tile (+) its total, then element by element.
+template <class Op>
+__global__ void thb_scan_chain_tail(float* dst, const float* src, thb_u32 n_main, thb_u32 n, thb_u32 nchunks,
+                                    const unsigned long long* totals, const double* row_carry) {
+  if (threadIdx.x != 0 || blockIdx.x != 0) return;
+  double run = Op::apply(row_carry[0], __longlong_as_double((long long)totals[nchunks - 1]));
+  for (thb_u32 k = n_main; k < n; ++k) {
+    run = Op::apply(run, (double)src[k]);
+    dst[k] = (float)run;
+  }
 }

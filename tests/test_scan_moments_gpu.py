@@ -96,7 +96,9 @@ SCAN_SHAPES = [((50, 60), 0), ((50, 60), 1), ((3, 1000, 7), 1), ((3, 1000, 8), 1
                ((2000, 12800), 0), ((1000, 12700), 0), ((12, 500, 1028), 1), ((70, 16384), 0),
                # few long rows: single pass over 8192-element tiles that wait for their carries (rows that end
                # inside a round of tiles, ragged last tiles, fewer tiles than SMs, more than one round)
-               ((3, (1 << 20) + 32), 1), ((3, (1 << 20) + 4), 1), ((1 << 24,), 0), ((7, 81920), 1), ((2, 16384), 1), ((150, 40000), 1)]
+               ((3, (1 << 20) + 32), 1), ((3, (1 << 20) + 4), 1), ((1 << 24,), 0), ((7, 81920), 1), ((2, 16384), 1), ((150, 40000), 1),
+               # one vector of any length: the elements after the last multiple of 32 follow in a second kernel
+               (((1 << 20) + 17,), 0), ((1, 16384 + 31), 1)]
 
 
 def scan_close(got, want_f32, src, dim, is_mul, what):
