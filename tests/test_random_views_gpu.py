@@ -1,0 +1,144 @@
+"""Seeded differential runs over randomly laid-out views: every case draws shapes, permuted and
+gapped strides and storage offsets, performs the same operation through the THCl API on the GPU
+and through the CPU oracle, and compares the WHOLE storages (stray writes are caught too).
+
+The reference's engine accepts any strided operand (src/lib/THClApply.cpp:152-237 pairs elements
+by linear index in each tensor's own shape; src/lib/THClReduce.cpp:93-160 reduces any layout);
+its own tests only use a handful of hand-written layouts (src/test/unit_tensor.lua), so these
+cases widen the coverage of the same contract.
+
+Tolerance: bit-exact for + - * copies, fills and max/min with their indices; 1e-5 relative (of
+the sum of magnitudes) for sums, <= 1 ulp or 1e-12 of the running magnitude for scans.
+"""
+import numpy as np
+import pytest
+
+from oracle import oracle as O
+from tests.util import Pair
+
+pytestmark = pytest.mark.gpu
+
+
+def _factor_shape(g, n: int, nd: int):
+    """A random shape of `nd` dims whose product is n (n's prime factors dealt out at random)."""
+    shape = [1] * nd
+    m, p = n, 2
+    while m > 1:
+        while m % p == 0:
+            shape[int(g.integers(nd))] *= p
+            m //= p
+        p += 1
+    return shape
+
+
+def _random_layout(g, shape, allow_unit_gap=True):
+    """(storage length, offset, strides): the dims in a random memory order, each with a random
+    gap (so rows are padded / elements are strided), at a random storage offset."""
+    nd = len(shape)
+    order = list(g.permutation(nd))          # order[0] is the fastest-varying dim in memory
+    strides = [0] * nd
+    step = int(g.choice([1, 1, 1, 2, 3])) if allow_unit_gap else 1
+    for d in order:
+        strides[d] = step
+        pad = int(g.choice([0, 0, 1, 3, 4]))
+        step = step * (shape[d] + pad)
+    offset = int(g.choice([0, 0, 1, 3, 4, 16]))
+    length = offset + sum((s - 1) * st for s, st in zip(shape, strides)) + 1 + int(g.integers(0, 5))
+    return length, offset, strides
+
+
+def _pair(g, n: int, lo=-1.0, hi=1.0, nd=None, contiguous=False, eighths=False) -> Pair:
+    nd = int(g.integers(1, 5)) if nd is None else nd
+    shape = _factor_shape(g, n, nd)
+    if contiguous:
+        length, offset, strides = n, 0, None
+    else:
+        length, offset, strides = _random_layout(g, shape)
+    base = (g.random(length, dtype=np.float32) * np.float32(hi - lo) + np.float32(lo)).astype(np.float32)
+    if eighths:  # few distinct values: ties
+        base = (np.round(base * 8) / 8).astype(np.float32)
+    return Pair(base, offset, shape, strides)
+
+
+# element counts with many factorisations; the larger ones reach the vector, tile and TMA kernels
+COUNTS = [1, 2, 7, 24, 210, 840, 4096, 30030, 65536, 2 * 3 * 5 * 7 * 64, 1 << 20, 3 * (1 << 18)]
+
+
+@pytest.mark.parametrize("seed", range(36))
+def test_apply_on_random_views(seed):
+    g = np.random.Generator(np.random.PCG64(1000 + seed))
+    n = COUNTS[seed % len(COUNTS)]
+    r, a, b = _pair(g, n), _pair(g, n), _pair(g, n, 0.5, 2.0)
+    tag = f"seed {seed} n {n}: r {r.view.sizes}/{r.view.strides}+{r.view.offset} a {a.view.sizes}/{a.view.strides}+{a.view.offset} " \
+          f"b {b.view.sizes}/{b.view.strides}+{b.view.offset}"
+    r.cl.add(a.cl); O.apply("ADD_2", [r.view, a.view])
+    r.check(0, "add " + tag)
+    r.cl.cmul(b.cl); O.apply("MUL_2", [r.view, b.view])
+    r.check(0, "cmul " + tag)
+    r.cl.addcmul(0.25, a.cl, b.cl); O.apply("ADDCMUL_3", [r.view, a.view, b.view], 0.25)
+    r.check(0, "addcmul " + tag)
+    r.cl.cdiv(b.cl); O.apply("DIV_2", [r.view, b.view])
+    r.check(0, "cdiv " + tag)
+    r.cl.copy(a.cl); O.apply("COPY_2", [r.view, a.view])
+    r.check(0, "copy " + tag)
+    r.cl.mul(1.5); O.apply("MULC_1", [r.view], 1.5)
+    r.cl.clamp(-0.75, 0.5); O.apply("CLAMP_1", [r.view], -0.75, 0.5)
+    r.check(0, "mul, clamp " + tag)
+    a.check(0, "source a untouched " + tag)
+    b.check(0, "source b untouched " + tag)
+
+
+@pytest.mark.parametrize("seed", range(12))
+def test_expressions_on_random_views(seed):
+    g = np.random.Generator(np.random.PCG64(2000 + seed))
+    n = COUNTS[(seed * 5 + 3) % len(COUNTS)]
+    r, a, b = _pair(g, n, 0.0, 1.0), _pair(g, n, 0.0, 1.0), _pair(g, n, 0.5, 2.0)
+    expr = "x = sqrt(1000 * x + y * 10 + z * z)"                            # + * sqrt only: exactly rounded on both sides
+    want = O.eval_expr(expr, r.view.numpy().reshape(-1).copy(), a.view.numpy().reshape(-1).copy(),
+                       b.view.numpy().reshape(-1).copy())
+    r.cl.map2_on_gpu(a.cl, b.cl, expr)
+    r.view.numpy()[...] = np.asarray(want, np.float32).reshape(r.view.sizes)
+    r.check(0, f"map2 seed {seed} n {n} {r.view.sizes}/{r.view.strides}")
+    a.check(0, "source untouched")
+
+
+@pytest.mark.parametrize("seed", range(24))
+def test_reductions_on_random_views(seed):
+    g = np.random.Generator(np.random.PCG64(3000 + seed))
+    n = [24, 840, 30030, 65536, 2 * 3 * 5 * 7 * 64, 1 << 20][seed % 6]
+    nd = int(g.integers(2, 5))
+    a = _pair(g, n, nd=nd, eighths=True)   # values with ties, so that "first occurrence" is exercised
+    arr = np.ascontiguousarray(a.view.numpy())
+    tag = f"seed {seed} {a.view.sizes}/{a.view.strides}+{a.view.offset}"
+    total = a.cl.sum()
+    assert abs(total - float(arr.astype(np.float64).sum())) <= 1e-5 * float(np.abs(arr).astype(np.float64).sum()) + 1e-30, tag
+    assert a.cl.max() == float(arr.max()) and a.cl.min() == float(arr.min()), tag
+    for dim in range(nd):
+        got = a.cl.sum(dim + 1).float()
+        want = arr.astype(np.float64).sum(axis=dim, keepdims=True)
+        scale = np.abs(arr).astype(np.float64).sum(axis=dim, keepdims=True)
+        assert got.shape == want.shape, tag
+        assert np.all(np.abs(got - want) <= 1e-5 * scale + 1e-30), f"sum({dim + 1}) {tag}"
+        for is_max in (True, False):
+            v, i = (a.cl.max(dim + 1) if is_max else a.cl.min(dim + 1))
+            wv, wi = O.reduce_dim_index(arr, dim, is_max)
+            assert np.array_equal(v.float(), wv), f"{'max' if is_max else 'min'}({dim + 1}) values {tag}"
+            assert np.array_equal(i.float(), wi), f"{'max' if is_max else 'min'}({dim + 1}) indices {tag}"
+    a.check(0, "source untouched " + tag)
+
+
+@pytest.mark.parametrize("seed", range(12))
+def test_scans_on_random_views(seed):
+    g = np.random.Generator(np.random.PCG64(4000 + seed))
+    n = [840, 30030, 65536, 2 * 3 * 5 * 7 * 64, 1 << 20, 1 << 21][seed % 6]
+    nd = int(g.integers(1, 4))
+    a = _pair(g, n, -0.5, 0.5, nd=nd, contiguous=seed % 2 == 0)
+    arr = np.ascontiguousarray(a.view.numpy())
+    for dim in range(nd):
+        got = a.cl.cumsum(dim + 1).float()
+        want = O.scan(arr, dim, False)
+        d = O.ulp_diff(got, want)
+        scale = np.cumsum(np.abs(arr.astype(np.float64)), axis=dim)
+        bad = (d > 1) & (np.abs(got.astype(np.float64) - want.astype(np.float64)) > 1e-12 * scale)
+        assert not bad.any(), f"cumsum({dim + 1}) seed {seed} {a.view.sizes}/{a.view.strides}: {int(bad.sum())} elements off"
+    a.check(0, "source untouched")
