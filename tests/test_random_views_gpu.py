@@ -8,7 +8,8 @@ its own tests only use a handful of hand-written layouts (src/test/unit_tensor.l
 cases widen the coverage of the same contract.
 
 Tolerance: bit-exact for + - * copies, fills and max/min with their indices; 1e-5 relative (of
-the sum of magnitudes) for sums, <= 1 ulp or 1e-12 of the running magnitude for scans.
+the sum of magnitudes) for sums, <= 1 ulp or 1e-12 of the running magnitude for scans, 1e-5 in the
+Frobenius norm for matrix products.
 """
 import numpy as np
 import pytest
@@ -142,3 +143,47 @@ def test_scans_on_random_views(seed):
         bad = (d > 1) & (np.abs(got.astype(np.float64) - want.astype(np.float64)) > 1e-12 * scale)
         assert not bad.any(), f"cumsum({dim + 1}) seed {seed} {a.view.sizes}/{a.view.strides}: {int(bad.sum())} elements off"
     a.check(0, "source untouched")
+
+
+def _matrix(g, rows: int, cols: int, lo=-1.0, hi=1.0):
+    """(ClTensor view, numpy array of its values): row-major, column-major (a transposed view) or a
+    window of a wider matrix, at random."""
+    import cltorch_b200 as cl
+    kind = int(g.integers(3))
+    vals = (g.random((rows, cols), dtype=np.float32) * np.float32(hi - lo) + np.float32(lo)).astype(np.float32)
+    if kind == 0:
+        return cl.ClTensor(vals), vals
+    if kind == 1:
+        return cl.ClTensor(np.ascontiguousarray(vals.T)).t(), vals
+    pad = int(g.choice([1, 3, 4, 8]))
+    wide = np.zeros((rows, cols + pad), np.float32)
+    wide[:, :cols] = vals
+    return cl.ClTensor(wide).narrow(2, 1, cols), vals
+
+
+@pytest.mark.parametrize("seed", range(30))
+def test_addmm_on_random_shapes_and_layouts(seed):
+    """THClTensor_addmm (src/lib/THClTensorMathBlas.cpp:107-214) normalises any combination of
+    row-major, transposed and padded operands; beta = 0 must not read the result. The contract is 1e-4
+    relative; the three-term TF32 split with fp32 accumulation in tensor memory lands at 1e-6 for short K and
+    4e-6 to 7e-6 for K in the thousands, so the bar here is 1e-5 in the Frobenius norm and 2e-5 of
+    |alpha| |A| |B| + |beta| |C| per element."""
+    import cltorch_b200 as cl
+    g = np.random.Generator(np.random.PCG64(5000 + seed))
+    pick = lambda: int(g.choice([1, 3, 17, 64, 100, 128, 129, 200, 256, 300, 512, 700]))
+    M, N = pick(), pick()
+    K = int(g.choice([1, 5, 32, 64, 100, 128, 260, 1024, 1100, 2048, 4100]))
+    alpha = float(g.choice([1.0, 2.0, -0.5]))
+    beta = float(g.choice([0.0, 1.0, 0.5]))
+    A, a = _matrix(g, M, K)
+    B, b = _matrix(g, K, N)
+    R, t = _matrix(g, M, N)
+    R.addmm(beta, R, alpha, A, B)
+    want = O.addmm(beta, t, alpha, a, b)
+    got = R.float()
+    tag = f"seed {seed}: {M}x{N}x{K} alpha {alpha} beta {beta} strides A {A.stride()} B {B.stride()} C {R.stride()}"
+    err = np.linalg.norm(got.astype(np.float64) - want) / max(np.linalg.norm(want), 1e-30)
+    assert err <= 1e-5, f"{tag}: relative error {err:.3e}"
+    scale = abs(alpha) * (np.abs(a).astype(np.float64) @ np.abs(b).astype(np.float64)) + abs(beta) * np.abs(t) + 1e-30
+    worst = float((np.abs(got.astype(np.float64) - want) / scale).max())
+    assert worst <= 2e-5, f"{tag}: worst element error {worst:.3e} of its scale"
