@@ -187,3 +187,88 @@ def test_addmm_on_random_shapes_and_layouts(seed):
     scale = abs(alpha) * (np.abs(a).astype(np.float64) @ np.abs(b).astype(np.float64)) + abs(beta) * np.abs(t) + 1e-30
     worst = float((np.abs(got.astype(np.float64) - want) / scale).max())
     assert worst <= 2e-5, f"{tag}: worst element error {worst:.3e} of its scale"
+
+
+@pytest.mark.parametrize("seed", range(18))
+def test_moments_norms_renorm_on_random_views(seed):
+    """var/std (both normalisations), norm and renorm along every dim of a randomly laid-out view, and
+    dist / varall / stdall / normall of it (src/lib/THClTensorMath2.cl:5-143, THClTensorMath2.cpp:293-474)."""
+    g = np.random.Generator(np.random.PCG64(6000 + seed))
+    n = [840, 30030, 65536, 2 * 3 * 5 * 7 * 64, 1 << 18, 1 << 20][seed % 6]
+    nd = int(g.integers(2, 4))
+    a = _pair(g, n, -1.0, 1.0, nd=nd)
+    b = _pair(g, n, -1.0, 1.0, nd=nd)
+    arr = np.ascontiguousarray(a.view.numpy())
+    tag = f"seed {seed} {a.view.sizes}/{a.view.strides}+{a.view.offset}"
+    a64 = arr.astype(np.float64)
+    for dim in range(nd):
+        if arr.shape[dim] > 1:
+            for flag in (False, True):
+                got = a.cl.var(dim + 1, flag).float()
+                want = O.var_dim(arr, dim, flag, False)
+                assert np.all(np.abs(got - want) <= 2e-5 * np.abs(want) + 1e-7), f"var({dim + 1}, {flag}) {tag}"
+                got = a.cl.std(dim + 1, flag).float()
+                want = O.var_dim(arr, dim, flag, True)
+                assert np.all(np.abs(got - want) <= 2e-5 * np.abs(want) + 1e-7), f"std({dim + 1}, {flag}) {tag}"
+        for p in (1.0, 2.0, 3.0):
+            got = a.cl.norm(p, dim + 1).float()
+            want = (np.abs(a64) ** p).sum(axis=dim, keepdims=True) ** (1.0 / p)
+            assert np.all(np.abs(got - want) <= 1e-5 * want + 1e-30), f"norm({p}, {dim + 1}) {tag}"
+        norms = (np.abs(np.swapaxes(a64, dim, 0).reshape(arr.shape[dim], -1)) ** 2).sum(axis=1) ** 0.5
+        maxnorm = float(np.median(norms))
+        if np.abs(norms - maxnorm).min() < 1e-4 * maxnorm:
+            maxnorm *= 1.0 + 1e-3                                           # keep every norm clear of the threshold
+        got = a.cl.renorm(2.0, dim + 1, maxnorm).float()
+        want = O.renorm(arr, 2.0, dim, maxnorm)
+        assert np.all(np.abs(got - want) <= 2e-6 * np.abs(want) + 1e-30), f"renorm(2, {dim + 1}) {tag}"
+    barr = np.ascontiguousarray(b.view.numpy())
+    for p in (1.0, 2.0, 2.5):
+        want = O.dist(arr.reshape(-1), barr.reshape(-1), p)
+        assert abs(a.cl.dist(b.cl, p) - want) <= 1e-5 * want, f"dist({p}) {tag}"
+        want = float((np.abs(a64) ** p).sum() ** (1.0 / p))
+        assert abs(a.cl.norm(p) - want) <= 1e-5 * want, f"normall({p}) {tag}"
+    var = float(a64.var(ddof=1))
+    assert abs(a.cl.var() - var) <= 1e-5 * var and abs(a.cl.std() - var ** 0.5) <= 1e-5 * var ** 0.5, tag
+    a.check(0, "source untouched " + tag)
+    b.check(0, "source untouched " + tag)
+
+
+@pytest.mark.parametrize("seed", range(16))
+def test_addmv_addr_dot_on_random_layouts(seed):
+    """THClTensor_addmv / addr / dot (src/lib/THClTensorMathBlas.cpp:17-105, 216-277) on row-major, transposed
+    and padded matrices and strided vectors. Products rounded to fp32, sums in double: 1e-5 of |A||x| + |y|;
+    addr rounds like the pointwise operator: bit-exact."""
+    import cltorch_b200 as cl
+    g = np.random.Generator(np.random.PCG64(7000 + seed))
+    M = int(g.choice([1, 3, 100, 129, 512, 2000, 4099]))
+    K = int(g.choice([1, 5, 128, 257, 1024, 3000, 8200]))
+    A, a = _matrix(g, M, K)
+
+    def vector(length):
+        step = int(g.choice([1, 1, 2, 3]))
+        base = (g.random(length * step + 2, dtype=np.float32) * 2 - 1).astype(np.float32)
+        t = cl.ClTensor(cl.ClStorage(base), 2, [length], [step])
+        return t, base[1:1 + length * step:step].copy()
+
+    X, x = vector(K)
+    Y, y = vector(M)
+    tag = f"seed {seed}: {M}x{K} A strides {A.stride()} x stride {X.stride()} y stride {Y.stride()}"
+    beta, alpha = float(g.choice([0.0, 1.0, 0.5])), float(g.choice([1.0, -2.0]))
+    R = cl.ClTensor(M)
+    R.addmv(beta, Y, alpha, A, X)
+    want = beta * y.astype(np.float64) + alpha * (a.astype(np.float64) @ x.astype(np.float64))
+    scale = abs(alpha) * (np.abs(a).astype(np.float64) @ np.abs(x).astype(np.float64)) + abs(beta) * np.abs(y) + 1e-30
+    assert np.all(np.abs(R.float() - want) <= 1e-5 * scale), "addmv " + tag
+    At = A.t()
+    R2 = cl.ClTensor(K)
+    R2.addmv(0.0, X, 1.0, At, Y)
+    want = a.astype(np.float64).T @ y.astype(np.float64)
+    scale = np.abs(a).astype(np.float64).T @ np.abs(y).astype(np.float64) + 1e-30
+    assert np.all(np.abs(R2.float() - want) <= 1e-5 * scale), "addmv of the transposed view " + tag
+    want = float(x.astype(np.float64) @ x.astype(np.float64))
+    assert abs(X.dot(X) - want) <= 1e-6 * want + 1e-30, "dot " + tag
+    Rm, rm = _matrix(g, M, K)
+    Rm.addr(0.5, Rm, 2.0, Y, X)
+    want = (np.float32(0.5) * rm + np.float32(2.0) * (y[:, None] * x[None, :]).astype(np.float32)).astype(np.float32)
+    got = Rm.float()
+    assert O.ulp_diff(got, want).max() <= 1, "addr " + tag
