@@ -435,8 +435,8 @@ def n3(T):
     # renorm in place along dimension 1 (rows of 16384 normal values have 2-norms close to 128:
     # about half of them exceed the limit and are rescaled); A is restored before every call
     A0 = cl.ClTensor(rows, rows).copy(A)
-    T.time("renorm(A, 2, 1, 128) in place [4 B/elt norms + 8 B/elt for the half of the rows rescaled]",
-           lambda: A.renorm(A, 2, 1, 128.0), 4 * n + 4 * n, setup=lambda: A.copy(A0))
+    T.time("renorm(A, 2, 1, 128) in place [one pass: 4 B/elt read + 4 B/elt written for the half of the rows rescaled]",
+           lambda: A.renorm(A, 2, 1, 128.0), 4 * n + 2 * n, setup=lambda: A.copy(A0))
 
 
 def n1(T):

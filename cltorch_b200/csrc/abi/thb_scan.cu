@@ -3,6 +3,7 @@
 #include "../kernels/math_policy.cuh"
 #include "../kernels/scan_strip_kernels.cuh"
 #include "../kernels/scan_chain_kernels.cuh"
+#include "../kernels/renorm_kernels.cuh"
 
 #define THB_SCH_TILE 8192  // elements per tile of the chained scan
 #include "thb_strips.h"
@@ -201,6 +202,37 @@ static int run_scan(cudaStream_t st, float* dst, const float* src, int64_t outer
   return 0;
 }
 
+// Rows that fit in the registers of a warp or of a CTA are renormed in one pass.
+template <int PMODE>
+static bool launch_renorm_fused(cudaStream_t st, float* data, int64_t rows, int64_t size, float p, float maxnorm) {
+  const int64_t nvec = size / 4;
+  const int sms = sm_count();
+  const thb_u32 size32 = (thb_u32)size;
+#define THB_RNF_WARP(U)                                                                                              \
+  do {                                                                                                               \
+    int64_t blocks = (rows + THB_RNF_THREADS / 32 - 1) / (THB_RNF_THREADS / 32);                                     \
+    if (blocks > (int64_t)sms * 8) blocks = (int64_t)sms * 8;                                                        \
+    thb_renorm_rows_warp<U, PMODE><<<(unsigned)blocks, THB_RNF_THREADS, 0, st>>>(data, rows, size32, p, maxnorm);     \
+  } while (0)
+#define THB_RNF_BLOCK(U, PER_SM)                                                                                     \
+  do {                                                                                                               \
+    int64_t blocks = rows < (int64_t)sms * (PER_SM) ? rows : (int64_t)sms * (PER_SM);                                \
+    thb_renorm_rows_block<U, PMODE><<<(unsigned)blocks, THB_RNF_THREADS, 0, st>>>(data, rows, size32, p, maxnorm);    \
+  } while (0)
+  if (nvec <= 32) THB_RNF_WARP(1);
+  else if (nvec <= 64) THB_RNF_WARP(2);
+  else if (nvec <= 128) THB_RNF_WARP(4);
+  else if (nvec <= 256) THB_RNF_WARP(8);
+  else if (nvec <= 2 * THB_RNF_THREADS) THB_RNF_BLOCK(2, 8);
+  else if (nvec <= 4 * THB_RNF_THREADS) THB_RNF_BLOCK(4, 8);
+  else if (nvec <= 8 * THB_RNF_THREADS) THB_RNF_BLOCK(8, 4);
+  else if (nvec <= 16 * THB_RNF_THREADS) THB_RNF_BLOCK(16, 2);
+  else return false;
+#undef THB_RNF_WARP
+#undef THB_RNF_BLOCK
+  return true;
+}
+
 static int64_t dist_blocks(int64_t n) {
   const int64_t per_block = (int64_t)THB_RA_THREADS * 16;
   int64_t blocks = (n + per_block - 1) / per_block;
@@ -251,6 +283,17 @@ int thb200_renorm_rows(void* stream, float* data, int64_t rows, int64_t size, fl
   if (!(p > 0.f)) return fail("renorm: non-positive-norm not supported");
   if (rows >= (int64_t(1) << 31) || size >= (int64_t(1) << 31)) return fail("renorm: extent too large");
   if (!scratch || scratch_bytes < (size_t)rows * sizeof(float)) return fail("renorm: scratch too small");
+  if ((((uintptr_t)data) & 15) == 0 && (size & 3) == 0 && size <= 64 * THB_RNF_THREADS) {
+    cudaStream_t st = (cudaStream_t)stream;
+    const bool done = p == 1.0f   ? launch_renorm_fused<1>(st, data, rows, size, p, maxnorm)
+                      : p == 2.0f ? launch_renorm_fused<2>(st, data, rows, size, p, maxnorm)
+                      : p == 3.0f ? launch_renorm_fused<3>(st, data, rows, size, p, maxnorm)
+                                  : launch_renorm_fused<0>(st, data, rows, size, p, maxnorm);
+    if (done) {
+      THB_CUDA(cudaGetLastError());
+      return 0;
+    }
+  }
   // sum |x|^p of every row: the contiguous-dimension reduction, [rows][size] -> [rows][1]
   const int64_t in_size[2] = {rows, size}, in_stride[2] = {size, 1};
   const int64_t out_size[2] = {rows, 1}, out_stride[2] = {1, 1};

@@ -182,7 +182,9 @@ def test_scan_abi_rejects_bad_arguments():
 
 # ---- renorm ----------------------------------------------------------------------------------
 
-@pytest.mark.parametrize("shape,dim", [((200, 300), 0), ((200, 300), 1), ((20, 30, 40), 1), ((64, 8192 + 8), 0)])
+# rows of 300 (a warp per row), 200, 40 * 20 = 800, 8200 (a CTA per row), 20000 (two kernels), 301 (not a multiple of 4: two kernels)
+@pytest.mark.parametrize("shape,dim", [((200, 300), 0), ((200, 300), 1), ((20, 30, 40), 1), ((64, 8192 + 8), 0),
+                                       ((40, 20000), 0), ((50, 301), 0), ((3000, 64), 0), ((300, 1500), 0), ((90, 4000), 0)])
 @pytest.mark.parametrize("p", [1.0, 2.0, 3.0])
 def test_renorm(shape, dim, p):
     import cltorch_b200 as cl
@@ -203,6 +205,22 @@ def test_renorm(shape, dim, p):
     assert_rel(t.float(), want, tol=2e-6, what="in place")
     untouched = want == a
     assert np.array_equal(t.float()[untouched], a[untouched])                # rows within the limit are bit-identical
+
+
+@pytest.mark.parametrize("shape", [(100, 256), (30, 5000), (12, 30000)])
+def test_renorm_general_power_and_zero_limit(shape):
+    import cltorch_b200 as cl
+    a = normal(54, shape)
+    norms = (np.abs(a.astype(np.float64)) ** 2.5).sum(axis=1) ** (1.0 / 2.5)
+    maxnorm = float(np.median(norms)) * (1.0 + 1e-3)
+    out = cl.ClTensor(a).renorm(2.5, 1, maxnorm)
+    assert_rel(out.float(), O.renorm(a, 2.5, 0, maxnorm), tol=1e-5, what="p = 2.5 (power on the special-function unit)")
+    # a limit of zero scales every row with a positive norm to zero; an all-zero row has norm 0, not above the limit
+    b = a.copy()
+    b[3] = 0.0
+    z = cl.ClTensor(b).renorm(2.0, 1, 0.0).float()
+    assert np.array_equal(z, np.zeros_like(b) * b)                           # signed zeros as x * 0 gives them
+    assert np.array_equal(z[3], b[3])
 
 
 def test_renorm_argument_checks():
