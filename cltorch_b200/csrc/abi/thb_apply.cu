@@ -122,7 +122,17 @@ int launch_apply(const ApplyKernels& k, cudaStream_t st, int nt, const thb200_te
       if (blocks > cap) blocks = cap;
       if (blocks < 1) blocks = 1;
       void* args[] = {&a, &b, &cc, &nn, &head, &s};
-      THB_CUDA(cudaLaunchKernel(k.contig, dim3((unsigned)blocks), dim3(THB_CONTIG_THREADS), args, 0, st));
+      // the kernel starts with a grid-dependency wait, so its blocks may be placed while the previous kernel drains
+      cudaLaunchConfig_t cfg = {};
+      cfg.gridDim = dim3((unsigned)blocks);
+      cfg.blockDim = dim3(THB_CONTIG_THREADS);
+      cfg.stream = st;
+      cudaLaunchAttribute attr[1];
+      attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+      attr[0].val.programmaticStreamSerializationAllowed = 1;
+      cfg.attrs = attr;
+      cfg.numAttrs = 1;
+      THB_CUDA(cudaLaunchKernelExC(&cfg, k.contig, args));
       return 0;
     }
   }

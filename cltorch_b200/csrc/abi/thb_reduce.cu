@@ -146,8 +146,18 @@ struct ReduceAllArgs {
     F.push_cells = F.ticket ? push_cells : nullptr; F.push_count = push_count; F.push_epoch = push_epoch;
     pushed = F.push_cells != nullptr;
     if (contig) {
-      thb_reduce_all_pass1_contig<Mod, Red><<<blocks, THB_RA_THREADS, 0, st>>>(
-          in->data, n, head, init, mparam, mpoint, (typename Red::acc_t*)scratch, F);
+      // the kernel starts with a grid-dependency wait, so its blocks may be placed while the previous kernel drains
+      cudaLaunchConfig_t cfg = {};
+      cfg.gridDim = dim3((unsigned)blocks);
+      cfg.blockDim = dim3(THB_RA_THREADS);
+      cfg.stream = st;
+      cudaLaunchAttribute attr[1];
+      attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+      attr[0].val.programmaticStreamSerializationAllowed = 1;
+      cfg.attrs = attr;
+      cfg.numAttrs = 1;
+      cudaLaunchKernelEx(&cfg, thb_reduce_all_pass1_contig<Mod, Red>, (const float*)in->data, (thb_i64)n, head, init, mparam,
+                         mpoint, (typename Red::acc_t*)scratch, F);
     } else {
       ThbLayout L;
       fill_layout(&L, in->data, c);

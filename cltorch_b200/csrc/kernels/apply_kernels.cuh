@@ -83,9 +83,19 @@ struct ThbScalars {
 #define THB_CONTIG_THREADS 256
 #define THB_CONTIG_UNROLL 4
 
+// For kernels launched with programmatic stream serialisation (their blocks may become resident
+// while the previous kernel of the stream drains): wait until that kernel has completed and its
+// writes are visible, then let the next kernel's blocks be placed in turn. Without the launch
+// attribute both instructions do nothing.
+__device__ __forceinline__ void thb_grid_dependency_sync() {
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+
 template <class Op, int NT>
 __global__ void __launch_bounds__(THB_CONTIG_THREADS)
 thb_apply_contig(float* a, const float* b, const float* c, thb_i64 n, int head, ThbScalars s) {
+  thb_grid_dependency_sync();
   float p1 = 0.f, p2 = 0.f;
   if (s.pointTensor1) p1 = *s.pointTensor1;
   if (s.pointTensor2) p2 = *s.pointTensor2;

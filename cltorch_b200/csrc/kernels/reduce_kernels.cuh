@@ -250,6 +250,9 @@ thb_reduce_all_pass1_contig(const float* in, thb_i64 n, int head, float init, fl
                             const float* mpoint, typename Red::acc_t* partials, ThbFinish F) {
   typedef typename Red::acc_t acc_t;
   __shared__ acc_t smem[32];
+  // launched with programmatic stream serialisation: the previous kernel of the stream has to be complete
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   const float mp = mpoint ? *mpoint : 0.f;
   const thb_i64 nvec = (n - head) >> 2;
   const float4* in4 = reinterpret_cast<const float4*>(in + head);
