@@ -121,6 +121,11 @@ int launch_apply(const ApplyKernels& k, cudaStream_t st, int nt, const thb200_te
       int64_t cap = kMaxGridBlocks;
       if (blocks > cap) blocks = cap;
       if (blocks < 1) blocks = 1;
+      // start at the end that the previous streaming kernel left in L2 (bit 8 of the head argument)
+      const void* ptrs[3] = {a, b, cc};
+      const bool descending = stream_prefers_descending(ptrs, nt, (size_t)n * sizeof(float));
+      stream_note_end(ptrs, nt, (size_t)n * sizeof(float), descending);
+      if (descending) head |= 256;
       void* args[] = {&a, &b, &cc, &nn, &head, &s};
       // the kernel starts with a grid-dependency wait, so its blocks may be placed while the previous kernel drains
       cudaLaunchConfig_t cfg = {};

@@ -98,6 +98,68 @@ int sm_count() {
   return cached[dev];
 }
 
+// ---- which end of its operands the last streaming kernel left in L2 ----------------------------------
+// A kernel that streams through operands larger than L2 leaves the part it touched last in L2 (dirty, if it
+// wrote it). The next kernel over the same memory saves that much HBM traffic, and the write-back of lines
+// it overwrites, when it starts at that end. Per device, the last kernel's final window of every operand is
+// remembered; a contiguous apply walks its batches downwards when more of the remembered bytes lie in the
+// last window of its operands than in the first. Only the order in time changes, never a result.
+namespace {
+struct HotState {
+  uintptr_t lo[3] = {0, 0, 0}, hi[3] = {0, 0, 0};
+  int count = 0;
+  size_t l2_bytes = 0;
+};
+std::mutex g_hot_mu;
+HotState g_hot[64];
+
+HotState* hot_state() {
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
+  HotState* h = &g_hot[dev];
+  if (h->l2_bytes == 0) {
+    int v = 0;
+    h->l2_bytes = (cudaDeviceGetAttribute(&v, cudaDevAttrL2CacheSize, dev) == cudaSuccess && v > 0) ? (size_t)v : 1;
+  }
+  return h;
+}
+size_t overlap(uintptr_t a0, uintptr_t a1, uintptr_t b0, uintptr_t b1) {
+  const uintptr_t lo = a0 > b0 ? a0 : b0, hi = a1 < b1 ? a1 : b1;
+  return hi > lo ? (size_t)(hi - lo) : 0;
+}
+}  // namespace
+
+bool stream_prefers_descending(const void* const* ptrs, int n, size_t bytes) {
+  std::lock_guard<std::mutex> lock(g_hot_mu);
+  HotState* h = hot_state();
+  if (!h || n < 1 || n > 3) return false;
+  const size_t window = h->l2_bytes * 3 / 4 / (size_t)n;
+  if (bytes <= 2 * window) return false;  // (nearly) all of it can be in L2: the order does not matter
+  size_t first = 0, last = 0;
+  for (int i = 0; i < n; ++i) {
+    const uintptr_t p = (uintptr_t)ptrs[i];
+    for (int k = 0; k < h->count; ++k) {
+      first += overlap(p, p + window, h->lo[k], h->hi[k]);
+      last += overlap(p + bytes - window, p + bytes, h->lo[k], h->hi[k]);
+    }
+  }
+  return last > first;
+}
+
+void stream_note_end(const void* const* ptrs, int n, size_t bytes, bool descending) {
+  std::lock_guard<std::mutex> lock(g_hot_mu);
+  HotState* h = hot_state();
+  if (!h || n < 1 || n > 3) return;
+  size_t window = h->l2_bytes * 3 / 4 / (size_t)n;
+  if (window > bytes) window = bytes;
+  h->count = n;
+  for (int i = 0; i < n; ++i) {
+    const uintptr_t p = (uintptr_t)ptrs[i];
+    h->lo[i] = descending ? p : p + bytes - window;
+    h->hi[i] = descending ? p + window : p + bytes;
+  }
+}
+
 }  // namespace thb
 
 extern "C" {

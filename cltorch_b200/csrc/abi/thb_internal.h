@@ -41,6 +41,12 @@ int64_t num_elements(const thb200_tensor& t);  // 0 for ndim == 0, as THClTensor
 bool collapse(int ndim, const int64_t* size, const int64_t* stride, int reduce_dim, Collapsed* out);
 bool can_use_32bit(int ndim, const int64_t* size, const int64_t* stride);
 int sm_count();  // of the current device, cached per device
+
+// Order heuristic of the streaming kernels (thb_common.cpp): whether the contiguous operands `ptrs`
+// (`bytes` each) should be walked from their end, given where the previous streaming kernel on this device
+// stopped; and the note a kernel leaves for the next one.
+bool stream_prefers_descending(const void* const* ptrs, int n, size_t bytes);
+void stream_note_end(const void* const* ptrs, int n, size_t bytes, bool descending);
 // The streaming kernels keep their grid-stride loops but are launched with one batch per block up
 // to this bound (the largest gridDim.x): on B200 a block per batch, handed out by the hardware
 // scheduler, measured 3-10% faster than a grid of 32 blocks per SM looping over the batches.

@@ -146,6 +146,8 @@ struct ReduceAllArgs {
     F.push_cells = F.ticket ? push_cells : nullptr; F.push_count = push_count; F.push_epoch = push_epoch;
     pushed = F.push_cells != nullptr;
     if (contig) {
+      const void* ptrs[1] = {in->data};
+      stream_note_end(ptrs, 1, (size_t)n * sizeof(float), false);  // always walked upwards: the order of the additions is fixed
       // the kernel starts with a grid-dependency wait, so its blocks may be placed while the previous kernel drains
       cudaLaunchConfig_t cfg = {};
       cfg.gridDim = dim3((unsigned)blocks);

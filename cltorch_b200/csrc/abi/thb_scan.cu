@@ -4,8 +4,15 @@
 #include "../kernels/scan_strip_kernels.cuh"
 #include "../kernels/scan_chain_kernels.cuh"
 #include "../kernels/renorm_kernels.cuh"
+#include <stdlib.h>
 
 #define THB_SCH_TILE 8192  // elements per tile of the chained scan
+// 3 stages of first visits, 4 of second visits, at most 4 tiles between the two: measured 349-352 us on 2^28
+// elements; 3/3/4 363 us, 2/4/4 385 us, 3/3/3 414 us, 3/3/5 and 4/3/4 423 us (a longer lead of the first
+// visits pushes tiles out of L2 before their second visit).
+#define THB_SCH_SA 3
+#define THB_SCH_SB 4
+#define THB_SCH_NSLOT 4
 #include "thb_strips.h"
 
 namespace thb {
@@ -25,15 +32,22 @@ static size_t scan_scratch_need(const ScanPlan& p, int64_t outer, int64_t inner)
   return ((size_t)outer * p.nchunks * inner + (p.chain ? (size_t)outer : 0)) * sizeof(double);
 }
 
-// Whether kernels can be launched with all their CTAs guaranteed resident (the chained scan's
-// CTAs wait for one another's totals).
+// Whether the chained scan can run here: kernels can be launched with all their CTAs guaranteed resident
+// (its CTAs wait for one another's totals) and one CTA of it fits on an SM.
 static bool cooperative_launch_ok() {
   static int cached[64];  // 0 unknown, 1 yes, 2 no
   int dev = 0;
   if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return false;
   if (!cached[dev]) {
-    int v = 0;
-    cached[dev] = (cudaDeviceGetAttribute(&v, cudaDevAttrCooperativeLaunch, dev) == cudaSuccess && v) ? 1 : 2;
+    int v = 0, per_sm = 0;
+    auto kern = thb_scan_chain<ScanAdd, THB_SCH_TILE, THB_SCH_SA, THB_SCH_SB, THB_SCH_NSLOT>;
+    const int smem = THB_SCH_SMEM_BYTES(THB_SCH_TILE, THB_SCH_SA, THB_SCH_SB, THB_SCH_NSLOT);
+    const bool ok = cudaDeviceGetAttribute(&v, cudaDevAttrCooperativeLaunch, dev) == cudaSuccess && v &&
+                    cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) == cudaSuccess &&
+                    cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kern, THB_SCH_THREADS, smem) == cudaSuccess &&
+                    per_sm >= 1;
+    if (!ok) cudaGetLastError();
+    cached[dev] = ok ? 1 : 2;
   }
   return cached[dev] == 1;
 }
@@ -61,7 +75,8 @@ static ScanPlan plan_scan(const float* dst, const float* src, int64_t outer, int
     p.nchunks = (uint32_t)((n + len - 1) / len);
     // Rows that have to be cut (three phases, 12 bytes per element) go through the chained
     // single-pass kernel instead when the layout suits bulk copies.
-    if (p.nchunks > 1 && aligned && ((n & 31) == 0 || outer == 1) && n >= 2 * THB_SCH_TILE &&
+    static const bool force_chain = getenv("THB200_SCAN_FORCE_CHAIN") != nullptr;
+    if ((p.nchunks > 1 || force_chain) && aligned && ((n & 31) == 0 || outer == 1) && n >= 2 * THB_SCH_TILE &&
         outer < (int64_t(1) << 31) && cooperative_launch_ok() && tensor_map_encoder_ptr() != nullptr) {
       p.chain = true;
       p.tail = (uint32_t)(n & 31);
@@ -140,13 +155,26 @@ static int run_scan_chain(cudaStream_t st, float* dst, const float* src, int64_t
   if (int rc = make_chain_map(&map_src, src, outer, n)) return rc;
   if (int rc = make_chain_map(&map_dst, dst, outer, n)) return rc;
   void* args[] = {&map_src, &map_dst, &n32, &nchunks, &nwork, &totals, &row_carry, &status};
-  // 3 stages of first visits, 4 of second visits, at most 4 tiles between the two: measured 349-352 us on 2^28
-  // elements; 3/3/4 363 us, 2/4/4 385 us, 3/3/3 414 us, 3/3/5 and 4/3/4 423 us (a longer lead of the first
-  // visits pushes tiles out of L2 before their second visit).
-  auto kern = thb_scan_chain<Op, THB_SCH_TILE, 3, 4, 4>;
-  const int smem = THB_SCH_SMEM_BYTES(THB_SCH_TILE, 3, 4, 4);
-  THB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
-  THB_CUDA(cudaLaunchCooperativeKernel((const void*)kern, dim3(ctas), dim3(THB_SCH_THREADS), args, smem, st));
+  static int variant = -1;
+  if (variant < 0) { const char* e = getenv("THB200_SCAN_CHAIN_VARIANT"); variant = e ? atoi(e) : 0; }
+#define THB_SCH_LAUNCH(SA, SB, NSLOT, HINTS)                                                                          \
+  do {                                                                                                                \
+    auto kern = thb_scan_chain<Op, THB_SCH_TILE, SA, SB, NSLOT, HINTS>;                                               \
+    const int smem = THB_SCH_SMEM_BYTES(THB_SCH_TILE, SA, SB, NSLOT);                                                 \
+    THB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));                          \
+    THB_CUDA(cudaLaunchCooperativeKernel((const void*)kern, dim3(ctas), dim3(THB_SCH_THREADS), args, smem, st));      \
+  } while (0)
+  switch (variant) {
+    case 1: THB_SCH_LAUNCH(3, 4, 4, 1); break;
+    case 2: THB_SCH_LAUNCH(3, 4, 4, 3); break;
+    case 3: THB_SCH_LAUNCH(3, 4, 6, 1); break;
+    case 4: THB_SCH_LAUNCH(3, 4, 6, 3); break;
+    case 5: THB_SCH_LAUNCH(3, 4, 8, 3); break;
+    case 6: THB_SCH_LAUNCH(3, 4, 5, 3); break;
+    case 7: THB_SCH_LAUNCH(3, 4, 4, 2); break;
+    default: THB_SCH_LAUNCH(3, 4, 4, 0); break;
+  }
+#undef THB_SCH_LAUNCH
   if (p.tail) {
     thb_scan_chain_tail<Op><<<1, 32, 0, st>>>(dst, src, n32, (thb_u32)n_all, nchunks, totals, row_carry);
     THB_CUDA(cudaGetLastError());

@@ -100,14 +100,19 @@ thb_apply_contig(float* a, const float* b, const float* c, thb_i64 n, int head, 
   if (s.pointTensor1) p1 = *s.pointTensor1;
   if (s.pointTensor2) p2 = *s.pointTensor2;
 
+  // bit 8 of `head`: walk the batches from the last to the first (the host asks for it when the end of the
+  // operands is what the previous kernel left in L2)
+  const bool reverse = (head & 256) != 0;
+  head &= 255;
   const thb_i64 nvec = (n - head) >> 2;
   float4* a4 = reinterpret_cast<float4*>(a + head);
   const float4* b4 = reinterpret_cast<const float4*>(b + head);
   const float4* c4 = reinterpret_cast<const float4*>(c + head);
 
-  const thb_i64 step = (thb_i64)gridDim.x * (THB_CONTIG_THREADS * THB_CONTIG_UNROLL);
-  for (thb_i64 base = (thb_i64)blockIdx.x * (THB_CONTIG_THREADS * THB_CONTIG_UNROLL) + threadIdx.x;
-       base < nvec; base += step) {
+  constexpr int kBatch = THB_CONTIG_THREADS * THB_CONTIG_UNROLL;
+  const thb_i64 nbatch = (nvec + kBatch - 1) / kBatch;
+  for (thb_i64 batch = blockIdx.x; batch < nbatch; batch += gridDim.x) {
+    const thb_i64 base = (reverse ? nbatch - 1 - batch : batch) * kBatch + threadIdx.x;
     float4 va[THB_CONTIG_UNROLL], vb[THB_CONTIG_UNROLL], vc[THB_CONTIG_UNROLL];
 #pragma unroll
     for (int u = 0; u < THB_CONTIG_UNROLL; ++u) {

@@ -43,6 +43,30 @@
 #define THB_SCH_MAX_CTAS 256  // the carry warp reads at most 8 totals per lane
 #define THB_SCH_UNSET 0xFFFFFFFFFFFFFFFFull
 
+// TMA copies with an L2 eviction priority: tiles on their first visit should stay in L2 until their second
+// visit, which (like the results) has no later use.
+__device__ __forceinline__ uint64_t thb_l2_policy_evict_last() {
+  uint64_t p;
+  asm volatile("createpolicy.fractional.L2::evict_last.b64 %0, 1.0;" : "=l"(p));
+  return p;
+}
+__device__ __forceinline__ uint64_t thb_l2_policy_evict_first() {
+  uint64_t p;
+  asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(p));
+  return p;
+}
+__device__ __forceinline__ void thb_tma_load_3d_hint(uint32_t dst, const CUtensorMap* map, uint32_t bar, int x, int y, int z,
+                                                     uint64_t policy) {
+  asm volatile(
+      "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1, {%3, %4, %5}], [%2], %6;"
+      ::"r"(dst), "l"(map), "r"(bar), "r"(x), "r"(y), "r"(z), "l"(policy)
+      : "memory");
+}
+__device__ __forceinline__ void thb_tma_store_3d_hint(const CUtensorMap* map, uint32_t src, int x, int y, int z, uint64_t policy) {
+  asm volatile("cp.async.bulk.tensor.3d.global.shared::cta.bulk_group.L2::cache_hint [%0, {%2, %3, %4}], [%1], %5;"
+               ::"l"(map), "r"(src), "r"(x), "r"(y), "r"(z), "l"(policy)
+               : "memory");
+}
 __device__ __forceinline__ unsigned long long thb_ld_relaxed_u64(const unsigned long long* p) {
   unsigned long long v;
   asm volatile("ld.relaxed.gpu.global.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
@@ -59,7 +83,7 @@ __device__ __forceinline__ void thb_st_relaxed_u64(unsigned long long* p, unsign
    (NSLOT) * (THB_SCH_CWARPS + 1) * 8 /*warp offsets and carry per tile under way*/ +                              \
    (2 * (SA) + 3 * (SB) + 3 * (NSLOT)) * 8 /*barriers*/ + 16 /*flags*/)
 
-template <class Op, int TILE, int SA, int SB, int NSLOT>
+template <class Op, int TILE, int SA, int SB, int NSLOT, int HINTS = 0>
 __global__ void __launch_bounds__(THB_SCH_THREADS, 1)
 thb_scan_chain(const __grid_constant__ CUtensorMap map_src, const __grid_constant__ CUtensorMap map_dst, thb_u32 n,
                thb_u32 nchunks, thb_i64 nwork, unsigned long long* totals, double* row_carry, int* status) {
@@ -128,6 +152,7 @@ thb_scan_chain(const __grid_constant__ CUtensorMap map_src, const __grid_constan
       uint64_t* full_r = second ? bar_full_b : bar_full_a;
       uint64_t* empty_r = second ? bar_empty_b : bar_empty_a;
       uint8_t* ring = second ? ring_b : ring_a;
+      const uint64_t policy = second ? thb_l2_policy_evict_first() : thb_l2_policy_evict_last();
       int i = 0;
       for (; i < iters; ++i) {
         const int s = i % nst;
@@ -141,7 +166,8 @@ thb_scan_chain(const __grid_constant__ CUtensorMap map_src, const __grid_constan
         const thb_u32 c0 = (thb_u32)(w - row * nchunks) * TILE;
         const uint32_t full = thb_smem_u32(&full_r[s]);
         thb_mbar_expect_tx(full, STAGE_BYTES);  // 128-byte rows past the end of the row arrive as zeros
-        thb_tma_load_3d(thb_smem_u32(ring + s * STAGE_BYTES), &map_src, full, 0, (int)(c0 >> 5), (int)row);
+        if (HINTS & 1) thb_tma_load_3d_hint(thb_smem_u32(ring + s * STAGE_BYTES), &map_src, full, 0, (int)(c0 >> 5), (int)row, policy);
+        else thb_tma_load_3d(thb_smem_u32(ring + s * STAGE_BYTES), &map_src, full, 0, (int)(c0 >> 5), (int)row);
       }
       if (*abort_flag) {
         // do not leave while copies into this CTA's shared memory are in flight
@@ -232,7 +258,8 @@ thb_scan_chain(const __grid_constant__ CUtensorMap map_src, const __grid_constan
         const thb_i64 row = w / nchunks;
         const thb_u32 c0 = (thb_u32)(w - row * nchunks) * TILE;
         // 128-byte rows past the end of the row are clipped by the TMA unit
-        thb_tma_store_3d(&map_dst, thb_smem_u32(ring_b + s * STAGE_BYTES), 0, (int)(c0 >> 5), (int)row);
+        if (HINTS & 2) thb_tma_store_3d_hint(&map_dst, thb_smem_u32(ring_b + s * STAGE_BYTES), 0, (int)(c0 >> 5), (int)row, thb_l2_policy_evict_first());
+        else thb_tma_store_3d(&map_dst, thb_smem_u32(ring_b + s * STAGE_BYTES), 0, (int)(c0 >> 5), (int)row);
         asm volatile("cp.async.bulk.commit_group;" ::: "memory");
         asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
         thb_mbar_arrive(thb_smem_u32(&bar_empty_b[s]));
