@@ -4,15 +4,16 @@
 #include "../kernels/scan_strip_kernels.cuh"
 #include "../kernels/scan_chain_kernels.cuh"
 #include "../kernels/renorm_kernels.cuh"
-#include <stdlib.h>
 
 #define THB_SCH_TILE 8192  // elements per tile of the chained scan
-// 3 stages of first visits, 4 of second visits, at most 4 tiles between the two: measured 349-352 us on 2^28
-// elements; 3/3/4 363 us, 2/4/4 385 us, 3/3/3 414 us, 3/3/5 and 4/3/4 423 us (a longer lead of the first
-// visits pushes tiles out of L2 before their second visit).
+// 3 stages of first visits, 4 of second visits, at most 6 tiles between the two, first visits loaded with the
+// L2 evict-last priority, second visits and results with evict-first: 342-344 us on 2^28 elements. Without the
+// priorities: 349-352 us with at most 4 tiles between the visits (3/3/4 stages 363 us, 2/4/4 385 us, 3/3/3
+// 414 us) and 423-480 us with 5 or more (a longer lead of the first visits then pushes tiles out of L2 before
+// their second visit); with them 346 us at 5, 366 us at 8.
 #define THB_SCH_SA 3
 #define THB_SCH_SB 4
-#define THB_SCH_NSLOT 4
+#define THB_SCH_NSLOT 6
 #include "thb_strips.h"
 
 namespace thb {
@@ -40,7 +41,7 @@ static bool cooperative_launch_ok() {
   if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return false;
   if (!cached[dev]) {
     int v = 0, per_sm = 0;
-    auto kern = thb_scan_chain<ScanAdd, THB_SCH_TILE, THB_SCH_SA, THB_SCH_SB, THB_SCH_NSLOT>;
+    auto kern = thb_scan_chain<ScanAdd, THB_SCH_TILE, THB_SCH_SA, THB_SCH_SB, THB_SCH_NSLOT, 3>;
     const int smem = THB_SCH_SMEM_BYTES(THB_SCH_TILE, THB_SCH_SA, THB_SCH_SB, THB_SCH_NSLOT);
     const bool ok = cudaDeviceGetAttribute(&v, cudaDevAttrCooperativeLaunch, dev) == cudaSuccess && v &&
                     cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) == cudaSuccess &&
@@ -73,10 +74,11 @@ static ScanPlan plan_scan(const float* dst, const float* src, int64_t outer, int
     len = (len + piece - 1) / piece * piece;
     p.chunk_len = (uint32_t)len;
     p.nchunks = (uint32_t)((n + len - 1) / len);
-    // Rows that have to be cut (three phases, 12 bytes per element) go through the chained
-    // single-pass kernel instead when the layout suits bulk copies.
-    static const bool force_chain = getenv("THB200_SCAN_FORCE_CHAIN") != nullptr;
-    if ((p.nchunks > 1 || force_chain) && aligned && ((n & 31) == 0 || outer == 1) && n >= 2 * THB_SCH_TILE &&
+    // Rows that have to be cut (three phases, 12 bytes per element) go through the chained single-pass
+    // kernel instead when the layout suits TMA: 349 against 621 us on one vector of 2^28 elements. With enough
+    // rows for a warp per row the two are level (16384 rows of 16384: 352 against 362 us over ten calls, but
+    // 389 against 372 us in a 0.25 s loop under the power cap), so those keep the warp per row.
+    if (p.nchunks > 1 && aligned && ((n & 31) == 0 || outer == 1) && n >= 2 * THB_SCH_TILE &&
         outer < (int64_t(1) << 31) && cooperative_launch_ok() && tensor_map_encoder_ptr() != nullptr) {
       p.chain = true;
       p.tail = (uint32_t)(n & 31);
@@ -155,26 +157,10 @@ static int run_scan_chain(cudaStream_t st, float* dst, const float* src, int64_t
   if (int rc = make_chain_map(&map_src, src, outer, n)) return rc;
   if (int rc = make_chain_map(&map_dst, dst, outer, n)) return rc;
   void* args[] = {&map_src, &map_dst, &n32, &nchunks, &nwork, &totals, &row_carry, &status};
-  static int variant = -1;
-  if (variant < 0) { const char* e = getenv("THB200_SCAN_CHAIN_VARIANT"); variant = e ? atoi(e) : 0; }
-#define THB_SCH_LAUNCH(SA, SB, NSLOT, HINTS)                                                                          \
-  do {                                                                                                                \
-    auto kern = thb_scan_chain<Op, THB_SCH_TILE, SA, SB, NSLOT, HINTS>;                                               \
-    const int smem = THB_SCH_SMEM_BYTES(THB_SCH_TILE, SA, SB, NSLOT);                                                 \
-    THB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));                          \
-    THB_CUDA(cudaLaunchCooperativeKernel((const void*)kern, dim3(ctas), dim3(THB_SCH_THREADS), args, smem, st));      \
-  } while (0)
-  switch (variant) {
-    case 1: THB_SCH_LAUNCH(3, 4, 4, 1); break;
-    case 2: THB_SCH_LAUNCH(3, 4, 4, 3); break;
-    case 3: THB_SCH_LAUNCH(3, 4, 6, 1); break;
-    case 4: THB_SCH_LAUNCH(3, 4, 6, 3); break;
-    case 5: THB_SCH_LAUNCH(3, 4, 8, 3); break;
-    case 6: THB_SCH_LAUNCH(3, 4, 5, 3); break;
-    case 7: THB_SCH_LAUNCH(3, 4, 4, 2); break;
-    default: THB_SCH_LAUNCH(3, 4, 4, 0); break;
-  }
-#undef THB_SCH_LAUNCH
+  auto kern = thb_scan_chain<Op, THB_SCH_TILE, THB_SCH_SA, THB_SCH_SB, THB_SCH_NSLOT, 3>;
+  const int smem = THB_SCH_SMEM_BYTES(THB_SCH_TILE, THB_SCH_SA, THB_SCH_SB, THB_SCH_NSLOT);
+  THB_CUDA(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+  THB_CUDA(cudaLaunchCooperativeKernel((const void*)kern, dim3(ctas), dim3(THB_SCH_THREADS), args, smem, st));
   if (p.tail) {
     thb_scan_chain_tail<Op><<<1, 32, 0, st>>>(dst, src, n32, (thb_u32)n_all, nchunks, totals, row_carry);
     THB_CUDA(cudaGetLastError());
