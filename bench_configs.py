@@ -458,7 +458,7 @@ def n1(T):
 
 
 def n3small(T):
-    """var, cumsum and dist on 8192 x 8192 and cumsum of a 2^26 vector (profiler captures of the moments and scan kernels)."""
+    """var, cumsum, dist and renorm on 8192 x 8192 and cumsum of a 2^26 vector (profiler captures of the moments, scan and renorm kernels)."""
     cl = T.cl
     g = np.random.Generator(np.random.PCG64(5))
     n = 8192
@@ -472,6 +472,10 @@ def n3small(T):
     V = cl.ClTensor(g.standard_normal((1 << 26,), dtype=np.float32))
     W = cl.ClTensor(1 << 26)
     T.time("cumsum of a 2^26 vector", lambda: W.cumsum(V, 1), 8 << 26)
+    # rows of 8192 standard-normal values have 2-norms close to 90.5: about half of them are rescaled
+    A0 = cl.ClTensor(n, n).copy(A)
+    T.time("renorm(A, 2, 1, 90.5) in place [4 B/elt read + 4 B/elt written for the rows rescaled]",
+           lambda: A.renorm(A, 2, 1, 90.5), 4 * n * n + 2 * n * n, setup=lambda: A.copy(A0))
 
 
 GROUPS = {"c1": c1, "c2": c2, "c3": c3, "c4": c4, "c4small": c4small, "c4batched": c4batched, "c4mlp": c4mlp, "c2small": c2small,

@@ -222,25 +222,29 @@ static bool launch_renorm_fused(cudaStream_t st, float* data, int64_t rows, int6
   const int64_t nvec = size / 4;
   const int sms = sm_count();
   const thb_u32 size32 = (thb_u32)size;
-#define THB_RNF_WARP(U)                                                                                              \
+#define THB_RNF_WARP(L, U, R)                                                                                        \
   do {                                                                                                               \
-    int64_t blocks = (rows + THB_RNF_THREADS / 32 - 1) / (THB_RNF_THREADS / 32);                                     \
+    const int64_t per_block = (int64_t)(THB_RNF_THREADS / 32) * (R) * (32 / (L));                                    \
+    int64_t blocks = (rows + per_block - 1) / per_block;                                                             \
     if (blocks > (int64_t)sms * 8) blocks = (int64_t)sms * 8;                                                        \
-    thb_renorm_rows_warp<U, PMODE><<<(unsigned)blocks, THB_RNF_THREADS, 0, st>>>(data, rows, size32, p, maxnorm);     \
+    thb_renorm_rows_warp<L, U, R, PMODE><<<(unsigned)blocks, THB_RNF_THREADS, 0, st>>>(data, rows, size32, p, maxnorm); \
   } while (0)
-#define THB_RNF_BLOCK(U, PER_SM)                                                                                     \
+#define THB_RNF_BLOCK(THREADS)                                                                                       \
   do {                                                                                                               \
-    int64_t blocks = rows < (int64_t)sms * (PER_SM) ? rows : (int64_t)sms * (PER_SM);                                \
-    thb_renorm_rows_block<U, PMODE><<<(unsigned)blocks, THB_RNF_THREADS, 0, st>>>(data, rows, size32, p, maxnorm);    \
+    const int64_t resident = (int64_t)sms * (512 / (THREADS));                                                       \
+    const int64_t blocks = rows < resident * 4 ? rows : resident * 4;                                                \
+    thb_renorm_rows_block<THREADS, PMODE><<<(unsigned)blocks, THREADS, 0, st>>>(data, rows, size32, p, maxnorm);      \
   } while (0)
-  if (nvec <= 32) THB_RNF_WARP(1);
-  else if (nvec <= 64) THB_RNF_WARP(2);
-  else if (nvec <= 128) THB_RNF_WARP(4);
-  else if (nvec <= 256) THB_RNF_WARP(8);
-  else if (nvec <= 2 * THB_RNF_THREADS) THB_RNF_BLOCK(2, 8);
-  else if (nvec <= 4 * THB_RNF_THREADS) THB_RNF_BLOCK(4, 8);
-  else if (nvec <= 8 * THB_RNF_THREADS) THB_RNF_BLOCK(8, 4);
-  else if (nvec <= 16 * THB_RNF_THREADS) THB_RNF_BLOCK(16, 2);
+  if (nvec <= 8) THB_RNF_WARP(8, 1, 8);
+  else if (nvec <= 16) THB_RNF_WARP(16, 1, 8);
+  else if (nvec <= 32) THB_RNF_WARP(32, 1, 8);
+  else if (nvec <= 64) THB_RNF_WARP(32, 2, 4);
+  else if (nvec <= 128) THB_RNF_WARP(32, 4, 2);
+  else if (nvec <= 256) THB_RNF_WARP(32, 8, 1);
+  else if (nvec <= 512) THB_RNF_WARP(32, 16, 1);
+  else if (nvec <= 64 * THB_RNF_BLOCK_U) THB_RNF_BLOCK(64);
+  else if (nvec <= 128 * THB_RNF_BLOCK_U) THB_RNF_BLOCK(128);
+  else if (nvec <= 256 * THB_RNF_BLOCK_U) THB_RNF_BLOCK(256);
   else return false;
 #undef THB_RNF_WARP
 #undef THB_RNF_BLOCK
@@ -297,7 +301,7 @@ int thb200_renorm_rows(void* stream, float* data, int64_t rows, int64_t size, fl
   if (!(p > 0.f)) return fail("renorm: non-positive-norm not supported");
   if (rows >= (int64_t(1) << 31) || size >= (int64_t(1) << 31)) return fail("renorm: extent too large");
   if (!scratch || scratch_bytes < (size_t)rows * sizeof(float)) return fail("renorm: scratch too small");
-  if ((((uintptr_t)data) & 15) == 0 && (size & 3) == 0 && size <= 64 * THB_RNF_THREADS) {
+  if ((((uintptr_t)data) & 15) == 0 && (size & 3) == 0 && size <= 4 * 256 * THB_RNF_BLOCK_U) {
     cudaStream_t st = (cudaStream_t)stream;
     const bool done = p == 1.0f   ? launch_renorm_fused<1>(st, data, rows, size, p, maxnorm)
                       : p == 2.0f ? launch_renorm_fused<2>(st, data, rows, size, p, maxnorm)

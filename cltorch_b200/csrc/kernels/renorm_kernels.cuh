@@ -1,4 +1,4 @@
-// Row-wise renorm in one pass for rows that fit in the registers of a warp or a CTA: the row is
+// Row-wise renorm in one pass for rows that fit in the registers of a warp or a CTA (up to 16384 elements): the row is
 // loaded once, its p-norm is folded in double, and the registers are written back scaled only
 // when the norm exceeds the limit. HBM traffic: 4 bytes per element read, 4 more written for
 // the rows that are rescaled (the two-kernel form, a row reduction followed by thb_renorm_scale,
@@ -30,50 +30,93 @@ __device__ __forceinline__ double thb_rnf_terms(const float4& v, float p) {
          ((double)thb_rnf_term<PMODE>(v.z, p) + (double)thb_rnf_term<PMODE>(v.w, p));
 }
 
+// sum^(1/p), rounded to fp32 from a double-precision root (pow in double costs a few hundred instructions,
+// which short rows would notice: p = 1, 2, 3 take the exact, square and cube root instead).
+template <int PMODE>
+__device__ __forceinline__ float thb_rnf_root(float sum, float p) {
+  if (PMODE == 1) return sum;
+  if (PMODE == 2) return (float)sqrt((double)sum);
+  if (PMODE == 3) return (float)cbrt((double)sum);
+  return thb_pow(sum, 1.0f / p);
+}
+
 // Whether a row whose sum of |x|^p is `sum` is rescaled (not for a NaN norm), and by what.
+template <int PMODE>
 __device__ __forceinline__ bool thb_rnf_factor(double sum, float p, float maxnorm, float* f) {
-  const float norm = thb_pow((float)sum, 1.0f / p);
+  const float norm = thb_rnf_root<PMODE>((float)sum, p);
   if (!(norm > maxnorm)) return false;
   *f = (float)((double)maxnorm / ((double)norm + 1e-7));
   return true;
 }
 
-// One warp per row of at most 128 * U elements.
-template <int U, int PMODE>
-__global__ void __launch_bounds__(THB_RNF_THREADS)
+// A group of L lanes (8, 16 or 32) takes R rows of at most 4 * L * U elements at a time, so a lane has R * U = 8
+// (16 when U = 16) vectors in flight and a warp works on R * 32 / L rows. The factor of row r of a group is
+// worked out by the group's lane r (one pass through the root for all rows of the warp) and handed round.
+template <int L, int U, int R, int PMODE>
+__global__ void __launch_bounds__(THB_RNF_THREADS, 2)
 thb_renorm_rows_warp(float* data, thb_i64 rows, thb_u32 size, float p, float maxnorm) {
-  const int lane = threadIdx.x & 31;
+  static_assert(R <= L, "lane r of a group serves row r");
+  constexpr int kGroups = 32 / L;
+  const int lane = threadIdx.x & 31, sub = lane % L, group = lane / L;
   const thb_u32 nvec = size >> 2;
+  const thb_i64 per_warp = (thb_i64)R * kGroups;
   const thb_i64 warps = (thb_i64)gridDim.x * (THB_RNF_THREADS / 32);
-  for (thb_i64 row = (thb_i64)blockIdx.x * (THB_RNF_THREADS / 32) + (threadIdx.x >> 5); row < rows; row += warps) {
-    float4* r4 = reinterpret_cast<float4*>(data + row * (thb_i64)size);
-    float4 v[U];
+  for (thb_i64 row0 = ((thb_i64)blockIdx.x * (THB_RNF_THREADS / 32) + (threadIdx.x >> 5)) * per_warp; row0 < rows;
+       row0 += warps * per_warp) {
+    float4 v[R][U];
 #pragma unroll
-    for (int j = 0; j < U; ++j) {
-      const thb_u32 i = j * 32 + lane;
-      v[j] = i < nvec ? r4[i] : make_float4(0.f, 0.f, 0.f, 0.f);
-    }
-    double acc = 0.0;
-#pragma unroll
-    for (int j = 0; j < U; ++j)
-      if (j * 32 + lane < nvec) acc += thb_rnf_terms<PMODE>(v[j], p);
-#pragma unroll
-    for (int off = 16; off > 0; off >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, off);
-    float f = 1.f;
-    if (thb_rnf_factor(acc, p, maxnorm, &f)) {
+    for (int r = 0; r < R; ++r) {
+      const thb_i64 row = row0 + r * kGroups + group;
+      const float4* r4 = reinterpret_cast<const float4*>(data + row * (thb_i64)size);
 #pragma unroll
       for (int j = 0; j < U; ++j) {
-        const thb_u32 i = j * 32 + lane;
-        if (i < nvec) r4[i] = make_float4(v[j].x * f, v[j].y * f, v[j].z * f, v[j].w * f);
+        const thb_u32 i = j * L + sub;
+        v[r][j] = (row < rows && i < nvec) ? r4[i] : make_float4(0.f, 0.f, 0.f, 0.f);
+      }
+    }
+    double acc[R];
+#pragma unroll
+    for (int r = 0; r < R; ++r) {
+      acc[r] = 0.0;
+#pragma unroll
+      for (int j = 0; j < U; ++j)
+        if (j * L + sub < nvec) acc[r] += thb_rnf_terms<PMODE>(v[r][j], p);
+    }
+#pragma unroll
+    for (int off = L / 2; off > 0; off >>= 1) {
+#pragma unroll
+      for (int r = 0; r < R; ++r) acc[r] += __shfl_xor_sync(0xffffffffu, acc[r], off);
+    }
+    double mine = 0.0;
+#pragma unroll
+    for (int r = 0; r < R; ++r)
+      if (sub == r) mine = acc[r];
+    float f_mine = 1.f;
+    const int scale_mine = thb_rnf_factor<PMODE>(mine, p, maxnorm, &f_mine) ? 1 : 0;
+#pragma unroll
+    for (int r = 0; r < R; ++r) {
+      const float f = __shfl_sync(0xffffffffu, f_mine, group * L + r);
+      const int scale = __shfl_sync(0xffffffffu, scale_mine, group * L + r);
+      const thb_i64 row = row0 + r * kGroups + group;
+      if (row < rows && scale) {
+        float4* r4 = reinterpret_cast<float4*>(data + row * (thb_i64)size);
+#pragma unroll
+        for (int j = 0; j < U; ++j) {
+          const thb_u32 i = j * L + sub;
+          if (i < nvec) r4[i] = make_float4(v[r][j].x * f, v[r][j].y * f, v[r][j].z * f, v[r][j].w * f);
+        }
       }
     }
   }
 }
 
-// One CTA per row of at most 1024 * U elements.
-template <int U, int PMODE>
-__global__ void __launch_bounds__(THB_RNF_THREADS, 2)
+// One CTA of THREADS threads per row of at most 64 * THREADS elements: 16 vectors in flight per thread, and as many
+// CTAs per SM as the registers allow (2 of 256 threads, 4 of 128, 8 of 64), so 128 KB of loads per SM either way.
+#define THB_RNF_BLOCK_U 16
+template <int THREADS, int PMODE>
+__global__ void __launch_bounds__(THREADS, 512 / THREADS)
 thb_renorm_rows_block(float* data, thb_i64 rows, thb_u32 size, float p, float maxnorm) {
+  constexpr int U = THB_RNF_BLOCK_U;
   __shared__ double smem[32];
   __shared__ float s_factor;
   __shared__ int s_scale;
@@ -83,17 +126,17 @@ thb_renorm_rows_block(float* data, thb_i64 rows, thb_u32 size, float p, float ma
     float4 v[U];
 #pragma unroll
     for (int j = 0; j < U; ++j) {
-      const thb_u32 i = j * THB_RNF_THREADS + threadIdx.x;
+      const thb_u32 i = j * THREADS + threadIdx.x;
       v[j] = i < nvec ? r4[i] : make_float4(0.f, 0.f, 0.f, 0.f);
     }
     double acc[2] = {0.0, 0.0};
 #pragma unroll
     for (int j = 0; j < U; ++j)
-      if (j * THB_RNF_THREADS + threadIdx.x < nvec) acc[j & 1] += thb_rnf_terms<PMODE>(v[j], p);
+      if (j * THREADS + threadIdx.x < nvec) acc[j & 1] += thb_rnf_terms<PMODE>(v[j], p);
     const double total = thb_block_fold<RedAdd>(acc[0] + acc[1], 0.0, smem);
     if (threadIdx.x == 0) {
       float f0 = 1.f;
-      s_scale = thb_rnf_factor(total, p, maxnorm, &f0) ? 1 : 0;
+      s_scale = thb_rnf_factor<PMODE>(total, p, maxnorm, &f0) ? 1 : 0;
       s_factor = f0;
     }
     __syncthreads();
@@ -101,7 +144,7 @@ thb_renorm_rows_block(float* data, thb_i64 rows, thb_u32 size, float p, float ma
     if (s_scale) {
 #pragma unroll
       for (int j = 0; j < U; ++j) {
-        const thb_u32 i = j * THB_RNF_THREADS + threadIdx.x;
+        const thb_u32 i = j * THREADS + threadIdx.x;
         if (i < nvec) r4[i] = make_float4(v[j].x * f, v[j].y * f, v[j].z * f, v[j].w * f);
       }
     }

@@ -182,9 +182,11 @@ def test_scan_abi_rejects_bad_arguments():
 
 # ---- renorm ----------------------------------------------------------------------------------
 
-# rows of 300 (a warp per row), 200, 40 * 20 = 800, 8200 (a CTA per row), 20000 (two kernels), 301 (not a multiple of 4: two kernels)
+# rows of 300 (a warp per row), 200, 40 * 20 = 800, 8200 (a CTA per row), 20000 (two kernels), 301 (not a multiple of 4:
+# two kernels), 8 / 24 / 32 (8, 8 and 16 lanes per row), 100, 2048 (16 vectors per lane)
 @pytest.mark.parametrize("shape,dim", [((200, 300), 0), ((200, 300), 1), ((20, 30, 40), 1), ((64, 8192 + 8), 0),
-                                       ((40, 20000), 0), ((50, 301), 0), ((3000, 64), 0), ((300, 1500), 0), ((90, 4000), 0)])
+                                       ((40, 20000), 0), ((50, 301), 0), ((3000, 64), 0), ((300, 1500), 0), ((90, 4000), 0),
+                                       ((5000, 8), 0), ((777, 24), 0), ((1001, 32), 0), ((333, 100), 0), ((67, 2048), 0)])
 @pytest.mark.parametrize("p", [1.0, 2.0, 3.0])
 def test_renorm(shape, dim, p):
     import cltorch_b200 as cl
