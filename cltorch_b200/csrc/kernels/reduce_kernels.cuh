@@ -41,6 +41,11 @@ __device__ __forceinline__ float thb_abs_pow_general(float x, float p) {
   return p == 0.0f ? 1.0f : r;
 }
 struct ModAbsPow { static constexpr bool kFirst = false; static __device__ __forceinline__ float apply(float x, float p, float) { return thb_abs_pow_general(x, p); } };
+// Whether the four terms of a 128-bit vector may be added in fp32 before they join the double-precision sum.
+// Only for the general power, whose terms carry the special-function unit's relative error of about 1e-6
+// anyway: it saves three of four fp32 -> fp64 conversions, which share that unit with log2 and exp2.
+template <class Mod> struct ThbAddsVectorInFloat { static constexpr bool value = false; };
+template <> struct ThbAddsVectorInFloat<ModAbsPow> { static constexpr bool value = true; };
 // |x|^p for the exponents norms are usually taken with: the host picks these when p is 1, 2 or 3,
 // so that the loop carries no comparison of p per element.
 struct ModAbs { static constexpr bool kFirst = false; static __device__ __forceinline__ float apply(float x, float, float) { return fabsf(x); } };
@@ -275,10 +280,16 @@ thb_reduce_all_pass1_contig(const float* in, thb_i64 n, int head, float init, fl
     for (int u = 0; u < THB_RA_UNROLL; ++u) {
       thb_i64 i = base + u * THB_RA_THREADS;
       if (i < nvec) {
-        acc[0] = Red::apply(acc[0], Mod::apply(v[u].x, mparam, mp));
-        acc[1] = Red::apply(acc[1], Mod::apply(v[u].y, mparam, mp));
-        acc[2] = Red::apply(acc[2], Mod::apply(v[u].z, mparam, mp));
-        acc[3] = Red::apply(acc[3], Mod::apply(v[u].w, mparam, mp));
+        if (ThbAddsVectorInFloat<Mod>::value) {
+          const float t = (Mod::apply(v[u].x, mparam, mp) + Mod::apply(v[u].y, mparam, mp)) +
+                          (Mod::apply(v[u].z, mparam, mp) + Mod::apply(v[u].w, mparam, mp));
+          acc[u & 3] = Red::apply(acc[u & 3], t);
+        } else {
+          acc[0] = Red::apply(acc[0], Mod::apply(v[u].x, mparam, mp));
+          acc[1] = Red::apply(acc[1], Mod::apply(v[u].y, mparam, mp));
+          acc[2] = Red::apply(acc[2], Mod::apply(v[u].z, mparam, mp));
+          acc[3] = Red::apply(acc[3], Mod::apply(v[u].w, mparam, mp));
+        }
       }
     }
   }

@@ -130,14 +130,17 @@ def _two_gpu_child():
 
 def test_two_processes_on_two_gpus_over_cuda_ipc():
     """The exchange between processes (CUDA IPC, stores over NVLink). Needs two GPUs; skipped on one."""
+    import os
     import subprocess
     import sys
     import torch
     if torch.cuda.device_count() < 2:
         pytest.skip("needs two GPUs")
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    env = dict(os.environ, PYTHONPATH=root + os.pathsep + os.environ.get("PYTHONPATH", ""))   # this file's own imports
     r = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2",
                         "--master-addr", "127.0.0.1", "--master-port", "29541", __file__], capture_output=True, text=True,
-                       timeout=300)
+                       timeout=300, env=env, cwd=root)
     assert r.returncode == 0 and r.stdout.count("TWO_GPU_OK") == 2, r.stdout[-2000:] + r.stderr[-3000:]
 
 
