@@ -424,3 +424,22 @@ def test_expression_errors_are_reported():
     with pytest.raises(cl.ClError, match="element size mismatch"):
         a.map_on_gpu(cl.ClTensor(np.ones(5, np.float32)), "x = y")
     assert np.array_equal(a.float(), np.ones(4, np.float32))   # the library is still usable
+
+
+def test_large_chain_walks_the_operands_from_either_end():
+    """Operands larger than L2: a contiguous apply starts at the end that the previous kernel left in
+    L2, so every second kernel of a chain walks its batches downwards. The order in time must not show
+    in any result, ragged head and tail included."""
+    import cltorch_b200 as cl
+    n = (1 << 26) + 5
+    base = rng_uniform(77, (n + 3,), 0.0, 4.0)
+    for offset in (0, 3):                                                 # 16-byte aligned / three elements off
+        host = base[offset:offset + n]
+        x = cl.ClTensor(cl.ClStorage(base.copy()), offset + 1, [n], [1])
+        y = cl.ClTensor(host * np.float32(0.5))
+        want = host.copy()
+        for _ in range(2):                                                # four applies in a row over the same memory
+            x.apply_on_gpu("x = x * 1.0001 + 0.5"); want = want * np.float32(1.0001) + np.float32(0.5)
+            x.map_on_gpu(y, "x = sqrt(x + y)"); want = np.sqrt(want + host * np.float32(0.5))
+        assert np.array_equal(x.float(), want)
+        assert abs(x.sum() - float(want.astype(np.float64).sum())) <= 1e-6 * float(want.astype(np.float64).sum())
