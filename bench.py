@@ -11,7 +11,9 @@ element (8 + 8 + 4); `value` is that traffic divided by the step time, inputs re
 HBM. Total work is fixed as N grows ("strong" scaling).
 
 `e2e` times the same step through the C API with the shard starting in pinned host
-memory: host->device copy of the shard, the chain, and the 4-byte result read back.
+memory: host->device copy of the shard, the chain, and the 4-byte result read back, every step;
+the upload of the next step's shard (second device buffer, copy stream) runs while the kernels
+of the current step work.
 `check` compares the global sum of that end-to-end step with a double-precision sum
 computed on the host from the same pinned shards (1e-5 relative); the run exits non-zero
 when it fails. The vector is drawn per fixed block of 2^26 elements, so it is the same
@@ -231,17 +233,18 @@ def run_gpu(args):
 
     ev = lambda: torch.cuda.Event(enable_timing=True)
 
-    def step(events=None, gs=None):
+    def step(events=None, gs=None, t=None):
         gs = gs or gsum
+        t = x if t is None else t
         if events is not None:
             events[0].record()
-        x.apply_on_gpu(EXPR1)
+        t.apply_on_gpu(EXPR1)
         if events is not None:
             events[1].record()
-        x.apply_on_gpu(EXPR2)
+        t.apply_on_gpu(EXPR2)
         if events is not None:
             events[2].record()
-        r = gs(x)
+        r = gs(t)
         if events is not None:
             events[3].record()
         return r
@@ -285,15 +288,32 @@ def run_gpu(args):
         barrier()
         alt_ms = a0.elapsed_time(a1)
 
-    # e2e: host buffer -> device, chain, result back to the host; every step
+    # e2e: host buffer -> device, chain, result back to the host; every step. Two device buffers: the upload of
+    # step k+1 (its own stream, THClTensor_copyFloatAsync) runs while the kernels of step k work on the other
+    # buffer; a buffer is uploaded into again only after the result of its previous step has reached the host.
     e2e_steps = args.steps
-    for _ in range(2):
-        x.copy(hview); step().s()
+    bufs = (x, cl.ClTensor(n_local))
+    compute_stream, copy_stream = torch.cuda.current_stream(), torch.cuda.Stream()
+    uploaded = [torch.cuda.Event(), torch.cuda.Event()]
+
+    def upload(k):
+        bufs[k % 2].copy_async(hview, copy_stream.cuda_stream)
+        uploaded[k % 2].record(copy_stream)
+
+    def run_e2e(count):
+        upload(0)
+        total = None
+        for k in range(count):
+            if k + 1 < count:
+                upload(k + 1)
+            compute_stream.wait_event(uploaded[k % 2])
+            total = step(t=bufs[k % 2]).s()          # the device -> host read of the step's result
+        return total
+
+    run_e2e(2)
     barrier()
     t0 = time.perf_counter()
-    for _ in range(e2e_steps):
-        x.copy(hview)
-        total_e2e = step().s()
+    total_e2e = run_e2e(e2e_steps)
     torch.cuda.synchronize()
     e2e_s = time.perf_counter() - t0
 
@@ -317,7 +337,7 @@ def run_gpu(args):
         dist.all_reduce(block_sums, op=dist.ReduceOp.SUM)      # every block is non-zero on one rank only: exact
     oracle_sum = math.fsum(block_sums.tolist())
     launches_c5 = args.steps * (2 + gsum.launches_per_call)
-    del x, host, hview
+    del x, bufs, host, hview
     if world > 1:
         dist.destroy_process_group()
     if rank != 0:
@@ -359,7 +379,9 @@ def run_gpu(args):
                                             "note": "mean CUDA-event windows on each rank; the third window ends when the "
                                                     "slowest rank's partial has arrived"}},
         "e2e": {"value": BYTES_PER_ELT * n_total / (e2e_ms / e2e_steps * 1e-3) / 1e9, "unit": "GB/s",
-                "h2d_bytes_per_step": 4 * n_local, "d2h_bytes_per_step": 4, "steps": e2e_steps},
+                "h2d_bytes_per_step": 4 * n_local, "d2h_bytes_per_step": 4, "steps": e2e_steps,
+                "pipeline": "two device buffers; the upload of step k+1 overlaps the kernels of step k; the result of "
+                            "every step is read back before its buffer is uploaded into again"},
         "gpu_launches": launches_c5,
         "check": {"global_sum_e2e": float(total_e2e), "oracle_sum": oracle_sum, "rel_err": rel_err,
                   "tolerance": 1e-5, "ok": rel_err <= 1e-5,

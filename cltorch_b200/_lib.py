@@ -173,6 +173,7 @@ PROTOTYPES = {
     "THClTensor_copy": (v, [S, T, T]), "THClTensor_copyCl": (v, [S, T, T]),
     "THClTensor_copyIgnoringOverlaps": (v, [S, T, T]),
     "THClTensor_copyFloat": (v, [S, T, C.POINTER(THFloatTensor)]),
+    "THClTensor_copyFloatAsync": (v, [S, T, C.c_void_p, l, C.c_void_p]),
     "THFloatTensor_copyCl": (v, [S, C.POINTER(THFloatTensor), T]),
     "THClTensor_copyDouble": (v, [S, T, C.POINTER(THDoubleTensor)]),
     "THDoubleTensor_copyCl": (v, [S, C.POINTER(THDoubleTensor), T]),

@@ -162,6 +162,21 @@ void THClTensor_copyIgnoringOverlaps(THClState* state, THClTensor* dst, THClTens
     copy_to_host<TH##Name##Tensor, T>(state, self, src);                                         \
     THCL_END_VOID                                                                                \
   }
+void THClTensor_copyFloatAsync(THClState* state, THClTensor* self, const float* src, long n, void* stream) {
+  THCL_BEGIN
+  arg_check(n == THClTensor_nElement(state, self), 3, "sizes do not match");
+  arg_check(THClTensor_isContiguous(state, self), 1, "the destination of an asynchronous upload must be contiguous");
+  if (n == 0) return;
+  arg_check(src != nullptr, 2, "null host pointer");
+  THClDeviceContext* ctx = context(state, self->device);
+  use_device(self->device);
+  if (state->trace) printf("THCl: host -> device %ld floats (asynchronous)\n", n);
+  check_cuda(cudaMemcpyAsync(THClTensor_data(state, self), src, (size_t)n * sizeof(float), cudaMemcpyHostToDevice,
+                             stream ? (cudaStream_t)stream : ctx->stream),
+             "cudaMemcpyAsync");
+  THCL_END_VOID
+}
+
 THCL_HOST_COPY(Byte, unsigned char)
 THCL_HOST_COPY(Char, char)
 THCL_HOST_COPY(Short, short)

@@ -441,6 +441,16 @@ class ClTensor:
         del keep
         return self
 
+    def copy_async(self, src: np.ndarray, stream: int = 0) -> "ClTensor":
+        """Upload from a contiguous float32 array in page-locked memory without waiting: the copy is enqueued
+        on `stream` (a cudaStream_t as an integer; 0 = the library's current stream); the array must stay alive
+        and unchanged until the stream passes it."""
+        arr = np.asarray(src)
+        if arr.dtype != np.float32 or not arr.flags.c_contiguous:
+            raise ClError("copy_async needs a contiguous float32 array")
+        call("THClTensor_copyFloatAsync", state(), self._p, C.c_void_p(arr.ctypes.data), int(arr.size), C.c_void_p(stream))
+        return self
+
     def copy_into(self, out: np.ndarray) -> np.ndarray:
         """Device -> host into an existing float32 array (any strides): FloatTensor:copy(clTensor)."""
         ht, keep = _host_tensor(out, _lib.THFloatTensor, _lib.THFloatStorage)

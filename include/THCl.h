@@ -260,6 +260,13 @@ THCL_DECLARE_HOST_COPY(Int)
 THCL_DECLARE_HOST_COPY(Long)
 THCL_DECLARE_HOST_COPY(Float)
 THCL_DECLARE_HOST_COPY(Double)
+/* Extension (the reference's host copies all block, src/lib/THClTensorCopy.cpp:18-115): the upload of `n`
+ * floats from page-locked host memory into a contiguous tensor of n elements is enqueued on `stream` (a
+ * cudaStream_t of the tensor's device; NULL = the device's THCl stream) and the call returns; the host
+ * memory must stay as it is until the stream has passed the copy. With a stream of its own a caller uploads
+ * the next input while kernels work on the previous one on the THCl stream, with events of its own between
+ * the two (THClState_setStream is no substitute: it waits for the stream it replaces). */
+THCL_API void THClTensor_copyFloatAsync(THClState* state, THClTensor* self, const float* src, long n, void* stream);
 
 /* ---- pointwise math: src/lib/THClTensorMath.h:7-155 ------------------------ */
 

@@ -443,3 +443,27 @@ def test_large_chain_walks_the_operands_from_either_end():
             x.map_on_gpu(y, "x = sqrt(x + y)"); want = np.sqrt(want + host * np.float32(0.5))
         assert np.array_equal(x.float(), want)
         assert abs(x.sum() - float(want.astype(np.float64).sum())) <= 1e-6 * float(want.astype(np.float64).sum())
+
+
+def test_asynchronous_upload_on_a_second_stream():
+    """THClTensor_copyFloatAsync: the upload is enqueued on a stream of the caller's and ordered against the
+    library's stream by the caller's events."""
+    import torch
+    import cltorch_b200 as cl
+    n = 1 << 22
+    host = torch.empty(n, dtype=torch.float32, pin_memory=True)
+    hv = host.numpy()
+    hv[:] = rng_uniform(78, (n,), 0.0, 2.0)
+    compute, copy = torch.cuda.current_stream(), torch.cuda.Stream()
+    t = cl.ClTensor(n).fill(-1.0)
+    cl.synchronize()
+    t.copy_async(hv, copy.cuda_stream)
+    done = torch.cuda.Event()
+    done.record(copy)
+    compute.wait_event(done)
+    t.mul(2.0)
+    assert np.array_equal(t.float(), hv * np.float32(2.0))
+    with pytest.raises(cl.ClError, match="sizes do not match"):
+        cl.ClTensor(5).copy_async(hv)
+    with pytest.raises(cl.ClError, match="contiguous"):
+        cl.ClTensor(n // 2, 2).t().copy_async(hv)
