@@ -454,7 +454,7 @@ def test_asynchronous_upload_on_a_second_stream():
     host = torch.empty(n, dtype=torch.float32, pin_memory=True)
     hv = host.numpy()
     hv[:] = rng_uniform(78, (n,), 0.0, 2.0)
-    compute, copy = torch.cuda.current_stream(), torch.cuda.Stream()
+    compute, copy = torch.cuda.ExternalStream(cl.getStream()), torch.cuda.Stream()   # the library's stream, a second one
     t = cl.ClTensor(n).fill(-1.0)
     cl.synchronize()
     t.copy_async(hv, copy.cuda_stream)
