@@ -489,8 +489,19 @@ struct ExchangeFoldArgs {
   cudaError_t err = cudaSuccess;
   template <class Red>
   void operator()() {
-    thb_exchange_wait_fold<Red><<<1, 1024, 0, st>>>(cells, count, epoch, init, d_out, limit_ns, status);
-    err = cudaGetLastError();
+    // a programmatic dependent of the reduction before it: the block is resident and watching the cells
+    // when the last of them arrives (the kernel waits for that reduction to complete before it writes)
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(1);
+    cfg.blockDim = dim3(1024);
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    err = cudaLaunchKernelEx(&cfg, thb_exchange_wait_fold<Red>, cells, count, epoch, init, d_out, limit_ns, status);
+    if (err == cudaSuccess) err = cudaGetLastError();
   }
 };
 int exchange_fold_launch(void* stream, int reduce, const unsigned long long* cells, int count, unsigned int epoch,

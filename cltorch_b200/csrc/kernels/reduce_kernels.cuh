@@ -404,6 +404,10 @@ thb_exchange_wait_fold(const unsigned long long* cells, int count, unsigned int 
   }
   __syncthreads();
   r = thb_block_fold<Red>(r, (acc_t)init, smem);
+  // Launched as a programmatic dependent, the block has been watching the cells while the kernel before it
+  // (this GPU's own reduction) was still running: the result is written only after that kernel has completed,
+  // like everything a later kernel of the stream does.
+  asm volatile("griddepcontrol.wait;" ::: "memory");
   if (threadIdx.x == 0) {
     if (missing != 0x7fffffff) {
       if (status) atomicCAS(status, 0, 1 + (missing < 254 ? missing : 254));

@@ -164,8 +164,11 @@ int thb200_selftest_wait_expiry(void* stream, uint64_t limit_ns, int code);
  *            block also stores the result, tagged with the step number, into this rank's cell on
  *            every GPU: plain 8-byte stores over NVLink. It waits for nobody.
  *   fold     one block waits until this GPU's cells of all ranks carry the current step number and
- *            folds them in rank order into *d_out. The wait is bounded by wait_limit_ns (a rank
- *            that is absent or late): on expiry *d_out is NaN, the status word of family 7 gets
+ *            folds them in rank order into *d_out. The block may take its place while the kernel
+ *            before it in the stream (this rank's push) is still running, so that it is watching
+ *            when the last cell arrives; it writes only after that kernel has completed. The wait is
+ *            bounded by wait_limit_ns, counted from the block's start (a rank that is absent or
+ *            late; allow for this rank's own reduction): on expiry *d_out is NaN, the status word of family 7 gets
  *            1 + the first missing rank (see thb200_kernel_status) and the stream stays usable.
  *   reduce   push followed by fold.
  * push and fold of one step must be issued in that order on every rank, steps in the same order
