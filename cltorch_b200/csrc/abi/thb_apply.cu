@@ -48,6 +48,22 @@ static bool make_tile_map(CUtensorMap* map, const float* data, int64_t inner, in
 }
 
 // The TMA tile kernel when the operands qualify: 0 launched, -1 not applicable, 1 error.
+// Every apply kernel starts with a grid-dependency wait, so its blocks may be placed while the previous kernel
+// of the stream drains (programmatic stream serialisation).
+static cudaError_t launch_dependent(const void* func, dim3 grid, dim3 block, void** args, size_t smem, cudaStream_t st) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  return cudaLaunchKernelExC(&cfg, func, args);
+}
+
 static int launch_tile_tma(const ApplyKernels& k, cudaStream_t st, int nt, const ThbTile2d& T, const ThbScalars& s) {
   if (!k.tile_tma || (nt < 2 && !k.reads_out)) return -1;
   const int sms = sm_count();
@@ -74,7 +90,7 @@ static int launch_tile_tma(const ApplyKernels& k, cudaStream_t st, int nt, const
   }
   ThbScalars sc = s;
   void* args[] = {&maps[0], &maps[1], &maps[2], &P, &sc};
-  THB_CUDA(cudaLaunchKernel(k.tile_tma, dim3((unsigned)(ntiles < sms ? ntiles : sms)), dim3(THB_AT_THREADS), args, smem, st));
+  THB_CUDA(launch_dependent(k.tile_tma, dim3((unsigned)(ntiles < sms ? ntiles : sms)), dim3(THB_AT_THREADS), args, smem, st));
   return 0;
 }
 
@@ -127,17 +143,7 @@ int launch_apply(const ApplyKernels& k, cudaStream_t st, int nt, const thb200_te
       stream_note_end(ptrs, nt, (size_t)n * sizeof(float), descending);
       if (descending) head |= 256;
       void* args[] = {&a, &b, &cc, &nn, &head, &s};
-      // the kernel starts with a grid-dependency wait, so its blocks may be placed while the previous kernel drains
-      cudaLaunchConfig_t cfg = {};
-      cfg.gridDim = dim3((unsigned)blocks);
-      cfg.blockDim = dim3(THB_CONTIG_THREADS);
-      cfg.stream = st;
-      cudaLaunchAttribute attr[1];
-      attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-      attr[0].val.programmaticStreamSerializationAllowed = 1;
-      cfg.attrs = attr;
-      cfg.numAttrs = 1;
-      THB_CUDA(cudaLaunchKernelExC(&cfg, k.contig, args));
+      THB_CUDA(launch_dependent(k.contig, dim3((unsigned)blocks), dim3(THB_CONTIG_THREADS), args, 0, st));
       return 0;
     }
   }
@@ -183,7 +189,7 @@ int launch_apply(const ApplyKernels& k, cudaStream_t st, int nt, const thb200_te
         uint64_t cap = (uint64_t)kMaxGridBlocks;
         if (blocks > cap) blocks = cap;
         void* args[] = {&Q, &s};
-        THB_CUDA(cudaLaunchKernel(k.rows2d, dim3((unsigned)blocks), dim3(THB_CONTIG_THREADS), args, 0, st));
+        THB_CUDA(launch_dependent(k.rows2d, dim3((unsigned)blocks), dim3(THB_CONTIG_THREADS), args, 0, st));
         return 0;
       }
     }
@@ -224,7 +230,7 @@ int launch_apply(const ApplyKernels& k, cudaStream_t st, int nt, const thb200_te
           uint64_t cap = (uint64_t)kMaxGridBlocks;
           if (blocks > cap) blocks = cap;
           void* args[] = {&P, &s};
-          THB_CUDA(cudaLaunchKernel(k.tile2d_v4, dim3((unsigned)blocks), dim3(256), args, 0, st));
+          THB_CUDA(launch_dependent(k.tile2d_v4, dim3((unsigned)blocks), dim3(256), args, 0, st));
           return 0;
         }
         P.tilesC = (uint32_t)((C + THB_TILE - 1) / THB_TILE);
@@ -234,7 +240,7 @@ int launch_apply(const ApplyKernels& k, cudaStream_t st, int nt, const thb200_te
         uint64_t cap = (uint64_t)kMaxGridBlocks;
         if (blocks > cap) blocks = cap;
         void* args[] = {&P, &s};
-        THB_CUDA(cudaLaunchKernel(k.tile2d, dim3((unsigned)blocks), dim3(THB_TILE, THB_TILE_ROWS), args, 0, st));
+        THB_CUDA(launch_dependent(k.tile2d, dim3((unsigned)blocks), dim3(THB_TILE, THB_TILE_ROWS), args, 0, st));
         return 0;
       }
     }
@@ -251,7 +257,7 @@ int launch_apply(const ApplyKernels& k, cudaStream_t st, int nt, const thb200_te
   uint64_t cap = (uint64_t)kMaxGridBlocks;
   if (blocks > cap) blocks = cap;
   void* args[] = {&L[0], &L[1], &L[2], &nn, &s};
-  THB_CUDA(cudaLaunchKernel(k.strided, dim3((unsigned)blocks), dim3(THB_STRIDED_THREADS), args, 0, st));
+  THB_CUDA(launch_dependent(k.strided, dim3((unsigned)blocks), dim3(THB_STRIDED_THREADS), args, 0, st));
   return 0;
 }
 

@@ -164,6 +164,7 @@ thb_apply_contig(float* a, const float* b, const float* c, thb_i64 n, int head, 
 template <class Op, int NT>
 __global__ void __launch_bounds__(THB_STRIDED_THREADS)
 thb_apply_strided(ThbLayout A, ThbLayout B, ThbLayout C, thb_u64 n, ThbScalars s) {
+  thb_grid_dependency_sync();
   float p1 = 0.f, p2 = 0.f;
   if (s.pointTensor1) p1 = *s.pointTensor1;
   if (s.pointTensor2) p2 = *s.pointTensor2;
@@ -213,6 +214,7 @@ struct ThbRows2d {
 template <class Op, int NT>
 __global__ void __launch_bounds__(THB_CONTIG_THREADS)
 thb_apply_rows2d(ThbRows2d P, ThbScalars s) {
+  thb_grid_dependency_sync();
   float p1 = 0.f, p2 = 0.f;
   if (s.pointTensor1) p1 = *s.pointTensor1;
   if (s.pointTensor2) p2 = *s.pointTensor2;
@@ -270,6 +272,7 @@ template <class Op, int NT>
 __global__ void __launch_bounds__(THB_TILE * THB_TILE_ROWS)
 thb_apply_tile2d(ThbTile2d P, ThbScalars s) {
   __shared__ float tile[3][THB_TILE][THB_TILE + 1];
+  thb_grid_dependency_sync();
   float p1 = 0.f, p2 = 0.f;
   if (s.pointTensor1) p1 = *s.pointTensor1;
   if (s.pointTensor2) p2 = *s.pointTensor2;
@@ -348,6 +351,7 @@ template <class Op, int NT>
 __global__ void __launch_bounds__(256)
 thb_apply_tile2d_v4(ThbTile2d P, ThbScalars s) {
   __shared__ float tile[3][THB_T4_C][THB_T4_PITCH];
+  thb_grid_dependency_sync();
   float p1 = 0.f, p2 = 0.f;
   if (s.pointTensor1) p1 = *s.pointTensor1;
   if (s.pointTensor2) p2 = *s.pointTensor2;

@@ -66,6 +66,7 @@ template <class Op, int NT>
 __global__ void __launch_bounds__(THB_AT_THREADS, 1)
 thb_apply_tile_tma(const __grid_constant__ CUtensorMap map0, const __grid_constant__ CUtensorMap map1,
                    const __grid_constant__ CUtensorMap map2, ThbTileTma P, ThbScalars s) {
+  thb_grid_dependency_sync();
   constexpr int kStage = NT * THB_AT_OPERAND_BYTES;
   constexpr int kStages = THB_AT_STAGES(NT);
   constexpr int kFirstLoaded = Op::kReadsOut ? 0 : 1;
